@@ -1,0 +1,396 @@
+#!/usr/bin/env python
+"""Benchmark of the decode-time retrieval path (hash -> Hamming scan + top-k -> sparse attention).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME]
+
+Metric: decode-attention microseconds per layer at a 128K-token context, Llama-3-8B shape
+(32 layers, 32 query / 8 KV heads, head_dim 128, bf16, batch 1, MLP hash 128->256->128, 90 % of
+the keys pruned per head, + sink 4 and recent 64). One "step" is one decode token through the
+retrieval path of all 32 layers. Data is synthetic and seeded (K,V ~ N(0,1), four outlier key
+channels x8, key 0 x4, RoPE theta 5e5), generated on the device; the 17.7 GB of caches exceed
+the L2 by two orders of magnitude, so no flush is needed between steps.
+
+One JSON line is printed by rank 0:
+  value       device-resident inputs, CUDA-graph replay of the step, CUDA events, max over ranks
+  e2e         the same step through DecodeSession.step_host: pinned HOST q/k/v in, outputs back
+  roofline    the dominant kernel: algorithmic bytes / its mean launch time / measured HBM peak
+  cpu_baseline  the reference modifier's operator sequence (CPU restatement) on the host cores
+With --impl reference the CPU restatement itself is the timed arm (rank 0 only)."""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+from spotlight_b200.workloads import CONFIGS, HEAD_DIM, budget, make_hash_params  # noqa: E402
+
+METRIC = "decode_attn_us_per_layer_128k_llama3_8b_shape"
+UNIT = "us/layer"
+# DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) from the ncu captures
+# summarised under profiles/; None until a capture of that kernel exists.
+NCU_TRAFFIC = {"scan_topk": None, "sparse_attn": None, "decode_prepare": None}
+
+
+def peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        with open(p) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+         "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.idx = gpu_index
+        self.f = tempfile.NamedTemporaryFile("w+", suffix=".csv", delete=False)
+        self.p = None
+
+    def __enter__(self):
+        try:
+            self.p = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                       "-lms", "100", "-i", str(self.idx)], stdout=self.f, stderr=subprocess.DEVNULL)
+        except OSError:
+            self.p = None
+        return self
+
+    def __exit__(self, *a):
+        if self.p is not None:
+            self.p.terminate()
+            try:
+                self.p.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.p.kill()
+
+    def summary(self):
+        self.f.flush()
+        self.f.seek(0)
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self.f.read().splitlines():
+            parts = [x.strip() for x in line.split(",")]
+            if len(parts) < 9:
+                continue
+            try:
+                sm.append(float(parts[1]))
+                mx.append(float(parts[2]))
+            except ValueError:
+                continue
+            for n, v in zip(names, parts[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        os.unlink(self.f.name)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "reasons": sorted(reasons), "samples": len(sm)}
+
+
+# ------------------------------------------------------------------------------------------
+# CPU arm: the reference modifier's operator sequence on the host cores
+# ------------------------------------------------------------------------------------------
+def cpu_layer_step_factory(cfg, heads: int, n: int, threads: int):
+    """Returns f() running ONE layer-step of the reference modifier path
+    (oracle.modifier_path_dense) on `heads` of the q heads at context n, fp32."""
+    from oracle import spotlight_oracle as O
+    torch.set_num_threads(threads)
+    g = torch.Generator().manual_seed(cfg.seed)
+    k = torch.randn((1, heads, n, HEAD_DIM), generator=g)
+    v = torch.randn((1, heads, n, HEAD_DIM), generator=g)
+    q = torch.randn((1, heads, 1, HEAD_DIM), generator=g)
+    ch = torch.randperm(HEAD_DIM, generator=g)[:4]
+    k[..., ch] *= 8.0
+    k[:, :, 0] *= 4.0
+    params = make_hash_params(cfg.hash, heads, cfg.mlp_dims, g, torch.float32)
+
+    def f():
+        with torch.no_grad():
+            return O.modifier_path_dense(q, k, v, params, cfg.mask_out, cfg.min_remain, cfg.sink, cfg.recent,
+                                         cfg.mlp_residue, cfg.rope_theta)
+    return f
+
+
+def time_cpu(cfg, n: int, steps: int, warmup: int, budget_s: float):
+    """(us_per_layer, heads_used, threads, per-step seconds): per-head cost is uniform, so a
+    bounded sample runs a subset of the q heads and scales by q_heads / heads."""
+    threads = os.cpu_count() or 1
+    probe = cpu_layer_step_factory(cfg, 1, n, threads)
+    probe()
+    t0 = time.perf_counter()
+    probe()
+    t1 = time.perf_counter() - t0
+    total = max(1, steps + warmup)
+    heads = int(max(1, min(cfg.q_heads, budget_s / total / max(t1, 1e-6))))
+    f = cpu_layer_step_factory(cfg, heads, n, threads)
+    for _ in range(warmup):
+        f()
+    ts = []
+    for _ in range(steps):
+        t0 = time.perf_counter()
+        f()
+        ts.append(time.perf_counter() - t0)
+    med = statistics.median(ts)
+    return med * 1e6 * cfg.q_heads / heads, heads, threads, med
+
+
+def run_reference(args, cfg):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    us, heads, threads, sec = time_cpu(cfg, cfg.context, args.steps, args.warmup, budget_s=150.0)
+    sample = (f"one layer-step of the reference modifier path (RoPE all keys, hash all keys, sign matmul, topk, "
+              f"mask, dense SDPA) at N={cfg.context}, fp32, {heads} of {cfg.q_heads} q heads per step, "
+              f"scaled x{cfg.q_heads / heads:g}")
+    line = {
+        "impl": "reference", "metric": METRIC, "value": us, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": us * cfg.layers / 1e3, "higher_is_better": False, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": workload_config(cfg),
+        "cpu_baseline": {"value": us, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample},
+        "e2e": {"value": us, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def workload_config(cfg):
+    return {"workload": f"{cfg.name}: Llama-3-8B-shaped decode attention, batch {cfg.batch}, {cfg.layers} layers, "
+                        f"{cfg.q_heads}/{cfg.kv_heads} heads, context {cfg.context}, {cfg.hash} hash {list(cfg.mlp_dims)}, "
+                        f"mask_out {cfg.mask_out}, sink {cfg.sink}, recent {cfg.recent}",
+            "context": cfg.context, "batch_per_gpu": cfg.batch, "layers": cfg.layers, "mask_out": cfg.mask_out,
+            "l2": "inputs larger than L2 (per-layer caches rotate; working set >> 126 MB)"}
+
+
+# ------------------------------------------------------------------------------------------
+# GPU arm
+# ------------------------------------------------------------------------------------------
+def build_session(cfg, device):
+    from spotlight_b200 import ops
+    from spotlight_b200.session import DecodeSession, SessionConfig
+    from spotlight_b200.workloads import apply_rope, rope_tables, torch_dtype
+    dt = torch_dtype(cfg.dtype)
+    n = cfg.context
+    gen = torch.Generator().manual_seed(cfg.seed)
+    hq, hk = [], []
+    for layer in range(cfg.layers):
+        pq = make_hash_params(cfg.hash, cfg.q_heads, cfg.mlp_dims, gen, dt)
+        pk = pq if cfg.q_heads == cfg.kv_heads else make_hash_params(cfg.hash, cfg.kv_heads, cfg.mlp_dims, gen, dt)
+        hq.append(ops.HashParams.from_dict(pq, device, cfg.mlp_residue))
+        hk.append(ops.HashParams.from_dict(pk, device, cfg.mlp_residue))
+    scfg = SessionConfig(cfg.batch, cfg.q_heads, cfg.kv_heads, cfg.layers, n, dt, cfg.mask_out, cfg.min_remain,
+                         cfg.sink, cfg.recent)
+    s = DecodeSession(scfg, hq, hk, device)
+    dgen = torch.Generator(device=device).manual_seed(cfg.seed)
+    ch = torch.randperm(HEAD_DIM, generator=gen)[:4].to(device)
+    chunk = 16384
+    t_codes = 0.0
+    for layer in range(cfg.layers):
+        for lo in range(0, n, chunk):
+            hi = min(n, lo + chunk)
+            k = torch.randn((cfg.batch, hi - lo, cfg.kv_heads, HEAD_DIM), generator=dgen, device=device)
+            v = torch.randn((cfg.batch, hi - lo, cfg.kv_heads, HEAD_DIM), generator=dgen, device=device)
+            k[..., ch] *= 8.0
+            if lo == 0:
+                k[:, 0] *= 4.0
+            cos, sin = rope_tables(torch.arange(lo, hi), cfg.rope_theta)
+            k = apply_rope(k, cos.to(device)[None, :, None, :], sin.to(device)[None, :, None, :])
+            s.load_context(layer, k.to(dt), v.to(dt), lo, codes=False)
+        torch.cuda.synchronize(device)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        ops.hash_encode(s.k_cache[layer][:, :n], s.hash_k[layer], out=s.codes[layer][:, :n])
+        e1.record()
+        torch.cuda.synchronize(device)
+        t_codes += e0.elapsed_time(e1)
+    s.q_in.copy_(torch.randn(s.q_in.shape, generator=dgen, device=device).to(dt))
+    s.k_in.copy_(torch.randn(s.k_in.shape, generator=dgen, device=device).to(dt))
+    s.v_in.copy_(torch.randn(s.v_in.shape, generator=dgen, device=device).to(dt))
+    s.set_position(n - 1, cfg.rope_theta)
+    return s, t_codes / cfg.layers
+
+
+def time_graph(g, steps, warmup, device, dist=None):
+    for _ in range(warmup):
+        g.replay()
+    torch.cuda.synchronize(device)
+    if dist is not None:
+        dist.barrier()
+        torch.cuda.synchronize(device)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        g.replay()
+    e1.record()
+    torch.cuda.synchronize(device)
+    if dist is not None:
+        dist.barrier()
+    return e0.elapsed_time(e1) / steps          # ms per replay
+
+
+def run_ours(args, cfg):
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the retrieval path has no CPU fallback")
+    torch.cuda.set_device(local)
+    device = torch.device("cuda", local)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist_
+        dist_.init_process_group("nccl", device_id=device)
+        dist = dist_
+    from spotlight_b200 import ops
+
+    s, code_build_ms = build_session(cfg, device)
+    n, L = cfg.context, cfg.layers
+    pos = n - 1
+
+    # one eager pass: attended-set sizes per layer (for the algorithmic byte count)
+    nsel = []
+    for layer in range(L):
+        s.layer_step(layer, pos)
+        nsel.append(int(s.cnt.sum().item()))
+    ops.check_status(device)
+    mean_nsel = sum(nsel) / L
+
+    use_graph = not args.no_graph
+    launches0 = ops.launch_count
+    try:
+        g_all = s.capture(pos) if use_graph else None
+    except RuntimeError as e:                    # capture unsupported: fall back to eager launches
+        print(f"# graph capture failed ({e}); timing eager launches", file=sys.stderr)
+        use_graph, g_all = False, None
+
+    class Eager:
+        def __init__(self, stage=None, host=False):
+            self.stage, self.host = stage, host
+
+        def replay(self):
+            s._run(pos, self.stage, self.host)
+
+    with ClockSampler(local) as clocks:
+        ms_step = time_graph(g_all if use_graph else Eager(), args.steps, args.warmup, device, dist)
+        stage_ms = {}
+        for stage in ("prepare", "scan", "attn"):
+            g = s.capture(pos, stage) if use_graph else Eager(stage)
+            stage_ms[stage] = time_graph(g, max(3, args.steps // 2), 3, device) / L
+        # end to end: pinned host inputs in, outputs back, one host sync per token
+        hq = torch.randn(s.q_in.shape).to(s.cfg.dtype)
+        hk = torch.randn(s.k_in.shape).to(s.cfg.dtype)
+        hv = torch.randn(s.v_in.shape).to(s.cfg.dtype)
+        for _ in range(max(3, args.warmup)):
+            s.step_host(hq, hk, hv, pos, graph=use_graph)
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize(device)
+        t0 = time.perf_counter()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(args.steps):
+            out_host = s.step_host(hq, hk, hv, pos, graph=use_graph)
+        e1.record()
+        torch.cuda.synchronize(device)
+        ms_e2e = e0.elapsed_time(e1) / args.steps
+        wall_e2e = (time.perf_counter() - t0) * 1e3 / args.steps
+    ops.check_status(device)
+    clk = clocks.summary()
+
+    if dist is not None:
+        t = torch.tensor([ms_step, ms_e2e, wall_e2e], device=device, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms_step, ms_e2e, wall_e2e = t.tolist()
+    if rank != 0:
+        if dist is not None:
+            dist.destroy_process_group()
+        return
+
+    us_layer = ms_step * 1e3 / L
+    peak, peak_kind = peaks()
+    by_scan = cfg.batch * n * cfg.kv_heads * 16 + cfg.batch * cfg.q_heads * 16
+    by_attn = mean_nsel * HEAD_DIM * 2 * 2 + cfg.batch * cfg.q_heads * HEAD_DIM * 2
+    wbytes = sum(w.numel() * w.element_size() for w in s.hash_q[0].weights + s.hash_k[0].weights)
+    kern = {
+        "scan_topk": {"bytes": by_scan, "us": stage_ms["scan"] * 1e3},
+        "sparse_attn": {"bytes": by_attn, "us": stage_ms["attn"] * 1e3},
+        "decode_prepare": {"bytes": wbytes, "us": stage_ms["prepare"] * 1e3},
+    }
+    for k_, d in kern.items():
+        d["gbs"] = d["bytes"] / (d["us"] * 1e-6) / 1e9
+        d["frac"] = d["gbs"] / peak
+    dom = max(("scan_topk", "sparse_attn"), key=lambda k_: kern[k_]["us"])
+    path_gbs = (by_scan + by_attn) / (us_layer * 1e-6) / 1e9
+    line = {
+        "metric": METRIC, "value": us_layer, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": ms_step, "higher_is_better": False, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic", "config": workload_config(cfg),
+        "tokens_per_s": world * cfg.batch / (ms_step * 1e-3),
+        "e2e": {"value": max(ms_e2e, wall_e2e) * 1e3 / L, "unit": UNIT,
+                "h2d_bytes_per_step": s.host_bytes_per_step[0], "d2h_bytes_per_step": s.host_bytes_per_step[1],
+                "device_ms_per_step": ms_e2e, "wall_ms_per_step": wall_e2e},
+        "gpu_launches": 3 * L * args.steps,
+        "cuda_graph": use_graph,
+        "roofline": {"bound": "hbm", "kernel": dom, "achieved": kern[dom]["gbs"], "peak": peak, "unit": "GB/s",
+                     "frac": kern[dom]["frac"], "traffic": NCU_TRAFFIC[dom], "peak_kind": peak_kind,
+                     "algorithmic_bytes_per_launch": kern[dom]["bytes"], "us_per_launch": kern[dom]["us"],
+                     "frac_of_nominal_8TBs": kern[dom]["gbs"] / 8000.0},
+        "kernels": kern,
+        "path": {"algorithmic_bytes_per_layer": by_scan + by_attn, "gbs": path_gbs, "frac": path_gbs / peak,
+                 "attended_keys_per_head": mean_nsel / (cfg.batch * cfg.kv_heads), "budget_k": budget(n, cfg.mask_out, cfg.min_remain)},
+        "code_build_ms_per_layer": code_build_ms,
+        "clocks": clk,
+        "checksum": float(out_host.float().abs().sum()),
+    }
+    if world == 1 and not args.no_cpu_baseline:
+        us, heads, threads, sec = time_cpu(cfg, n, steps=2, warmup=1, budget_s=25.0)
+        line["cpu_baseline"] = {
+            "value": us, "unit": UNIT, "cores": threads, "kind": "port",
+            "sample": f"one layer-step of the reference modifier path at N={n}, fp32, {heads} of {cfg.q_heads} q heads, "
+                      f"scaled x{cfg.q_heads / heads:g}; median of 2 after 1 warm-up ({sec:.2f} s each)"}
+    print(json.dumps(line), flush=True)
+    if dist is not None:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="headline", choices=sorted(CONFIGS))
+    ap.add_argument("--context", type=int, default=None)
+    ap.add_argument("--layers", type=int, default=None)
+    ap.add_argument("--batch", type=int, default=None)
+    ap.add_argument("--mask-out", type=float, default=None)
+    ap.add_argument("--no-graph", action="store_true")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "ours":
+        args.warmup = max(args.warmup, 3)
+    cfg = CONFIGS[args.workload]
+    over = {k: v for k, v in (("context", args.context), ("layers", args.layers), ("batch", args.batch),
+                              ("mask_out", args.mask_out)) if v is not None}
+    if over:
+        import dataclasses
+        cfg = dataclasses.replace(cfg, **over)
+    if args.impl == "reference":
+        run_reference(args, cfg)
+    else:
+        run_ours(args, cfg)
+
+
+if __name__ == "__main__":
+    main()

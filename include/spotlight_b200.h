@@ -1,0 +1,201 @@
+/*
+ * spotlight_b200 -- C ABI of the B200 (sm_100a) decode-time retrieval path of Spotlight Attention.
+ *
+ * Conventions
+ *  - Every pointer named d_* is a DEVICE pointer owned by the caller. The library never
+ *    allocates or frees device memory (the one exception is documented at its declaration).
+ *  - Every entry point returns SL_OK (0) or a negative sl_status; the message of the last
+ *    failure on the calling thread is available from sl_last_error_string(). Nothing throws.
+ *  - `stream` is a cudaStream_t passed as void*. All work is enqueued asynchronously on it;
+ *    no entry point synchronises with the host.
+ *  - Layouts follow the reference's caches (spotlight/modifiers/gpu_cache.py:28-36): token-major
+ *    with heads interleaved. Keys/values: [B, N, KH, 128]; codes: [B, N, KH, 4] uint32
+ *    (one 128-bit code = 16 contiguous bytes). A batch row may be a slice of a longer
+ *    pre-allocated cache, hence the explicit batch strides.
+ *  - gqa_layout says which query heads share kv head h (G = QH / KH):
+ *      SL_GQA_INTERLEAVED: q heads { g*KH + h }   (the reference kernels,
+ *                          spotlight/kernel/attn_k4_q28.cu:75, attn_dx_u32.py:110-113)
+ *      SL_GQA_BLOCKED:     q heads { h*G + g }    (HF repeat_kv, spotlight_generation.py:128)
+ */
+#ifndef SPOTLIGHT_B200_H
+#define SPOTLIGHT_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum {
+    SL_OK = 0,
+    SL_EINVAL = -1,     /* null pointer, negative size, unknown enum            */
+    SL_ESHAPE = -2,     /* shape outside what the kernels are built for         */
+    SL_EALIGN = -3,     /* pointer or stride not 16-byte aligned                */
+    SL_EWORKSPACE = -4, /* workspace too small                                  */
+    SL_ECUDA = -5,      /* a CUDA runtime call failed                           */
+    SL_ETIMEOUT = -6    /* a bounded device-side wait ran out (status word set) */
+} sl_status;
+
+typedef enum { SL_BF16 = 0, SL_F32 = 1, SL_F16 = 2, SL_BOOL = 3 } sl_dtype;
+typedef enum { SL_GQA_INTERLEAVED = 0, SL_GQA_BLOCKED = 1 } sl_gqa_layout;
+
+int sl_version(void);
+const char* sl_last_error_string(void);
+
+/* Makes `device` current for the calling thread inside the library's CUDA runtime. Launches go
+ * to the current device; callers that juggle several devices call this before the other entry
+ * points (the reference sets a DeviceGuard per call, spotlight/kernel/attn_k4_q28.cu:116). */
+int sl_set_device(int device);
+
+/* Sign-bit packing: bit j of output byte i  <=>  x[8*i + j] > 0 (LSB first). Read as uint32
+ * words on a little-endian machine this is the 32-bit packing of the reference.
+ * Replaces packbits (spotlight/kernel/packbits.cu:28-63), pack_dx_u32_func
+ * (spotlight/kernel/pack_dx_u32.py:35-59) and pack_dx_u8_func (spotlight/kernel/pack_dx_u8.py:34-56).
+ * d_x: n_elems contiguous values of `dtype` (n_elems % 8 == 0, 16-byte aligned);
+ * d_out: n_elems/8 bytes. */
+int sl_pack_signbits(const void* d_x, int dtype, int64_t n_elems, void* d_out, void* stream);
+
+/* Hamming match count, 32-bit code words:
+ *   out[b,n,h] = sum_g sum_w popc(~(q[b, qhead(g,h), w] ^ k[b,n,h,w]))     (int16)
+ * Replaces attn_k4_q28 (spotlight/kernel/attn_k4_q28.cu:100-138) and attn_dx_u32_func
+ * (spotlight/kernel/attn_dx_u32.py:131-162). d_q: [B,QH,W]; d_k: [B,N,KH,W] with batch stride
+ * k_batch_stride (in uint32 words); d_out: [B,N,KH] contiguous. W in {1,2,4,8}. */
+int sl_hamming_scores(const uint32_t* d_q, const uint32_t* d_k, int64_t k_batch_stride,
+                      int16_t* d_out, int B, int64_t N, int KH, int QH, int W, int gqa_layout,
+                      void* stream);
+
+/* Hamming match count, 8-bit code words, one score per head (no group sum):
+ *   out[r,n] = sum_d popc(~(q[r,d] ^ k[r,n,d])) mod 256, r = b*H + h.
+ * Replaces attn_dx_u8_func (spotlight/kernel/attn_dx_u8.py:46-74).
+ * d_q: [R,D] uint8; d_k: [R,N,D] uint8; d_out: [R,N] uint8. */
+int sl_hamming_scores_u8(const uint8_t* d_q, const uint8_t* d_k, uint8_t* d_out, int64_t R,
+                         int64_t N, int D, void* stream);
+
+/* Workspace protocol for the fused scan + top-k. The workspace must be zero-filled once with
+ * sl_workspace_init (or cudaMemset) before its first use; every successful call leaves it
+ * zeroed again. After SL_ETIMEOUT / a non-zero status word it must be re-initialised. */
+size_t sl_scan_topk_workspace_bytes(int B, int64_t N, int KH, int QH);
+int sl_workspace_init(void* d_workspace, size_t bytes, void* stream);
+
+/* Fused Hamming scan + exact top-k + sink/recent window for the decode query.
+ * For each (b, kv head h): score every key 0..N-1 as in sl_hamming_scores (W = 4), keep the k
+ * highest scores with ties broken by LOWEST index, then add keys [0, min(sink,N)) and
+ * [N-recent, N). d_idx[b,h,0..cnt) receives the attended keys in ascending order,
+ * d_cnt[b,h] their number (<= min(N, k+sink+recent) <= idx_capacity).
+ * Replaces attn_cuda_func (spotlight/kernel/__init__.py:31-40) followed by the top-k of
+ * topk_and_gather (spotlight/modifiers/gpu_cache.py:48-50) / aggregate_topk
+ * (spotlight/modifiers/spotlight_generation.py:157-165) and the window of
+ * spotlight/modifiers/spotlight_evaluation.py:341-346.
+ * d_scores_out (optional, may be NULL): int16 [B,N,KH] copy of the scores.
+ * d_status: one int32 the kernel sets non-zero if a bounded wait ran out (may be NULL). */
+int sl_scan_topk(const uint32_t* d_q_codes, const uint32_t* d_k_codes, int64_t k_batch_stride,
+                 int B, int64_t N, int KH, int QH, int gqa_layout, int k, int sink, int recent,
+                 int32_t* d_idx, int idx_capacity, int32_t* d_cnt, int16_t* d_scores_out,
+                 void* d_workspace, size_t workspace_bytes, int32_t* d_status, void* stream);
+
+/* Exact top-k (lowest-index ties) + sink/recent window from scores that already exist:
+ * d_scores int16 [B,N,KH] with values in [0, max_score]. Same output contract as sl_scan_topk.
+ * Replaces the `attn.topk(budget, dim=1)` of topk_and_gather
+ * (spotlight/modifiers/gpu_cache.py:48-50) when the caller holds attn_cuda_func's scores. */
+size_t sl_topk_from_scores_workspace_bytes(int B, int64_t N, int KH, int max_score);
+int sl_topk_from_scores(const int16_t* d_scores, int B, int64_t N, int KH, int max_score, int k,
+                        int sink, int recent, int32_t* d_idx, int idx_capacity, int32_t* d_cnt,
+                        void* d_workspace, size_t workspace_bytes, int32_t* d_status, void* stream);
+
+/* Sequence-sharded selection, step 1: score the local shard (keys [0,N_local) of this rank),
+ * write int16 scores [B,N_local,KH] and ADD the local histogram into d_hist [B,KH,nbins]
+ * uint32 (nbins = 128*G + 1; the caller zeroes d_hist). No reference counterpart: the
+ * reference has no sequence parallelism. */
+int sl_scan_hist(const uint32_t* d_q_codes, const uint32_t* d_k_codes, int64_t k_batch_stride,
+                 int B, int64_t N_local, int KH, int QH, int gqa_layout, int16_t* d_scores,
+                 uint32_t* d_hist, void* stream);
+
+/* Sequence-sharded selection, step 2: given the histograms of ALL ranks
+ * d_hist_all [R,B,KH,nbins] (e.g. from an all-gather), derive the global threshold and this
+ * rank's share of the threshold ties (lower ranks first = lowest global index first) and emit
+ * the LOCAL indices (0-based within the shard) of the attended keys, ascending.
+ * tok_offset = global index of local key 0; N_global = total context. The workspace follows
+ * the same zero-once protocol as sl_scan_topk's. */
+size_t sl_select_emit_workspace_bytes(int B, int64_t N_local, int KH, int QH);
+int sl_select_emit(const int16_t* d_scores, const uint32_t* d_hist_all, int R, int rank, int B,
+                   int64_t N_local, int64_t tok_offset, int64_t N_global, int KH, int QH, int k,
+                   int sink, int recent, int32_t* d_idx, int idx_capacity, int32_t* d_cnt,
+                   void* d_workspace, size_t workspace_bytes, int32_t* d_status, void* stream);
+
+/* Hash parameters of one head set (query heads or key heads): an MLP of n_layers layers,
+ * layer i: dx = act(x @ W_i + b_i), act = SiLU for i < n_layers-1 else identity,
+ * x = dx + x when residue. n_layers = 1 with no bias is the linear hash.
+ * Replaces MLPHashingFunction / MLPLayer (spotlight/modifiers/spotlight_generation.py:229-255)
+ * and LinearHashingFunction (spotlight/modifiers/linearhashing_generation.py:224-231).
+ * d_w[i]: [H, dims[i], dims[i+1]]; d_b[i]: [H, dims[i+1]] or NULL; all of `dtype`. */
+typedef struct {
+    int n_layers;          /* 1..3                                   */
+    int dims[4];           /* dims[0] = 128, dims[n_layers] = 128    */
+    int residue;
+    const void* d_w[3];
+    const void* d_b[3];
+} sl_hash_params;
+
+/* Stage 1 of a decode step, one launch: optional RoPE of q and the new key at the given
+ * position, hash + sign + pack of both, append of the new key code / key / value rows to the
+ * caches at token `pos`. Rounding follows the reference's operators in `dtype` (each matmul,
+ * bias add, SiLU and residual rounds to `dtype`; fp32 accumulation inside a matmul).
+ *   d_q [B,QH,128], d_k [B,KH,128], d_v [B,KH,128]  of `dtype` (the decode token)
+ *   d_cos, d_sin: [128] of `dtype` for position pos, or NULL when q/k are already rotated
+ *   d_q_rot [B,QH,128] (out, may alias d_q)         rotated query for the attention stage
+ *   d_q_codes [B,QH,4] (out)
+ *   d_code_cache [B,*,KH,4], d_k_cache / d_v_cache [B,*,KH,128] with batch strides in ELEMENTS
+ *   (uint32 words resp. values); row `pos` of each is written. Caches may be NULL to skip.
+ * Replaces, for one decode token, check_and_apply_qk_rope (spotlight/modifiers/modify_llama.py:
+ * 68-80) + hash_fn + sign (spotlight_generation.py:13-20) + pack_cuda_func
+ * (spotlight/kernel/__init__.py:23-24) + KVHash.update / KVCache.update
+ * (spotlight/modifiers/gpu_cache.py:38-45,108-118). */
+int sl_decode_prepare(const void* d_q, const void* d_k, const void* d_v, int dtype, int B, int QH,
+                      int KH, const void* d_cos, const void* d_sin,
+                      const sl_hash_params* hash_q, const sl_hash_params* hash_k,
+                      void* d_q_rot, uint32_t* d_q_codes, uint32_t* d_code_cache,
+                      int64_t code_batch_stride, void* d_k_cache, void* d_v_cache,
+                      int64_t kv_batch_stride, int64_t pos, void* stream);
+
+/* Hash + sign + pack of many rows (code-cache build at prefill):
+ * d_x [B,T,H,128] with batch stride x_batch_stride (elements) -> d_codes [B,T,H,4] with batch
+ * stride code_batch_stride (words). Same rounding as sl_decode_prepare. */
+int sl_hash_encode(const void* d_x, int64_t x_batch_stride, int dtype, int B, int64_t T, int H,
+                   const sl_hash_params* hash, uint32_t* d_codes, int64_t code_batch_stride,
+                   void* stream);
+
+/* Sparse GQA decode attention over the attended keys only:
+ *   out[b,qh,:] = softmax_j( q[b,qh] . K[b, idx[b,h,j], h] / sqrt(128) ) V[b, idx[b,h,j], h]
+ * with fp32 online softmax; q heads of kv head h per gqa_layout. Rows are gathered straight
+ * from the caches; no gathered copy is materialised.
+ * Replaces the mask build + dense SDPA of the reference (spotlight/modifiers/
+ * spotlight_generation.py:200-215, modify_llama.py:151-186) and the gather of
+ * topk_and_gather (spotlight/modifiers/gpu_cache.py:51-54).
+ *   d_q [B,QH,128], d_k/d_v caches of `dtype` (bf16 or f32) with batch stride in elements,
+ *   d_idx [B,KH,idx_capacity] int32, d_cnt [B,KH] int32,
+ *   d_out [B,QH,128] of `dtype`; d_lse (optional) [B,QH] float natural-log-sum-exp of the
+ *   scaled logits, for merging partial results of sequence shards.
+ * Workspace: sl_sparse_attn_workspace_bytes(B,KH,QH); zero-initialised once like the scan's. */
+size_t sl_sparse_attn_workspace_bytes(int B, int KH, int QH);
+int sl_sparse_attn_decode(const void* d_q, const void* d_k, const void* d_v, int dtype,
+                          int64_t kv_batch_stride, const int32_t* d_idx, int idx_capacity,
+                          const int32_t* d_cnt, int B, int KH, int QH, int gqa_layout,
+                          void* d_out, float* d_lse, void* d_workspace, size_t workspace_bytes,
+                          void* stream);
+
+/* Log-sum-exp merge of R partial attention results (sequence shards):
+ * d_o [R,rows,128] float, d_lse [R,rows] float -> d_out [rows,128] of `dtype`. */
+int sl_merge_lse(const float* d_o, const float* d_lse, int R, int64_t rows, int dtype, void* d_out,
+                 void* stream);
+
+/* Row gather for API parity with KVCache.gather (spotlight/modifiers/gpu_cache.py:100-106):
+ * out[b,j,h,:] = cache[b, idx[b,h,j], h, :] for j < budget. */
+int sl_gather_rows(const void* d_cache, int64_t batch_stride, int elem_bytes,
+                   const int32_t* d_idx, int idx_capacity, int B, int KH, int budget,
+                   void* d_out, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* SPOTLIGHT_B200_H */

@@ -1,0 +1,75 @@
+"""ctypes binding of libspotlight_b200.so (the C ABI declared in include/spotlight_b200.h).
+
+There is no fallback: if the library has not been built, importing this module raises
+ImportError, as the reference does when its compiled kernels are missing
+(spotlight/kernel/__init__.py:7-11)."""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "lib", "libspotlight_b200.so")
+
+SL_OK, SL_EINVAL, SL_ESHAPE, SL_EALIGN, SL_EWORKSPACE, SL_ECUDA, SL_ETIMEOUT = 0, -1, -2, -3, -4, -5, -6
+SL_BF16, SL_F32, SL_F16, SL_BOOL = 0, 1, 2, 3
+GQA_INTERLEAVED, GQA_BLOCKED = 0, 1
+
+
+class HashParamsStruct(C.Structure):
+    _fields_ = [("n_layers", C.c_int), ("dims", C.c_int * 4), ("residue", C.c_int),
+                ("d_w", C.c_void_p * 3), ("d_b", C.c_void_p * 3)]
+
+
+_P, _I, _L, _Z = C.c_void_p, C.c_int, C.c_int64, C.c_size_t
+_HP = C.POINTER(HashParamsStruct)
+
+# name -> (restype, argtypes); must list every symbol of include/spotlight_b200.h
+SIGNATURES = {
+    "sl_version": (_I, []),
+    "sl_last_error_string": (C.c_char_p, []),
+    "sl_set_device": (_I, [_I]),
+    "sl_pack_signbits": (_I, [_P, _I, _L, _P, _P]),
+    "sl_hamming_scores": (_I, [_P, _P, _L, _P, _I, _L, _I, _I, _I, _I, _P]),
+    "sl_hamming_scores_u8": (_I, [_P, _P, _P, _L, _L, _I, _P]),
+    "sl_scan_topk_workspace_bytes": (_Z, [_I, _L, _I, _I]),
+    "sl_workspace_init": (_I, [_P, _Z, _P]),
+    "sl_scan_topk": (_I, [_P, _P, _L, _I, _L, _I, _I, _I, _I, _I, _I, _P, _I, _P, _P, _P, _Z, _P, _P]),
+    "sl_topk_from_scores_workspace_bytes": (_Z, [_I, _L, _I, _I]),
+    "sl_topk_from_scores": (_I, [_P, _I, _L, _I, _I, _I, _I, _I, _P, _I, _P, _P, _Z, _P, _P]),
+    "sl_scan_hist": (_I, [_P, _P, _L, _I, _L, _I, _I, _I, _P, _P, _P]),
+    "sl_select_emit_workspace_bytes": (_Z, [_I, _L, _I, _I]),
+    "sl_select_emit": (_I, [_P, _P, _I, _I, _I, _L, _L, _L, _I, _I, _I, _I, _I, _P, _I, _P, _P, _Z, _P, _P]),
+    "sl_decode_prepare": (_I, [_P, _P, _P, _I, _I, _I, _I, _P, _P, _HP, _HP, _P, _P, _P, _L, _P, _P, _L, _L, _P]),
+    "sl_hash_encode": (_I, [_P, _L, _I, _I, _L, _I, _HP, _P, _L, _P]),
+    "sl_sparse_attn_workspace_bytes": (_Z, [_I, _I, _I]),
+    "sl_sparse_attn_decode": (_I, [_P, _P, _P, _I, _L, _P, _I, _P, _I, _I, _I, _I, _P, _P, _P, _Z, _P]),
+    "sl_merge_lse": (_I, [_P, _P, _I, _L, _I, _P, _P]),
+    "sl_gather_rows": (_I, [_P, _L, _I, _P, _I, _I, _I, _I, _P, _P]),
+}
+
+
+def _load():
+    if not os.path.exists(LIB_PATH):
+        raise ImportError(
+            f"{LIB_PATH} is missing: build the CUDA library first with `python -m spotlight_b200.build` "
+            "(there is no CPU or PyTorch fallback)")
+    lib = C.CDLL(LIB_PATH)
+    for name, (res, args) in SIGNATURES.items():
+        fn = getattr(lib, name)
+        fn.restype = res
+        fn.argtypes = args
+    return lib
+
+
+lib = _load()
+
+_ERRORS = {SL_EINVAL: ValueError, SL_ESHAPE: ValueError, SL_EALIGN: ValueError, SL_EWORKSPACE: ValueError,
+           SL_ECUDA: RuntimeError, SL_ETIMEOUT: RuntimeError}
+
+
+def check(rc: int) -> None:
+    """Map a negative status to an exception carrying the library's message."""
+    if rc != SL_OK:
+        msg = lib.sl_last_error_string().decode("utf-8", "replace")
+        raise _ERRORS.get(rc, RuntimeError)(f"spotlight_b200 [{rc}]: {msg}")

@@ -1,0 +1,343 @@
+// Sparse GQA decode attention over an index list: rows are gathered straight from the K/V
+// caches (16-byte loads, one 256-byte row = half a warp for 2-byte types), online softmax in
+// fp32, split over the list (flash-decoding style) with the last CTA of a (b, kv head)
+// merging the partials. Also the LSE merge across sequence shards and the row-gather shim.
+#include "sl_common.cuh"
+
+namespace {
+
+constexpr int AT = 256;            // threads per CTA
+constexpr int AW = AT / 32;        // warps
+constexpr int PF = 4;              // row groups in flight per warp
+constexpr int MAX_SPLITS = 64;
+constexpr float LOG2E = 1.4426950408889634f;
+constexpr float LN2 = 0.6931471805599453f;
+
+struct AttnArgs {
+    const void* q; const void* k; const void* v;
+    long long kv_b;                // batch stride in elements
+    const int* idx; int cap; const int* cnt;
+    int B, KH, layout, splits;
+    void* out; float* lse;
+    unsigned* counters;            // [B*KH], zero between launches
+    float* part;                   // [B*KH][splits][G][130]: o[128], m, l
+};
+
+__device__ __forceinline__ float ex2(float x) { return exp2f(x); }
+
+template <typename T, int G>
+__global__ void __launch_bounds__(AT, (G * (16 / sizeof(T)) > 32) ? 1 : 2) sparse_attn_kernel(const AttnArgs a) {
+    constexpr int EPL = 16 / sizeof(T);       // elements per lane
+    constexpr int LPR = 128 / EPL;            // lanes per row
+    constexpr int RPW = 32 / LPR;             // rows per warp step
+    __shared__ float sm_acc[AW][G][128];
+    __shared__ float sm_m[AW][G], sm_l[AW][G];
+    __shared__ int s_last;
+
+    const int sp = blockIdx.x, h = blockIdx.y, b = blockIdx.z, KH = a.KH;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int sub = lane % LPR, rs = lane / LPR;
+    const int n = a.cnt[b * KH + h];
+    const int per = (n + a.splits - 1) / a.splits;
+    const int lo = min(n, sp * per), hi = min(n, lo + per);
+    const int* list = a.idx + ((long long)b * KH + h) * a.cap;
+    const T* kb = reinterpret_cast<const T*>(a.k) + (long long)b * a.kv_b + (long long)h * 128 + sub * EPL;
+    const T* vb = reinterpret_cast<const T*>(a.v) + (long long)b * a.kv_b + (long long)h * 128 + sub * EPL;
+    const long long row_stride = (long long)KH * 128;
+
+    float qf[G][EPL];
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+        const int qh = a.layout == SL_GQA_INTERLEAVED ? g * KH + h : h * G + g;
+        const T* qp = reinterpret_cast<const T*>(a.q) + ((long long)b * KH * G + qh) * 128 + sub * EPL;
+        const uint4 raw = *reinterpret_cast<const uint4*>(qp);
+        const T* qv = reinterpret_cast<const T*>(&raw);
+#pragma unroll
+        for (int e = 0; e < EPL; ++e) qf[g][e] = sl::VT<T>::to_f(qv[e]) * (0.08838834764831845f * LOG2E);
+    }
+    float m[G], l[G], acc[G][EPL];
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+        m[g] = -INFINITY; l[g] = 0.0f;
+#pragma unroll
+        for (int e = 0; e < EPL; ++e) acc[g][e] = 0.0f;
+    }
+
+    const int step = AW * RPW;
+    const int nit = (hi - lo + step - 1) / step;
+    uint4 kbuf[PF], vbuf[PF];
+    bool okb[PF];
+    auto issue = [&](int it, int slot) {
+        const int j = lo + it * step + warp * RPW + rs;
+        const bool ok = it < nit && j < hi;
+        okb[slot] = ok;
+        if (ok) {
+            const long long tok = list[j];
+            kbuf[slot] = sl::ld_gather_v4(kb + tok * row_stride);
+            vbuf[slot] = sl::ld_gather_v4(vb + tok * row_stride);
+        }
+    };
+#pragma unroll
+    for (int p = 0; p < PF; ++p) issue(p, p);
+    for (int it0 = 0; it0 < nit; it0 += PF) {
+#pragma unroll
+        for (int p = 0; p < PF; ++p) {
+            if (it0 + p < nit) {   // warp-uniform
+                const bool ok = okb[p];
+                const T* kv = reinterpret_cast<const T*>(&kbuf[p]);
+                const T* vv = reinterpret_cast<const T*>(&vbuf[p]);
+                float kf[EPL], vf[EPL];
+#pragma unroll
+                for (int e = 0; e < EPL; ++e) {
+                    kf[e] = ok ? sl::VT<T>::to_f(kv[e]) : 0.0f;
+                    vf[e] = ok ? sl::VT<T>::to_f(vv[e]) : 0.0f;
+                }
+#pragma unroll
+                for (int g = 0; g < G; ++g) {
+                    float s = 0.0f;
+#pragma unroll
+                    for (int e = 0; e < EPL; ++e) s = fmaf(qf[g][e], kf[e], s);
+#pragma unroll
+                    for (int d = LPR / 2; d > 0; d >>= 1) s += __shfl_xor_sync(0xffffffffu, s, d);
+                    if (ok) {
+                        const float mn = fmaxf(m[g], s);
+                        const float corr = ex2(m[g] - mn);      // m = -inf -> 0
+                        const float p_ = ex2(s - mn);
+                        l[g] = l[g] * corr + p_;
+#pragma unroll
+                        for (int e = 0; e < EPL; ++e) acc[g][e] = fmaf(acc[g][e], corr, p_ * vf[e]);
+                        m[g] = mn;
+                    }
+                }
+                issue(it0 + p + PF, p);
+            }
+        }
+    }
+
+    // ---- merge the row slots of a warp (lanes holding the same columns)
+#pragma unroll
+    for (int d = LPR; d < 32; d <<= 1) {
+#pragma unroll
+        for (int g = 0; g < G; ++g) {
+            const float mo = __shfl_xor_sync(0xffffffffu, m[g], d);
+            const float lo_ = __shfl_xor_sync(0xffffffffu, l[g], d);
+            const float mn = fmaxf(m[g], mo);
+            const float c0 = mn == -INFINITY ? 0.0f : ex2(m[g] - mn);
+            const float c1 = mn == -INFINITY ? 0.0f : ex2(mo - mn);
+            l[g] = l[g] * c0 + lo_ * c1;
+#pragma unroll
+            for (int e = 0; e < EPL; ++e) {
+                const float ao = __shfl_xor_sync(0xffffffffu, acc[g][e], d);
+                acc[g][e] = acc[g][e] * c0 + ao * c1;
+            }
+            m[g] = mn;
+        }
+    }
+    if (rs == 0) {
+#pragma unroll
+        for (int g = 0; g < G; ++g) {
+#pragma unroll
+            for (int e = 0; e < EPL; ++e) sm_acc[warp][g][sub * EPL + e] = acc[g][e];
+            if (sub == 0) { sm_m[warp][g] = m[g]; sm_l[warp][g] = l[g]; }
+        }
+    }
+    __syncthreads();
+
+    // ---- merge the warps of the CTA
+    const long long bh = (long long)b * KH + h;
+    float* part = a.part + (bh * a.splits + sp) * G * 130;
+    for (int e = tid; e < G * 128; e += AT) {
+        const int g = e >> 7, col = e & 127;
+        float M = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < AW; ++w) M = fmaxf(M, sm_m[w][g]);
+        float L = 0.0f, O = 0.0f;
+        if (M != -INFINITY) {
+#pragma unroll
+            for (int w = 0; w < AW; ++w) {
+                const float c = ex2(sm_m[w][g] - M);
+                L += sm_l[w][g] * c;
+                O += sm_acc[w][g][col] * c;
+            }
+        }
+        if (a.splits == 1) {
+            const int qh = a.layout == SL_GQA_INTERLEAVED ? g * KH + h : h * G + g;
+            const long long o = ((long long)b * KH * G + qh) * 128 + col;
+            reinterpret_cast<T*>(a.out)[o] = sl::VT<T>::from_f(L > 0.0f ? O / L : 0.0f);
+            if (a.lse && col == 0) a.lse[(long long)b * KH * G + qh] = L > 0.0f ? (M + log2f(L)) * LN2 : -INFINITY;
+        } else {
+            part[g * 130 + col] = O;
+            if (col == 0) { part[g * 130 + 128] = M; part[g * 130 + 129] = L; }
+        }
+    }
+    if (a.splits == 1) return;
+
+    // ---- the last CTA of this (b, kv head) merges the splits
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) {
+        const unsigned old = atomicAdd(&a.counters[bh], 1u);
+        s_last = old == (unsigned)a.splits - 1u;
+    }
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    const float* pb = a.part + bh * a.splits * G * 130;
+    for (int e = tid; e < G * 128; e += AT) {
+        const int g = e >> 7, col = e & 127;
+        float M = -INFINITY;
+        for (int s = 0; s < a.splits; ++s) M = fmaxf(M, __ldcg(pb + (s * G + g) * 130 + 128));
+        float L = 0.0f, O = 0.0f;
+        if (M != -INFINITY) {
+            for (int s = 0; s < a.splits; ++s) {
+                const float* ps = pb + (s * G + g) * 130;
+                const float c = ex2(__ldcg(ps + 128) - M);
+                L += __ldcg(ps + 129) * c;
+                O += __ldcg(ps + col) * c;
+            }
+        }
+        const int qh = a.layout == SL_GQA_INTERLEAVED ? g * KH + h : h * G + g;
+        const long long o = ((long long)b * KH * G + qh) * 128 + col;
+        reinterpret_cast<T*>(a.out)[o] = sl::VT<T>::from_f(L > 0.0f ? O / L : 0.0f);
+        if (a.lse && col == 0) a.lse[(long long)b * KH * G + qh] = L > 0.0f ? (M + log2f(L)) * LN2 : -INFINITY;
+    }
+    if (tid == 0) a.counters[bh] = 0;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(128) merge_lse_kernel(const float* __restrict__ o, const float* __restrict__ lse,
+                                                        int R, long long rows, T* __restrict__ out) {
+    const long long row = blockIdx.x;
+    const int col = threadIdx.x;
+    float M = -INFINITY;
+    for (int r = 0; r < R; ++r) M = fmaxf(M, lse[r * rows + row]);
+    float L = 0.0f, O = 0.0f;
+    if (M != -INFINITY) {
+        for (int r = 0; r < R; ++r) {
+            const float w = expf(lse[r * rows + row] - M);
+            L += w;
+            O += w * o[(r * rows + row) * 128 + col];
+        }
+    }
+    out[row * 128 + col] = sl::VT<T>::from_f(L > 0.0f ? O / L : 0.0f);
+}
+
+__global__ void __launch_bounds__(256) gather_rows_kernel(const unsigned char* __restrict__ cache, long long bstride_bytes,
+                                                          int row_bytes, const int* __restrict__ idx, int cap, int KH,
+                                                          int budget, unsigned char* __restrict__ out) {
+    // one warp-group of row_bytes/16 lanes copies one row
+    const int lanes = row_bytes / 16;
+    const int rows_per_block = 256 / lanes;
+    const int b = blockIdx.y;
+    const long long r = (long long)blockIdx.x * rows_per_block + threadIdx.x / lanes;   // r = j*KH + h
+    if (threadIdx.x / lanes >= rows_per_block || r >= (long long)budget * KH) return;
+    const int j = (int)(r / KH), h = (int)(r % KH);
+    const long long tok = idx[((long long)b * KH + h) * cap + j];
+    const uint4 v = sl::ld_gather_v4(cache + b * bstride_bytes + (tok * KH + h) * row_bytes + (threadIdx.x % lanes) * 16);
+    *reinterpret_cast<uint4*>(out + (((long long)b * budget + j) * KH + h) * row_bytes + (threadIdx.x % lanes) * 16) = v;
+}
+
+int pick_splits(int B, int KH, int cap) {
+    const int ctas = B * KH;
+    int s = (4 * sl::sm_count() + ctas - 1) / ctas;
+    const int by_rows = std::max(1, cap / 64);
+    s = std::min(s, std::min(by_rows, MAX_SPLITS));
+    return std::max(s, 1);
+}
+
+template <typename T, int G>
+int launch_attn(const AttnArgs& a, cudaStream_t s) {
+    dim3 grid((unsigned)a.splits, (unsigned)a.KH, (unsigned)a.B);
+    sparse_attn_kernel<T, G><<<grid, AT, 0, s>>>(a);
+    SL_CUDA_OK(cudaGetLastError());
+    return SL_OK;
+}
+
+template <typename T>
+int dispatch_g(const AttnArgs& a, int G, cudaStream_t s) {
+    switch (G) {
+        case 1: return launch_attn<T, 1>(a, s);
+        case 2: return launch_attn<T, 2>(a, s);
+        case 3: return launch_attn<T, 3>(a, s);
+        case 4: return launch_attn<T, 4>(a, s);
+        case 5: return launch_attn<T, 5>(a, s);
+        case 6: return launch_attn<T, 6>(a, s);
+        case 7: return launch_attn<T, 7>(a, s);
+        case 8: return launch_attn<T, 8>(a, s);
+        default: return sl::fail(SL_ESHAPE, "sl_sparse_attn_decode: group size %d not in 1..8", G);
+    }
+}
+
+}  // namespace
+
+extern "C" size_t sl_sparse_attn_workspace_bytes(int B, int KH, int QH) {
+    if (B <= 0 || KH <= 0 || QH <= 0) return 0;
+    const size_t counters = ((size_t)B * KH * 4 + 255) / 256 * 256;
+    return counters + (size_t)B * QH * MAX_SPLITS * 130 * 4;
+}
+
+extern "C" int sl_sparse_attn_decode(const void* d_q, const void* d_k, const void* d_v, int dtype,
+                                     int64_t kv_batch_stride, const int32_t* d_idx, int idx_capacity,
+                                     const int32_t* d_cnt, int B, int KH, int QH, int gqa_layout, void* d_out,
+                                     float* d_lse, void* d_workspace, size_t workspace_bytes, void* stream) {
+    SL_REQUIRE(d_q && d_k && d_v && d_idx && d_cnt && d_out && d_workspace, SL_EINVAL, "sl_sparse_attn_decode: null pointer");
+    SL_REQUIRE(B > 0 && KH > 0 && QH > 0 && QH % KH == 0 && idx_capacity > 0, SL_ESHAPE, "sl_sparse_attn_decode: bad shape");
+    SL_REQUIRE(B <= 65535 && KH <= 65535, SL_ESHAPE, "sl_sparse_attn_decode: B or KH > 65535");
+    SL_REQUIRE(gqa_layout == SL_GQA_INTERLEAVED || gqa_layout == SL_GQA_BLOCKED, SL_EINVAL,
+               "sl_sparse_attn_decode: unknown gqa_layout %d", gqa_layout);
+    SL_REQUIRE(dtype == SL_BF16 || dtype == SL_F32 || dtype == SL_F16, SL_EINVAL, "sl_sparse_attn_decode: unsupported dtype %d", dtype);
+    const int esz = dtype == SL_F32 ? 4 : 2;
+    SL_REQUIRE(sl::aligned16(d_q) && sl::aligned16(d_k) && sl::aligned16(d_v) && (kv_batch_stride * esz) % 16 == 0, SL_EALIGN,
+               "sl_sparse_attn_decode: q/k/v must be 16-byte aligned");
+    SL_REQUIRE(workspace_bytes >= sl_sparse_attn_workspace_bytes(B, KH, QH), SL_EWORKSPACE,
+               "sl_sparse_attn_decode: workspace %zu < required %zu", workspace_bytes, sl_sparse_attn_workspace_bytes(B, KH, QH));
+    AttnArgs a;
+    a.q = d_q; a.k = d_k; a.v = d_v; a.kv_b = kv_batch_stride;
+    a.idx = d_idx; a.cap = idx_capacity; a.cnt = d_cnt;
+    a.B = B; a.KH = KH; a.layout = gqa_layout;
+    a.splits = pick_splits(B, KH, idx_capacity);
+    a.out = d_out; a.lse = d_lse;
+    a.counters = static_cast<unsigned*>(d_workspace);
+    a.part = reinterpret_cast<float*>(static_cast<unsigned char*>(d_workspace) + ((size_t)B * KH * 4 + 255) / 256 * 256);
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const int G = QH / KH;
+    switch (dtype) {
+        case SL_BF16: return dispatch_g<__nv_bfloat16>(a, G, s);
+        case SL_F16: return dispatch_g<__half>(a, G, s);
+        default: return dispatch_g<float>(a, G, s);
+    }
+}
+
+extern "C" int sl_merge_lse(const float* d_o, const float* d_lse, int R, int64_t rows, int dtype, void* d_out, void* stream) {
+    SL_REQUIRE(d_o && d_lse && d_out, SL_EINVAL, "sl_merge_lse: null pointer");
+    SL_REQUIRE(R > 0 && rows >= 0 && rows <= 0x7fffffffLL, SL_ESHAPE, "sl_merge_lse: bad shape");
+    if (rows == 0) return SL_OK;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    switch (dtype) {
+        case SL_BF16: merge_lse_kernel<__nv_bfloat16><<<(unsigned)rows, 128, 0, s>>>(d_o, d_lse, R, rows, (__nv_bfloat16*)d_out); break;
+        case SL_F16: merge_lse_kernel<__half><<<(unsigned)rows, 128, 0, s>>>(d_o, d_lse, R, rows, (__half*)d_out); break;
+        case SL_F32: merge_lse_kernel<float><<<(unsigned)rows, 128, 0, s>>>(d_o, d_lse, R, rows, (float*)d_out); break;
+        default: return sl::fail(SL_EINVAL, "sl_merge_lse: unsupported dtype %d", dtype);
+    }
+    SL_CUDA_OK(cudaGetLastError());
+    return SL_OK;
+}
+
+extern "C" int sl_gather_rows(const void* d_cache, int64_t batch_stride, int elem_bytes, const int32_t* d_idx,
+                              int idx_capacity, int B, int KH, int budget, void* d_out, void* stream) {
+    SL_REQUIRE(d_cache && d_idx && d_out, SL_EINVAL, "sl_gather_rows: null pointer");
+    SL_REQUIRE(B > 0 && B <= 65535 && KH > 0 && budget >= 0 && budget <= idx_capacity, SL_ESHAPE, "sl_gather_rows: bad shape");
+    SL_REQUIRE(elem_bytes == 2 || elem_bytes == 4, SL_EINVAL, "sl_gather_rows: elem_bytes must be 2 or 4");
+    SL_REQUIRE(sl::aligned16(d_cache) && sl::aligned16(d_out) && (batch_stride * elem_bytes) % 16 == 0, SL_EALIGN,
+               "sl_gather_rows: buffers must be 16-byte aligned");
+    if (budget == 0) return SL_OK;
+    const int row_bytes = 128 * elem_bytes;
+    const int rows_per_block = 256 / (row_bytes / 16);
+    const long long rows = (long long)budget * KH;
+    dim3 grid((unsigned)((rows + rows_per_block - 1) / rows_per_block), (unsigned)B);
+    gather_rows_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const unsigned char*>(d_cache), batch_stride * elem_bytes, row_bytes, d_idx, idx_capacity, KH, budget,
+        static_cast<unsigned char*>(d_out));
+    SL_CUDA_OK(cudaGetLastError());
+    return SL_OK;
+}

@@ -1,0 +1,109 @@
+// Shared host/device helpers of libspotlight_b200 (sm_100a only).
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <cstdarg>
+#include <cstdio>
+#include <algorithm>
+
+#include "../../include/spotlight_b200.h"
+
+namespace sl {
+
+// ---- host-side error plumbing ---------------------------------------------------------
+char* err_buf();
+int fail(int code, const char* fmt, ...);
+int sm_count();          // SMs of the current device (cached per device)
+
+#define SL_CUDA_OK(expr)                                                                    \
+    do {                                                                                    \
+        cudaError_t e__ = (expr);                                                           \
+        if (e__ != cudaSuccess)                                                             \
+            return sl::fail(SL_ECUDA, "%s failed: %s", #expr, cudaGetErrorString(e__));     \
+    } while (0)
+
+#define SL_REQUIRE(cond, code, ...)                                                         \
+    do {                                                                                    \
+        if (!(cond)) return sl::fail(code, __VA_ARGS__);                                    \
+    } while (0)
+
+static inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+// ---- device helpers -------------------------------------------------------------------
+// Streaming 128-bit load that bypasses L1 allocation: the code stream is read once.
+__device__ __forceinline__ uint4 ld_stream_v4(const uint4* p) {
+    uint4 r;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w)
+                 : "l"(p));
+    return r;
+}
+// Gathered 128-bit load (rows are touched once per launch; keep them out of L1).
+__device__ __forceinline__ uint4 ld_gather_v4(const void* p) {
+    uint4 r;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w)
+                 : "l"(p));
+    return r;
+}
+__device__ __forceinline__ unsigned ld_acquire_u32(const unsigned* p) {
+    unsigned v;
+    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void red_release_add_u32(unsigned* p, unsigned v) {
+    asm volatile("red.release.gpu.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ int popc4(uint4 a) {
+    return __popc(a.x) + __popc(a.y) + __popc(a.z) + __popc(a.w);
+}
+__device__ __forceinline__ uint4 xor4(uint4 a, uint4 b) {
+    return make_uint4(a.x ^ b.x, a.y ^ b.y, a.z ^ b.z, a.w ^ b.w);
+}
+
+// value type traits: load/round in the run dtype
+template <typename T> struct VT;
+template <> struct VT<__nv_bfloat16> {
+    static __device__ __forceinline__ float to_f(__nv_bfloat16 v) { return __bfloat162float(v); }
+    static __device__ __forceinline__ __nv_bfloat16 from_f(float f) { return __float2bfloat16_rn(f); }
+    static __device__ __forceinline__ float round(float f) { return __bfloat162float(__float2bfloat16_rn(f)); }
+};
+template <> struct VT<__half> {
+    static __device__ __forceinline__ float to_f(__half v) { return __half2float(v); }
+    static __device__ __forceinline__ __half from_f(float f) { return __float2half_rn(f); }
+    static __device__ __forceinline__ float round(float f) { return __half2float(__float2half_rn(f)); }
+};
+template <> struct VT<float> {
+    static __device__ __forceinline__ float to_f(float v) { return v; }
+    static __device__ __forceinline__ float from_f(float f) { return f; }
+    static __device__ __forceinline__ float round(float f) { return f; }
+};
+
+// A bounded grid-wide barrier over `n_ctas` co-resident CTAs. `counter` counts arrivals and
+// only grows during a launch (target of the j-th barrier is (j+1)*n_ctas). Gives up after
+// `limit` polls, sets *status and returns false; callers carry on with bounded work.
+__device__ __forceinline__ bool grid_barrier(unsigned* counter, unsigned target, int* status,
+                                             unsigned limit = 4000000u) {
+    __shared__ int ok_s;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        __threadfence();
+        red_release_add_u32(counter, 1u);
+        unsigned it = 0;
+        int ok = 1;
+        while (ld_acquire_u32(counter) < target) {
+            if (++it > limit) { ok = 0; break; }
+            __nanosleep(32);
+        }
+        if (!ok && status) atomicExch(status, 1);
+        __threadfence();
+        ok_s = ok;
+    }
+    __syncthreads();
+    return ok_s != 0;
+}
+
+}  // namespace sl

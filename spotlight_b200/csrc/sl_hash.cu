@@ -1,0 +1,266 @@
+// Hash stage: (optional RoPE) -> per-head MLP / linear projection -> sign -> 128-bit code,
+// with the decode-step appends (code cache, K cache, V cache) fused into the same launch.
+//
+// One CTA owns one head and a tile of R rows (a row = one token of that head). The weight
+// matrix of a layer is streamed once per CTA with 16-byte loads: thread (ks, cg) multiplies
+// input rows ks, ks+KS, ... of W against columns [cg*CPT, cg*CPT+CPT), partial sums meet in
+// shared memory. Rounding points follow the reference's torch operators in the run dtype:
+// matmul (fp32 accumulate) -> round, + bias -> round, SiLU -> round, + residual -> round.
+#include "sl_common.cuh"
+
+namespace {
+
+constexpr int HT = 256;      // threads per CTA
+constexpr int MAXD = 256;    // largest layer width
+
+struct HashJob {
+    const void* x; long long xs_b; long long T; int H; int B;
+    sl_hash_params hp;
+    uint32_t* codes; long long cs_b;
+    void* x_rot; long long xr_b;
+    const void* cosr; const void* sinr;
+    const void* v_src; void* v_dst; long long v_b;   // optional value-row append (decode)
+    long long row_tiles;
+};
+
+struct HashArgs {
+    HashJob job[2];
+    int heads0;
+};
+
+template <typename T, int R>
+__global__ void __launch_bounds__(HT) hash_kernel(const HashArgs args) {
+    constexpr int CPT = 16 / sizeof(T);
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    float* xa = reinterpret_cast<float*>(smem_raw);            // [R][MAXD]
+    float* xb = xa + R * MAXD;                                 // [R][MAXD]
+    float* red = xb + R * MAXD;                                // [KS][R][dout]
+
+    const int hy = blockIdx.y;
+    const HashJob& J = hy < args.heads0 ? args.job[0] : args.job[1];
+    const int h = hy < args.heads0 ? hy : hy - args.heads0;
+    if ((long long)blockIdx.x >= J.row_tiles) return;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const long long rows = (long long)J.B * J.T;
+    const long long r0 = (long long)blockIdx.x * R;
+
+    // ---- stage the raw rows, then rotate (the rotated copy may overwrite the input in place)
+    for (int e = tid; e < R * 128; e += HT) {
+        const int r = e >> 7, j = e & 127;
+        const long long rg = r0 + r;
+        float val = 0.0f;
+        if (rg < rows) {
+            const long long b = rg / J.T, t = rg % J.T;
+            val = sl::VT<T>::to_f((reinterpret_cast<const T*>(J.x) + b * J.xs_b + (t * J.H + h) * 128)[j]);
+            if (J.v_dst)
+                (reinterpret_cast<T*>(J.v_dst) + b * J.v_b + (t * J.H + h) * 128)[j] =
+                    (reinterpret_cast<const T*>(J.v_src) + ((b * J.T + t) * J.H + h) * 128)[j];
+        }
+        xb[r * MAXD + j] = val;
+    }
+    __syncthreads();
+    for (int e = tid; e < R * 128; e += HT) {
+        const int r = e >> 7, j = e & 127;
+        const long long rg = r0 + r;
+        float val = xb[r * MAXD + j];
+        if (J.cosr) {
+            const float other = xb[r * MAXD + (j < 64 ? j + 64 : j - 64)];
+            const float rot = j < 64 ? -other : other;
+            const float c = sl::VT<T>::to_f(reinterpret_cast<const T*>(J.cosr)[j]);
+            const float s = sl::VT<T>::to_f(reinterpret_cast<const T*>(J.sinr)[j]);
+            val = sl::VT<T>::round(sl::VT<T>::round(val * c) + sl::VT<T>::round(rot * s));
+        }
+        if (J.x_rot && rg < rows) {
+            const long long b = rg / J.T, t = rg % J.T;
+            (reinterpret_cast<T*>(J.x_rot) + b * J.xr_b + (t * J.H + h) * 128)[j] = sl::VT<T>::from_f(val);
+        }
+        xa[r * MAXD + j] = val;
+    }
+    __syncthreads();
+
+    float* xin = xa;
+    float* xout = xb;
+    for (int layer = 0; layer < J.hp.n_layers; ++layer) {
+        const int din = J.hp.dims[layer], dout = J.hp.dims[layer + 1];
+        const int ncg = dout / CPT;            // column groups
+        const int KS = HT / ncg;               // k-splits
+        const int cg = tid % ncg, ks = tid / ncg;
+        const T* W = reinterpret_cast<const T*>(J.hp.d_w[layer]) + (long long)h * din * dout;
+        float acc[R][CPT];
+#pragma unroll
+        for (int r = 0; r < R; ++r)
+#pragma unroll
+            for (int c = 0; c < CPT; ++c) acc[r][c] = 0.0f;
+        if (ks < KS) {
+#pragma unroll 4
+            for (int i = ks; i < din; i += KS) {
+                const uint4 raw = sl::ld_gather_v4(W + (long long)i * dout + cg * CPT);
+                const T* wv = reinterpret_cast<const T*>(&raw);
+                float wf[CPT];
+#pragma unroll
+                for (int c = 0; c < CPT; ++c) wf[c] = sl::VT<T>::to_f(wv[c]);
+#pragma unroll
+                for (int r = 0; r < R; ++r) {
+                    const float xv = xin[r * MAXD + i];
+#pragma unroll
+                    for (int c = 0; c < CPT; ++c) acc[r][c] = fmaf(xv, wf[c], acc[r][c]);
+                }
+            }
+#pragma unroll
+            for (int r = 0; r < R; ++r)
+#pragma unroll
+                for (int c = 0; c < CPT; ++c) red[(ks * R + r) * dout + cg * CPT + c] = acc[r][c];
+        }
+        __syncthreads();
+        const T* bias = J.hp.d_b[layer] ? reinterpret_cast<const T*>(J.hp.d_b[layer]) + (long long)h * dout : nullptr;
+        for (int e = tid; e < R * dout; e += HT) {
+            const int r = e / dout, j = e % dout;
+            float y = 0.0f;
+            for (int s = 0; s < KS; ++s) y += red[(s * R + r) * dout + j];
+            y = sl::VT<T>::round(y);
+            if (bias) y = sl::VT<T>::round(y + sl::VT<T>::to_f(bias[j]));
+            if (layer < J.hp.n_layers - 1) y = sl::VT<T>::round(y / (1.0f + expf(-y)));
+            if (J.hp.residue) y = sl::VT<T>::round(y + xin[r * MAXD + j]);
+            xout[r * MAXD + j] = y;
+        }
+        __syncthreads();
+        float* t = xin; xin = xout; xout = t;
+    }
+
+    // ---- sign + pack: warp w of the first four builds word w of each row's code
+    if (warp < 4) {
+        for (int r = 0; r < R; ++r) {
+            const long long rg = r0 + r;
+            const unsigned word = __ballot_sync(0xffffffffu, xin[r * MAXD + warp * 32 + lane] > 0.0f);
+            if (lane == 0 && rg < rows) {
+                const long long b = rg / J.T, t = rg % J.T;
+                J.codes[b * J.cs_b + (t * J.H + h) * 4 + warp] = word;
+            }
+        }
+    }
+}
+
+int check_params(const char* fn, const sl_hash_params* p, int dtype) {
+    SL_REQUIRE(p != nullptr, SL_EINVAL, "%s: null hash params", fn);
+    SL_REQUIRE(p->n_layers >= 1 && p->n_layers <= 3, SL_ESHAPE, "%s: n_layers=%d not in 1..3", fn, p->n_layers);
+    SL_REQUIRE(p->dims[0] == 128 && p->dims[p->n_layers] == 128, SL_ESHAPE, "%s: first and last hash dims must be 128", fn);
+    const int cpt = dtype == SL_F32 ? 4 : 8;
+    for (int i = 0; i <= p->n_layers; ++i) {
+        const int d = p->dims[i];
+        SL_REQUIRE(d == 32 || d == 64 || d == 128 || d == 256, SL_ESHAPE, "%s: hash dim %d not in {32,64,128,256}", fn, d);
+        SL_REQUIRE(HT % (d / cpt) == 0, SL_ESHAPE, "%s: hash dim %d unsupported", fn, d);
+    }
+    for (int i = 0; i < p->n_layers; ++i) {
+        SL_REQUIRE(p->d_w[i] != nullptr, SL_EINVAL, "%s: null weight of layer %d", fn, i);
+        SL_REQUIRE(sl::aligned16(p->d_w[i]), SL_EALIGN, "%s: weight of layer %d not 16-byte aligned", fn, i);
+        if (p->residue) SL_REQUIRE(p->dims[i] == p->dims[i + 1], SL_ESHAPE, "%s: residue needs equal layer widths", fn);
+    }
+    return SL_OK;
+}
+
+size_t hash_smem(const sl_hash_params* a, const sl_hash_params* b, int R) {
+    // red = KS*R*dout floats with KS*ncg = HT  =>  HT*R*CPT floats at most; CPT <= 8
+    (void)a; (void)b;
+    return (size_t)2 * R * MAXD * 4 + (size_t)HT * R * 8 * 4;
+}
+
+template <typename T>
+int launch_T(const HashArgs& args, int total_heads, long long max_tiles, int R, size_t smem, cudaStream_t s) {
+    dim3 grid((unsigned)max_tiles, (unsigned)total_heads);
+    void (*kern)(const HashArgs) = nullptr;
+    switch (R) {
+        case 1: kern = hash_kernel<T, 1>; break;
+        case 2: kern = hash_kernel<T, 2>; break;
+        case 4: kern = hash_kernel<T, 4>; break;
+        default: kern = hash_kernel<T, 8>; break;
+    }
+    SL_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    kern<<<grid, HT, smem, s>>>(args);
+    SL_CUDA_OK(cudaGetLastError());
+    return SL_OK;
+}
+
+int launch(const HashArgs& args, int dtype, int total_heads, long long rows_max, cudaStream_t s) {
+    const int R = rows_max >= 8 ? 8 : rows_max >= 4 ? 4 : rows_max >= 2 ? 2 : 1;
+    HashArgs a = args;
+    long long max_tiles = 0;
+    for (int j = 0; j < 2; ++j) {
+        const long long rows = (long long)a.job[j].B * a.job[j].T;
+        a.job[j].row_tiles = a.job[j].H > 0 ? (rows + R - 1) / R : 0;
+        max_tiles = std::max(max_tiles, a.job[j].row_tiles);
+    }
+    SL_REQUIRE(max_tiles <= 0x7fffffffLL && total_heads <= 65535, SL_ESHAPE, "hash: grid too large");
+    if (max_tiles == 0) return SL_OK;
+    const size_t smem = hash_smem(nullptr, nullptr, R);
+    switch (dtype) {
+        case SL_BF16: return launch_T<__nv_bfloat16>(a, total_heads, max_tiles, R, smem, s);
+        case SL_F16: return launch_T<__half>(a, total_heads, max_tiles, R, smem, s);
+        case SL_F32: return launch_T<float>(a, total_heads, max_tiles, R, smem, s);
+        default: return sl::fail(SL_EINVAL, "hash: unsupported dtype %d", dtype);
+    }
+}
+
+}  // namespace
+
+extern "C" int sl_decode_prepare(const void* d_q, const void* d_k, const void* d_v, int dtype, int B, int QH, int KH,
+                                 const void* d_cos, const void* d_sin, const sl_hash_params* hash_q,
+                                 const sl_hash_params* hash_k, void* d_q_rot, uint32_t* d_q_codes,
+                                 uint32_t* d_code_cache, int64_t code_batch_stride, void* d_k_cache, void* d_v_cache,
+                                 int64_t kv_batch_stride, int64_t pos, void* stream) {
+    SL_REQUIRE(d_q && d_q_codes, SL_EINVAL, "sl_decode_prepare: null query pointer");
+    SL_REQUIRE(B > 0 && QH > 0 && KH >= 0 && pos >= 0, SL_ESHAPE, "sl_decode_prepare: bad shape");
+    SL_REQUIRE((d_cos == nullptr) == (d_sin == nullptr), SL_EINVAL, "sl_decode_prepare: cos and sin must come together");
+    if (int rc = check_params("sl_decode_prepare", hash_q, dtype)) return rc;
+    const bool with_k = d_k != nullptr && KH > 0;
+    if (with_k) {
+        if (int rc = check_params("sl_decode_prepare", hash_k, dtype)) return rc;
+        SL_REQUIRE(d_code_cache != nullptr, SL_EINVAL, "sl_decode_prepare: key given without a code cache");
+        SL_REQUIRE((d_v == nullptr) == (d_v_cache == nullptr), SL_EINVAL, "sl_decode_prepare: value and value cache must come together");
+    }
+    HashArgs args = {};
+    HashJob& q = args.job[0];
+    q.x = d_q; q.xs_b = (long long)QH * 128; q.T = 1; q.H = QH; q.B = B;
+    q.hp = *hash_q;
+    q.codes = d_q_codes; q.cs_b = (long long)QH * 4;
+    q.x_rot = d_q_rot; q.xr_b = (long long)QH * 128;
+    q.cosr = d_cos; q.sinr = d_sin;
+    args.heads0 = QH;
+    int total = QH;
+    if (with_k) {
+        HashJob& k = args.job[1];
+        k.x = d_k; k.xs_b = (long long)KH * 128; k.T = 1; k.H = KH; k.B = B;
+        k.hp = *hash_k;
+        k.codes = d_code_cache + pos * KH * 4; k.cs_b = code_batch_stride;
+        if (d_k_cache) {
+            const size_t esz = dtype == SL_F32 ? 4 : 2;
+            k.x_rot = static_cast<unsigned char*>(d_k_cache) + (size_t)pos * KH * 128 * esz;
+            k.xr_b = kv_batch_stride;
+        }
+        if (d_v_cache) {
+            const size_t esz = dtype == SL_F32 ? 4 : 2;
+            k.v_src = d_v;
+            k.v_dst = static_cast<unsigned char*>(d_v_cache) + (size_t)pos * KH * 128 * esz;
+            k.v_b = kv_batch_stride;
+        }
+        k.cosr = d_cos; k.sinr = d_sin;
+        total += KH;
+    }
+    return launch(args, dtype, total, B, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int sl_hash_encode(const void* d_x, int64_t x_batch_stride, int dtype, int B, int64_t T, int H,
+                              const sl_hash_params* hash, uint32_t* d_codes, int64_t code_batch_stride, void* stream) {
+    SL_REQUIRE(d_x && d_codes, SL_EINVAL, "sl_hash_encode: null pointer");
+    SL_REQUIRE(B > 0 && T >= 0 && H > 0, SL_ESHAPE, "sl_hash_encode: bad shape");
+    SL_REQUIRE(x_batch_stride >= T * H * 128 && code_batch_stride >= T * H * 4, SL_ESHAPE,
+               "sl_hash_encode: batch stride shorter than a batch row");
+    if (int rc = check_params("sl_hash_encode", hash, dtype)) return rc;
+    if (T == 0) return SL_OK;
+    HashArgs args = {};
+    HashJob& j = args.job[0];
+    j.x = d_x; j.xs_b = x_batch_stride; j.T = T; j.H = H; j.B = B;
+    j.hp = *hash;
+    j.codes = d_codes; j.cs_b = code_batch_stride;
+    args.heads0 = H;
+    return launch(args, dtype, H, (long long)B * T, static_cast<cudaStream_t>(stream));
+}

@@ -1,0 +1,382 @@
+"""Torch-facing wrappers over the C ABI: tensors in, tensors out. PyTorch is used only for
+device memory and streams; every computation is a kernel of libspotlight_b200.so.
+
+All tensors must live on a CUDA device. There is no CPU path."""
+from __future__ import annotations
+
+import ctypes as C
+from typing import List, Optional, Sequence, Tuple
+
+import torch
+
+from . import _lib
+from ._lib import GQA_BLOCKED, GQA_INTERLEAVED, check, lib
+
+_DTYPES = {torch.bfloat16: _lib.SL_BF16, torch.float32: _lib.SL_F32, torch.float16: _lib.SL_F16,
+           torch.bool: _lib.SL_BOOL}
+
+launch_count = 0     # kernels launched through this module (bench accounting)
+
+
+def _count(n: int = 1) -> None:
+    global launch_count
+    launch_count += n
+
+
+def _dt(t: torch.Tensor) -> int:
+    try:
+        return _DTYPES[t.dtype]
+    except KeyError:
+        raise TypeError(f"unsupported dtype {t.dtype}") from None
+
+
+def _cuda(*tensors: torch.Tensor) -> torch.device:
+    dev = tensors[0].device
+    for t in tensors:
+        if t is None:
+            continue
+        if not t.is_cuda:
+            raise RuntimeError("spotlight_b200 kernels need CUDA tensors (there is no CPU path)")
+        if t.device != dev:
+            raise RuntimeError("all tensors must be on the same device")
+    check(lib.sl_set_device(dev.index if dev.index is not None else torch.cuda.current_device()))
+    return dev
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
+    return None if t is None else t.data_ptr()
+
+
+def _rows_view(t: torch.Tensor, inner: int) -> int:
+    """Batch stride (in elements) of a [B, N, H, inner] tensor whose batch rows are contiguous
+    [N,H,inner] blocks (a `cache[:, :end]` view qualifies)."""
+    B, N, H, D = t.shape
+    assert D == inner
+    if N * H * D and t.stride()[1:] != (H * D, D, 1):
+        raise ValueError("expected token-major rows [N, H, D] contiguous inside each batch row")
+    return t.stride(0) if B > 1 else max(t.stride(0), N * H * D)
+
+
+# ----------------------------------------------------------------------------- workspaces
+class _Workspaces:
+    """Zero-initialised scratch buffers, one per (kind, device, size class); the kernels leave
+    them zeroed, so they are allocated once and reused. A status word rides along."""
+
+    def __init__(self):
+        self._bufs = {}
+
+    def get(self, kind: str, device: torch.device, nbytes: int) -> Tuple[torch.Tensor, torch.Tensor]:
+        key = (kind, device)
+        cur = self._bufs.get(key)
+        if cur is None or cur[0].numel() < nbytes:
+            buf = torch.zeros(max(nbytes, 256), dtype=torch.uint8, device=device)
+            status = torch.zeros(1, dtype=torch.int32, device=device)
+            cur = (buf, status)
+            self._bufs[key] = cur
+        return cur
+
+    def reset(self):
+        self._bufs.clear()
+
+
+workspaces = _Workspaces()
+
+
+def check_status(device=None) -> None:
+    """Host-side read of every status word (synchronises). Raises if a bounded device-side wait
+    ran out; the affected workspace is dropped so the next call starts from a clean one."""
+    bad = []
+    for key, (buf, status) in list(workspaces._bufs.items()):
+        if device is not None and key[1] != torch.device(device):
+            continue
+        if int(status.item()) != 0:
+            bad.append((key, int(status.item())))
+            del workspaces._bufs[key]
+    if bad:
+        raise RuntimeError(f"spotlight_b200 [{_lib.SL_ETIMEOUT}]: device-side status set: {bad}")
+
+
+# ----------------------------------------------------------------------------- hash params
+class HashParams:
+    """Device-resident hash parameters of one head set. ``weights[i]``: [H, in_i, out_i];
+    ``biases[i]``: [H, out_i] or None. One layer without bias is the linear hash."""
+
+    def __init__(self, weights: Sequence[torch.Tensor], biases: Optional[Sequence[Optional[torch.Tensor]]] = None,
+                 residue: bool = False):
+        assert 1 <= len(weights) <= 3
+        biases = list(biases) if biases is not None else [None] * len(weights)
+        self.weights = [w.contiguous() for w in weights]
+        self.biases = [None if b is None else b.contiguous() for b in biases]
+        self.residue = bool(residue)
+        self.heads = self.weights[0].shape[0]
+        self.dtype = self.weights[0].dtype
+        s = _lib.HashParamsStruct()
+        s.n_layers = len(self.weights)
+        dims = [self.weights[0].shape[1]] + [w.shape[2] for w in self.weights]
+        for i, w in enumerate(self.weights):
+            assert w.dim() == 3 and w.shape[0] == self.heads and w.shape[1] == dims[i] and w.dtype == self.dtype
+            s.d_w[i] = w.data_ptr()
+            b = self.biases[i]
+            if b is not None:
+                assert b.shape == (self.heads, dims[i + 1]) and b.dtype == self.dtype
+                s.d_b[i] = b.data_ptr()
+        for i, d in enumerate(dims):
+            s.dims[i] = d
+        s.residue = int(self.residue)
+        self.struct = s
+
+    @classmethod
+    def from_dict(cls, params: dict, device, residue: bool = False) -> "HashParams":
+        """From workloads.make_hash_params output."""
+        ws = [w.to(device) for w in params["w"]]
+        bs = [None if b is None else b.to(device) for b in params["b"]]
+        return cls(ws, bs, residue if params["kind"] == "mlp" else False)
+
+    def ref(self):
+        return C.byref(self.struct)
+
+
+# ----------------------------------------------------------------------------- pack / scores
+def pack_signbits(x: torch.Tensor, word_bits: int = 32) -> torch.Tensor:
+    """[..., 32m] (bf16/fp16/fp32/bool) -> uint32 [..., m] (or uint8 [..., 4m] for word_bits=8)."""
+    assert word_bits in (8, 32)
+    last = x.shape[-1]
+    assert last % word_bits == 0, f"suppose `last_dim % {word_bits} == 0`"
+    _cuda(x)
+    x = x.contiguous()
+    out_dtype = torch.uint32 if word_bits == 32 else torch.uint8
+    out = torch.empty((*x.shape[:-1], last // word_bits), dtype=out_dtype, device=x.device)
+    check(lib.sl_pack_signbits(x.data_ptr(), _dt(x), x.numel(), out.data_ptr(), _stream()))
+    _count()
+    return out
+
+
+def hamming_scores(q_hash: torch.Tensor, k_hash: torch.Tensor, layout: int = GQA_INTERLEAVED) -> torch.Tensor:
+    """uint32 [B,1,QH,W] x uint32 [B,N,KH,W] -> int16 [B,N,KH] match counts."""
+    B, QN, QH, W = q_hash.shape
+    B2, N, KH, W2 = k_hash.shape
+    assert QN == 1, "only support single query"
+    assert QH % KH == 0, "query head must be multiple of key head"
+    assert B == B2 and W == W2
+    assert q_hash.dtype == torch.uint32 and k_hash.dtype == torch.uint32, "Inputs must be uint32"
+    _cuda(q_hash, k_hash)
+    q_hash = q_hash.contiguous()
+    kb = _rows_view(k_hash, W)
+    out = torch.empty((B, N, KH), dtype=torch.int16, device=q_hash.device)
+    check(lib.sl_hamming_scores(q_hash.data_ptr(), k_hash.data_ptr(), kb, out.data_ptr(), B, N, KH, QH, W,
+                                layout, _stream()))
+    _count()
+    return out
+
+
+def hamming_scores_u8(q_hash: torch.Tensor, k_hash: torch.Tensor) -> torch.Tensor:
+    """uint8 [B,H,1,D] x uint8 [B,H,N,D] -> uint8 [B,H,N] per-head match counts."""
+    B, H, q_len, D = q_hash.shape
+    _, _, N, _ = k_hash.shape
+    assert q_len == 1, "only support single query"
+    assert q_hash.dtype == torch.uint8 and k_hash.dtype == torch.uint8
+    _cuda(q_hash, k_hash)
+    q = q_hash.reshape(-1, D).contiguous()
+    k = k_hash.reshape(-1, N, D).contiguous()
+    out = torch.empty((B * H, N), dtype=torch.uint8, device=q.device)
+    check(lib.sl_hamming_scores_u8(q.data_ptr(), k.data_ptr(), out.data_ptr(), B * H, N, D, _stream()))
+    _count()
+    return out.view(B, H, N)
+
+
+# ----------------------------------------------------------------------------- scan + top-k
+def scan_topk(q_codes: torch.Tensor, k_codes: torch.Tensor, k: int, sink: int = 4, recent: int = 64,
+              layout: int = GQA_BLOCKED, idx: Optional[torch.Tensor] = None, cnt: Optional[torch.Tensor] = None,
+              return_scores: bool = False):
+    """Fused Hamming scan + exact top-k (lowest-index ties) + sink/recent window.
+    q_codes uint32 [B,QH,4] (or [B,1,QH,4]); k_codes uint32 [B,N,KH,4] (a cache view is fine).
+    Returns (idx int32 [B,KH,cap] ascending, cnt int32 [B,KH]) [+ scores int16 [B,N,KH]]."""
+    if q_codes.dim() == 4:
+        q_codes = q_codes[:, 0]
+    B, QH, W = q_codes.shape
+    B2, N, KH, W2 = k_codes.shape
+    assert W == 4 and W2 == 4 and B == B2, "only support head dim = 4 now"
+    dev = _cuda(q_codes, k_codes)
+    q_codes = q_codes.contiguous()
+    kb = _rows_view(k_codes, 4)
+    cap = max(1, min(N, k + sink + recent))
+    if idx is None:
+        idx = torch.empty((B, KH, cap), dtype=torch.int32, device=dev)
+    if cnt is None:
+        cnt = torch.empty((B, KH), dtype=torch.int32, device=dev)
+    assert idx.shape[0] == B and idx.shape[1] == KH and idx.is_contiguous() and idx.dtype == torch.int32
+    scores = torch.empty((B, N, KH), dtype=torch.int16, device=dev) if return_scores else None
+    need = lib.sl_scan_topk_workspace_bytes(B, N, KH, QH)
+    ws, status = workspaces.get("scan", dev, need)
+    check(lib.sl_scan_topk(q_codes.data_ptr(), k_codes.data_ptr(), kb, B, N, KH, QH, layout, k, sink, recent,
+                           idx.data_ptr(), idx.shape[2], cnt.data_ptr(), _ptr(scores), ws.data_ptr(), ws.numel(),
+                           status.data_ptr(), _stream()))
+    _count()
+    return (idx, cnt, scores) if return_scores else (idx, cnt)
+
+
+def topk_from_scores(scores: torch.Tensor, k: int, max_score: int, sink: int = 0, recent: int = 0):
+    """scores int16 [B,N,KH] in [0,max_score] -> (idx int32 [B,KH,cap] ascending, cnt int32 [B,KH])."""
+    B, N, KH = scores.shape
+    assert scores.dtype == torch.int16
+    dev = _cuda(scores)
+    scores = scores.contiguous()
+    cap = max(1, min(N, k + sink + recent))
+    idx = torch.empty((B, KH, cap), dtype=torch.int32, device=dev)
+    cnt = torch.empty((B, KH), dtype=torch.int32, device=dev)
+    need = lib.sl_topk_from_scores_workspace_bytes(B, N, KH, max_score)
+    ws, status = workspaces.get("topk", dev, need)
+    check(lib.sl_topk_from_scores(scores.data_ptr(), B, N, KH, max_score, k, sink, recent, idx.data_ptr(), cap,
+                                  cnt.data_ptr(), ws.data_ptr(), ws.numel(), status.data_ptr(), _stream()))
+    _count()
+    return idx, cnt
+
+
+def scan_hist(q_codes: torch.Tensor, k_codes: torch.Tensor, layout: int = GQA_BLOCKED):
+    """Sequence-shard step 1: local scores int16 [B,N,KH] and local histogram uint32 [B,KH,nbins]."""
+    if q_codes.dim() == 4:
+        q_codes = q_codes[:, 0]
+    B, QH, _ = q_codes.shape
+    _, N, KH, _ = k_codes.shape
+    dev = _cuda(q_codes, k_codes)
+    q_codes = q_codes.contiguous()
+    kb = _rows_view(k_codes, 4)
+    nbins = 128 * (QH // KH) + 1
+    scores = torch.empty((B, N, KH), dtype=torch.int16, device=dev)
+    hist = torch.zeros((B, KH, nbins), dtype=torch.int32, device=dev)
+    check(lib.sl_scan_hist(q_codes.data_ptr(), k_codes.data_ptr(), kb, B, N, KH, QH, layout, scores.data_ptr(),
+                           hist.data_ptr(), _stream()))
+    _count()
+    return scores, hist
+
+
+def select_emit(scores: torch.Tensor, hist_all: torch.Tensor, rank: int, tok_offset: int, n_global: int, QH: int,
+                k: int, sink: int = 4, recent: int = 64):
+    """Sequence-shard step 2: local attended indices from the all-gathered histograms
+    hist_all [R,B,KH,nbins]."""
+    B, N, KH = scores.shape
+    R = hist_all.shape[0]
+    dev = _cuda(scores, hist_all)
+    hist_all = hist_all.contiguous()
+    s_end = min(sink, n_global)
+    r_start = max(s_end, n_global - recent)
+    forced = max(0, min(s_end - tok_offset, N)) + max(0, tok_offset + N - max(r_start, tok_offset))
+    cap = max(1, min(N, k + forced))
+    idx = torch.empty((B, KH, cap), dtype=torch.int32, device=dev)
+    cnt = torch.empty((B, KH), dtype=torch.int32, device=dev)
+    need = lib.sl_select_emit_workspace_bytes(B, N, KH, QH)
+    ws, status = workspaces.get("emit", dev, need)
+    check(lib.sl_select_emit(scores.data_ptr(), hist_all.data_ptr(), R, rank, B, N, tok_offset, n_global, KH, QH, k,
+                             sink, recent, idx.data_ptr(), cap, cnt.data_ptr(), ws.data_ptr(), ws.numel(),
+                             status.data_ptr(), _stream()))
+    _count()
+    return idx, cnt
+
+
+# ----------------------------------------------------------------------------- hash stage
+def decode_prepare(q: torch.Tensor, k: Optional[torch.Tensor], v: Optional[torch.Tensor], hash_q: HashParams,
+                   hash_k: Optional[HashParams], pos: int, code_cache: Optional[torch.Tensor] = None,
+                   k_cache: Optional[torch.Tensor] = None, v_cache: Optional[torch.Tensor] = None,
+                   cos: Optional[torch.Tensor] = None, sin: Optional[torch.Tensor] = None,
+                   q_rot: Optional[torch.Tensor] = None, q_codes: Optional[torch.Tensor] = None):
+    """Stage 1 of a decode step in one launch (see sl_decode_prepare). q [B,QH,128], k/v [B,KH,128];
+    caches are full pre-allocated tensors [B,Nmax,KH,*]; row `pos` of each is written.
+    Returns (q_rot [B,QH,128], q_codes uint32 [B,QH,4])."""
+    B, QH, D = q.shape
+    assert D == 128
+    dev = _cuda(q)
+    q = q.contiguous()
+    KH = 0 if k is None else k.shape[1]
+    if q_rot is None:
+        q_rot = torch.empty_like(q)
+    if q_codes is None:
+        q_codes = torch.empty((B, QH, 4), dtype=torch.uint32, device=dev)
+    code_b = kv_b = 0
+    if k is not None:
+        k = k.contiguous()
+        v = None if v is None else v.contiguous()
+        assert code_cache is not None and code_cache.shape[0] == B and code_cache.shape[2:] == (KH, 4)
+        assert pos < code_cache.shape[1], "code cache is full"
+        code_b = _rows_view(code_cache, 4)
+        if k_cache is not None:
+            assert pos < k_cache.shape[1], "kv cache is full"
+            kv_b = _rows_view(k_cache, 128)
+            if v_cache is not None:
+                assert _rows_view(v_cache, 128) == kv_b
+    check(lib.sl_decode_prepare(q.data_ptr(), _ptr(k), _ptr(v), _dt(q), B, QH, KH, _ptr(cos), _ptr(sin),
+                                hash_q.ref(), hash_k.ref() if hash_k is not None else None, q_rot.data_ptr(),
+                                q_codes.data_ptr(), _ptr(code_cache), code_b, _ptr(k_cache), _ptr(v_cache), kv_b,
+                                pos, _stream()))
+    _count()
+    return q_rot, q_codes
+
+
+def hash_encode(x: torch.Tensor, params: HashParams, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """x [B,T,H,128] -> codes uint32 [B,T,H,4] (hash + sign + pack)."""
+    B, T, H, D = x.shape
+    assert D == 128 and H == params.heads
+    dev = _cuda(x)
+    xb = _rows_view(x, 128)
+    if out is None:
+        out = torch.empty((B, T, H, 4), dtype=torch.uint32, device=dev)
+    ob = _rows_view(out, 4)
+    check(lib.sl_hash_encode(x.data_ptr(), xb, _dt(x), B, T, H, params.ref(), out.data_ptr(), ob, _stream()))
+    _count()
+    return out
+
+
+# ----------------------------------------------------------------------------- attention
+def sparse_attn_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, idx: torch.Tensor,
+                       cnt: torch.Tensor, layout: int = GQA_BLOCKED, out: Optional[torch.Tensor] = None,
+                       return_lse: bool = False):
+    """q [B,QH,128]; k_cache/v_cache [B,N,KH,128] (views of a larger cache are fine);
+    idx int32 [B,KH,cap], cnt int32 [B,KH] -> out [B,QH,128] (+ lse float [B,QH])."""
+    B, QH, D = q.shape
+    _, _, KH, _ = k_cache.shape
+    assert D == 128 and k_cache.dtype == q.dtype and v_cache.dtype == q.dtype
+    dev = _cuda(q, k_cache, v_cache, idx, cnt)
+    q = q.contiguous()
+    kvb = _rows_view(k_cache, 128)
+    assert _rows_view(v_cache, 128) == kvb
+    assert idx.is_contiguous() and cnt.is_contiguous() and idx.dtype == torch.int32 and cnt.dtype == torch.int32
+    if out is None:
+        out = torch.empty_like(q)
+    lse = torch.empty((B, QH), dtype=torch.float32, device=dev) if return_lse else None
+    need = lib.sl_sparse_attn_workspace_bytes(B, KH, QH)
+    ws, _ = workspaces.get("attn", dev, need)
+    check(lib.sl_sparse_attn_decode(q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), _dt(q), kvb,
+                                    idx.data_ptr(), idx.shape[2], cnt.data_ptr(), B, KH, QH, layout,
+                                    out.data_ptr(), _ptr(lse), ws.data_ptr(), ws.numel(), _stream()))
+    _count()
+    return (out, lse) if return_lse else out
+
+
+def merge_lse(o_parts: torch.Tensor, lse_parts: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:
+    """o_parts float [R,...,128], lse_parts float [R,...] -> merged [...,128] of `dtype`."""
+    R = o_parts.shape[0]
+    dev = _cuda(o_parts, lse_parts)
+    o_parts = o_parts.contiguous().float()
+    lse_parts = lse_parts.contiguous().float()
+    rows = lse_parts[0].numel()
+    out = torch.empty(o_parts.shape[1:], dtype=dtype, device=dev)
+    check(lib.sl_merge_lse(o_parts.data_ptr(), lse_parts.data_ptr(), R, rows, _DTYPES[dtype], out.data_ptr(), _stream()))
+    _count()
+    return out
+
+
+def gather_rows(cache: torch.Tensor, idx: torch.Tensor, budget: int) -> torch.Tensor:
+    """cache [B,N,KH,128], idx int32 [B,KH,cap] -> [B,budget,KH,128] with
+    out[b,j,h] = cache[b, idx[b,h,j], h]."""
+    B, N, KH, D = cache.shape
+    assert D == 128
+    dev = _cuda(cache, idx)
+    cb = _rows_view(cache, 128)
+    out = torch.empty((B, budget, KH, D), dtype=cache.dtype, device=dev)
+    check(lib.sl_gather_rows(cache.data_ptr(), cb, cache.element_size(), idx.data_ptr(), idx.shape[2], B, KH, budget,
+                             out.data_ptr(), _stream()))
+    _count()
+    return out

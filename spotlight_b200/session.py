@@ -1,0 +1,168 @@
+"""A decode session over the retrieval path for models whose attention layers share one shape:
+per-layer code / K / V caches, per-layer hash parameters, and the three-launch layer step
+
+    decode_prepare -> scan_topk -> sparse_attn_decode
+
+for all layers of one decode token, eagerly or as a replayed CUDA graph, with device-resident
+inputs or with pinned host buffers (host->device copy of the token's q/k/v and device->host
+copy of the attention outputs inside the step).
+
+This is the host-side counterpart of the reference's per-layer loop
+(spotlight/modifiers/spotlight_generation.py:58-79 calling :109-226) with its caches
+(spotlight/modifiers/gpu_cache.py) for callers that drive the attention path themselves."""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import List, Optional
+
+import torch
+
+from . import ops
+from ._lib import GQA_BLOCKED
+from .workloads import budget
+
+
+@dataclass
+class SessionConfig:
+    batch: int
+    q_heads: int
+    kv_heads: int
+    layers: int
+    capacity: int                      # tokens per cache row
+    dtype: torch.dtype = torch.bfloat16
+    mask_out: float = 0.98
+    min_remain: int = 20
+    sink: int = 4
+    recent: int = 64
+    layout: int = GQA_BLOCKED
+    fix_layers: tuple = ()             # layers that attend to every key
+
+
+class DecodeSession:
+    def __init__(self, cfg: SessionConfig, hash_q: List[ops.HashParams], hash_k: List[ops.HashParams],
+                 device="cuda"):
+        assert len(hash_q) == cfg.layers and len(hash_k) == cfg.layers
+        self.cfg, self.device = cfg, torch.device(device)
+        B, QH, KH, L, C = cfg.batch, cfg.q_heads, cfg.kv_heads, cfg.layers, cfg.capacity
+        dev, dt = self.device, cfg.dtype
+        self.hash_q, self.hash_k = hash_q, hash_k
+        self.k_cache = [torch.empty((B, C, KH, 128), dtype=dt, device=dev) for _ in range(L)]
+        self.v_cache = [torch.empty((B, C, KH, 128), dtype=dt, device=dev) for _ in range(L)]
+        self.codes = [torch.empty((B, C, KH, 4), dtype=torch.uint32, device=dev) for _ in range(L)]
+        self.length = 0
+        # one token's inputs and outputs for all layers
+        self.q_in = torch.zeros((L, B, QH, 128), dtype=dt, device=dev)
+        self.k_in = torch.zeros((L, B, KH, 128), dtype=dt, device=dev)
+        self.v_in = torch.zeros((L, B, KH, 128), dtype=dt, device=dev)
+        self.out = torch.zeros((L, B, QH, 128), dtype=dt, device=dev)
+        self.cos = torch.zeros((128,), dtype=dt, device=dev)
+        self.sin = torch.zeros((128,), dtype=dt, device=dev)
+        self.q_rot = torch.empty((B, QH, 128), dtype=dt, device=dev)
+        self.q_codes = torch.empty((B, QH, 4), dtype=torch.uint32, device=dev)
+        cap = min(C, budget(C, cfg.mask_out, cfg.min_remain) + cfg.sink + cfg.recent + 1)
+        self.idx = torch.empty((B, KH, cap), dtype=torch.int32, device=dev)
+        self.cnt = torch.zeros((B, KH), dtype=torch.int32, device=dev)
+        self._graphs = {}
+        self._host = None
+
+    # ------------------------------------------------------------------ cache filling
+    def load_context(self, layer: int, k: torch.Tensor, v: torch.Tensor, start: int = 0, codes: bool = True):
+        """Copy post-RoPE keys / values [B,T,KH,128] into the caches at [start, start+T) and build
+        their codes with the layer's key hash."""
+        T = k.shape[1]
+        self.k_cache[layer][:, start:start + T] = k
+        self.v_cache[layer][:, start:start + T] = v
+        if codes:
+            ops.hash_encode(self.k_cache[layer][:, start:start + T], self.hash_k[layer],
+                            out=self.codes[layer][:, start:start + T])
+
+    def set_position(self, pos: int, theta: float):
+        """RoPE row of the decode position (host-computed, as the reference's tables are)."""
+        inv = 1.0 / (theta ** (torch.arange(0, 128, 2, dtype=torch.float32) / 128))
+        f = float(pos) * inv
+        emb = torch.cat([f, f])
+        self.cos.copy_(emb.cos().to(self.cfg.dtype))
+        self.sin.copy_(emb.sin().to(self.cfg.dtype))
+
+    # ------------------------------------------------------------------ one token
+    def layer_step(self, layer: int, pos: int, stage: Optional[str] = None):
+        """The three launches of one layer for the token at position `pos` (its key/value are
+        appended at row `pos`; keys 0..pos are scanned). `stage` restricts to one launch."""
+        c = self.cfg
+        n = pos + 1
+        if stage in (None, "prepare"):
+            ops.decode_prepare(self.q_in[layer], self.k_in[layer], self.v_in[layer], self.hash_q[layer],
+                               self.hash_k[layer], pos, self.codes[layer], self.k_cache[layer], self.v_cache[layer],
+                               self.cos, self.sin, q_rot=self.q_rot, q_codes=self.q_codes)
+        if stage in (None, "scan"):
+            if layer in c.fix_layers:
+                raise NotImplementedError("dense layers are served by the attention hook, not the session")
+            ops.scan_topk(self.q_codes, self.codes[layer][:, :n], budget(n, c.mask_out, c.min_remain), c.sink,
+                          c.recent, c.layout, idx=self.idx, cnt=self.cnt)
+        if stage in (None, "attn"):
+            ops.sparse_attn_decode(self.q_rot, self.k_cache[layer][:, :n], self.v_cache[layer][:, :n], self.idx,
+                                   self.cnt, c.layout, out=self.out[layer])
+
+    def step(self, pos: int, stage: Optional[str] = None):
+        for layer in range(self.cfg.layers):
+            self.layer_step(layer, pos, stage)
+
+    # ------------------------------------------------------------------ graphs
+    def capture(self, pos: int, stage: Optional[str] = None, host_io: bool = False) -> torch.cuda.CUDAGraph:
+        """Capture `step(pos)` (optionally one stage only, optionally with the pinned-host copies)
+        into a CUDA graph; replays reuse the same position and buffers."""
+        key = (pos, stage, host_io)
+        if key in self._graphs:
+            return self._graphs[key]
+        if host_io:
+            self._ensure_host()
+        s = torch.cuda.Stream(device=self.device)
+        s.wait_stream(torch.cuda.current_stream(self.device))
+        with torch.cuda.stream(s):
+            self._run(pos, stage, host_io)            # warm-up outside capture (workspaces allocate here)
+        torch.cuda.current_stream(self.device).wait_stream(s)
+        torch.cuda.synchronize(self.device)
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            self._run(pos, stage, host_io)
+        self._graphs[key] = g
+        return g
+
+    def _run(self, pos, stage, host_io):
+        if host_io:
+            self.q_in.copy_(self._host["q"], non_blocking=True)
+            self.k_in.copy_(self._host["k"], non_blocking=True)
+            self.v_in.copy_(self._host["v"], non_blocking=True)
+        self.step(pos, stage)
+        if host_io:
+            self._host["out"].copy_(self.out, non_blocking=True)
+
+    # ------------------------------------------------------------------ host buffers
+    def _ensure_host(self):
+        if self._host is None:
+            self._host = {
+                "q": torch.zeros(self.q_in.shape, dtype=self.cfg.dtype).pin_memory(),
+                "k": torch.zeros(self.k_in.shape, dtype=self.cfg.dtype).pin_memory(),
+                "v": torch.zeros(self.v_in.shape, dtype=self.cfg.dtype).pin_memory(),
+                "out": torch.zeros(self.out.shape, dtype=self.cfg.dtype).pin_memory(),
+            }
+        return self._host
+
+    def step_host(self, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, pos: int, graph: bool = True) -> torch.Tensor:
+        """One token with HOST inputs q [L,B,QH,128], k/v [L,B,KH,128]: stage them in pinned memory,
+        copy to the device, run every layer, copy the outputs [L,B,QH,128] back and wait for them."""
+        h = self._ensure_host()
+        h["q"].copy_(q)
+        h["k"].copy_(k)
+        h["v"].copy_(v)
+        if graph:
+            self.capture(pos, None, True).replay()
+        else:
+            self._run(pos, None, True)
+        torch.cuda.current_stream(self.device).synchronize()
+        return h["out"]
+
+    @property
+    def host_bytes_per_step(self):
+        e = self.q_in.element_size()
+        return (self.q_in.numel() + self.k_in.numel() + self.v_in.numel()) * e, self.out.numel() * e
