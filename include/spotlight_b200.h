@@ -74,7 +74,9 @@ int sl_hamming_scores_u8(const uint8_t* d_q, const uint8_t* d_k, uint8_t* d_out,
 
 /* Workspace protocol for the fused scan + top-k. The workspace must be zero-filled once with
  * sl_workspace_init (or cudaMemset) before its first use; every successful call leaves it
- * zeroed again. After SL_ETIMEOUT / a non-zero status word it must be re-initialised. */
+ * zeroed again FOR THE SAME (B, KH, QH): the internal layout depends on those three, so a
+ * workspace is bound to one shape (N may change freely) and must be re-initialised before it is
+ * used with another. After SL_ETIMEOUT / a non-zero status word it must be re-initialised too. */
 size_t sl_scan_topk_workspace_bytes(int B, int64_t N, int KH, int QH);
 int sl_workspace_init(void* d_workspace, size_t bytes, void* stream);
 

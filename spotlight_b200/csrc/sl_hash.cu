@@ -68,7 +68,7 @@ __global__ void __launch_bounds__(HT) hash_kernel(const HashArgs args) {
             const float rot = j < 64 ? -other : other;
             const float c = sl::VT<T>::to_f(reinterpret_cast<const T*>(J.cosr)[j]);
             const float s = sl::VT<T>::to_f(reinterpret_cast<const T*>(J.sinr)[j]);
-            val = sl::VT<T>::round(sl::VT<T>::round(val * c) + sl::VT<T>::round(rot * s));
+            val = sl::VT<T>::round(__fadd_rn(sl::VT<T>::round(__fmul_rn(val, c)), sl::VT<T>::round(__fmul_rn(rot, s))));
         }
         if (J.x_rot && rg < rows) {
             const long long b = rg / J.T, t = rg % J.T;

@@ -63,14 +63,16 @@ def _rows_view(t: torch.Tensor, inner: int) -> int:
 
 # ----------------------------------------------------------------------------- workspaces
 class _Workspaces:
-    """Zero-initialised scratch buffers, one per (kind, device, size class); the kernels leave
+    """Zero-initialised scratch buffers, one per (kind, device, shape); the kernels leave
     them zeroed, so they are allocated once and reused. A status word rides along."""
 
     def __init__(self):
         self._bufs = {}
 
-    def get(self, kind: str, device: torch.device, nbytes: int) -> Tuple[torch.Tensor, torch.Tensor]:
-        key = (kind, device)
+    def get(self, kind: str, device: torch.device, nbytes: int, shape=()) -> Tuple[torch.Tensor, torch.Tensor]:
+        """`shape` = (B, KH, QH): the library lays a workspace out per shape and only guarantees
+        to leave it zeroed for that shape, so every shape gets its own buffer."""
+        key = (kind, device, tuple(shape))
         cur = self._bufs.get(key)
         if cur is None or cur[0].numel() < nbytes:
             buf = torch.zeros(max(nbytes, 256), dtype=torch.uint8, device=device)
@@ -211,7 +213,7 @@ def scan_topk(q_codes: torch.Tensor, k_codes: torch.Tensor, k: int, sink: int = 
     assert idx.shape[0] == B and idx.shape[1] == KH and idx.is_contiguous() and idx.dtype == torch.int32
     scores = torch.empty((B, N, KH), dtype=torch.int16, device=dev) if return_scores else None
     need = lib.sl_scan_topk_workspace_bytes(B, N, KH, QH)
-    ws, status = workspaces.get("scan", dev, need)
+    ws, status = workspaces.get("scan", dev, need, (B, KH, QH))
     check(lib.sl_scan_topk(q_codes.data_ptr(), k_codes.data_ptr(), kb, B, N, KH, QH, layout, k, sink, recent,
                            idx.data_ptr(), idx.shape[2], cnt.data_ptr(), _ptr(scores), ws.data_ptr(), ws.numel(),
                            status.data_ptr(), _stream()))
@@ -229,7 +231,7 @@ def topk_from_scores(scores: torch.Tensor, k: int, max_score: int, sink: int = 0
     idx = torch.empty((B, KH, cap), dtype=torch.int32, device=dev)
     cnt = torch.empty((B, KH), dtype=torch.int32, device=dev)
     need = lib.sl_topk_from_scores_workspace_bytes(B, N, KH, max_score)
-    ws, status = workspaces.get("topk", dev, need)
+    ws, status = workspaces.get("topk", dev, need, (B, KH, max_score))
     check(lib.sl_topk_from_scores(scores.data_ptr(), B, N, KH, max_score, k, sink, recent, idx.data_ptr(), cap,
                                   cnt.data_ptr(), ws.data_ptr(), ws.numel(), status.data_ptr(), _stream()))
     _count()
@@ -269,7 +271,7 @@ def select_emit(scores: torch.Tensor, hist_all: torch.Tensor, rank: int, tok_off
     idx = torch.empty((B, KH, cap), dtype=torch.int32, device=dev)
     cnt = torch.empty((B, KH), dtype=torch.int32, device=dev)
     need = lib.sl_select_emit_workspace_bytes(B, N, KH, QH)
-    ws, status = workspaces.get("emit", dev, need)
+    ws, status = workspaces.get("emit", dev, need, (B, KH, QH))
     check(lib.sl_select_emit(scores.data_ptr(), hist_all.data_ptr(), R, rank, B, N, tok_offset, n_global, KH, QH, k,
                              sink, recent, idx.data_ptr(), cap, cnt.data_ptr(), ws.data_ptr(), ws.numel(),
                              status.data_ptr(), _stream()))
@@ -347,7 +349,7 @@ def sparse_attn_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Te
         out = torch.empty_like(q)
     lse = torch.empty((B, QH), dtype=torch.float32, device=dev) if return_lse else None
     need = lib.sl_sparse_attn_workspace_bytes(B, KH, QH)
-    ws, _ = workspaces.get("attn", dev, need)
+    ws, _ = workspaces.get("attn", dev, need, (B, KH, QH))
     check(lib.sl_sparse_attn_decode(q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), _dt(q), kvb,
                                     idx.data_ptr(), idx.shape[2], cnt.data_ptr(), B, KH, QH, layout,
                                     out.data_ptr(), _ptr(lse), ws.data_ptr(), ws.numel(), _stream()))

@@ -102,12 +102,28 @@ def test_path_against_reference_fixtures(name):
     k_keep = O.budget(N, c["mask_out"], 20)
     assert k_keep == int(f["k"])
     idx, cnt, scores = ops.scan_topk(q_codes, k_codes, k_keep, 4, 64, O.BLOCKED, return_scores=True)
-    sim = 2 * scores[0].cpu().numpy().T.astype(np.int32) - 128                # [H,N]
-    mismatch = sim != f["sim"].astype(np.int32)
-    assert mismatch.mean() < 0.02 if dtype == torch.bfloat16 else mismatch.mean() < 2e-3
-    if not mismatch.any():
-        for h in range(H):
-            np.testing.assert_array_equal(idx[0, h, : cnt[0, h]].cpu().numpy(), O.attended_set(f["sim"][h], k_keep))
+    # the kernel's integers are exactly the match counts of the codes it was given
+    ours = O.match_count(np_u32(q_codes)[:, None], np_u32(k_codes), O.BLOCKED)
+    np.testing.assert_array_equal(scores.cpu().numpy(), ours)
+    ref_idx, ref_cnt = O.select(ours, k_keep, 4, 64)
+    np.testing.assert_array_equal(cnt.cpu().numpy(), ref_cnt)
+    for h in range(H):
+        np.testing.assert_array_equal(idx[0, h, : ref_cnt[0, h]].cpu().numpy(), ref_idx[0, h, : ref_cnt[0, h]])
+    # codes against the reference's own sign bits (differences only where a pre-sign value is
+    # within rounding of zero), then the score relation sim = 2*match - 128
+    q_bits_ref = O.pack_signbits(f["hq_pre"])                                  # [H,4]
+    assert (np_u32(q_codes)[0] != q_bits_ref).sum() <= 1
+    if f["hk_bits"].size:
+        k_ref = np.ascontiguousarray(f["hk_bits"]).view(np.uint32).reshape(H, N, 4).transpose(1, 0, 2)
+        diff_bits = np.bitwise_count(np_u32(k_codes)[0] ^ k_ref).sum()
+        assert diff_bits <= 2e-3 * k_ref.size * 32, f"{diff_bits} key code bits differ from the reference's"
+    if (np_u32(q_codes)[0] == q_bits_ref).all():
+        sim = 2 * ours[0].T.astype(np.int32) - 128                             # [H,N]
+        mismatch = sim != f["sim"].astype(np.int32)                            # zeros (sign 0) and near-zero flips
+        assert mismatch.mean() < (0.2 if dtype == torch.bfloat16 else 2e-3)
+        if not mismatch.any():
+            for h in range(H):
+                np.testing.assert_array_equal(idx[0, h, : cnt[0, h]].cpu().numpy(), O.attended_set(f["sim"][h], k_keep))
     # attention on the reference's attended set
     att = f["attended"]
     cap = int(att.sum(1).max())

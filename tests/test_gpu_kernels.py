@@ -356,6 +356,6 @@ def test_errors_are_exceptions_not_crashes(ops):
     with pytest.raises(ValueError):
         ops.scan_topk(q, k, 50, idx=torch.empty((1, 8, 10), dtype=torch.int32, device=DEV))  # idx too small
     with pytest.raises(ValueError):
-        ops.hamming_scores(q[:, None], k.permute(0, 2, 1, 3))                 # not token-major
+        ops.hamming_scores(q[:, None], k.transpose(1, 2).contiguous().transpose(1, 2))  # not token-major
     with pytest.raises(AssertionError):
         ops.pack_signbits(torch.zeros((4, 100), device=DEV))                  # last dim % 32
