@@ -17,11 +17,18 @@
 
 namespace {
 
-constexpr int NT = 1024;
+#ifndef SL_SCAN_NT
+#define SL_SCAN_NT 512
+#endif
+#ifndef SL_SCAN_U
+#define SL_SCAN_U 8
+#endif
+constexpr int NT = SL_SCAN_NT;     // threads per CTA
 constexpr int NW = NT / 32;
-constexpr int U = 4;
+constexpr int U = SL_SCAN_U;       // 16-byte loads in flight per thread
 constexpr int SMEM_BUDGET = 200 * 1024;
 constexpr int MIN_CHUNK = 256;
+constexpr int NCOPY = 4;           // copies of the global histogram in the workspace
 
 enum { MODE_FUSED = 0, MODE_HIST_ONLY = 1, MODE_EMIT_ONLY = 2, MODE_FROM_SCORES = 3 };
 
@@ -38,11 +45,14 @@ struct ScanArgs {
     short* scores_out;         // optional [B,N,KH]
     unsigned short* gscores;   // scores in global memory (spill, or the sharded halves), else null
     unsigned* hist;            // global histogram [R,B,KH,nbins]; this rank adds to / reads slice `rank`
-    unsigned* seg;             // [B,ctas_per_b,KH,3]
+    uint4* seg;                // [B,ctas_per_b,KH] {>tau, ==tau, ==tau inside the sink, -}
     unsigned* sync;            // [B,2]
     int* status;
-    int ctas_per_b, chunk, nbins, S, mode, R, rank;
+    int ctas_per_b, chunk, nbins, S, mode, R, rank, ncopy;
+    unsigned long long* dbg;   // optional [grid][16] phase timestamps (ns)
 };
+
+static unsigned long long* g_dbg_timing = nullptr;   // set by sl_debug_scan_timing (development aid)
 
 struct Plan {
     int ctas_per_b, chunk, nbins, S;
@@ -54,7 +64,7 @@ inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
 inline size_t fixed_smem(int KH, int G, int nbins, int S) {
     return align_up((size_t)KH * G * 16, 16) + (size_t)KH * nbins * 4 + (size_t)KH * 2 * 4 +
-           (size_t)KH * S * 3 * 4 + (size_t)KH * 4 * 4 + 64;
+           (size_t)KH * S * 3 * 4 + (size_t)KH * 4 * 4 + (size_t)KH * 32 * 4 + 64;
 }
 
 Plan make_plan(int B, long long N, int KH, int G, bool scores_in_global, int nbins = 0) {
@@ -72,7 +82,7 @@ Plan make_plan(int B, long long N, int KH, int G, bool scores_in_global, int nbi
     p.chunk = (int)((chunk + 31) / 32 * 32);
     if (p.chunk < 32) p.chunk = 32;
     const size_t fixed = fixed_smem(KH, G, p.nbins, p.S);
-    const size_t sc = (size_t)p.chunk * KH * 2;
+    const size_t sc = (size_t)(p.chunk + 64) * KH * 2;      // transposed rows, padded to 4 (mod 32) words
     p.spill = scores_in_global || fixed + sc > (size_t)SMEM_BUDGET;
     p.smem = fixed + (p.spill ? 0 : sc);
     p.cooperative = p.ctas_per_b > 1;
@@ -85,28 +95,109 @@ __device__ __forceinline__ int warp_sum(int v) {
     return v;
 }
 
-template <int GT>  // GT > 0: group size known at compile time (q codes in registers); 0: generic
+
+// ---- bit-sliced group score -----------------------------------------------------------
+// POPC issues at a quarter of the integer rate, and the direct score needs 4*G of them per
+// key. Instead: per bit position b let cq_b = #{g : q_g has bit b set}. A key bit k_b = 1
+// matches cq_b query heads, k_b = 0 matches G - cq_b. With M_j / M'_j the bit planes of cq and
+// G - cq (P = bits(G) planes), X_{j,w} = select(k_w, M_{j,w}, M'_{j,w}) has weight 2^j and
+//   score = sum_j 2^j sum_w popc(X_{j,w}).
+// The 4*P words are added vertically with carry-save adders (LOP3 at full rate), leaving one
+// word per power of two: P + 2 popcounts per key whatever G is.
+#define SL_FA(a, b, c, s, cy) { const uint32_t t_ = (a) ^ (b); s = t_ ^ (c); cy = ((a) & (b)) | ((c) & t_); }
+#define SL_HA(a, b, s, cy) { s = (a) ^ (b); cy = (a) & (b); }
+
+template <int P>
+__device__ __forceinline__ int sliced_score(const uint4 k, const uint32_t (&M)[P][4], const uint32_t (&Mp)[P][4]) {
+    const uint32_t kw[4] = {k.x, k.y, k.z, k.w};
+    uint32_t X[P][4];
+#pragma unroll
+    for (int j = 0; j < P; ++j)
+#pragma unroll
+        for (int w = 0; w < 4; ++w) X[j][w] = (kw[w] & M[j][w]) | (~kw[w] & Mp[j][w]);
+    uint32_t s1, c1, c2, L0;
+    SL_FA(X[0][0], X[0][1], X[0][2], s1, c1)
+    SL_HA(s1, X[0][3], L0, c2)
+    int score = __popc(L0);
+    if constexpr (P == 1) {
+        uint32_t L1, L2;
+        SL_HA(c1, c2, L1, L2)
+        score += 2 * __popc(L1) + 4 * __popc(L2);
+    } else {
+        uint32_t s, sp, d1, d2, d3, L1;
+        SL_FA(X[1][0], X[1][1], X[1][2], s, d1)
+        SL_FA(X[1][3], c1, c2, sp, d2)
+        SL_HA(s, sp, L1, d3)
+        score += 2 * __popc(L1);
+        if constexpr (P == 2) {
+            uint32_t L2, L3;
+            SL_FA(d1, d2, d3, L2, L3)
+            score += 4 * __popc(L2) + 8 * __popc(L3);
+        } else {
+            uint32_t e1, e2, e3, L2;
+            SL_FA(X[2][0], X[2][1], X[2][2], s, e1)
+            SL_FA(X[2][3], d1, d2, sp, e2)
+            SL_FA(s, sp, d3, L2, e3)
+            score += 4 * __popc(L2);
+            if constexpr (P == 3) {
+                uint32_t L3, L4;
+                SL_FA(e1, e2, e3, L3, L4)
+                score += 8 * __popc(L3) + 16 * __popc(L4);
+            } else {
+                uint32_t f1, f2, f3, L3, L4, L5;
+                SL_FA(X[3][0], X[3][1], X[3][2], s, f1)
+                SL_FA(X[3][3], e1, e2, sp, f2)
+                SL_FA(s, sp, e3, L3, f3)
+                SL_FA(f1, f2, f3, L4, L5)
+                score += 8 * __popc(L3) + 16 * __popc(L4) + 32 * __popc(L5);
+            }
+        }
+    }
+    return score;
+}
+
+__device__ __forceinline__ void touch(const void* p) {   // warms the TLB for a page used later
+    unsigned v;
+    asm volatile("ld.global.cg.u32 %0, [%1];" : "=r"(v) : "l"(p));
+}
+
+template <int PT>  // PT > 0: bit-sliced scoring with PT planes (needs 32 % KH == 0); 0: direct popcounts
 __global__ void __launch_bounds__(NT, 1) scan_topk_kernel(const ScanArgs a) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
-    const int KH = a.KH, G = GT > 0 ? GT : a.G, nbins = a.nbins, S = a.S, N = a.N;
+    const int KH = a.KH, G = a.G, nbins = a.nbins, S = a.S, N = a.N;
     uint4* sq = reinterpret_cast<uint4*>(smem_raw);                                  // [KH][G]
     unsigned* shist = reinterpret_cast<unsigned*>(smem_raw + ((size_t)KH * G * 16));  // [KH][nbins]
     int* s_tau = reinterpret_cast<int*>(shist + (size_t)KH * nbins);                  // [KH]
     int* s_r = s_tau + KH;                                                            // [KH]
     unsigned* s_task = reinterpret_cast<unsigned*>(s_r + KH);                         // [KH][S][3]
     int* s_base = reinterpret_cast<int*>(s_task + (size_t)KH * S * 3);                // [KH][4]
+    uint32_t* s_planes = reinterpret_cast<uint32_t*>(s_base + KH * 4);                // [KH][2][4][4]
     unsigned short* sscores = reinterpret_cast<unsigned short*>(
-        smem_raw + (((size_t)((unsigned char*)(s_base + KH * 4) - smem_raw) + 15) & ~(size_t)15));
+        smem_raw + (((size_t)((unsigned char*)(s_planes + KH * 32) - smem_raw) + 15) & ~(size_t)15));
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int b = blockIdx.x / a.ctas_per_b, c = blockIdx.x % a.ctas_per_b;
     const int t0 = min(N, c * a.chunk), t1 = min(N, t0 + a.chunk);
     const int ncodes = (t1 - t0) * KH;
-    unsigned short* sc = a.gscores ? a.gscores + ((long long)b * N + t0) * KH : sscores;
-    unsigned* ghist = a.hist + ((long long)a.rank * a.B + b) * KH * nbins;           // this rank's slice
+    // Scores live either in shared memory, TRANSPOSED as [head][local key] with a row stride of
+    // 4 (mod 32) words so that the interleaved writes of pass A spread over the banks, or in
+    // global memory as [key][head] (spill of huge chunks, and the modes fed with scores).
+    const bool fast = a.gscores == nullptr;
+    const int roww = (a.chunk >> 1) + ((4 - (a.chunk >> 1)) & 31);
+    const int rowh = 2 * roww;
+    unsigned short* sc = fast ? sscores : a.gscores + ((long long)b * N + t0) * KH;
+    const long long hslice = (long long)a.B * KH * nbins;                            // one histogram copy / rank
+    unsigned* hist_b = a.hist + (long long)b * KH * nbins;                            // slice 0 of this batch row
     unsigned* sync = a.sync ? a.sync + 2 * b : nullptr;
     const bool multi = a.ctas_per_b > 1;
     unsigned barriers = 0;
+#define SL_STAMP(i)                                                                         \
+    if (a.dbg && tid == 0) {                                                                \
+        unsigned long long t_;                                                              \
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_));                              \
+        a.dbg[blockIdx.x * 16 + (i)] = t_;                                                   \
+    }
+    SL_STAMP(0)
 
     // ---------------------------------------------------------------- pass A: scan + histogram
     if (a.mode == MODE_FROM_SCORES) {
@@ -118,14 +209,21 @@ __global__ void __launch_bounds__(NT, 1) scan_topk_kernel(const ScanArgs a) {
             atomicAdd(&shist[(i % KH) * nbins + s], 1u);
         }
         __syncthreads();
-        if (multi) {
-            for (int i = tid; i < KH * nbins; i += NT) {
-                const unsigned v = shist[i];
-                if (v) atomicAdd(&ghist[i], v);
-            }
-            sl::grid_barrier(&sync[0], ++barriers * (unsigned)a.ctas_per_b, a.status);
-        }
     } else if (a.mode != MODE_EMIT_ONLY) {
+        // the first tile's loads are in flight while the query codes are staged
+        const uint4* base = a.k + (long long)b * a.k_bstride + (long long)t0 * KH;
+        uint4 cd[U];
+        int tile = warp;
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int i = tile * (32 * U) + u * 32 + lane;
+            if (i < ncodes) cd[u] = sl::ld_stream_v4(base + i);
+        }
+        if (tid == NT - 32 && a.idx) {   // pages the later passes store to / load from
+            touch(a.idx + ((long long)b * KH) * a.cap);
+            touch(a.cnt + b * KH);
+            if (a.seg) touch(a.seg + (long long)b * a.ctas_per_b * KH);
+        }
         for (int i = tid; i < KH * G; i += NT) {
             const int h = i / G, g = i % G;
             const int qh = a.layout == SL_GQA_INTERLEAVED ? g * KH + h : h * G + g;
@@ -133,101 +231,160 @@ __global__ void __launch_bounds__(NT, 1) scan_topk_kernel(const ScanArgs a) {
         }
         for (int i = tid; i < KH * nbins; i += NT) shist[i] = 0;
         __syncthreads();
-
-        const bool headfixed = (32 % KH) == 0;
-        uint4 qreg[GT > 0 ? GT : 1];
-        if (GT > 0 && headfixed) {
+        constexpr int PP = PT > 0 ? PT : 1;
+        uint32_t M[PP][4], Mp[PP][4];
+        if (PT > 0) {
+            // bit planes of cq and G - cq, built by ballot: lane = bit position, one warp per (head, word)
+            for (int hw = warp; hw < KH * 4; hw += NW) {
+                const int h = hw >> 2, w = hw & 3;
+                int cq = 0;
+                for (int g = 0; g < G; ++g) cq += (reinterpret_cast<const uint32_t*>(sq + h * G + g)[w] >> lane) & 1u;
+                const int cn = G - cq;
 #pragma unroll
-            for (int g = 0; g < GT; ++g) qreg[g] = sq[(lane % KH) * GT + g];
+                for (int j = 0; j < PT; ++j) {
+                    const unsigned m = __ballot_sync(0xffffffffu, (cq >> j) & 1);
+                    const unsigned mp = __ballot_sync(0xffffffffu, (cn >> j) & 1);
+                    if (lane == 0) {
+                        s_planes[((h * 2 + 0) * PT + j) * 4 + w] = m;
+                        s_planes[((h * 2 + 1) * PT + j) * 4 + w] = mp;
+                    }
+                }
+            }
+            __syncthreads();
+            const int h = lane % KH;
+#pragma unroll
+            for (int j = 0; j < PT; ++j)
+#pragma unroll
+                for (int w = 0; w < 4; ++w) {
+                    M[j][w] = s_planes[((h * 2 + 0) * PT + j) * 4 + w];
+                    Mp[j][w] = s_planes[((h * 2 + 1) * PT + j) * 4 + w];
+                }
         }
-        const uint4* base = a.k + (long long)b * a.k_bstride + (long long)t0 * KH;
         short* so = a.scores_out ? a.scores_out + ((long long)b * N + t0) * KH : nullptr;
         const int full = 128 * G;
-        for (int tile = warp; tile * (32 * U) < ncodes; tile += NW) {
+        const int khs = 31 - __clz(KH);             // log2(KH) when KH is a power of two (PT > 0)
+        while (tile * (32 * U) < ncodes) {
             const int i0 = tile * (32 * U) + lane;
-            uint4 cd[U];
+            int sv[U];
 #pragma unroll
             for (int u = 0; u < U; ++u) {
                 const int i = i0 + u * 32;
+                sv[u] = 0;
+                if (i < ncodes) {
+                    if (PT > 0) {
+                        sv[u] = sliced_score<PP>(cd[u], M, Mp);
+                    } else {
+                        const uint4* qh = sq + (i % KH) * G;
+                        int diff = 0;
+                        for (int g = 0; g < G; ++g) diff += sl::popc4(sl::xor4(qh[g], cd[u]));
+                        sv[u] = full - diff;
+                    }
+                }
+            }
+            tile += NW;
+#pragma unroll
+            for (int u = 0; u < U; ++u) {       // next tile's loads before the stores of this one
+                const int i = tile * (32 * U) + u * 32 + lane;
                 if (i < ncodes) cd[u] = sl::ld_stream_v4(base + i);
             }
 #pragma unroll
             for (int u = 0; u < U; ++u) {
                 const int i = i0 + u * 32;
                 if (i < ncodes) {
-                    const int h = headfixed ? (lane % KH) : (i % KH);
-                    int diff = 0;
-                    if (GT > 0 && headfixed) {
-#pragma unroll
-                        for (int g = 0; g < GT; ++g) diff += sl::popc4(sl::xor4(qreg[g], cd[u]));
-                    } else {
-                        const uint4* qh = sq + h * G;
-                        for (int g = 0; g < G; ++g) diff += sl::popc4(sl::xor4(qh[g], cd[u]));
-                    }
-                    const int s = full - diff;
-                    sc[i] = (unsigned short)s;
-                    atomicAdd(&shist[h * nbins + s], 1u);
-                    if (so) so[i] = (short)s;
+                    const int h = PT > 0 ? (lane % KH) : (i % KH);
+                    const int tl = PT > 0 ? (i >> khs) : (i / KH);
+                    if (fast) sscores[h * rowh + tl] = (unsigned short)sv[u];
+                    else sc[i] = (unsigned short)sv[u];
+                    atomicAdd(&shist[h * nbins + sv[u]], 1u);
+                    if (so) so[i] = (short)sv[u];
                 }
             }
         }
         __syncthreads();
-        if (multi || a.mode == MODE_HIST_ONLY) {
-            for (int i = tid; i < KH * nbins; i += NT) {
-                const unsigned v = shist[i];
-                if (v) atomicAdd(&ghist[i], v);
-            }
-        }
-        if (a.mode == MODE_HIST_ONLY) return;
-        if (multi) sl::grid_barrier(&sync[0], ++barriers * (unsigned)a.ctas_per_b, a.status);
     }
+    SL_STAMP(7)
+    if (a.mode != MODE_EMIT_ONLY && (multi || a.mode == MODE_HIST_ONLY)) {
+        // one global add per non-empty bin; CTAs spread over the histogram copies and start at
+        // different bins so that simultaneous adds rarely meet on one address
+        unsigned* dst = hist_b + (long long)(c % a.ncopy) * hslice;
+        const int total = KH * nbins;
+        const int start = (int)(((long long)c * 977) % total);
+        for (int j = tid; j < total; j += NT) {
+            int i = j + start;
+            if (i >= total) i -= total;
+            const unsigned v = shist[i];
+            if (v) atomicAdd(&dst[i], v);
+        }
+    }
+    SL_STAMP(1)
+    if (a.mode == MODE_HIST_ONLY) return;
+    if (multi && a.mode != MODE_EMIT_ONLY) sl::grid_barrier(&sync[0], ++barriers * (unsigned)a.ctas_per_b, a.status);
+    SL_STAMP(2)
 
     // ---------------------------------------------------------------- pass B1: threshold per head
-    // s_base[h][3] temporarily holds E_lower: threshold ties owned by lower ranks.
+    // The global histogram (sum of its copies, or of all ranks' histograms) is staged into
+    // shared memory by all threads with every load in flight at once. Then one warp per head:
+    // each lane sums a block of bins, a suffix scan over the lanes finds the block holding the
+    // threshold, and that lane walks its block from the top.
+    const int nslices = a.mode == MODE_EMIT_ONLY ? a.R : a.ncopy;
+    if (multi || a.mode == MODE_EMIT_ONLY) {
+        const int total = KH * nbins;
+        for (int i0 = tid; i0 < total; i0 += NT * 4) {
+            unsigned v[4] = {0u, 0u, 0u, 0u};
+            for (int sl_ = 0; sl_ < nslices; ++sl_) {
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const int i = i0 + j * NT;
+                    if (i < total) v[j] += __ldcg(hist_b + sl_ * hslice + i);
+                }
+            }
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const int i = i0 + j * NT;
+                if (i < total) shist[i] = v[j];
+            }
+        }
+        __syncthreads();
+    }
+    SL_STAMP(8)
     {
         const int kk = min(a.k_budget, a.mode == MODE_EMIT_ONLY ? 0x7fffffff : N);
-        const bool from_global = multi || a.mode == MODE_EMIT_ONLY;
-        const long long rstride = (long long)a.B * KH * nbins;
+        const int BW = (nbins + 31) >> 5;
         for (int h = warp; h < KH; h += NW) {
             int tau = nbins, r = 0, e_lower = 0;
             if (kk > 0) {
-                const unsigned* H0 = a.hist + ((long long)b * KH + h) * nbins;   // rank 0 slice
-                unsigned cum = 0;
-                bool found = false;
-                for (int top = nbins - 1; top >= 0 && !found; top -= 32) {
-                    const int bin = top - lane;
-                    unsigned v = 0;
-                    if (bin >= 0) {
-                        if (from_global) {
-                            for (int rr = 0; rr < a.R; ++rr) v += __ldcg(H0 + rr * rstride + bin);
-                        } else {
-                            v = shist[h * nbins + bin];
-                        }
-                    }
-                    unsigned inc = v;
+                const unsigned* H = shist + h * nbins;
+                const int blo = lane * BW, bhi = min(nbins, blo + BW);
+                unsigned bs = 0;
+                for (int bin = blo; bin < bhi; ++bin) bs += H[bin];
+                unsigned suf = bs;                                   // bins of this lane's block and above
 #pragma unroll
-                    for (int d = 1; d < 32; d <<= 1) {
-                        const unsigned t = __shfl_up_sync(0xffffffffu, inc, d);
-                        if (lane >= d) inc += t;
-                    }
-                    const unsigned ball = __ballot_sync(0xffffffffu, cum + inc >= (unsigned)kk);
-                    if (ball) {
-                        const int l = __ffs(ball) - 1;
-                        const unsigned incl = __shfl_sync(0xffffffffu, inc, l);
-                        const unsigned vl = __shfl_sync(0xffffffffu, v, l);
-                        tau = top - l;
-                        r = kk - (int)(cum + incl - vl);
-                        found = true;
-                    } else {
-                        cum += __shfl_sync(0xffffffffu, inc, 31);
-                    }
+                for (int d = 1; d < 32; d <<= 1) {
+                    const unsigned t = __shfl_down_sync(0xffffffffu, suf, d);
+                    if (lane + d < 32) suf += t;
                 }
-                if (!found) {  // fewer than kk keys in total: everything is selected
+                const unsigned ball = __ballot_sync(0xffffffffu, suf >= (unsigned)kk);
+                if (ball == 0) {        // fewer than kk keys in total: everything is selected
                     tau = -1;
                     r = 0;
-                } else if (a.mode == MODE_EMIT_ONLY) {
-                    for (int rr = lane; rr < a.rank; rr += 32) e_lower += (int)__ldcg(H0 + rr * rstride + tau);
-                    e_lower = warp_sum(e_lower);
+                } else {
+                    const int L = 31 - __clz(ball);                  // highest block whose suffix reaches kk
+                    int tau_l = 0, gt_l = 0;
+                    if (lane == L) {
+                        unsigned cum = suf - bs;
+                        for (int bin = bhi - 1; bin >= blo; --bin) {
+                            const unsigned v = H[bin];
+                            if (cum + v >= (unsigned)kk) { tau_l = bin; gt_l = (int)cum; break; }
+                            cum += v;
+                        }
+                    }
+                    tau = __shfl_sync(0xffffffffu, tau_l, L);
+                    r = kk - __shfl_sync(0xffffffffu, gt_l, L);
+                    if (a.mode == MODE_EMIT_ONLY) {                  // threshold ties owned by lower ranks
+                        for (int rr = lane; rr < a.rank; rr += 32)
+                            e_lower += (int)__ldcg(hist_b + rr * hslice + h * nbins + tau);
+                        e_lower = warp_sum(e_lower);
+                    }
                 }
             }
             if (lane == 0) {
@@ -238,24 +395,57 @@ __global__ void __launch_bounds__(NT, 1) scan_topk_kernel(const ScanArgs a) {
         }
     }
     __syncthreads();
+    SL_STAMP(3)
 
     // ---------------------------------------------------------------- pass B2: own counts per task
+    // A task is (head, sub-range of the chunk). In the shared-memory layout a lane tests four
+    // consecutive keys of one head per 8-byte load: adding (0x7fff - tau) to a 16-bit score sets
+    // bit 15 iff score > tau, adding (0x8000 - tau) iff score >= tau, two scores per 32-bit add.
     const int len = t1 - t0;
-    const int sub = ((len + S - 1) / S + 31) / 32 * 32;
+    const int sub = ((len + S - 1) / S + 127) / 128 * 128;
     const int ntasks = KH * S;
     for (int task = warp; task < ntasks; task += NW) {
         const int h = task % KH, s = task / KH;
         const int lo = t0 + min(len, s * sub), hi = t0 + min(len, (s + 1) * sub);
         const int tau = s_tau[h];
         int gtM = 0, eqM = 0, eqS = 0;
-        for (int tb = lo; tb < hi; tb += 32) {
-            const int t = tb + lane;
-            const bool valid = t < hi;
-            const int v = valid ? (int)sc[(t - t0) * KH + h] : -2;
-            const bool mid = valid && t >= a.s_end && t < a.r_start;
-            gtM += __popc(__ballot_sync(0xffffffffu, mid && v > tau));
-            eqM += __popc(__ballot_sync(0xffffffffu, mid && v == tau));
-            eqS += __popc(__ballot_sync(0xffffffffu, valid && t < a.s_end && v == tau));
+        if (fast) {
+            const unsigned short* row = sscores + h * rowh;
+            const int elo = max(lo, a.s_end) - t0, ehi = min(hi, a.r_start) - t0;
+            const unsigned cgt = (unsigned)(0x7fff - tau) * 0x10001u, cge = (unsigned)(0x8000 - tau) * 0x10001u;
+            for (int g0 = elo & ~3; g0 < ehi; g0 += 128) {
+                const int tl = g0 + 4 * lane;
+                uint2 x = make_uint2(0u, 0u);
+                if (tl < ehi) x = *reinterpret_cast<const uint2*>(row + tl);
+                unsigned vlo = 0x80008000u, vhi = 0x80008000u;
+                if (tl < elo || tl + 3 >= ehi) {
+                    vlo = ((tl >= elo && tl < ehi) ? 0x8000u : 0u) | ((tl + 1 >= elo && tl + 1 < ehi) ? 0x80000000u : 0u);
+                    vhi = ((tl + 2 >= elo && tl + 2 < ehi) ? 0x8000u : 0u) | ((tl + 3 >= elo && tl + 3 < ehi) ? 0x80000000u : 0u);
+                }
+                const unsigned glo = (x.x + cgt) & vlo, ghi = (x.y + cgt) & vhi;
+                const unsigned elo_ = (x.x + cge) & vlo & ~glo, ehi_ = (x.y + cge) & vhi & ~ghi;
+                gtM += __popc(glo | (ghi >> 1));
+                eqM += __popc(elo_ | (ehi_ >> 1));
+            }
+            gtM = __reduce_add_sync(0xffffffffu, gtM);
+            eqM = __reduce_add_sync(0xffffffffu, eqM);
+            if (s == 0) {       // threshold ties inside the sink part of this chunk
+                for (int tb = t0; tb < min(t1, a.s_end); tb += 32) {
+                    const int t = tb + lane;
+                    const bool tie = t < min(t1, a.s_end) && (int)row[t - t0] == tau;
+                    eqS += __popc(__ballot_sync(0xffffffffu, tie));
+                }
+            }
+        } else {
+            for (int tb = lo; tb < hi; tb += 32) {
+                const int t = tb + lane;
+                const bool valid = t < hi;
+                const int v = valid ? (int)sc[(t - t0) * KH + h] : -2;
+                const bool mid = valid && t >= a.s_end && t < a.r_start;
+                gtM += __popc(__ballot_sync(0xffffffffu, mid && v > tau));
+                eqM += __popc(__ballot_sync(0xffffffffu, mid && v == tau));
+                eqS += __popc(__ballot_sync(0xffffffffu, valid && t < a.s_end && v == tau));
+            }
         }
         if (lane == 0) {
             s_task[(h * S + s) * 3 + 0] = gtM;
@@ -264,25 +454,39 @@ __global__ void __launch_bounds__(NT, 1) scan_topk_kernel(const ScanArgs a) {
         }
     }
     __syncthreads();
+    SL_STAMP(10)
     if (multi) {
-        for (int i = tid; i < KH * 3; i += NT) {
-            const int h = i / 3, j = i % 3;
-            unsigned v = 0;
-            for (int s = 0; s < S; ++s) v += s_task[(h * S + s) * 3 + j];
-            a.seg[(((long long)b * a.ctas_per_b + c) * KH + h) * 3 + j] = v;
+        for (int h = tid; h < KH; h += NT) {
+            uint4 v = make_uint4(0, 0, 0, 0);
+            for (int s = 0; s < S; ++s) {
+                v.x += s_task[(h * S + s) * 3 + 0];
+                v.y += s_task[(h * S + s) * 3 + 1];
+                v.z += s_task[(h * S + s) * 3 + 2];
+            }
+            a.seg[((long long)b * KH + h) * a.ctas_per_b + c] = v;
         }
         sl::grid_barrier(&sync[0], ++barriers * (unsigned)a.ctas_per_b, a.status);
     }
+    SL_STAMP(4)
 
     // ---------------------------------------------------------------- pass B3: prefix over chunks
     for (int h = warp; h < KH; h += NW) {
         int pre_gt = 0, pre_eq = 0, tot_gt = 0, tot_eq = 0, tot_eqS = 0;
         if (multi) {
-            for (int cc = lane; cc < a.ctas_per_b; cc += 32) {
-                const unsigned* p = a.seg + (((long long)b * a.ctas_per_b + cc) * KH + h) * 3;
-                const int g = (int)__ldcg(p), e = (int)__ldcg(p + 1), es = (int)__ldcg(p + 2);
-                tot_gt += g; tot_eq += e; tot_eqS += es;
-                if (cc < c) { pre_gt += g; pre_eq += e; }
+            const uint4* segb = a.seg + ((long long)b * KH + h) * a.ctas_per_b;
+            for (int cc0 = 0; cc0 < a.ctas_per_b; cc0 += 32 * 5) {
+                uint4 v[5];
+#pragma unroll
+                for (int j = 0; j < 5; ++j) {            // all loads first: one round trip
+                    const int cc = cc0 + j * 32 + lane;
+                    v[j] = cc < a.ctas_per_b ? __ldcg(segb + cc) : make_uint4(0, 0, 0, 0);
+                }
+#pragma unroll
+                for (int j = 0; j < 5; ++j) {
+                    const int cc = cc0 + j * 32 + lane;
+                    tot_gt += v[j].x; tot_eq += v[j].y; tot_eqS += v[j].z;
+                    if (cc < c) { pre_gt += v[j].x; pre_eq += v[j].y; }
+                }
             }
             pre_gt = warp_sum(pre_gt); pre_eq = warp_sum(pre_eq);
             tot_gt = warp_sum(tot_gt); tot_eq = warp_sum(tot_eq); tot_eqS = warp_sum(tot_eqS);
@@ -305,6 +509,7 @@ __global__ void __launch_bounds__(NT, 1) scan_topk_kernel(const ScanArgs a) {
         }
     }
     __syncthreads();
+    SL_STAMP(5)
 
     // ---------------------------------------------------------------- pass C: ordered emission
     for (int task = warp; task < ntasks; task += NW) {
@@ -318,28 +523,98 @@ __global__ void __launch_bounds__(NT, 1) scan_topk_kernel(const ScanArgs a) {
         }
         int* oi = a.idx + ((long long)b * KH + h) * a.cap;
         const unsigned lt = (1u << lane) - 1u;
-        for (int tb = lo; tb < hi; tb += 32) {
-            const int t = tb + lane;
-            const bool valid = t < hi;
-            const int v = valid ? (int)sc[(t - t0) * KH + h] : -2;
-            const bool mid = valid && t >= a.s_end && t < a.r_start;
-            const bool isgt = mid && v > tau, iseq = mid && v == tau;
-            const unsigned bgt = __ballot_sync(0xffffffffu, isgt);
-            const unsigned beq = __ballot_sync(0xffffffffu, iseq);
-            const bool taken = iseq && (eq_before + __popc(beq & lt)) < rM;
-            const unsigned btk = __ballot_sync(0xffffffffu, taken);
-            int pos = -1;
-            if (isgt || taken) pos = a.s_end + gt_before + min(eq_before, rM) + __popc((bgt | btk) & lt);
-            else if (valid && t < a.s_end) pos = t;
-            else if (valid && t >= a.r_start) pos = a.s_end + selM + (t - a.r_start);
-            if (pos >= 0) {
-                if (pos < a.cap) oi[pos] = t;
-                else if (a.status) atomicExch(a.status, 2);
+        if (fast) {
+            const unsigned short* row = sscores + h * rowh;
+            const int elo = max(lo, a.s_end) - t0, ehi = min(hi, a.r_start) - t0;
+            const unsigned cgt = (unsigned)(0x7fff - tau) * 0x10001u, cge = (unsigned)(0x8000 - tau) * 0x10001u;
+            int out_base = a.s_end + gt_before + min(eq_before, rM);
+            for (int g0 = elo & ~3; g0 < ehi; g0 += 128) {
+                const int tl = g0 + 4 * lane;
+                uint2 x = make_uint2(0u, 0u);
+                if (tl < ehi) x = *reinterpret_cast<const uint2*>(row + tl);
+                unsigned vlo = 0x80008000u, vhi = 0x80008000u;
+                if (tl < elo || tl + 3 >= ehi) {
+                    vlo = ((tl >= elo && tl < ehi) ? 0x8000u : 0u) | ((tl + 1 >= elo && tl + 1 < ehi) ? 0x80000000u : 0u);
+                    vhi = ((tl + 2 >= elo && tl + 2 < ehi) ? 0x8000u : 0u) | ((tl + 3 >= elo && tl + 3 < ehi) ? 0x80000000u : 0u);
+                }
+                const unsigned glo = (x.x + cgt) & vlo, ghi = (x.y + cgt) & vhi;
+                const unsigned elo_ = (x.x + cge) & vlo & ~glo, ehi_ = (x.y + cge) & vhi & ~ghi;
+                // four flag bits per lane, bit i = key tl + i
+                const unsigned gb = ((glo >> 15) & 1u) | ((glo >> 30) & 2u) | ((ghi >> 13) & 4u) | ((ghi >> 28) & 8u);
+                const unsigned eb = ((elo_ >> 15) & 1u) | ((elo_ >> 30) & 2u) | ((ehi_ >> 13) & 4u) | ((ehi_ >> 28) & 8u);
+                const int ne = __popc(eb);
+                const int tot_e = __reduce_add_sync(0xffffffffu, ne);
+                unsigned tb = 0;
+                if (eq_before + tot_e <= rM) {
+                    tb = eb;                                    // every tie of this group is inside the quota
+                } else if (eq_before < rM) {                    // the quota runs out inside this group
+                    int inc = ne;
+#pragma unroll
+                    for (int d = 1; d < 32; d <<= 1) {
+                        const int t = __shfl_up_sync(0xffffffffu, inc, d);
+                        if (lane >= d) inc += t;
+                    }
+                    const int ex = eq_before + inc - ne;
+#pragma unroll
+                    for (int i = 0; i < 4; ++i)
+                        if (((eb >> i) & 1u) && ex + __popc(eb & ((1u << i) - 1u)) < rM) tb |= 1u << i;
+                }
+                const unsigned sb = gb | tb;
+                const int ns = __popc(sb);
+                int inc = ns;
+#pragma unroll
+                for (int d = 1; d < 32; d <<= 1) {
+                    const int t = __shfl_up_sync(0xffffffffu, inc, d);
+                    if (lane >= d) inc += t;
+                }
+                const int ex = out_base + inc - ns;
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    if ((sb >> i) & 1u) {
+                        const int pos = ex + __popc(sb & ((1u << i) - 1u));
+                        if (pos < a.cap) oi[pos] = t0 + tl + i;
+                        else if (a.status) atomicExch(a.status, 2);
+                    }
+                }
+                out_base += __shfl_sync(0xffffffffu, inc, 31);
+                eq_before += tot_e;
             }
-            gt_before += __popc(bgt);
-            eq_before += __popc(beq);
+            if (task == 0) { SL_STAMP(9) }
+            // always-kept keys of this sub-range: the sink at its own index, the recent window at the end
+            for (int tb2 = lo; tb2 < min(hi, a.s_end); tb2 += 32)
+                if (tb2 + lane < min(hi, a.s_end) && tb2 + lane < a.cap) oi[tb2 + lane] = tb2 + lane;
+            for (int tb2 = max(lo, a.r_start); tb2 < hi; tb2 += 32) {
+                const int t = tb2 + lane, pos = a.s_end + selM + (t - a.r_start);
+                if (t < hi) {
+                    if (pos < a.cap) oi[pos] = t;
+                    else if (a.status) atomicExch(a.status, 2);
+                }
+            }
+        } else {
+            for (int tb = lo; tb < hi; tb += 32) {
+                const int t = tb + lane;
+                const bool valid = t < hi;
+                const int v = valid ? (int)sc[(t - t0) * KH + h] : -2;
+                const bool mid = valid && t >= a.s_end && t < a.r_start;
+                const bool isgt = mid && v > tau, iseq = mid && v == tau;
+                const unsigned bgt = __ballot_sync(0xffffffffu, isgt);
+                const unsigned beq = __ballot_sync(0xffffffffu, iseq);
+                const bool taken = iseq && (eq_before + __popc(beq & lt)) < rM;
+                const unsigned btk = __ballot_sync(0xffffffffu, taken);
+                int pos = -1;
+                if (isgt || taken) pos = a.s_end + gt_before + min(eq_before, rM) + __popc((bgt | btk) & lt);
+                else if (valid && t < a.s_end) pos = t;
+                else if (valid && t >= a.r_start) pos = a.s_end + selM + (t - a.r_start);
+                if (pos >= 0) {
+                    if (pos < a.cap) oi[pos] = t;
+                    else if (a.status) atomicExch(a.status, 2);
+                }
+                gt_before += __popc(bgt);
+                eq_before += __popc(beq);
+            }
         }
     }
+    SL_STAMP(6)
 
     // ---------------------------------------------------------------- leave the workspace zeroed
     if (multi) {
@@ -347,7 +622,8 @@ __global__ void __launch_bounds__(NT, 1) scan_topk_kernel(const ScanArgs a) {
             const int total = KH * nbins;
             const int slice = (total + a.ctas_per_b - 1) / a.ctas_per_b;
             const int z0 = c * slice, z1 = min(total, z0 + slice);
-            for (int i = z0 + tid; i < z1; i += NT) ghist[i] = 0;
+            for (int cp = 0; cp < a.ncopy; ++cp)
+                for (int i = z0 + tid; i < z1; i += NT) hist_b[cp * hslice + i] = 0;
         }
         __syncthreads();
         if (tid == 0) {
@@ -364,18 +640,12 @@ __global__ void __launch_bounds__(NT, 1) scan_topk_kernel(const ScanArgs a) {
 
 typedef void (*kernel_t)(const ScanArgs);
 
-kernel_t pick_kernel(int G) {
-    switch (G) {
-        case 1: return scan_topk_kernel<1>;
-        case 2: return scan_topk_kernel<2>;
-        case 3: return scan_topk_kernel<3>;
-        case 4: return scan_topk_kernel<4>;
-        case 5: return scan_topk_kernel<5>;
-        case 6: return scan_topk_kernel<6>;
-        case 7: return scan_topk_kernel<7>;
-        case 8: return scan_topk_kernel<8>;
-        default: return scan_topk_kernel<0>;
-    }
+kernel_t pick_kernel(int G, int KH) {
+    if (32 % KH != 0 || G > 15) return scan_topk_kernel<0>;      // lanes do not keep one head: direct popcounts
+    if (G == 1) return scan_topk_kernel<1>;
+    if (G <= 3) return scan_topk_kernel<2>;
+    if (G <= 7) return scan_topk_kernel<3>;
+    return scan_topk_kernel<4>;
 }
 
 struct WsLayout {
@@ -387,8 +657,8 @@ WsLayout ws_layout(int B, long long N, int KH, int G, bool with_hist, bool spill
     const int max_cpb = std::max(1, sl::sm_count() * 2);
     size_t off = 0;
     w.sync_off = off; off = align_up(off + (size_t)B * 2 * 4, 256);
-    w.hist_off = off; if (with_hist) off = align_up(off + (size_t)B * KH * (nbins > 0 ? nbins : 128 * G + 1) * 4, 256);
-    w.seg_off = off; off = align_up(off + (size_t)B * max_cpb * KH * 3 * 4, 256);
+    w.hist_off = off; if (with_hist) off = align_up(off + (size_t)NCOPY * B * KH * (nbins > 0 ? nbins : 128 * G + 1) * 4, 256);
+    w.seg_off = off; off = align_up(off + (size_t)B * max_cpb * KH * 16, 256);
     w.score_off = off; if (spill) off = align_up(off + (size_t)B * N * KH * 2, 256);
     w.total = off;
     return w;
@@ -405,8 +675,10 @@ int check_common(const char* fn, int B, long long N, int KH, int QH) {
     return SL_OK;
 }
 
-int launch(const ScanArgs& a, const Plan& p, cudaStream_t s) {
-    kernel_t kern = pick_kernel(a.G);
+int launch(const ScanArgs& a_in, const Plan& p, cudaStream_t s) {
+    ScanArgs a = a_in;
+    a.dbg = g_dbg_timing;
+    kernel_t kern = pick_kernel(a.G, a.KH);
     SL_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)p.smem));
     const unsigned grid = (unsigned)(a.B * p.ctas_per_b);
     if (p.cooperative) {
@@ -455,7 +727,7 @@ extern "C" int sl_scan_topk(const uint32_t* d_q_codes, const uint32_t* d_k_codes
                w.total);
     SL_REQUIRE(sl::aligned16(d_workspace), SL_EALIGN, "sl_scan_topk: workspace not 16-byte aligned");
     unsigned char* ws = static_cast<unsigned char*>(d_workspace);
-    ScanArgs a;
+    ScanArgs a = {};
     a.q = reinterpret_cast<const uint4*>(d_q_codes);
     a.k = reinterpret_cast<const uint4*>(d_k_codes);
     a.k_bstride = k_batch_stride / 4;
@@ -467,11 +739,11 @@ extern "C" int sl_scan_topk(const uint32_t* d_q_codes, const uint32_t* d_k_codes
     a.scores_out = d_scores_out;
     a.gscores = p.spill ? reinterpret_cast<unsigned short*>(ws + w.score_off) : nullptr;
     a.hist = reinterpret_cast<unsigned*>(ws + w.hist_off);
-    a.seg = reinterpret_cast<unsigned*>(ws + w.seg_off);
+    a.seg = reinterpret_cast<uint4*>(ws + w.seg_off);
     a.sync = reinterpret_cast<unsigned*>(ws + w.sync_off);
     a.status = d_status;
     a.ctas_per_b = p.ctas_per_b; a.chunk = p.chunk; a.nbins = p.nbins; a.S = p.S;
-    a.mode = MODE_FUSED; a.R = 1; a.rank = 0;
+    a.mode = MODE_FUSED; a.R = 1; a.rank = 0; a.ncopy = NCOPY;
     return launch(a, p, s);
 }
 
@@ -497,7 +769,7 @@ extern "C" int sl_scan_hist(const uint32_t* d_q_codes, const uint32_t* d_k_codes
     a.gscores = reinterpret_cast<unsigned short*>(d_scores);
     a.hist = d_hist;
     a.ctas_per_b = p.ctas_per_b; a.chunk = p.chunk; a.nbins = p.nbins; a.S = p.S;
-    a.mode = MODE_HIST_ONLY; a.R = 1; a.rank = 0;
+    a.mode = MODE_HIST_ONLY; a.R = 1; a.rank = 0; a.ncopy = 1;
     return launch(a, p, static_cast<cudaStream_t>(stream));
 }
 
@@ -540,11 +812,11 @@ extern "C" int sl_select_emit(const int16_t* d_scores, const uint32_t* d_hist_al
     a.idx = d_idx; a.cap = idx_capacity; a.cnt = d_cnt;
     a.gscores = reinterpret_cast<unsigned short*>(const_cast<int16_t*>(d_scores));
     a.hist = const_cast<unsigned*>(d_hist_all);
-    a.seg = reinterpret_cast<unsigned*>(ws + w.seg_off);
+    a.seg = reinterpret_cast<uint4*>(ws + w.seg_off);
     a.sync = reinterpret_cast<unsigned*>(ws + w.sync_off);
     a.status = d_status;
     a.ctas_per_b = p.ctas_per_b; a.chunk = p.chunk; a.nbins = p.nbins; a.S = p.S;
-    a.mode = MODE_EMIT_ONLY; a.R = R; a.rank = rank;
+    a.mode = MODE_EMIT_ONLY; a.R = R; a.rank = rank; a.ncopy = 1;
     return launch(a, p, s);
 }
 
@@ -582,10 +854,14 @@ extern "C" int sl_topk_from_scores(const int16_t* d_scores, int B, int64_t N, in
     a.idx = d_idx; a.cap = idx_capacity; a.cnt = d_cnt;
     a.gscores = reinterpret_cast<unsigned short*>(const_cast<int16_t*>(d_scores));
     a.hist = reinterpret_cast<unsigned*>(ws + w.hist_off);
-    a.seg = reinterpret_cast<unsigned*>(ws + w.seg_off);
+    a.seg = reinterpret_cast<uint4*>(ws + w.seg_off);
     a.sync = reinterpret_cast<unsigned*>(ws + w.sync_off);
     a.status = d_status;
     a.ctas_per_b = p.ctas_per_b; a.chunk = p.chunk; a.nbins = p.nbins; a.S = p.S;
-    a.mode = MODE_FROM_SCORES; a.R = 1; a.rank = 0;
+    a.mode = MODE_FROM_SCORES; a.R = 1; a.rank = 0; a.ncopy = NCOPY;
     return launch(a, p, s);
 }
+
+// Development aid, not part of the public header: when set to a device buffer of grid*16 uint64,
+// thread 0 of every CTA of the scan kernels stores %globaltimer at its phase boundaries.
+extern "C" void sl_debug_scan_timing(void* d_buf) { g_dbg_timing = static_cast<unsigned long long*>(d_buf); }
