@@ -1,27 +1,21 @@
 // Sparse GQA decode attention over an index list: rows are gathered straight from the K/V
 // caches (16-byte loads, one 256-byte row = half a warp for 2-byte types), online softmax in
-// fp32, split over the list (flash-decoding style) with the last CTA of a (b, kv head)
-// merging the partials. Also the LSE merge across sequence shards and the row-gather shim.
-#include "sl_common.cuh"
+// fp32, split over the list (flash-decoding style) with a small merge kernel combining the
+// per-split partials. Also the LSE merge across sequence shards and the row-gather shim.
+#include <type_traits>
+
+#include "sl_attn.cuh"
 
 namespace {
 
 constexpr int AT = 256;            // threads per CTA
 constexpr int AW = AT / 32;        // warps
 constexpr int PF = 4;              // row groups in flight per warp
-constexpr int MAX_SPLITS = 64;
+constexpr int MAX_SPLITS = sl::ATTN_MAX_SPLITS;
 constexpr float LOG2E = 1.4426950408889634f;
 constexpr float LN2 = 0.6931471805599453f;
 
-struct AttnArgs {
-    const void* q; const void* k; const void* v;
-    long long kv_b;                // batch stride in elements
-    const int* idx; int cap; const int* cnt;
-    int B, KH, layout, splits;
-    void* out; float* lse;
-    unsigned* counters;            // [B*KH], zero between launches
-    float* part;                   // [B*KH][splits][G][130]: o[128], m, l
-};
+using sl::AttnArgs;
 
 __device__ __forceinline__ float ex2(float x) { return exp2f(x); }
 
@@ -32,7 +26,6 @@ __global__ void __launch_bounds__(AT, (G * (16 / sizeof(T)) > 32) ? 1 : 2) spars
     constexpr int RPW = 32 / LPR;             // rows per warp step
     __shared__ float sm_acc[AW][G][128];
     __shared__ float sm_m[AW][G], sm_l[AW][G];
-    __shared__ int s_last;
 
     const int sp = blockIdx.x, h = blockIdx.y, b = blockIdx.z, KH = a.KH;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -170,38 +163,54 @@ __global__ void __launch_bounds__(AT, (G * (16 / sizeof(T)) > 32) ? 1 : 2) spars
             if (col == 0) { part[g * 130 + 128] = M; part[g * 130 + 129] = L; }
         }
     }
-    if (a.splits == 1) return;
+}
 
-    // ---- the last CTA of this (b, kv head) merges the splits
-    __threadfence();
-    __syncthreads();
-    if (tid == 0) {
-        const unsigned old = atomicAdd(&a.counters[bh], 1u);
-        s_last = old == (unsigned)a.splits - 1u;
+// One CTA per query head merges the partials of its splits: thread (grp, col) accumulates the
+// splits s = grp (mod 4) of output column col with every load in flight at once.
+template <typename T>
+__global__ void __launch_bounds__(512) attn_merge_kernel(const float* __restrict__ part, int splits, int G, int KH,
+                                                         int layout, T* __restrict__ out, float* __restrict__ lse) {
+    __shared__ float s_m[sl::ATTN_MAX_SPLITS], s_l[sl::ATTN_MAX_SPLITS], s_w[sl::ATTN_MAX_SPLITS];
+    __shared__ float red[4][128];
+    const int g = blockIdx.x % G;
+    const long long bh = blockIdx.x / G;
+    const int h = (int)(bh % KH);
+    const long long b = bh / KH;
+    const int tid = threadIdx.x, col = tid & 127, grp = tid >> 7;
+    const float* pb = part + (bh * splits * G + g) * 130;             // split s at pb + s*G*130
+    const long long sstride = (long long)G * 130;
+    float v[sl::ATTN_MAX_SPLITS / 4];
+#pragma unroll
+    for (int j = 0; j < sl::ATTN_MAX_SPLITS / 4; ++j) {
+        const int s = grp + 4 * j;
+        v[j] = s < splits ? __ldcg(pb + s * sstride + col) : 0.0f;
+    }
+    if (tid < splits) {
+        s_m[tid] = __ldcg(pb + tid * sstride + 128);
+        s_l[tid] = __ldcg(pb + tid * sstride + 129);
     }
     __syncthreads();
-    if (!s_last) return;
-    __threadfence();
-    const float* pb = a.part + bh * a.splits * G * 130;
-    for (int e = tid; e < G * 128; e += AT) {
-        const int g = e >> 7, col = e & 127;
-        float M = -INFINITY;
-        for (int s = 0; s < a.splits; ++s) M = fmaxf(M, __ldcg(pb + (s * G + g) * 130 + 128));
-        float L = 0.0f, O = 0.0f;
-        if (M != -INFINITY) {
-            for (int s = 0; s < a.splits; ++s) {
-                const float* ps = pb + (s * G + g) * 130;
-                const float c = ex2(__ldcg(ps + 128) - M);
-                L += __ldcg(ps + 129) * c;
-                O += __ldcg(ps + col) * c;
-            }
-        }
-        const int qh = a.layout == SL_GQA_INTERLEAVED ? g * KH + h : h * G + g;
+    float M = -INFINITY;
+    for (int s = 0; s < splits; ++s) M = fmaxf(M, s_m[s]);
+    if (tid < splits) s_w[tid] = M == -INFINITY ? 0.0f : exp2f(s_m[tid] - M);
+    __syncthreads();
+    float acc = 0.0f;
+#pragma unroll
+    for (int j = 0; j < sl::ATTN_MAX_SPLITS / 4; ++j) {
+        const int s = grp + 4 * j;
+        if (s < splits) acc = fmaf(v[j], s_w[s], acc);
+    }
+    red[grp][col] = acc;
+    __syncthreads();
+    if (grp == 0) {
+        float L = 0.0f;
+        for (int s = 0; s < splits; ++s) L = fmaf(s_l[s], s_w[s], L);
+        const float O = (red[0][col] + red[1][col]) + (red[2][col] + red[3][col]);
+        const int qh = layout == SL_GQA_INTERLEAVED ? g * KH + h : h * G + g;
         const long long o = ((long long)b * KH * G + qh) * 128 + col;
-        reinterpret_cast<T*>(a.out)[o] = sl::VT<T>::from_f(L > 0.0f ? O / L : 0.0f);
-        if (a.lse && col == 0) a.lse[(long long)b * KH * G + qh] = L > 0.0f ? (M + log2f(L)) * LN2 : -INFINITY;
+        out[o] = sl::VT<T>::from_f(L > 0.0f ? O / L : 0.0f);
+        if (lse && col == 0) lse[(long long)b * KH * G + qh] = L > 0.0f ? (M + log2f(L)) * LN2 : -INFINITY;
     }
-    if (tid == 0) a.counters[bh] = 0;
 }
 
 template <typename T>
@@ -250,6 +259,7 @@ int launch_attn(const AttnArgs& a, cudaStream_t s) {
     dim3 grid((unsigned)a.splits, (unsigned)a.KH, (unsigned)a.B);
     sparse_attn_kernel<T, G><<<grid, AT, 0, s>>>(a);
     SL_CUDA_OK(cudaGetLastError());
+    if (a.splits > 1) return sl::launch_attn_merge(a, G, sizeof(T) == 4 ? SL_F32 : (std::is_same<T, __half>::value ? SL_F16 : SL_BF16), s);
     return SL_OK;
 }
 
@@ -270,10 +280,23 @@ int dispatch_g(const AttnArgs& a, int G, cudaStream_t s) {
 
 }  // namespace
 
+namespace sl {
+int launch_attn_merge(const AttnArgs& a, int G, int dtype, cudaStream_t s) {
+    const unsigned blocks = (unsigned)(a.B * a.KH * G);
+    switch (dtype) {
+        case SL_BF16: attn_merge_kernel<__nv_bfloat16><<<blocks, 512, 0, s>>>(a.part, a.splits, G, a.KH, a.layout, (__nv_bfloat16*)a.out, a.lse); break;
+        case SL_F16: attn_merge_kernel<__half><<<blocks, 512, 0, s>>>(a.part, a.splits, G, a.KH, a.layout, (__half*)a.out, a.lse); break;
+        default: attn_merge_kernel<float><<<blocks, 512, 0, s>>>(a.part, a.splits, G, a.KH, a.layout, (float*)a.out, a.lse); break;
+    }
+    SL_CUDA_OK(cudaGetLastError());
+    return SL_OK;
+}
+}  // namespace sl
+
 extern "C" size_t sl_sparse_attn_workspace_bytes(int B, int KH, int QH) {
     if (B <= 0 || KH <= 0 || QH <= 0) return 0;
-    const size_t counters = ((size_t)B * KH * 4 + 255) / 256 * 256;
-    return counters + (size_t)B * QH * MAX_SPLITS * 130 * 4;
+    (void)KH;
+    return (size_t)B * QH * MAX_SPLITS * 130 * 4;
 }
 
 extern "C" int sl_sparse_attn_decode(const void* d_q, const void* d_k, const void* d_v, int dtype,
@@ -297,10 +320,13 @@ extern "C" int sl_sparse_attn_decode(const void* d_q, const void* d_k, const voi
     a.B = B; a.KH = KH; a.layout = gqa_layout;
     a.splits = pick_splits(B, KH, idx_capacity);
     a.out = d_out; a.lse = d_lse;
-    a.counters = static_cast<unsigned*>(d_workspace);
-    a.part = reinterpret_cast<float*>(static_cast<unsigned char*>(d_workspace) + ((size_t)B * KH * 4 + 255) / 256 * 256);
+    a.part = static_cast<float*>(d_workspace);
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     const int G = QH / KH;
+    if (dtype == SL_BF16 && G <= 16) {
+        a.splits = sl::attn_mma_splits(B, KH, idx_capacity);
+        return sl::launch_attn_mma(a, G, s);
+    }
     switch (dtype) {
         case SL_BF16: return dispatch_g<__nv_bfloat16>(a, G, s);
         case SL_F16: return dispatch_g<__half>(a, G, s);

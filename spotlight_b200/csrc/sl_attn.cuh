@@ -1,0 +1,26 @@
+// Arguments shared by the sparse decode-attention kernels.
+#pragma once
+#include "sl_common.cuh"
+
+namespace sl {
+
+constexpr int ATTN_MAX_SPLITS = 64;
+
+struct AttnArgs {
+    const void* q; const void* k; const void* v;
+    long long kv_b;                // batch stride in elements
+    const int* idx; int cap; const int* cnt;
+    int B, KH, layout, splits;
+    void* out; float* lse;
+    float* part;                   // [B*KH][splits][G][130]: o[128], m, l
+};
+
+
+// Merge of the per-split partials [B*KH][splits][G][130] into the output (one CTA per query head).
+int launch_attn_merge(const AttnArgs& a, int G, int dtype, cudaStream_t s);
+
+// bf16 tensor-core path (sl_attn_mma.cu); G = QH / KH <= 16.
+int launch_attn_mma(const AttnArgs& a, int G, cudaStream_t s);
+int attn_mma_splits(int B, int KH, int cap);
+
+}  // namespace sl

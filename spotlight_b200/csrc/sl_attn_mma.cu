@@ -1,0 +1,307 @@
+// Sparse GQA decode attention, bf16, on the warp-level tensor-core path (mma.sync m16n8k16).
+//
+// The kernel is bound by the random 256-byte row gathers, so it is organised around keeping many
+// of them in flight: every warp owns 16-row tiles of the index list and runs its own cp.async
+// ring (ST stages of 16 K rows + 16 V rows = 8 KB each) in shared memory -- no block-wide
+// barrier in the main loop, a half-warp copies one whole 256-byte row with 16-byte cp.async.
+// Rows are stored with their 16-byte chunks XOR-swizzled by the row number so that ldmatrix
+// reads 8 rows x 16 bytes without bank conflicts.
+//
+//   S = Q K^T   M = query heads of the group (padded to 16), N = 8 keys, K = head dim;
+//               B fragments by ldmatrix.x4 (two k-steps per instruction).
+//   O += P V    A = P straight from the accumulator layout of S; B fragments by
+//               ldmatrix.x4.trans (two 8-wide column tiles of V per instruction).
+//
+// Online softmax in fp32 (exp2 domain). Warps of a CTA merge through shared memory; the CTAs of
+// a (batch row, kv head) leave partials that a small merge kernel combines (sl_attn.cu).
+#include "sl_attn.cuh"
+
+namespace {
+
+using sl::AttnArgs;
+
+constexpr int MT = 128;            // threads per CTA
+constexpr int MW = MT / 32;        // warps
+constexpr int ST = 3;              // cp.async stages per warp
+constexpr int STAGE_BYTES = 8192;  // 16 K rows + 16 V rows of 256 B
+constexpr int RING_BYTES = MW * ST * STAGE_BYTES;
+constexpr float LOG2E = 1.4426950408889634f;
+constexpr float LN2 = 0.6931471805599453f;
+constexpr float QK_SCALE = 0.08838834764831845f * LOG2E;   // 1/sqrt(128) in the exp2 domain
+
+__device__ __forceinline__ void mma_bf16(float (&c)[4], unsigned a0, unsigned a1, unsigned a2, unsigned a3,
+                                         unsigned b0, unsigned b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void ldsm_x4(unsigned (&r)[4], unsigned addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void ldsm_x4_trans(unsigned (&r)[4], unsigned addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void cp_async16(unsigned smem, const void* gmem) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem), "l"(gmem) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+__device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
+    const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<const unsigned*>(&v);
+}
+// byte offset of 16-byte chunk c (0..15) of row r (0..15) inside a swizzled 16 x 256 B tile
+__device__ __forceinline__ unsigned swz(int r, int c) { return (unsigned)(r * 256 + (((c & 8) | ((c ^ r) & 7)) << 4)); }
+
+template <bool HI>   // HI: the group has more than 8 query heads (rows 8..15 of the tile are used)
+__global__ void __launch_bounds__(MT, 2) sparse_attn_mma_kernel(const AttnArgs a, const int G) {
+    extern __shared__ __align__(128) unsigned char ring[];          // [MW][ST][K 4 KB | V 4 KB]; reused by the epilogue
+    __shared__ float sm_m[MW][16], sm_l[MW][16];
+
+    const int sp = blockIdx.x, h = blockIdx.y, b = blockIdx.z, KH = a.KH;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int grp = lane >> 2, tig = lane & 3;
+    const int n = a.cnt[b * KH + h];
+    const int ntiles = (n + 15) >> 4;
+    const int per = (ntiles + a.splits - 1) / a.splits;
+    const int tile_lo = min(ntiles, sp * per), tile_hi = min(ntiles, tile_lo + per);
+    const int* list = a.idx + ((long long)b * KH + h) * a.cap;
+    const long long row_stride = (long long)KH * 128;
+    const __nv_bfloat16* kb = reinterpret_cast<const __nv_bfloat16*>(a.k) + (long long)b * a.kv_b + h * 128;
+    const __nv_bfloat16* vb = reinterpret_cast<const __nv_bfloat16*>(a.v) + (long long)b * a.kv_b + h * 128;
+    const unsigned wring = (unsigned)__cvta_generic_to_shared(ring) + warp * (ST * STAGE_BYTES);
+
+    // one tile = list entries [16 t, 16 t + 16); lane l < 16 fetches entry l (clamped to the last one)
+    auto entry = [&](int t) -> int { return list[min(t * 16 + (lane & 15), n - 1)]; };
+    // a half-warp copies one 256-byte row per step: 8 steps for K, 8 for V
+    auto issue = [&](int t, int tok, int stage) {
+        const unsigned sbase = wring + stage * STAGE_BYTES;
+        const int c = lane & 15;
+#pragma unroll
+        for (int it = 0; it < 8; ++it) {
+            const int r = 2 * it + (lane >> 4);
+            const long long off = (long long)__shfl_sync(0xffffffffu, tok, r) * row_stride + c * 8;
+            cp_async16(sbase + swz(r, c), kb + off);
+            cp_async16(sbase + 4096 + swz(r, c), vb + off);
+        }
+        (void)t;
+    };
+
+    // ---- prologue: fill ST-1 stages
+    int tile = tile_lo + warp;
+    int tok_next = 0;
+#pragma unroll
+    for (int s = 0; s < ST - 1; ++s) {
+        const int t = tile + s * MW;
+        if (t < tile_hi) issue(t, entry(t), s);
+        cp_async_commit();
+    }
+    if (tile + (ST - 1) * MW < tile_hi) tok_next = entry(tile + (ST - 1) * MW);
+
+    // ---- Q fragments (A operand), natural order
+    unsigned qa[8][HI ? 4 : 2];
+    {
+        const __nv_bfloat16* qbase = reinterpret_cast<const __nv_bfloat16*>(a.q) + (long long)b * KH * G * 128;
+#pragma unroll
+        for (int half = 0; half < (HI ? 2 : 1); ++half) {
+            const int g = grp + 8 * half;
+            const int qh = a.layout == SL_GQA_INTERLEAVED ? g * KH + h : h * G + g;
+            const unsigned* qrow = reinterpret_cast<const unsigned*>(qbase + (long long)qh * 128);
+#pragma unroll
+            for (int s = 0; s < 8; ++s) {
+                const unsigned lo = g < G ? qrow[8 * s + tig] : 0u;          // k = 16 s + 2 tig, +1
+                const unsigned hi = g < G ? qrow[8 * s + 4 + tig] : 0u;      // k = 16 s + 8 + 2 tig, +1
+                if (half == 0) { qa[s][0] = lo; qa[s][HI ? 2 : 1] = hi; }
+                else { qa[s][1] = lo; qa[s][3] = hi; }
+            }
+        }
+    }
+
+    float o[16][4];
+#pragma unroll
+    for (int t = 0; t < 16; ++t) { o[t][0] = o[t][1] = o[t][2] = o[t][3] = 0.0f; }
+    float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.0f, l1 = 0.0f;   // rows grp and grp + 8
+
+    int stage = 0;
+    for (; tile < tile_hi; tile += MW) {
+        // ---- keep the ring full: issue the tile ST-1 ahead, then wait for the current one
+        {
+            const int t = tile + (ST - 1) * MW;
+            int st2 = stage + (ST - 1);
+            if (st2 >= ST) st2 -= ST;
+            if (t < tile_hi) issue(t, tok_next, st2);
+            cp_async_commit();
+            if (t + MW < tile_hi) tok_next = entry(t + MW);
+        }
+        cp_async_wait<ST - 1>();
+        __syncwarp();
+        const unsigned kbase = wring + stage * STAGE_BYTES, vbase = kbase + 4096;
+        const int valid = n - tile * 16;                    // list entries of this tile that exist
+
+        // ---- S = Q K^T for keys 0..7 (s[0]) and 8..15 (s[1])
+        float s[2][4];
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+            s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.0f;
+#pragma unroll
+            for (int p = 0; p < 4; ++p) {                  // k-steps 2p, 2p+1
+                unsigned kf[4];
+                ldsm_x4(kf, kbase + swz(8 * j + (lane & 7), 4 * p + (lane >> 3)));
+                if (HI) {
+                    mma_bf16(s[j], qa[2 * p][0], qa[2 * p][1], qa[2 * p][2], qa[2 * p][3], kf[0], kf[1]);
+                    mma_bf16(s[j], qa[2 * p + 1][0], qa[2 * p + 1][1], qa[2 * p + 1][2], qa[2 * p + 1][3], kf[2], kf[3]);
+                } else {
+                    mma_bf16(s[j], qa[2 * p][0], 0u, qa[2 * p][1], 0u, kf[0], kf[1]);
+                    mma_bf16(s[j], qa[2 * p + 1][0], 0u, qa[2 * p + 1][1], 0u, kf[2], kf[3]);
+                }
+            }
+        }
+        // ---- online softmax; lane holds keys {2tig, 2tig+1} of each n-tile for rows grp (, grp+8)
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+            const int c0 = 8 * j + 2 * tig;
+            const bool v0 = c0 < valid, v1 = c0 + 1 < valid;
+            s[j][0] = v0 ? s[j][0] * QK_SCALE : -INFINITY;
+            s[j][1] = v1 ? s[j][1] * QK_SCALE : -INFINITY;
+            s[j][2] = v0 ? s[j][2] * QK_SCALE : -INFINITY;
+            s[j][3] = v1 ? s[j][3] * QK_SCALE : -INFINITY;
+        }
+        float t0 = fmaxf(fmaxf(s[0][0], s[0][1]), fmaxf(s[1][0], s[1][1]));
+        t0 = fmaxf(t0, __shfl_xor_sync(0xffffffffu, t0, 1));
+        t0 = fmaxf(t0, __shfl_xor_sync(0xffffffffu, t0, 2));
+        const float mn0 = fmaxf(m0, t0);                   // finite: key 0 of a tile always exists
+        const float corr0 = exp2f(m0 - mn0);
+        m0 = mn0;
+        float corr1 = 1.0f;
+        if (HI) {
+            float t1 = fmaxf(fmaxf(s[0][2], s[0][3]), fmaxf(s[1][2], s[1][3]));
+            t1 = fmaxf(t1, __shfl_xor_sync(0xffffffffu, t1, 1));
+            t1 = fmaxf(t1, __shfl_xor_sync(0xffffffffu, t1, 2));
+            const float mn1 = fmaxf(m1, t1);
+            corr1 = exp2f(m1 - mn1);
+            m1 = mn1;
+        }
+        if (__any_sync(0xffffffffu, corr0 != 1.0f || corr1 != 1.0f)) {
+            l0 *= corr0; l1 *= corr1;
+#pragma unroll
+            for (int t = 0; t < 16; ++t) {
+                o[t][0] *= corr0; o[t][1] *= corr0;
+                if (HI) { o[t][2] *= corr1; o[t][3] *= corr1; }
+            }
+        }
+        unsigned pa[4];
+        {
+            const float p00 = exp2f(s[0][0] - m0), p01 = exp2f(s[0][1] - m0);
+            const float p10 = exp2f(s[1][0] - m0), p11 = exp2f(s[1][1] - m0);
+            l0 += (p00 + p01) + (p10 + p11);
+            pa[0] = pack_bf16(p00, p01);                    // row grp, keys 2tig, 2tig+1
+            pa[2] = pack_bf16(p10, p11);                    // row grp, keys 2tig+8, 2tig+9
+            pa[1] = pa[3] = 0u;
+            if (HI) {
+                const float q00 = exp2f(s[0][2] - m1), q01 = exp2f(s[0][3] - m1);
+                const float q10 = exp2f(s[1][2] - m1), q11 = exp2f(s[1][3] - m1);
+                l1 += (q00 + q01) + (q10 + q11);
+                pa[1] = pack_bf16(q00, q01);
+                pa[3] = pack_bf16(q10, q11);
+            }
+        }
+        // ---- O += P V, two 8-wide column tiles per ldmatrix.trans
+#pragma unroll
+        for (int t = 0; t < 16; t += 2) {
+            unsigned vfr[4];
+            ldsm_x4_trans(vfr, vbase + swz(((lane >> 3) & 1) * 8 + (lane & 7), t + (lane >> 4)));
+            mma_bf16(o[t], pa[0], pa[1], pa[2], pa[3], vfr[0], vfr[1]);
+            mma_bf16(o[t + 1], pa[0], pa[1], pa[2], pa[3], vfr[2], vfr[3]);
+        }
+        __syncwarp();                                      // the stage may be overwritten next round
+        if (++stage == ST) stage = 0;
+    }
+    cp_async_wait<0>();
+    __syncthreads();                                       // ring is reused for the merge below
+    float (*sm_acc)[HI ? 16 : 8][128] = reinterpret_cast<float (*)[HI ? 16 : 8][128]>(ring);
+
+    // ---- row sums across the four lanes of a group, then the warps of the CTA
+    l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
+    l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
+    if (HI) {
+        l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
+        l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+    }
+#pragma unroll
+    for (int t = 0; t < 16; ++t) {
+        const int d0 = 8 * t + 2 * tig;
+        sm_acc[warp][grp][d0] = o[t][0];
+        sm_acc[warp][grp][d0 + 1] = o[t][1];
+        if (HI) {
+            sm_acc[warp][grp + 8][d0] = o[t][2];
+            sm_acc[warp][grp + 8][d0 + 1] = o[t][3];
+        }
+    }
+    if (tig == 0) {
+        sm_m[warp][grp] = m0; sm_l[warp][grp] = l0;
+        sm_m[warp][grp + 8] = HI ? m1 : -INFINITY; sm_l[warp][grp + 8] = HI ? l1 : 0.0f;
+    }
+    __syncthreads();
+
+    const long long bh = (long long)b * KH + h;
+    float* part = a.part + (bh * a.splits + sp) * G * 130;
+    for (int e = tid; e < G * 128; e += MT) {
+        const int g = e >> 7, col = e & 127;
+        float M = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < MW; ++w) M = fmaxf(M, sm_m[w][g]);
+        float L = 0.0f, O = 0.0f;
+        if (M != -INFINITY) {
+#pragma unroll
+            for (int w = 0; w < MW; ++w) {
+                const float c = exp2f(sm_m[w][g] - M);
+                L += sm_l[w][g] * c;
+                O += sm_acc[w][g][col] * c;
+            }
+        }
+        if (a.splits == 1) {
+            const int qh = a.layout == SL_GQA_INTERLEAVED ? g * KH + h : h * G + g;
+            const long long oo = ((long long)b * KH * G + qh) * 128 + col;
+            reinterpret_cast<__nv_bfloat16*>(a.out)[oo] = __float2bfloat16_rn(L > 0.0f ? O / L : 0.0f);
+            if (a.lse && col == 0) a.lse[(long long)b * KH * G + qh] = L > 0.0f ? (M + log2f(L)) * LN2 : -INFINITY;
+        } else {
+            part[g * 130 + col] = O;
+            if (col == 0) { part[g * 130 + 128] = M; part[g * 130 + 129] = L; }
+        }
+    }
+}
+
+}  // namespace
+
+namespace sl {
+
+int attn_mma_splits(int B, int KH, int cap) {
+    // two CTAs of four warps per SM, never more CTAs than fit at once; every warp should get
+    // at least one 16-row tile
+    const int ctas = B * KH;
+    const int tiles = (cap + 15) / 16;
+    int s = (2 * sm_count()) / ctas;
+    s = std::min(s, std::min(ATTN_MAX_SPLITS, std::max(1, tiles / MW)));
+    return std::max(s, 1);
+}
+
+int launch_attn_mma(const AttnArgs& a, int G, cudaStream_t s) {
+    dim3 grid((unsigned)a.splits, (unsigned)a.KH, (unsigned)a.B);
+    static bool attr_set = false;
+    if (!attr_set) {
+        SL_CUDA_OK(cudaFuncSetAttribute(sparse_attn_mma_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, RING_BYTES));
+        SL_CUDA_OK(cudaFuncSetAttribute(sparse_attn_mma_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, RING_BYTES));
+        attr_set = true;
+    }
+    if (G > 8) sparse_attn_mma_kernel<true><<<grid, MT, RING_BYTES, s>>>(a, G);
+    else sparse_attn_mma_kernel<false><<<grid, MT, RING_BYTES, s>>>(a, G);
+    SL_CUDA_OK(cudaGetLastError());
+    if (a.splits > 1) return launch_attn_merge(a, G, SL_BF16, s);
+    return SL_OK;
+}
+
+}  // namespace sl
