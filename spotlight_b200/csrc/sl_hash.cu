@@ -28,62 +28,183 @@ struct HashArgs {
     int heads0;
 };
 
+// Offsets of the R rows of a tile, computed once (integer divisions are kept out of the loops).
+struct RowInfo {
+    long long x, xrot, vsrc, vdst, code;
+    int valid;
+};
+
 template <typename T, int R>
-__global__ void __launch_bounds__(HT) hash_kernel(const HashArgs args) {
-    constexpr int CPT = 16 / sizeof(T);
-    extern __shared__ __align__(16) unsigned char smem_raw[];
-    float* xa = reinterpret_cast<float*>(smem_raw);            // [R][MAXD]
-    float* xb = xa + R * MAXD;                                 // [R][MAXD]
-    float* red = xb + R * MAXD;                                // [KS][R][dout]
-
-    const int hy = blockIdx.y;
-    const HashJob& J = hy < args.heads0 ? args.job[0] : args.job[1];
-    const int h = hy < args.heads0 ? hy : hy - args.heads0;
-    if ((long long)blockIdx.x >= J.row_tiles) return;
-    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const long long rows = (long long)J.B * J.T;
-    const long long r0 = (long long)blockIdx.x * R;
-
-    // ---- stage the raw rows, then rotate (the rotated copy may overwrite the input in place)
+__device__ __forceinline__ void stage_rows(const HashJob& J, int h, long long r0, RowInfo* rinfo, float* xa, float* xb) {
+    const int tid = threadIdx.x;
+    if (tid < R) {
+        const long long rg = r0 + tid, rows = (long long)J.B * J.T;
+        RowInfo ri = {};
+        ri.valid = rg < rows;
+        if (ri.valid) {
+            long long b = rg, t = 0;
+            if (J.T != 1) { b = rg / J.T; t = rg - b * J.T; }
+            const long long th = t * J.H + h;
+            ri.x = b * J.xs_b + th * 128;
+            ri.xrot = b * J.xr_b + th * 128;
+            ri.vsrc = ((b * J.T + t) * J.H + h) * 128;
+            ri.vdst = b * J.v_b + th * 128;
+            ri.code = b * J.cs_b + th * 4;
+        }
+        rinfo[tid] = ri;
+    }
+    __syncthreads();
+    // raw rows first, then the rotation (the rotated copy may overwrite the input in place)
     for (int e = tid; e < R * 128; e += HT) {
         const int r = e >> 7, j = e & 127;
-        const long long rg = r0 + r;
         float val = 0.0f;
-        if (rg < rows) {
-            const long long b = rg / J.T, t = rg % J.T;
-            val = sl::VT<T>::to_f((reinterpret_cast<const T*>(J.x) + b * J.xs_b + (t * J.H + h) * 128)[j]);
-            if (J.v_dst)
-                (reinterpret_cast<T*>(J.v_dst) + b * J.v_b + (t * J.H + h) * 128)[j] =
-                    (reinterpret_cast<const T*>(J.v_src) + ((b * J.T + t) * J.H + h) * 128)[j];
+        if (rinfo[r].valid) {
+            val = sl::VT<T>::to_f((reinterpret_cast<const T*>(J.x) + rinfo[r].x)[j]);
+            if (J.v_dst) (reinterpret_cast<T*>(J.v_dst) + rinfo[r].vdst)[j] = (reinterpret_cast<const T*>(J.v_src) + rinfo[r].vsrc)[j];
         }
         xb[r * MAXD + j] = val;
     }
     __syncthreads();
     for (int e = tid; e < R * 128; e += HT) {
         const int r = e >> 7, j = e & 127;
-        const long long rg = r0 + r;
         float val = xb[r * MAXD + j];
         if (J.cosr) {
-            const float other = xb[r * MAXD + (j < 64 ? j + 64 : j - 64)];
+            const float other = xb[r * MAXD + (j ^ 64)];
             const float rot = j < 64 ? -other : other;
             const float c = sl::VT<T>::to_f(reinterpret_cast<const T*>(J.cosr)[j]);
-            const float s = sl::VT<T>::to_f(reinterpret_cast<const T*>(J.sinr)[j]);
-            val = sl::VT<T>::round(__fadd_rn(sl::VT<T>::round(__fmul_rn(val, c)), sl::VT<T>::round(__fmul_rn(rot, s))));
+            const float sn = sl::VT<T>::to_f(reinterpret_cast<const T*>(J.sinr)[j]);
+            val = sl::VT<T>::round(__fadd_rn(sl::VT<T>::round(__fmul_rn(val, c)), sl::VT<T>::round(__fmul_rn(rot, sn))));
         }
-        if (J.x_rot && rg < rows) {
-            const long long b = rg / J.T, t = rg % J.T;
-            (reinterpret_cast<T*>(J.x_rot) + b * J.xr_b + (t * J.H + h) * 128)[j] = sl::VT<T>::from_f(val);
-        }
+        if (J.x_rot && rinfo[r].valid) (reinterpret_cast<T*>(J.x_rot) + rinfo[r].xrot)[j] = sl::VT<T>::from_f(val);
         xa[r * MAXD + j] = val;
     }
     __syncthreads();
+}
 
+// Partial sums of the k-splits -> rounded layer output (bias, SiLU, residual at torch's rounding points).
+template <typename T, int R>
+__device__ __forceinline__ void finish_layer(const HashJob& J, int h, int layer, int dout, int KS, const float* red,
+                                             const float* xin, float* xout) {
+    const T* bias = J.hp.d_b[layer] ? reinterpret_cast<const T*>(J.hp.d_b[layer]) + (long long)h * dout : nullptr;
+    const bool act = layer < J.hp.n_layers - 1;
+    for (int e = threadIdx.x; e < R * dout; e += HT) {
+        const int r = e / dout, j = e - r * dout;
+        float y0 = 0.0f, y1 = 0.0f;
+        for (int s = 0; s < KS; s += 2) {
+            y0 += red[(s * R + r) * dout + j];
+            y1 += red[((s + 1) * R + r) * dout + j];
+        }
+        float y = sl::VT<T>::round(y0 + y1);
+        if (bias) y = sl::VT<T>::round(y + sl::VT<T>::to_f(bias[j]));
+        if (act) y = sl::VT<T>::round(y / (1.0f + expf(-y)));
+        if (J.hp.residue) y = sl::VT<T>::round(y + xin[r * MAXD + j]);
+        xout[r * MAXD + j] = y;
+    }
+    __syncthreads();
+}
+
+template <int R>
+__device__ __forceinline__ void sign_pack(const HashJob& J, const RowInfo* rinfo, const float* x) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    if (warp < 4) {                // warp w builds word w of each row's code
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+            const unsigned word = __ballot_sync(0xffffffffu, x[r * MAXD + warp * 32 + lane] > 0.0f);
+            if (lane == 0 && rinfo[r].valid) J.codes[rinfo[r].code + warp] = word;
+        }
+    }
+}
+
+// One layer with compile-time widths: thread (ks, cg) owns columns [cg*CPT, +CPT) and the input
+// rows ks, ks + KS, ...; its NLOAD 16-byte weight loads are issued by `fetch` long before `mac`.
+template <typename T, int DIN, int DOUT>
+struct Layer {
+    static constexpr int CPT = 16 / sizeof(T), NCG = DOUT / CPT, KS = HT / NCG, NLOAD = DIN / KS;
+    uint4 w[NLOAD];
+    __device__ __forceinline__ void fetch(const void* wbase, int h) {
+        const T* W = reinterpret_cast<const T*>(wbase) + (long long)h * DIN * DOUT;
+        const int cg = threadIdx.x % NCG, ks = threadIdx.x / NCG;
+#pragma unroll
+        for (int j = 0; j < NLOAD; ++j) w[j] = sl::ld_gather_v4(W + (ks + j * KS) * DOUT + cg * CPT);
+    }
+    template <int R>
+    __device__ __forceinline__ void mac(const float* xin, float* red) {
+        const int cg = threadIdx.x % NCG, ks = threadIdx.x / NCG;
+        float acc[R][CPT];
+#pragma unroll
+        for (int r = 0; r < R; ++r)
+#pragma unroll
+            for (int c = 0; c < CPT; ++c) acc[r][c] = 0.0f;
+#pragma unroll
+        for (int j = 0; j < NLOAD; ++j) {
+            const T* wv = reinterpret_cast<const T*>(&w[j]);
+            float wf[CPT];
+#pragma unroll
+            for (int c = 0; c < CPT; ++c) wf[c] = sl::VT<T>::to_f(wv[c]);
+#pragma unroll
+            for (int r = 0; r < R; ++r) {
+                const float xv = xin[r * MAXD + ks + j * KS];
+#pragma unroll
+                for (int c = 0; c < CPT; ++c) acc[r][c] = fmaf(xv, wf[c], acc[r][c]);
+            }
+        }
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+            float4* dst = reinterpret_cast<float4*>(red + (ks * R + r) * DOUT + cg * CPT);
+#pragma unroll
+            for (int c = 0; c < CPT; c += 4) dst[c / 4] = make_float4(acc[r][c], acc[r][c + 1], acc[r][c + 2], acc[r][c + 3]);
+        }
+        __syncthreads();
+    }
+};
+
+// Fixed shapes 128 -> 128 (NL = 1) and 128 -> DH -> 128 (NL = 2) in 2-byte types: every weight
+// load of the whole MLP is in flight before the input rows are even staged.
+template <typename T, int R, int NL, int DH>
+__global__ void __launch_bounds__(HT) hash_kernel_fixed(const HashArgs args) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    float* xa = reinterpret_cast<float*>(smem_raw);            // [R][MAXD]
+    float* xb = xa + R * MAXD;                                 // [R][MAXD]
+    float* red = xb + R * MAXD;                                // [KS][R][dout]
+    __shared__ RowInfo rinfo[R];
+    const int hy = blockIdx.y;
+    const HashJob& J = hy < args.heads0 ? args.job[0] : args.job[1];
+    const int h = hy < args.heads0 ? hy : hy - args.heads0;
+    if ((long long)blockIdx.x >= J.row_tiles) return;
+    Layer<T, 128, NL == 1 ? 128 : DH> l0;
+    Layer<T, NL == 1 ? 128 : DH, 128> l1;
+    l0.fetch(J.hp.d_w[0], h);
+    if (NL == 2) l1.fetch(J.hp.d_w[1], h);
+    stage_rows<T, R>(J, h, (long long)blockIdx.x * R, rinfo, xa, xb);
+    l0.template mac<R>(xa, red);
+    finish_layer<T, R>(J, h, 0, NL == 1 ? 128 : DH, decltype(l0)::KS, red, xa, xb);
+    if (NL == 2) {
+        l1.template mac<R>(xb, red);
+        finish_layer<T, R>(J, h, 1, 128, decltype(l1)::KS, red, xb, xa);
+    }
+    sign_pack<R>(J, rinfo, NL == 2 ? xa : xb);
+}
+
+// Any supported shape (runtime widths, up to three layers): weights are loaded layer by layer.
+template <typename T, int R>
+__global__ void __launch_bounds__(HT) hash_kernel_generic(const HashArgs args) {
+    constexpr int CPT = 16 / sizeof(T);
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    float* xa = reinterpret_cast<float*>(smem_raw);
+    float* xb = xa + R * MAXD;
+    float* red = xb + R * MAXD;
+    __shared__ RowInfo rinfo[R];
+    const int hy = blockIdx.y;
+    const HashJob& J = hy < args.heads0 ? args.job[0] : args.job[1];
+    const int h = hy < args.heads0 ? hy : hy - args.heads0;
+    if ((long long)blockIdx.x >= J.row_tiles) return;
+    const int tid = threadIdx.x;
+    stage_rows<T, R>(J, h, (long long)blockIdx.x * R, rinfo, xa, xb);
     float* xin = xa;
     float* xout = xb;
     for (int layer = 0; layer < J.hp.n_layers; ++layer) {
         const int din = J.hp.dims[layer], dout = J.hp.dims[layer + 1];
-        const int ncg = dout / CPT;            // column groups
-        const int KS = HT / ncg;               // k-splits
+        const int ncg = dout / CPT, KS = HT / ncg;
         const int cg = tid % ncg, ks = tid / ncg;
         const T* W = reinterpret_cast<const T*>(J.hp.d_w[layer]) + (long long)h * din * dout;
         float acc[R][CPT];
@@ -91,53 +212,26 @@ __global__ void __launch_bounds__(HT) hash_kernel(const HashArgs args) {
         for (int r = 0; r < R; ++r)
 #pragma unroll
             for (int c = 0; c < CPT; ++c) acc[r][c] = 0.0f;
-        if (ks < KS) {
-#pragma unroll 4
-            for (int i = ks; i < din; i += KS) {
-                const uint4 raw = sl::ld_gather_v4(W + (long long)i * dout + cg * CPT);
-                const T* wv = reinterpret_cast<const T*>(&raw);
-                float wf[CPT];
+#pragma unroll 8
+        for (int i = ks; i < din; i += KS) {
+            const uint4 raw = sl::ld_gather_v4(W + (long long)i * dout + cg * CPT);
+            const T* wv = reinterpret_cast<const T*>(&raw);
 #pragma unroll
-                for (int c = 0; c < CPT; ++c) wf[c] = sl::VT<T>::to_f(wv[c]);
+            for (int r = 0; r < R; ++r) {
+                const float xv = xin[r * MAXD + i];
 #pragma unroll
-                for (int r = 0; r < R; ++r) {
-                    const float xv = xin[r * MAXD + i];
-#pragma unroll
-                    for (int c = 0; c < CPT; ++c) acc[r][c] = fmaf(xv, wf[c], acc[r][c]);
-                }
+                for (int c = 0; c < CPT; ++c) acc[r][c] = fmaf(xv, sl::VT<T>::to_f(wv[c]), acc[r][c]);
             }
-#pragma unroll
-            for (int r = 0; r < R; ++r)
-#pragma unroll
-                for (int c = 0; c < CPT; ++c) red[(ks * R + r) * dout + cg * CPT + c] = acc[r][c];
         }
+#pragma unroll
+        for (int r = 0; r < R; ++r)
+#pragma unroll
+            for (int c = 0; c < CPT; ++c) red[(ks * R + r) * dout + cg * CPT + c] = acc[r][c];
         __syncthreads();
-        const T* bias = J.hp.d_b[layer] ? reinterpret_cast<const T*>(J.hp.d_b[layer]) + (long long)h * dout : nullptr;
-        for (int e = tid; e < R * dout; e += HT) {
-            const int r = e / dout, j = e % dout;
-            float y = 0.0f;
-            for (int s = 0; s < KS; ++s) y += red[(s * R + r) * dout + j];
-            y = sl::VT<T>::round(y);
-            if (bias) y = sl::VT<T>::round(y + sl::VT<T>::to_f(bias[j]));
-            if (layer < J.hp.n_layers - 1) y = sl::VT<T>::round(y / (1.0f + expf(-y)));
-            if (J.hp.residue) y = sl::VT<T>::round(y + xin[r * MAXD + j]);
-            xout[r * MAXD + j] = y;
-        }
-        __syncthreads();
+        finish_layer<T, R>(J, h, layer, dout, KS, red, xin, xout);
         float* t = xin; xin = xout; xout = t;
     }
-
-    // ---- sign + pack: warp w of the first four builds word w of each row's code
-    if (warp < 4) {
-        for (int r = 0; r < R; ++r) {
-            const long long rg = r0 + r;
-            const unsigned word = __ballot_sync(0xffffffffu, xin[r * MAXD + warp * 32 + lane] > 0.0f);
-            if (lane == 0 && rg < rows) {
-                const long long b = rg / J.T, t = rg % J.T;
-                J.codes[b * J.cs_b + (t * J.H + h) * 4 + warp] = word;
-            }
-        }
-    }
+    sign_pack<R>(J, rinfo, xin);
 }
 
 int check_params(const char* fn, const sl_hash_params* p, int dtype) {
@@ -164,15 +258,35 @@ size_t hash_smem(const sl_hash_params* a, const sl_hash_params* b, int R) {
     return (size_t)2 * R * MAXD * 4 + (size_t)HT * R * 8 * 4;
 }
 
+typedef void (*hash_kernel_t)(const HashArgs);
+
+template <typename T, int R>
+hash_kernel_t pick_kernel(const HashArgs& args) {
+    // the fixed-shape kernels need both jobs to share one of the shapes below
+    const sl_hash_params& p = args.job[0].hp;
+    bool same = true;
+    if (args.job[1].H > 0) {
+        const sl_hash_params& q = args.job[1].hp;
+        same = q.n_layers == p.n_layers;
+        for (int i = 0; same && i <= p.n_layers; ++i) same = q.dims[i] == p.dims[i];
+    }
+    if (sizeof(T) == 2 && same) {
+        if (p.n_layers == 1) return hash_kernel_fixed<T, R, 1, 128>;
+        if (p.n_layers == 2 && p.dims[1] == 128) return hash_kernel_fixed<T, R, 2, 128>;
+        if (p.n_layers == 2 && p.dims[1] == 256) return hash_kernel_fixed<T, R, 2, 256>;
+    }
+    return hash_kernel_generic<T, R>;
+}
+
 template <typename T>
 int launch_T(const HashArgs& args, int total_heads, long long max_tiles, int R, size_t smem, cudaStream_t s) {
     dim3 grid((unsigned)max_tiles, (unsigned)total_heads);
-    void (*kern)(const HashArgs) = nullptr;
+    hash_kernel_t kern = nullptr;
     switch (R) {
-        case 1: kern = hash_kernel<T, 1>; break;
-        case 2: kern = hash_kernel<T, 2>; break;
-        case 4: kern = hash_kernel<T, 4>; break;
-        default: kern = hash_kernel<T, 8>; break;
+        case 1: kern = pick_kernel<T, 1>(args); break;
+        case 2: kern = pick_kernel<T, 2>(args); break;
+        case 4: kern = pick_kernel<T, 4>(args); break;
+        default: kern = pick_kernel<T, 8>(args); break;
     }
     SL_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     kern<<<grid, HT, smem, s>>>(args);
