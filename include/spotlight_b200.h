@@ -178,7 +178,8 @@ int sl_hash_encode(const void* d_x, int64_t x_batch_stride, int dtype, int B, in
  *   d_idx [B,KH,idx_capacity] int32, d_cnt [B,KH] int32,
  *   d_out [B,QH,128] of `dtype`; d_lse (optional) [B,QH] float natural-log-sum-exp of the
  *   scaled logits, for merging partial results of sequence shards.
- * Workspace: sl_sparse_attn_workspace_bytes(B,KH,QH); zero-initialised once like the scan's. */
+ * Workspace: sl_sparse_attn_workspace_bytes(B,KH,QH) bytes of scratch for the per-split
+ * partials (no initial contents required, nothing is kept between calls). */
 size_t sl_sparse_attn_workspace_bytes(int B, int KH, int QH);
 int sl_sparse_attn_decode(const void* d_q, const void* d_k, const void* d_v, int dtype,
                           int64_t kv_batch_stride, const int32_t* d_idx, int idx_capacity,
