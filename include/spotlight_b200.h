@@ -187,6 +187,23 @@ int sl_sparse_attn_decode(const void* d_q, const void* d_k, const void* d_v, int
                           void* d_out, float* d_lse, void* d_workspace, size_t workspace_bytes,
                           void* stream);
 
+/* sl_sparse_attn_decode for callers that may not allocate device memory where they run attention
+ * (an engine whose memory pool took all of HBM at start-up; a decode loop in which cudaMalloc and
+ * cudaFree are banned because they can stall the whole device). It has no counterpart in the
+ * reference. Arguments and results are those of sl_sparse_attn_decode without the workspace:
+ * the scratch for the per-split partials is a fixed array of SL_ATTN_STATIC_SCRATCH_BYTES inside
+ * the library, resident on every GPU that loads it until the process ends. Shapes that need more
+ * (B*QH > 252) are refused with SL_EWORKSPACE. The call allocates and frees nothing.
+ * The first call on a device looks up the array's device address; make that call before any
+ * stream capture begins. All calls share the one array and nothing in it has to be cleared
+ * between them, but two calls whose kernels may run at the same time on one GPU (different
+ * streams) race on it: serialise them or give the second a workspace of its own. */
+#define SL_ATTN_STATIC_SCRATCH_BYTES (8u << 20)
+int sl_sparse_attn_decode_static(const void* d_q, const void* d_k, const void* d_v, int dtype,
+                                 int64_t kv_batch_stride, const int32_t* d_idx, int idx_capacity,
+                                 const int32_t* d_cnt, int B, int KH, int QH, int gqa_layout,
+                                 void* d_out, float* d_lse, void* stream);
+
 /* Log-sum-exp merge of R partial attention results (sequence shards):
  * d_o [R,rows,128] float, d_lse [R,rows] float -> d_out [rows,128] of `dtype`. */
 int sl_merge_lse(const float* d_o, const float* d_lse, int R, int64_t rows, int dtype, void* d_out,

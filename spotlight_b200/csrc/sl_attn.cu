@@ -367,3 +367,37 @@ extern "C" int sl_gather_rows(const void* d_cache, int64_t batch_stride, int ele
     SL_CUDA_OK(cudaGetLastError());
     return SL_OK;
 }
+
+// ---- sparse attention without a caller workspace -------------------------------------------
+// Some callers of this library are not allowed to allocate device memory at the point where they
+// run attention: a serving engine that handed every free byte of HBM to its KV-cache pool at
+// start-up, or a latency-critical decode loop in which cudaMalloc / cudaFree are banned because
+// they can synchronise the whole device. For them the scratch of the split partials lives in
+// this fixed array, which every GPU that loads the library keeps until the process exits.
+// The name below is only a host-side handle: the device address is fetched once per device
+// with cudaGetSymbolAddress (that device being current) and handed to the kernels.
+static __device__ __align__(256) unsigned char g_attn_static_scratch[SL_ATTN_STATIC_SCRATCH_BYTES];
+
+extern "C" int sl_sparse_attn_decode_static(const void* d_q, const void* d_k, const void* d_v, int dtype,
+                                            int64_t kv_batch_stride, const int32_t* d_idx, int idx_capacity,
+                                            const int32_t* d_cnt, int B, int KH, int QH, int gqa_layout, void* d_out,
+                                            float* d_lse, void* stream) {
+    SL_REQUIRE(B > 0 && KH > 0 && QH > 0, SL_ESHAPE, "sl_sparse_attn_decode_static: bad shape");
+    const size_t need = sl_sparse_attn_workspace_bytes(B, KH, QH);
+    SL_REQUIRE(need <= (size_t)SL_ATTN_STATIC_SCRATCH_BYTES, SL_EWORKSPACE,
+               "sl_sparse_attn_decode_static: B*QH = %d needs %zu bytes of scratch but the built-in array holds %u; "
+               "use sl_sparse_attn_decode with a caller-owned workspace",
+               B * QH, need, (unsigned)SL_ATTN_STATIC_SCRATCH_BYTES);
+    static void* scratch_of_device[64] = {nullptr};
+    int dev = -1;
+    SL_CUDA_OK(cudaGetDevice(&dev));
+    SL_REQUIRE(dev >= 0 && dev < 64, SL_EINVAL, "sl_sparse_attn_decode_static: device ordinal %d out of range", dev);
+    if (scratch_of_device[dev] == nullptr) {          // first call on this device: resolve the array's device address
+        void* p = nullptr;
+        SL_CUDA_OK(cudaGetSymbolAddress(&p, g_attn_static_scratch));
+        SL_REQUIRE(p != nullptr, SL_ECUDA, "sl_sparse_attn_decode_static: no device address for the scratch array");
+        scratch_of_device[dev] = p;
+    }
+    return sl_sparse_attn_decode(d_q, d_k, d_v, dtype, kv_batch_stride, d_idx, idx_capacity, d_cnt, B, KH, QH, gqa_layout,
+                                 d_out, d_lse, scratch_of_device[dev], (size_t)SL_ATTN_STATIC_SCRATCH_BYTES, stream);
+}
