@@ -209,6 +209,27 @@ int sl_sparse_attn_decode_static(const void* d_q, const void* d_k, const void* d
 int sl_merge_lse(const float* d_o, const float* d_lse, int R, int64_t rows, int dtype, void* d_out,
                  void* stream);
 
+/* LRU-resident KV buffer, stage (3) of the decode path; one launch per decode step and layer.
+ * The reference has no counterpart (its nearest relatives are KVCache.gather,
+ * spotlight/modifiers/gpu_cache.py:100-106, and the host-offloaded gather of
+ * spotlight/modifiers/cpu_cache.py:105-113); the policy is this library's:
+ *  - per (b, kv head) C slots; attended keys already resident are hits and get stamped with `step`;
+ *  - each miss, in index-list order, takes the least recently attended slot not used in this
+ *    step: never-used slots first, then by age in steps (ages above 1023 count as 1023), ties
+ *    to the LOWEST slot index; its K and V rows are copied from the backing store
+ *    [B, N, KH, 128] (device memory or mapped pinned host memory) into the resident buffers
+ *    [B, C, KH, 128];
+ *  - d_slots_out[b,h,j] = slot of d_idx[b,h,j]: sl_sparse_attn_decode over the resident buffers
+ *    with d_slots_out as its index list performs exactly the arithmetic of the direct call.
+ * State (caller-owned, initialised to -1): d_tok2slot [B,KH,n_max], d_slot2tok [B,KH,C],
+ * d_last_used [B,KH,C], all int32. Requires cnt[b,h] <= C (else *d_status = 3).
+ * d_stats (optional) [B,KH,2] receives hits and misses of the step. */
+int sl_lru_update(const int32_t* d_idx, int idx_capacity, const int32_t* d_cnt, int B, int KH,
+                  const void* k_backing, const void* v_backing, int64_t backing_batch_stride,
+                  int elem_bytes, void* d_k_resident, void* d_v_resident, int C,
+                  int32_t* d_tok2slot, int64_t n_max, int32_t* d_slot2tok, int32_t* d_last_used,
+                  int step, int32_t* d_slots_out, int32_t* d_stats, int32_t* d_status, void* stream);
+
 /* Row gather for API parity with KVCache.gather (spotlight/modifiers/gpu_cache.py:100-106):
  * out[b,j,h,:] = cache[b, idx[b,h,j], h, :] for j < budget. */
 int sl_gather_rows(const void* d_cache, int64_t batch_stride, int elem_bytes,

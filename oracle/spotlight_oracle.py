@@ -354,3 +354,42 @@ def modifier_path_dense(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, hash_
     K = apply_rope(k, cos, sin, pos)
     o = torch.nn.functional.scaled_dot_product_attention(Q, K, v, attn_mask=mask, is_causal=False)
     return o.transpose(1, 2).flatten(2)
+
+
+# --------------------------------------------------------------------------------------
+# LRU-resident KV buffer (no reference counterpart; the policy of sl_lru_update restated)
+# --------------------------------------------------------------------------------------
+class LruModel:
+    """Slot table of ONE (batch row, kv head): hits are stamped, misses (in list order) take the
+    least recently attended slot not used in this step -- never-used slots first, then by age in
+    steps with ages above `age_max` counted as `age_max`, ties to the lowest slot index."""
+
+    def __init__(self, n_max: int, slots: int, age_max: int = 1023):
+        self.tok2slot = np.full(n_max, -1, np.int32)
+        self.slot2tok = np.full(slots, -1, np.int32)
+        self.last_used = np.full(slots, -1, np.int32)
+        self.age_max = age_max
+        self.step = 0
+
+    def update(self, tokens: np.ndarray):
+        t = self.step
+        slots = self.tok2slot[tokens].copy()
+        hit = slots >= 0
+        self.last_used[slots[hit]] = t
+        lu = self.last_used
+        age = np.where(lu < 0, self.age_max + 1, np.minimum(t - lu, self.age_max))
+        cand = np.nonzero(age > 0)[0]
+        order = cand[np.argsort(-age[cand], kind="stable")]          # oldest first, lowest slot on ties
+        m = int((~hit).sum())
+        assert m <= len(order), "table too small for this step"
+        victims = np.sort(order[:m])                                    # misses take victims in slot order
+        for tok, v in zip(tokens[~hit], victims):
+            old = self.slot2tok[v]
+            if old >= 0:
+                self.tok2slot[old] = -1
+            self.tok2slot[tok] = v
+            self.slot2tok[v] = tok
+            self.last_used[v] = t
+        slots[~hit] = victims
+        self.step += 1
+        return slots.astype(np.int32), int(hit.sum()), m

@@ -46,6 +46,7 @@ SIGNATURES = {
     "sl_sparse_attn_decode": (_I, [_P, _P, _P, _I, _L, _P, _I, _P, _I, _I, _I, _I, _P, _P, _P, _Z, _P]),
     "sl_sparse_attn_decode_static": (_I, [_P, _P, _P, _I, _L, _P, _I, _P, _I, _I, _I, _I, _P, _P, _P]),
     "sl_merge_lse": (_I, [_P, _P, _I, _L, _I, _P, _P]),
+    "sl_lru_update": (_I, [_P, _I, _P, _I, _I, _P, _P, _L, _I, _P, _P, _I, _P, _L, _P, _P, _I, _P, _P, _P, _P]),
     "sl_gather_rows": (_I, [_P, _L, _I, _P, _I, _I, _I, _I, _P, _P]),
 }
 

@@ -357,6 +357,46 @@ def sparse_attn_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Te
     return (out, lse) if return_lse else out
 
 
+class LruTable:
+    """Resident K/V buffers [B,C,KH,128] and the slot tables of one layer (see sl_lru_update)."""
+
+    def __init__(self, batch: int, kv_heads: int, n_max: int, slots: int, dtype: torch.dtype, device):
+        self.B, self.KH, self.n_max, self.C = batch, kv_heads, n_max, slots
+        self.k = torch.zeros((batch, slots, kv_heads, 128), dtype=dtype, device=device)
+        self.v = torch.zeros((batch, slots, kv_heads, 128), dtype=dtype, device=device)
+        self.tok2slot = torch.full((batch, kv_heads, n_max), -1, dtype=torch.int32, device=device)
+        self.slot2tok = torch.full((batch, kv_heads, slots), -1, dtype=torch.int32, device=device)
+        self.last_used = torch.full((batch, kv_heads, slots), -1, dtype=torch.int32, device=device)
+        self.stats = torch.zeros((batch, kv_heads, 2), dtype=torch.int32, device=device)
+        self.status = torch.zeros(1, dtype=torch.int32, device=device)
+        self.step = 0
+
+
+def lru_update(table: LruTable, idx: torch.Tensor, cnt: torch.Tensor, k_backing: torch.Tensor,
+               v_backing: torch.Tensor, slots_out: Optional[torch.Tensor] = None, backing_ptrs=None) -> torch.Tensor:
+    """Make this step's attended keys resident; returns their slots int32 [B,KH,cap] in list order.
+    k_backing / v_backing: [B,N,KH,128] device tensors (views of a larger cache are fine), or pass
+    backing_ptrs=(k_ptr, v_ptr, batch_stride_elems) for mapped pinned host memory."""
+    B, KH, cap = idx.shape
+    dev = _cuda(idx, cnt, table.k)
+    assert idx.is_contiguous() and cnt.is_contiguous() and (B, KH) == (table.B, table.KH)
+    if slots_out is None:
+        slots_out = torch.empty_like(idx)
+    if backing_ptrs is None:
+        kb = _rows_view(k_backing, 128)
+        assert _rows_view(v_backing, 128) == kb and k_backing.dtype == table.k.dtype
+        kp, vp = k_backing.data_ptr(), v_backing.data_ptr()
+    else:
+        kp, vp, kb = backing_ptrs
+    check(lib.sl_lru_update(idx.data_ptr(), cap, cnt.data_ptr(), B, KH, kp, vp, kb, table.k.element_size(),
+                            table.k.data_ptr(), table.v.data_ptr(), table.C, table.tok2slot.data_ptr(), table.n_max,
+                            table.slot2tok.data_ptr(), table.last_used.data_ptr(), table.step, slots_out.data_ptr(),
+                            table.stats.data_ptr(), table.status.data_ptr(), _stream()))
+    table.step += 1
+    _count()
+    return slots_out
+
+
 def merge_lse(o_parts: torch.Tensor, lse_parts: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:
     """o_parts float [R,...,128], lse_parts float [R,...] -> merged [...,128] of `dtype`."""
     R = o_parts.shape[0]

@@ -115,3 +115,14 @@ def test_merge_partials_identity():
         parts_o.append(p @ v[lo:hi]); parts_m.append(m); parts_l.append(p.sum(-1))
     got = O.merge_partials(torch.stack(parts_o), torch.stack(parts_m), torch.stack(parts_l))
     assert torch.allclose(got, whole, atol=1e-12)
+
+
+def test_lru_model_policy():
+    m = O.LruModel(n_max=50, slots=4)
+    s, hits, misses = m.update(np.array([3, 9, 20]))
+    assert (hits, misses) == (0, 3) and s.tolist() == [0, 1, 2]          # free slots, lowest index first
+    s, hits, misses = m.update(np.array([9, 30]))
+    assert (hits, misses) == (1, 1) and s.tolist() == [1, 3]             # the never-used slot goes before used ones
+    s, hits, misses = m.update(np.array([9, 40, 41]))
+    assert (hits, misses) == (1, 2) and s.tolist() == [1, 0, 2]          # oldest stamps (step 0) evicted, slot order
+    assert m.tok2slot[3] == -1 and m.tok2slot[20] == -1 and m.tok2slot[30] == 3

@@ -359,3 +359,65 @@ def test_errors_are_exceptions_not_crashes(ops):
         ops.hamming_scores(q[:, None], k.transpose(1, 2).contiguous().transpose(1, 2))  # not token-major
     with pytest.raises(AssertionError):
         ops.pack_signbits(torch.zeros((4, 100), device=DEV))                  # last dim % 32
+
+
+# ------------------------------------------------------------------------------------------ LRU
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("B,KH,N,C,keep", [(2, 4, 3000, 400, 300), (1, 8, 5000, 1500, 1400), (3, 2, 200, 64, 64)])
+def test_lru_resident_buffer_is_results_invisible(ops, dtype, B, KH, N, C, keep):
+    """A dozen decode steps with drifting attended sets: slot tables bit-exact against the CPU
+    model of the policy, resident rows equal to the backing rows, and attention over the resident
+    buffer bit-identical to attention over the full cache."""
+    QH = KH * 2
+    g = torch.Generator().manual_seed(B * 100 + C)
+    k = torch.randn((B, N, KH, 128), generator=g).to(dtype)
+    v = torch.randn((B, N, KH, 128), generator=g).to(dtype)
+    kd, vd = k.to(DEV), v.to(DEV)
+    table = ops.LruTable(B, KH, N, C, dtype, DEV)
+    models = [[O.LruModel(N, C) for _ in range(KH)] for _ in range(B)]
+    pool = [[torch.randperm(N, generator=g)[: 2 * keep] for _ in range(KH)] for _ in range(B)]   # working set
+    for step in range(12):
+        idx = np.zeros((B, KH, keep), np.int32)
+        cnt = np.zeros((B, KH), np.int32)
+        for b in range(B):
+            for h in range(KH):
+                n = keep - (step + b + h) % 5
+                if step % 4 == 3:                                   # now and then the working set moves
+                    pool[b][h] = torch.cat([pool[b][h][keep // 2:], torch.randperm(N, generator=g)[: keep // 2]])
+                pick = pool[b][h][torch.randperm(len(pool[b][h]), generator=g)].unique()[:n]
+                n = len(pick)
+                idx[b, h, :n] = np.sort(pick.numpy())
+                cnt[b, h] = n
+        idx_d, cnt_d = torch.from_numpy(idx).to(DEV), torch.from_numpy(cnt).to(DEV)
+        slots = ops.lru_update(table, idx_d, cnt_d, kd, vd)
+        assert int(table.status.item()) == 0
+        stats = table.stats.cpu().numpy()
+        for b in range(B):
+            for h in range(KH):
+                n = cnt[b, h]
+                ref_slots, hits, misses = models[b][h].update(idx[b, h, :n])
+                np.testing.assert_array_equal(slots[b, h, :n].cpu().numpy(), ref_slots)
+                assert (stats[b, h, 0], stats[b, h, 1]) == (hits, misses)
+                np.testing.assert_array_equal(table.tok2slot[b, h].cpu().numpy(), models[b][h].tok2slot)
+                np.testing.assert_array_equal(table.slot2tok[b, h].cpu().numpy(), models[b][h].slot2tok)
+                np.testing.assert_array_equal(table.last_used[b, h].cpu().numpy(), models[b][h].last_used)
+                res = models[b][h].slot2tok
+                live = np.nonzero(res >= 0)[0]
+                assert torch.equal(table.k[b, live, h].cpu(), k[b, res[live], h])
+                assert torch.equal(table.v[b, live, h].cpu(), v[b, res[live], h])
+        if step >= 1:
+            assert stats[..., 0].sum() > 0                           # overlapping sets do hit
+        q = torch.randn((B, QH, 128), generator=g).to(dtype).to(DEV)
+        direct = ops.sparse_attn_decode(q, kd, vd, idx_d, cnt_d)
+        resident = ops.sparse_attn_decode(q, table.k, table.v, slots, cnt_d)
+        assert torch.equal(direct, resident)
+
+
+def test_lru_refuses_a_table_smaller_than_the_attended_set(ops):
+    table = ops.LruTable(1, 2, 100, 8, torch.bfloat16, DEV)
+    kv = torch.zeros((1, 100, 2, 128), dtype=torch.bfloat16, device=DEV)
+    idx = torch.arange(20, dtype=torch.int32, device=DEV).expand(1, 2, 20).contiguous()
+    cnt = torch.full((1, 2), 20, dtype=torch.int32, device=DEV)
+    ops.lru_update(table, idx, cnt, kv, kv)
+    assert int(table.status.item()) == 3
+    assert int((table.slot2tok >= 0).sum()) == 0                      # nothing was touched
