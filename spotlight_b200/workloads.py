@@ -141,6 +141,28 @@ def make_inputs(cfg: PathConfig, context: Optional[int] = None, batch: Optional[
     return PathInputs(q.to(dt), k.to(dt), v.to(dt), hq, hk, ch)
 
 
+BLOCK_TOKENS = 131072
+
+
+def make_block(cfg: PathConfig, block: int, tokens: int = BLOCK_TOKENS):
+    """Keys/values of one fixed-size block of a long context (config 4): block j is seeded
+    ``cfg.seed * 1000 + j`` -- never by rank -- so any number of ranks, and the CPU checker, see
+    the same global tensor; a rank materialises only the blocks it owns. Returns post-RoPE
+    (k, v) of shape [B, tokens, KH, 128] in the run dtype."""
+    gen = torch.Generator().manual_seed(cfg.seed * 1000 + block)
+    k = torch.randn((cfg.batch, tokens, cfg.kv_heads, HEAD_DIM), generator=gen)
+    v = torch.randn((cfg.batch, tokens, cfg.kv_heads, HEAD_DIM), generator=gen)
+    ch = torch.randperm(HEAD_DIM, generator=torch.Generator().manual_seed(cfg.seed))[:4]
+    k[..., ch] *= 8.0
+    if block == 0:
+        k[:, 0] *= 4.0
+    pos = torch.arange(block * tokens, (block + 1) * tokens)
+    cos, sin = rope_tables(pos, cfg.rope_theta)
+    k = apply_rope(k, cos[None, :, None, :], sin[None, :, None, :])
+    dt = torch_dtype(cfg.dtype)
+    return k.to(dt), v.to(dt)
+
+
 def ar1_step(k_prev: torch.Tensor, gen: torch.Generator, rho: float = 0.95) -> torch.Tensor:
     """Seeded AR(1) drift of the keys, ``K_t = rho*K_{t-1} + sqrt(1-rho^2)*eps`` (config 2)."""
     eps = torch.randn(k_prev.shape, generator=gen)

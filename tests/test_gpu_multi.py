@@ -1,0 +1,72 @@
+"""Sequence-sharded decode attention on real devices over NCCL (needs >= 2 GPUs; skipped on a
+single-GPU machine). Every rank builds the same seeded global tensors, keeps its shard, and the
+merged output / the union of the index sets must equal the single-device kernels' and the CPU
+checker's."""
+import os
+import socket
+
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+from oracle import spotlight_oracle as O  # noqa: E402
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _inputs(n, B, KH, QH):
+    g = torch.Generator().manual_seed(77)
+    codes = torch.randint(0, 2 ** 31, (B, n, KH, 4), generator=g).to(torch.int32).view(torch.uint32)
+    q_codes = torch.randint(0, 2 ** 31, (B, QH, 4), generator=g).to(torch.int32).view(torch.uint32)
+    k = torch.randn((B, n, KH, 128), generator=g).to(torch.bfloat16)
+    v = torch.randn((B, n, KH, 128), generator=g).to(torch.bfloat16)
+    q = torch.randn((B, QH, 128), generator=g).to(torch.bfloat16)
+    return q, q_codes, codes, k, v
+
+
+def _worker(rank, world, port, n, keep, ret):
+    import torch.distributed as dist
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    try:
+        from spotlight_b200 import ops
+        from spotlight_b200.sharded import shard_bounds, sharded_decode_attention
+        q, q_codes, codes, k, v = _inputs(n, 1, 8, 40)
+        lo, hi = shard_bounds(n, world, rank)
+        out, idx, cnt = sharded_decode_attention(
+            q.to(dev), q_codes.to(dev), codes[:, lo:hi].contiguous().to(dev), k[:, lo:hi].contiguous().to(dev),
+            v[:, lo:hi].contiguous().to(dev), lo, n, keep, 4, 64, O.BLOCKED, return_selection=True)
+        torch.cuda.synchronize(dev)
+        ops.check_status(dev)
+        ret[rank] = (out.float().cpu().numpy(), idx.cpu().numpy() + lo, cnt.cpu().numpy())
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs at least two GPUs")
+def test_sequence_sharded_attention_over_nccl():
+    import torch.multiprocessing as mp
+    world = min(torch.cuda.device_count(), 4)
+    n, keep = 200000, 4000
+    ret = mp.Manager().dict()
+    mp.spawn(_worker, args=(world, _free_port(), n, keep, ret), nprocs=world, join=True)
+    q, q_codes, codes, k, v = _inputs(n, 1, 8, 40)
+    scores = O.match_count(q_codes.view(torch.int32).numpy().view(np.uint32)[:, None],
+                           codes.view(torch.int32).numpy().view(np.uint32), O.BLOCKED)
+    ref_idx, ref_cnt = O.select(scores, keep, 4, 64)
+    for h in range(8):
+        got = np.concatenate([ret[r][1][0, h, : ret[r][2][0, h]] for r in range(world)])
+        np.testing.assert_array_equal(got, ref_idx[0, h, : ref_cnt[0, h]])
+    ref_out = O.sparse_attention(q, k, v, ref_idx, ref_cnt, O.BLOCKED).numpy()
+    for r in range(world):
+        assert np.abs(ret[r][0] - ref_out).max() <= 2e-2           # bf16 tolerance
+        np.testing.assert_array_equal(ret[r][0], ret[0][0])
