@@ -340,7 +340,7 @@ def run_ours(args, cfg):
         "e2e": {"value": max(ms_e2e, wall_e2e) * 1e3 / L, "unit": UNIT,
                 "h2d_bytes_per_step": s.host_bytes_per_step[0], "d2h_bytes_per_step": s.host_bytes_per_step[1],
                 "device_ms_per_step": ms_e2e, "wall_ms_per_step": wall_e2e},
-        "gpu_launches": 3 * L * args.steps,
+        "gpu_launches": 4 * L * args.steps,
         "cuda_graph": use_graph,
         "roofline": {"bound": "hbm", "kernel": dom, "achieved": kern[dom]["gbs"], "peak": peak, "unit": "GB/s",
                      "frac": kern[dom]["frac"], "traffic": NCU_TRAFFIC[dom], "peak_kind": peak_kind,

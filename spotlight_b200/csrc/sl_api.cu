@@ -1,7 +1,10 @@
 // Error plumbing, version and workspace helpers of the C ABI.
+#include <cstdlib>
+
 #include "sl_common.cuh"
 
 namespace sl {
+void set_pdl(int on);
 
 static thread_local char g_err[512] = "";
 
@@ -14,6 +17,18 @@ int fail(int code, const char* fmt, ...) {
     va_end(ap);
     return code;
 }
+
+static int g_pdl = -1;
+
+bool pdl_enabled() {
+    if (g_pdl < 0) {
+        const char* e = getenv("SL_PDL");
+        g_pdl = (e && e[0] == '0') ? 0 : 1;
+    }
+    return g_pdl != 0;
+}
+
+void set_pdl(int on) { g_pdl = on ? 1 : 0; }
 
 int sm_count() {
     static int cached[64] = {0};
@@ -43,3 +58,7 @@ extern "C" int sl_workspace_init(void* d_workspace, size_t bytes, void* stream) 
     SL_CUDA_OK(cudaMemsetAsync(d_workspace, 0, bytes, static_cast<cudaStream_t>(stream)));
     return SL_OK;
 }
+
+// Development switch, not part of the public header: turns programmatic dependent launch of the
+// decode-path kernels on or off (default on; the environment variable SL_PDL=0 turns it off).
+extern "C" void sl_debug_set_pdl(int on) { sl::set_pdl(on); }

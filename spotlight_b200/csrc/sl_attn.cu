@@ -27,6 +27,8 @@ __global__ void __launch_bounds__(AT, (G * (16 / sizeof(T)) > 32) ? 1 : 2) spars
     __shared__ float sm_acc[AW][G][128];
     __shared__ float sm_m[AW][G], sm_l[AW][G];
 
+    sl::pdl_trigger();
+    sl::pdl_wait();
     const int sp = blockIdx.x, h = blockIdx.y, b = blockIdx.z, KH = a.KH;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int sub = lane % LPR, rs = lane / LPR;
@@ -172,6 +174,8 @@ __global__ void __launch_bounds__(512) attn_merge_kernel(const float* __restrict
                                                          int layout, T* __restrict__ out, float* __restrict__ lse) {
     __shared__ float s_m[sl::ATTN_MAX_SPLITS], s_l[sl::ATTN_MAX_SPLITS], s_w[sl::ATTN_MAX_SPLITS];
     __shared__ float red[4][128];
+    sl::pdl_trigger();
+    sl::pdl_wait();
     const int g = blockIdx.x % G;
     const long long bh = blockIdx.x / G;
     const int h = (int)(bh % KH);
@@ -257,8 +261,7 @@ int pick_splits(int B, int KH, int cap) {
 template <typename T, int G>
 int launch_attn(const AttnArgs& a, cudaStream_t s) {
     dim3 grid((unsigned)a.splits, (unsigned)a.KH, (unsigned)a.B);
-    sparse_attn_kernel<T, G><<<grid, AT, 0, s>>>(a);
-    SL_CUDA_OK(cudaGetLastError());
+    SL_CUDA_OK(sl::launch_kernel(sparse_attn_kernel<T, G>, grid, dim3(AT), 0, s, false, a));
     if (a.splits > 1) return sl::launch_attn_merge(a, G, sizeof(T) == 4 ? SL_F32 : (std::is_same<T, __half>::value ? SL_F16 : SL_BF16), s);
     return SL_OK;
 }
@@ -284,11 +287,10 @@ namespace sl {
 int launch_attn_merge(const AttnArgs& a, int G, int dtype, cudaStream_t s) {
     const unsigned blocks = (unsigned)(a.B * a.KH * G);
     switch (dtype) {
-        case SL_BF16: attn_merge_kernel<__nv_bfloat16><<<blocks, 512, 0, s>>>(a.part, a.splits, G, a.KH, a.layout, (__nv_bfloat16*)a.out, a.lse); break;
-        case SL_F16: attn_merge_kernel<__half><<<blocks, 512, 0, s>>>(a.part, a.splits, G, a.KH, a.layout, (__half*)a.out, a.lse); break;
-        default: attn_merge_kernel<float><<<blocks, 512, 0, s>>>(a.part, a.splits, G, a.KH, a.layout, (float*)a.out, a.lse); break;
+        case SL_BF16: SL_CUDA_OK(launch_kernel(attn_merge_kernel<__nv_bfloat16>, dim3(blocks), dim3(512), 0, s, false, (const float*)a.part, a.splits, G, a.KH, a.layout, (__nv_bfloat16*)a.out, a.lse)); break;
+        case SL_F16: SL_CUDA_OK(launch_kernel(attn_merge_kernel<__half>, dim3(blocks), dim3(512), 0, s, false, (const float*)a.part, a.splits, G, a.KH, a.layout, (__half*)a.out, a.lse)); break;
+        default: SL_CUDA_OK(launch_kernel(attn_merge_kernel<float>, dim3(blocks), dim3(512), 0, s, false, (const float*)a.part, a.splits, G, a.KH, a.layout, (float*)a.out, a.lse)); break;
     }
-    SL_CUDA_OK(cudaGetLastError());
     return SL_OK;
 }
 }  // namespace sl

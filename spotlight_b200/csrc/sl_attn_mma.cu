@@ -62,6 +62,8 @@ __global__ void __launch_bounds__(MT, 2) sparse_attn_mma_kernel(const AttnArgs a
     extern __shared__ __align__(128) unsigned char ring[];          // [MW][ST][K 4 KB | V 4 KB]; reused by the epilogue
     __shared__ float sm_m[MW][16], sm_l[MW][16];
 
+    sl::pdl_trigger();
+    sl::pdl_wait();                 // index list, counts, q and the new K/V row come from earlier kernels
     const int sp = blockIdx.x, h = blockIdx.y, b = blockIdx.z, KH = a.KH;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int grp = lane >> 2, tig = lane & 3;
@@ -297,9 +299,8 @@ int launch_attn_mma(const AttnArgs& a, int G, cudaStream_t s) {
         SL_CUDA_OK(cudaFuncSetAttribute(sparse_attn_mma_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, RING_BYTES));
         attr_set = true;
     }
-    if (G > 8) sparse_attn_mma_kernel<true><<<grid, MT, RING_BYTES, s>>>(a, G);
-    else sparse_attn_mma_kernel<false><<<grid, MT, RING_BYTES, s>>>(a, G);
-    SL_CUDA_OK(cudaGetLastError());
+    if (G > 8) SL_CUDA_OK(launch_kernel(sparse_attn_mma_kernel<true>, grid, dim3(MT), RING_BYTES, s, false, a, G));
+    else SL_CUDA_OK(launch_kernel(sparse_attn_mma_kernel<false>, grid, dim3(MT), RING_BYTES, s, false, a, G));
     if (a.splits > 1) return launch_attn_merge(a, G, SL_BF16, s);
     return SL_OK;
 }

@@ -17,6 +17,7 @@ namespace sl {
 char* err_buf();
 int fail(int code, const char* fmt, ...);
 int sm_count();          // SMs of the current device (cached per device)
+bool pdl_enabled();      // programmatic dependent launch on (default) / off (SL_PDL=0 or sl_set_pdl)
 
 #define SL_CUDA_OK(expr)                                                                    \
     do {                                                                                    \
@@ -32,7 +33,36 @@ int sm_count();          // SMs of the current device (cached per device)
 
 static inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
+// ---- launches ----------------------------------------------------------------------------
+// Kernels of the decode path are launched with programmatic stream serialisation: a kernel may
+// start while its predecessor in the stream drains, does whatever does not depend on it, and
+// blocks in pdl_wait() until the predecessor has completed and flushed. Every such kernel
+// executes pdl_wait() on every path before it touches data other kernels produce or consume, so
+// completion stays transitive along the stream. pdl_trigger() lets the successor begin.
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_kernel(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t s,
+                                 bool cooperative, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = s;
+    cudaLaunchAttribute attrs[2];
+    unsigned n = 0;
+    if (pdl_enabled()) {
+        attrs[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attrs[n].val.programmaticStreamSerializationAllowed = 1;
+        ++n;
+    }
+    if (cooperative) {
+        attrs[n].id = cudaLaunchAttributeCooperative;
+        attrs[n].val.cooperative = 1;
+        ++n;
+    }
+    cfg.attrs = attrs; cfg.numAttrs = n;
+    return cudaLaunchKernelEx(&cfg, kern, KArgs(args)...);
+}
+
 // ---- device helpers -------------------------------------------------------------------
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 // Streaming 128-bit load that bypasses L1 allocation: the code stream is read once.
 __device__ __forceinline__ uint4 ld_stream_v4(const uint4* p) {
     uint4 r;

@@ -170,11 +170,13 @@ __global__ void __launch_bounds__(HT) hash_kernel_fixed(const HashArgs args) {
     const int hy = blockIdx.y;
     const HashJob& J = hy < args.heads0 ? args.job[0] : args.job[1];
     const int h = hy < args.heads0 ? hy : hy - args.heads0;
-    if ((long long)blockIdx.x >= J.row_tiles) return;
+    sl::pdl_trigger();
+    if ((long long)blockIdx.x >= J.row_tiles) { sl::pdl_wait(); return; }
     Layer<T, 128, NL == 1 ? 128 : DH> l0;
     Layer<T, NL == 1 ? 128 : DH, 128> l1;
     l0.fetch(J.hp.d_w[0], h);
     if (NL == 2) l1.fetch(J.hp.d_w[1], h);
+    sl::pdl_wait();                 // weights are nobody's output; everything below may be
     stage_rows<T, R>(J, h, (long long)blockIdx.x * R, rinfo, xa, xb);
     l0.template mac<R>(xa, red);
     finish_layer<T, R>(J, h, 0, NL == 1 ? 128 : DH, decltype(l0)::KS, red, xa, xb);
@@ -197,6 +199,8 @@ __global__ void __launch_bounds__(HT) hash_kernel_generic(const HashArgs args) {
     const int hy = blockIdx.y;
     const HashJob& J = hy < args.heads0 ? args.job[0] : args.job[1];
     const int h = hy < args.heads0 ? hy : hy - args.heads0;
+    sl::pdl_trigger();
+    sl::pdl_wait();
     if ((long long)blockIdx.x >= J.row_tiles) return;
     const int tid = threadIdx.x;
     stage_rows<T, R>(J, h, (long long)blockIdx.x * R, rinfo, xa, xb);
@@ -289,8 +293,7 @@ int launch_T(const HashArgs& args, int total_heads, long long max_tiles, int R, 
         default: kern = pick_kernel<T, 8>(args); break;
     }
     SL_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    kern<<<grid, HT, smem, s>>>(args);
-    SL_CUDA_OK(cudaGetLastError());
+    SL_CUDA_OK(sl::launch_kernel(kern, grid, dim3(HT), smem, s, false, args));
     return SL_OK;
 }
 

@@ -198,6 +198,8 @@ __global__ void __launch_bounds__(NT, 1) scan_topk_kernel(const ScanArgs a) {
         a.dbg[blockIdx.x * 16 + (i)] = t_;                                                   \
     }
     SL_STAMP(0)
+    sl::pdl_trigger();
+    sl::pdl_wait();                 // codes, q codes and the workspace all come from earlier kernels
 
     // ---------------------------------------------------------------- pass A: scan + histogram
     if (a.mode == MODE_FROM_SCORES) {
@@ -681,13 +683,7 @@ int launch(const ScanArgs& a_in, const Plan& p, cudaStream_t s) {
     kernel_t kern = pick_kernel(a.G, a.KH);
     SL_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)p.smem));
     const unsigned grid = (unsigned)(a.B * p.ctas_per_b);
-    if (p.cooperative) {
-        void* params[] = {(void*)&a};
-        SL_CUDA_OK(cudaLaunchCooperativeKernel((const void*)kern, dim3(grid), dim3(NT), params, p.smem, s));
-    } else {
-        kern<<<grid, NT, p.smem, s>>>(a);
-        SL_CUDA_OK(cudaGetLastError());
-    }
+    SL_CUDA_OK(sl::launch_kernel(kern, dim3(grid), dim3(NT), p.smem, s, p.cooperative, a));
     return SL_OK;
 }
 
