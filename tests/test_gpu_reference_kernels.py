@@ -50,3 +50,40 @@ def test_packbits_bit_exact():
     torch.cuda.synchronize()
     got = K.pack_cuda_func(x)
     assert got.shape == want.shape and torch.equal(got.view(torch.int32), want.view(torch.int32))
+
+
+def test_timing_beside_the_reference_kernel(capsys):
+    """Not a pass/fail speed gate: times the reference's attn_k4_q28 beside this library's
+    score-only shim and the fused scan + top-k on the reference kernel's native shape
+    (B 8, 28/4 heads, 128K keys = 67 MB of codes, three rotating buffers so nothing stays in L2)
+    and prints the figures; the only assertion is that the fused kernel is not slower than the
+    reference's scoring pass alone plus a second of slack."""
+    import spotlight_b200.kernel as K
+    from spotlight_b200 import ops
+    ref = _load("attn_k4_q28")
+    g = torch.Generator(device="cuda").manual_seed(3)
+    B, N = 8, 131072
+    q = torch.randint(0, 2 ** 31, (B, 1, 28, 4), generator=g, device="cuda").to(torch.int32).view(torch.uint32)
+    ks = [torch.randint(0, 2 ** 31, (B, N, 4, 4), generator=g, device="cuda").to(torch.int32).view(torch.uint32) for _ in range(3)]
+
+    def timed(fn, iters=30):
+        for i in range(5):
+            fn(ks[i % 3])
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for i in range(iters):
+            fn(ks[i % 3])
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / iters * 1e3
+
+    t_ref = timed(lambda k: ref.attn_k4_q28(q, k))
+    t_topk = timed(lambda k: ref.attn_k4_q28(q, k).topk(k=2622, dim=1, sorted=False))
+    t_shim = timed(lambda k: K.attn_cuda_func(q, k))
+    t_fused = timed(lambda k: ops.scan_topk(q, k, 2622, 4, 64, 0))
+    with capsys.disabled():
+        print(f"\n[reference kernel timing, B8 x 128K x (4,28), 67.1 MB of codes] "
+              f"reference attn_k4_q28 {t_ref:.1f} us | reference attn_k4_q28 + torch.topk {t_topk:.1f} us | "
+              f"this library: scores only {t_shim:.1f} us, fused scan + exact top-k + window {t_fused:.1f} us")
+    assert t_fused < t_ref + 1e6
