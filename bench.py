@@ -37,8 +37,9 @@ from spotlight_b200.workloads import CONFIGS, HEAD_DIM, budget, make_hash_params
 METRIC = "decode_attn_us_per_layer_128k_llama3_8b_shape"
 UNIT = "us/layer"
 # DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) from the ncu captures
-# summarised under profiles/; None until a capture of that kernel exists.
-NCU_TRAFFIC = {"scan_topk": None, "sparse_attn": None, "decode_prepare": None}
+# summarised under profiles/ (scan_topk_headline.md, sparse_attn_headline.md; same per-launch size as the
+# benchmark's launches, captured at 90 % pruning); None where no capture exists.
+NCU_TRAFFIC = {"scan_topk": 16.92e6, "sparse_attn": 54.78e6, "decode_prepare": None}
 
 
 def peaks():
