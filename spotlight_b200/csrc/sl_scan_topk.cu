@@ -471,7 +471,53 @@ __global__ void __launch_bounds__(NT, 1) scan_topk_kernel(const ScanArgs a) {
             const int elo = max(lo, a.s_end) - t0, ehi = min(hi, a.r_start) - t0;
             const unsigned cgt = (unsigned)(0x7fff - tau) * 0x10001u, cge = (unsigned)(0x8000 - tau) * 0x10001u;
             int out_base = a.s_end + gt_before + min(eq_before, rM);
-            for (int g0 = elo & ~3; g0 < ehi; g0 += 128) {
+            // Nearly every task takes either all of its threshold ties or none (the quota runs out
+            // inside one task per head). Those go through a loop that handles 256 keys per trip:
+            // two independent groups, their per-lane counts packed into one word and ranked by a
+            // single warp scan.
+            const int eq_task = (int)s_task[(h * S + s) * 3 + 1];
+            const int mode = eq_before + eq_task <= rM ? 1 : (eq_before >= rM ? 0 : 2);
+            const unsigned cth = mode == 1 ? cge : cgt;          // ties count as selected, or do not
+            for (int g0 = elo & ~3; g0 < ehi && mode != 2; g0 += 256) {
+                unsigned sb2[2];
+#pragma unroll
+                for (int u = 0; u < 2; ++u) {
+                    const int tl = g0 + 128 * u + 4 * lane;
+                    uint2 x = make_uint2(0u, 0u);
+                    if (tl < ehi) x = *reinterpret_cast<const uint2*>(row + tl);
+                    unsigned vlo = 0x80008000u, vhi = 0x80008000u;
+                    if (tl < elo || tl + 3 >= ehi) {
+                        vlo = ((tl >= elo && tl < ehi) ? 0x8000u : 0u) | ((tl + 1 >= elo && tl + 1 < ehi) ? 0x80000000u : 0u);
+                        vhi = ((tl + 2 >= elo && tl + 2 < ehi) ? 0x8000u : 0u) | ((tl + 3 >= elo && tl + 3 < ehi) ? 0x80000000u : 0u);
+                    }
+                    const unsigned slo = (x.x + cth) & vlo, shi = (x.y + cth) & vhi;
+                    sb2[u] = ((slo >> 15) & 1u) | ((slo >> 30) & 2u) | ((shi >> 13) & 4u) | ((shi >> 28) & 8u);
+                }
+                const unsigned ns2 = (unsigned)__popc(sb2[0]) | ((unsigned)__popc(sb2[1]) << 16);
+                unsigned inc = ns2;
+#pragma unroll
+                for (int d = 1; d < 32; d <<= 1) {
+                    const unsigned t = __shfl_up_sync(0xffffffffu, inc, d);
+                    if (lane >= d) inc += t;
+                }
+                const unsigned tot = __shfl_sync(0xffffffffu, inc, 31);
+                const unsigned exc = inc - ns2;
+                const int ex0 = out_base + (int)(exc & 0xffffu), ex1 = out_base + (int)(tot & 0xffffu) + (int)(exc >> 16);
+#pragma unroll
+                for (int u = 0; u < 2; ++u) {
+                    const int tl = g0 + 128 * u + 4 * lane, ex = u ? ex1 : ex0;
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        if ((sb2[u] >> i) & 1u) {
+                            const int pos = ex + __popc(sb2[u] & ((1u << i) - 1u));
+                            if (pos < a.cap) oi[pos] = t0 + tl + i;
+                            else if (a.status) atomicExch(a.status, 2);
+                        }
+                    }
+                }
+                out_base += (int)(tot & 0xffffu) + (int)(tot >> 16);
+            }
+            for (int g0 = elo & ~3; g0 < ehi && mode == 2; g0 += 128) {
                 const int tl = g0 + 4 * lane;
                 uint2 x = make_uint2(0u, 0u);
                 if (tl < ehi) x = *reinterpret_cast<const uint2*>(row + tl);
