@@ -421,3 +421,28 @@ def test_lru_refuses_a_table_smaller_than_the_attended_set(ops):
     ops.lru_update(table, idx, cnt, kv, kv)
     assert int(table.status.item()) == 3
     assert int((table.slot2tok >= 0).sum()) == 0                      # nothing was touched
+
+
+def test_lru_with_host_backing_store(ops):
+    """The backing K/V store lives in pinned HOST memory (the offloaded variant of the reference,
+    spotlight/modifiers/cpu_cache.py:60-130): the kernel reads the missed rows straight from
+    it, and attention over the resident buffer equals attention over a device copy of the store."""
+    B, KH, QH, N, C, keep = 1, 4, 8, 4000, 600, 500
+    g = torch.Generator().manual_seed(8)
+    k_host = torch.randn((B, N, KH, 128), generator=g).to(torch.bfloat16).pin_memory()
+    v_host = torch.randn((B, N, KH, 128), generator=g).to(torch.bfloat16).pin_memory()
+    table = ops.LruTable(B, KH, N, C, torch.bfloat16, DEV)
+    kd, vd = k_host.to(DEV), v_host.to(DEV)
+    for step in range(3):
+        idx = torch.stack([torch.stack([torch.sort(torch.randperm(N, generator=g)[:keep]).values for _ in range(KH)])
+                           for _ in range(B)]).to(torch.int32).to(DEV)
+        if step == 2:
+            idx = prev                                                   # same set again: all hits, no host reads
+        prev = idx
+        cnt = torch.full((B, KH), keep, dtype=torch.int32, device=DEV)
+        slots = ops.lru_update(table, idx, cnt, None, None,
+                               backing_ptrs=(k_host.data_ptr(), v_host.data_ptr(), k_host.stride(0)))
+        q = torch.randn((B, QH, 128), generator=g).to(torch.bfloat16).to(DEV)
+        assert torch.equal(ops.sparse_attn_decode(q, kd, vd, idx, cnt), ops.sparse_attn_decode(q, table.k, table.v, slots, cnt))
+        assert int(table.status.item()) == 0
+    assert table.stats[..., 1].sum().item() == 0 and table.stats[..., 0].sum().item() == B * KH * keep
