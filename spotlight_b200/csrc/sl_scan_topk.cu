@@ -167,42 +167,55 @@ __global__ void __launch_bounds__(NT, 1) scan_topk_kernel(const ScanArgs a) {
             touch(a.cnt + b * KH);
             if (a.seg) touch(a.seg + (long long)b * a.ctas_per_b * KH);
         }
-        for (int i = tid; i < KH * G; i += NT) {
-            const int h = i / G, g = i % G;
-            const int qh = a.layout == SL_GQA_INTERLEAVED ? g * KH + h : h * G + g;
-            sq[i] = a.q[(long long)b * KH * G + qh];
-        }
-        for (int i = tid; i < KH * nbins; i += NT) shist[i] = 0;
-        __syncthreads();
         constexpr int PP = PT > 0 ? PT : 1;
         uint32_t M[PP][4], Mp[PP][4];
         if (PT > 0) {
-            // bit planes of cq and G - cq, built by ballot: lane = bit position, one warp per (head, word)
-            for (int hw = warp; hw < KH * 4; hw += NW) {
-                const int h = hw >> 2, w = hw & 3;
-                int cq = 0;
-                for (int g = 0; g < G; ++g) cq += (reinterpret_cast<const uint32_t*>(sq + h * G + g)[w] >> lane) & 1u;
-                const int cn = G - cq;
+            // Bit planes of cq (query heads of my kv head with the bit set) and of G - cq, built in
+            // registers: the G query codes come straight from global memory (all loads in flight at
+            // once) and are added bit-sliced, one ripple-carry step per plane -- no shared memory and
+            // no barrier before scoring can start.
+            constexpr int GMAX = PT > 0 ? (1 << PT) - 1 : 1;
+            const int hh = lane % KH;
+            uint4 qv[GMAX];
 #pragma unroll
-                for (int j = 0; j < PT; ++j) {
-                    const unsigned m = __ballot_sync(0xffffffffu, (cq >> j) & 1);
-                    const unsigned mp = __ballot_sync(0xffffffffu, (cn >> j) & 1);
-                    if (lane == 0) {
-                        s_planes[((h * 2 + 0) * PT + j) * 4 + w] = m;
-                        s_planes[((h * 2 + 1) * PT + j) * 4 + w] = mp;
-                    }
+            for (int g = 0; g < GMAX; ++g) {
+                if (g < G) {
+                    const int qh = a.layout == SL_GQA_INTERLEAVED ? g * KH + hh : hh * G + g;
+                    qv[g] = a.q[(long long)b * KH * G + qh];
                 }
             }
-            __syncthreads();
-            const int h = lane % KH;
+            for (int i = tid; i < KH * nbins; i += NT) shist[i] = 0;
 #pragma unroll
             for (int j = 0; j < PT; ++j)
 #pragma unroll
-                for (int w = 0; w < 4; ++w) {
-                    M[j][w] = s_planes[((h * 2 + 0) * PT + j) * 4 + w];
-                    Mp[j][w] = s_planes[((h * 2 + 1) * PT + j) * 4 + w];
+                for (int w = 0; w < 4; ++w) { M[j][w] = 0u; Mp[j][w] = 0u; }
+#pragma unroll
+            for (int g = 0; g < GMAX; ++g) {
+                if (g < G) {
+                    const uint32_t qw[4] = {qv[g].x, qv[g].y, qv[g].z, qv[g].w};
+#pragma unroll
+                    for (int w = 0; w < 4; ++w) {
+                        uint32_t c1 = qw[w], c0 = ~qw[w];
+#pragma unroll
+                        for (int j = 0; j < PT; ++j) {
+                            const uint32_t t1 = M[j][w] & c1, t0_ = Mp[j][w] & c0;
+                            M[j][w] ^= c1; Mp[j][w] ^= c0;
+                            c1 = t1; c0 = t0_;
+                        }
+                    }
                 }
+            }
+        } else {
+            for (int i = tid; i < KH * G; i += NT) {
+                const int h = i / G, g = i % G;
+                const int qh = a.layout == SL_GQA_INTERLEAVED ? g * KH + h : h * G + g;
+                sq[i] = a.q[(long long)b * KH * G + qh];
+            }
+            for (int i = tid; i < KH * nbins; i += NT) shist[i] = 0;
         }
+        __syncthreads();
+        SL_STAMP(11)
+        SL_STAMP(12)
         short* so = a.scores_out ? a.scores_out + ((long long)b * N + t0) * KH : nullptr;
         const int full = 128 * G;
         const int khs = 31 - __clz(KH);             // log2(KH) when KH is a power of two (PT > 0)
@@ -224,6 +237,7 @@ __global__ void __launch_bounds__(NT, 1) scan_topk_kernel(const ScanArgs a) {
                     }
                 }
             }
+            if (tile == 0) { SL_STAMP(13) }
             tile += NW;
 #pragma unroll
             for (int u = 0; u < U; ++u) {       // next tile's loads before the stores of this one

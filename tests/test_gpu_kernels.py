@@ -101,7 +101,10 @@ SCAN_CASES = [
     (2, 40000, 4, 28, 0, 4, 64, False),        # window only
     (1, 300, 4, 4, 1000, 4, 64, False),        # k >= N
     (1, 9000, 8, 40, 180, 100, 300, True),     # wide windows, G = 5
-    (1, 2048, 2, 24, 64, 4, 64, False),        # G = 12: generic group path
+    (1, 2048, 2, 24, 64, 4, 64, False),        # G = 12: four bit planes
+    (1, 1500, 2, 40, 64, 4, 64, True),         # G = 20: direct popcount path
+    (160, 700, 4, 8, 30, 4, 64, True),         # more batch rows than SMs: one CTA per row, no grid barrier
+    (150, 20000, 8, 8, 100, 4, 64, False),     # the same with scores spilled to global memory
 ]
 
 
