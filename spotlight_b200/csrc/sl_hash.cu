@@ -8,6 +8,11 @@
 // matmul (fp32 accumulate) -> round, + bias -> round, SiLU -> round, + residual -> round.
 #include "sl_common.cuh"
 
+namespace sl {
+int launch_hash_encode_mma(const void* x, long long xs_b, int B, long long T, int H, const sl_hash_params* hp,
+                           uint32_t* codes, long long cs_b, cudaStream_t s);
+}
+
 namespace {
 
 constexpr int HT = 256;      // threads per CTA
@@ -373,6 +378,12 @@ extern "C" int sl_hash_encode(const void* d_x, int64_t x_batch_stride, int dtype
                "sl_hash_encode: batch stride shorter than a batch row");
     if (int rc = check_params("sl_hash_encode", hash, dtype)) return rc;
     if (T == 0) return SL_OK;
+    if (dtype == SL_BF16 && (long long)B * T >= 64 && sl::aligned16(d_x) && x_batch_stride % 8 == 0) {
+        // many rows: the tensor-core kernel (weights resident in shared memory); 1 = shape not covered
+        const int rc = sl::launch_hash_encode_mma(d_x, x_batch_stride, B, T, H, hash, d_codes, code_batch_stride,
+                                                  static_cast<cudaStream_t>(stream));
+        if (rc <= 0) return rc;
+    }
     HashArgs args = {};
     HashJob& j = args.job[0];
     j.x = d_x; j.xs_b = x_batch_stride; j.T = T; j.H = H; j.B = B;
