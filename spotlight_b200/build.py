@@ -13,7 +13,7 @@ PKG = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(PKG, "csrc")
 LIB_DIR = os.path.join(PKG, "lib")
 LIB = os.path.join(LIB_DIR, "libspotlight_b200.so")
-SOURCES = ["sl_api.cu", "sl_pack.cu", "sl_scan_topk.cu", "sl_hash.cu", "sl_hash_mma.cu", "sl_attn.cu", "sl_attn_mma.cu", "sl_lru.cu"]
+SOURCES = ["sl_api.cu", "sl_pack.cu", "sl_scan_topk.cu", "sl_scan_fused.cu", "sl_hash.cu", "sl_hash_mma.cu", "sl_attn.cu", "sl_attn_mma.cu", "sl_lru.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-lineinfo", "-std=c++17",
               "-Xcompiler", "-fPIC"]
 
@@ -33,7 +33,7 @@ def _stale() -> bool:
     if not os.path.exists(LIB):
         return True
     t = os.path.getmtime(LIB)
-    deps = sources() + [os.path.join(CSRC, "sl_common.cuh"), os.path.join(CSRC, "sl_attn.cuh"), os.path.join(CSRC, "sl_mma.cuh"), os.path.join(CSRC, "sl_sliced.cuh"),
+    deps = sources() + [os.path.join(CSRC, "sl_common.cuh"), os.path.join(CSRC, "sl_attn.cuh"), os.path.join(CSRC, "sl_mma.cuh"), os.path.join(CSRC, "sl_sliced.cuh"), os.path.join(CSRC, "sl_scan.cuh"),
                         os.path.join(os.path.dirname(PKG), "include", "spotlight_b200.h")]
     return any(os.path.getmtime(d) > t for d in deps if os.path.exists(d))
 

@@ -30,6 +30,16 @@ bool pdl_enabled() {
 
 void set_pdl(int on) { g_pdl = on ? 1 : 0; }
 
+static int g_l2pf = -1;
+
+bool l2_prefetch_enabled() {
+    if (g_l2pf < 0) {
+        const char* e = getenv("SL_L2_PREFETCH");
+        g_l2pf = (e && e[0] == '0') ? 0 : 1;
+    }
+    return g_l2pf != 0;
+}
+
 int sm_count() {
     static int cached[64] = {0};
     int dev = 0;

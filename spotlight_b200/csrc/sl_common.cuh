@@ -18,6 +18,7 @@ char* err_buf();
 int fail(int code, const char* fmt, ...);
 int sm_count();          // SMs of the current device (cached per device)
 bool pdl_enabled();      // programmatic dependent launch on (default) / off (SL_PDL=0 or sl_set_pdl)
+bool l2_prefetch_enabled();   // the decode-step hash warms L2 with the code cache (SL_L2_PREFETCH=0: off)
 
 #define SL_CUDA_OK(expr)                                                                    \
     do {                                                                                    \

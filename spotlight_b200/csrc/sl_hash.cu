@@ -6,6 +6,8 @@
 // input rows ks, ks+KS, ... of W against columns [cg*CPT, cg*CPT+CPT), partial sums meet in
 // shared memory. Rounding points follow the reference's torch operators in the run dtype:
 // matmul (fp32 accumulate) -> round, + bias -> round, SiLU -> round, + residual -> round.
+#include <cstdlib>
+
 #include "sl_common.cuh"
 
 namespace sl {
@@ -31,7 +33,28 @@ struct HashJob {
 struct HashArgs {
     HashJob job[2];
     int heads0;
+    // Blocks with blockIdx.y >= heads do no hashing: they ask L2 for the code cache the scan of
+    // this decode step is about to stream (rows 0..pos-1 of every batch element), so the fetch
+    // from HBM overlaps this latency-bound kernel, which leaves most SMs idle.
+    int heads;
+    const unsigned char* pf_base; long long pf_bstride; long long pf_bytes; int pf_B;
 };
+
+constexpr int PF_PIECE = 2048;                     // bytes per bulk prefetch
+constexpr long long PF_MAX_BYTES = 64ll << 20;     // stay well inside the 126 MB L2
+
+__device__ __forceinline__ void prefetch_codes(const HashArgs& args) {
+    const long long per_b = (args.pf_bytes + PF_PIECE - 1) / PF_PIECE;
+    const long long total = per_b * args.pf_B;
+    const long long nthreads = (long long)(gridDim.y - args.heads) * gridDim.x * blockDim.x;
+    long long p = ((long long)(blockIdx.y - args.heads) * gridDim.x + blockIdx.x) * blockDim.x + threadIdx.x;
+    for (; p < total; p += nthreads) {
+        const long long b = p / per_b, off = (p % per_b) * PF_PIECE;
+        const unsigned size = (unsigned)min((long long)PF_PIECE, args.pf_bytes - off);
+        const unsigned char* ptr = args.pf_base + b * args.pf_bstride + off;
+        asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(ptr), "r"(size) : "memory");
+    }
+}
 
 // Offsets of the R rows of a tile, computed once (integer divisions are kept out of the loops).
 struct RowInfo {
@@ -176,6 +199,7 @@ __global__ void __launch_bounds__(HT) hash_kernel_fixed(const HashArgs args) {
     const HashJob& J = hy < args.heads0 ? args.job[0] : args.job[1];
     const int h = hy < args.heads0 ? hy : hy - args.heads0;
     sl::pdl_trigger();
+    if (hy >= args.heads) { prefetch_codes(args); sl::pdl_wait(); return; }
     if ((long long)blockIdx.x >= J.row_tiles) { sl::pdl_wait(); return; }
     Layer<T, 128, NL == 1 ? 128 : DH> l0;
     Layer<T, NL == 1 ? 128 : DH, 128> l1;
@@ -205,6 +229,7 @@ __global__ void __launch_bounds__(HT) hash_kernel_generic(const HashArgs args) {
     const HashJob& J = hy < args.heads0 ? args.job[0] : args.job[1];
     const int h = hy < args.heads0 ? hy : hy - args.heads0;
     sl::pdl_trigger();
+    if (hy >= args.heads) { prefetch_codes(args); sl::pdl_wait(); return; }
     sl::pdl_wait();
     if ((long long)blockIdx.x >= J.row_tiles) return;
     const int tid = threadIdx.x;
@@ -289,7 +314,12 @@ hash_kernel_t pick_kernel(const HashArgs& args) {
 
 template <typename T>
 int launch_T(const HashArgs& args, int total_heads, long long max_tiles, int R, size_t smem, cudaStream_t s) {
-    dim3 grid((unsigned)max_tiles, (unsigned)total_heads);
+    unsigned pf_rows = 0;
+    if (args.pf_base != nullptr && args.pf_bytes > 0) {     // fill the SMs the hash leaves idle
+        const long long busy = max_tiles * total_heads, sms = sl::sm_count();
+        pf_rows = (unsigned)std::max<long long>(1, (sms - busy) / max_tiles);
+    }
+    dim3 grid((unsigned)max_tiles, (unsigned)total_heads + pf_rows);
     hash_kernel_t kern = nullptr;
     switch (R) {
         case 1: kern = pick_kernel<T, 1>(args); break;
@@ -305,6 +335,7 @@ int launch_T(const HashArgs& args, int total_heads, long long max_tiles, int R, 
 int launch(const HashArgs& args, int dtype, int total_heads, long long rows_max, cudaStream_t s) {
     const int R = rows_max >= 8 ? 8 : rows_max >= 4 ? 4 : rows_max >= 2 ? 2 : 1;
     HashArgs a = args;
+    a.heads = total_heads;
     long long max_tiles = 0;
     for (int j = 0; j < 2; ++j) {
         const long long rows = (long long)a.job[j].B * a.job[j].T;
@@ -366,6 +397,13 @@ extern "C" int sl_decode_prepare(const void* d_q, const void* d_k, const void* d
         }
         k.cosr = d_cos; k.sinr = d_sin;
         total += KH;
+    }
+    if (d_code_cache != nullptr && KH > 0 && pos > 0 && sl::l2_prefetch_enabled() && sl::aligned16(d_code_cache) &&
+        code_batch_stride % 4 == 0) {
+        args.pf_base = reinterpret_cast<const unsigned char*>(d_code_cache);
+        args.pf_bstride = code_batch_stride * 4;
+        args.pf_bytes = std::min<long long>((long long)pos * KH * 16, PF_MAX_BYTES / B / 16 * 16);
+        args.pf_B = B;
     }
     return launch(args, dtype, total, B, static_cast<cudaStream_t>(stream));
 }

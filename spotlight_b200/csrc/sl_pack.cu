@@ -83,36 +83,14 @@ template <int P>
 __global__ void __launch_bounds__(256) scores_sliced_kernel(const uint32_t* __restrict__ q, const uint4* __restrict__ k,
                                                             int64_t k_bstride16, int16_t* __restrict__ out, int64_t N,
                                                             int KH, int G, int layout) {
-    __shared__ uint32_t planes[32 * 2 * 4 * 4];          // [KH][2][P][4], KH <= 32
-    const int b = blockIdx.y, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int QH = KH * G;
-    for (int hw = warp; hw < KH * 4; hw += 8) {
-        const int h = hw >> 2, w = hw & 3;
-        int cq = 0;
-        for (int g = 0; g < G; ++g) {
-            const int qh = layout == SL_GQA_INTERLEAVED ? g * KH + h : h * G + g;
-            cq += (q[((int64_t)b * QH + qh) * 4 + w] >> lane) & 1u;
-        }
-        unsigned m[P], mp[P];
-        build_planes<P>(cq, G, m, mp);
-        if (lane == 0) {
-#pragma unroll
-            for (int j = 0; j < P; ++j) {
-                planes[((h * 2 + 0) * P + j) * 4 + w] = m[j];
-                planes[((h * 2 + 1) * P + j) * 4 + w] = mp[j];
-            }
-        }
-    }
+    __shared__ __align__(16) uint32_t planes[32 * 2 * 4 * 4];          // [KH][2][P][4], KH <= 32
+    __shared__ __align__(16) int pbase[32 * 4];
+    const int b = blockIdx.y;
+    stage_planes<P>(q + (int64_t)b * KH * G * 4, KH, G, layout, planes, pbase, threadIdx.x >> 5, 8, threadIdx.x & 31);
     __syncthreads();
-    const int h = threadIdx.x % KH;
     uint32_t M[P][4], Mp[P][4];
-#pragma unroll
-    for (int j = 0; j < P; ++j)
-#pragma unroll
-        for (int w = 0; w < 4; ++w) {
-            M[j][w] = planes[((h * 2 + 0) * P + j) * 4 + w];
-            Mp[j][w] = planes[((h * 2 + 1) * P + j) * 4 + w];
-        }
+    const int base = load_planes<P>(planes, pbase, threadIdx.x % KH, M, Mp);
+    const int sh = sliced_shift(G);
     const int64_t total = N * KH, stride = (int64_t)gridDim.x * 256;
     const uint4* kb = k + (int64_t)b * k_bstride16;
     int16_t* ob = out + (int64_t)b * total;
@@ -123,7 +101,7 @@ __global__ void __launch_bounds__(256) scores_sliced_kernel(const uint32_t* __re
             if (i0 + u * stride < total) c[u] = sl::ld_stream_v4(kb + i0 + u * stride);
 #pragma unroll
         for (int u = 0; u < 4; ++u)
-            if (i0 + u * stride < total) ob[i0 + u * stride] = (int16_t)sliced_score<P>(c[u], M, Mp);
+            if (i0 + u * stride < total) ob[i0 + u * stride] = (int16_t)(base + (sliced_score<P>(c[u], M, Mp) << sh));
     }
 }
 
@@ -187,13 +165,15 @@ extern "C" int sl_hamming_scores(const uint32_t* d_q, const uint32_t* d_k, int64
     dim3 grid((unsigned)bx, (unsigned)B);
     const size_t smem = (size_t)QH * W * 4;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    if (W == 4 && KH <= 32 && 32 % KH == 0 && G <= 15) {
+    if (W == 4 && KH <= 32 && 32 % KH == 0 && sliced_planes(G) > 0) {
         const uint4* k16 = reinterpret_cast<const uint4*>(d_k);
         const int64_t kb16 = k_batch_stride / 4;
-        if (G == 1) scores_sliced_kernel<1><<<grid, 256, 0, s>>>(d_q, k16, kb16, d_out, N, KH, G, gqa_layout);
-        else if (G <= 3) scores_sliced_kernel<2><<<grid, 256, 0, s>>>(d_q, k16, kb16, d_out, N, KH, G, gqa_layout);
-        else if (G <= 7) scores_sliced_kernel<3><<<grid, 256, 0, s>>>(d_q, k16, kb16, d_out, N, KH, G, gqa_layout);
-        else scores_sliced_kernel<4><<<grid, 256, 0, s>>>(d_q, k16, kb16, d_out, N, KH, G, gqa_layout);
+        switch (sliced_planes(G)) {
+            case 1: scores_sliced_kernel<1><<<grid, 256, 0, s>>>(d_q, k16, kb16, d_out, N, KH, G, gqa_layout); break;
+            case 2: scores_sliced_kernel<2><<<grid, 256, 0, s>>>(d_q, k16, kb16, d_out, N, KH, G, gqa_layout); break;
+            case 3: scores_sliced_kernel<3><<<grid, 256, 0, s>>>(d_q, k16, kb16, d_out, N, KH, G, gqa_layout); break;
+            default: scores_sliced_kernel<4><<<grid, 256, 0, s>>>(d_q, k16, kb16, d_out, N, KH, G, gqa_layout); break;
+        }
         SL_CUDA_OK(cudaGetLastError());
         return SL_OK;
     }

@@ -1,0 +1,81 @@
+// Shared between the two scan + top-k translation units (sl_scan_topk.cu: every mode and shape;
+// sl_scan_fused.cu: the lean kernel of the decode step).
+#pragma once
+#include "sl_common.cuh"
+
+namespace slscan {
+
+constexpr int NT = 512;            // threads per CTA
+constexpr int NW = NT / 32;
+constexpr int U = 8;               // 16-byte loads in flight per thread
+constexpr int NCOPY = 4;           // copies of the global histograms in the workspace
+
+struct FusedArgs {
+    const uint4* q;            // [B,QH] codes
+    const uint4* k;            // code stream
+    long long k_bstride;       // batch stride in codes
+    int B, KH, G, layout, N;
+    int k_budget;
+    int s_end, r_start;        // forced ranges: [0,s_end) and [r_start,N)
+    int* idx;
+    int cap;
+    int* cnt;
+    short* scores_out;         // optional [B,N,KH]
+    unsigned* hist;            // fine global histogram [NCOPY,B,KH,nbins]
+    unsigned* chist;           // coarse global histogram [NCOPY,B,KH,NC]
+    unsigned long long* seg;   // [B,KH,ctas_per_b] flagged counts
+    unsigned* sync;            // [B,2]
+    int* status;
+    int ctas_per_b, chunk, nbins, S;
+    int cws;                   // log2 of the coarse bin width: NC = ((nbins - 1) >> cws) + 1 <= 32
+    int rowh;                  // row stride of the score rows in shared memory (halfwords)
+    int score_off;             // byte offset of the score rows in shared memory
+    unsigned long long* dbg;   // optional [grid][16] phase stamps (development aid)
+};
+
+bool fused_covers(int KH, int G);
+size_t fused_fixed_smem(int KH, int nbins, int S);
+int launch_fused(const FusedArgs& a, size_t smem, cudaStream_t s);
+extern unsigned long long* g_dbg_timing;   // set by sl_debug_scan_timing
+
+__device__ __forceinline__ void touch(const void* p) {   // warms the TLB for a page used later
+    unsigned v;
+    asm volatile("ld.global.cg.u32 %0, [%1];" : "=r"(v) : "l"(p));
+}
+__device__ __forceinline__ void st_relaxed_u64(unsigned long long* p, unsigned long long v) {
+    asm volatile("st.relaxed.gpu.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
+}
+__device__ __forceinline__ unsigned long long ld_relaxed_u64(const unsigned long long* p) {
+    unsigned long long v;
+    asm volatile("ld.relaxed.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+    return v;
+}
+// sum over this lane and the lanes above it
+__device__ __forceinline__ unsigned suffix_sum(unsigned v, int lane) {
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+        const unsigned t = __shfl_down_sync(0xffffffffu, v, d);
+        if (lane + d < 32) v += t;
+    }
+    return v;
+}
+// sum over this lane and the lanes below it
+__device__ __forceinline__ int prefix_sum(int v, int lane) {
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+        const int t = __shfl_up_sync(0xffffffffu, v, d);
+        if (lane >= d) v += t;
+    }
+    return v;
+}
+// bit 15 of each halfword of (vlo, vhi) says whether keys tl .. tl+3 lie inside [elo, ehi)
+static __device__ __noinline__ void edge_masks(int tl, int elo, int ehi, unsigned& vlo, unsigned& vhi) {
+    vlo = ((tl >= elo && tl < ehi) ? 0x8000u : 0u) | ((tl + 1 >= elo && tl + 1 < ehi) ? 0x80000000u : 0u);
+    vhi = ((tl + 2 >= elo && tl + 2 < ehi) ? 0x8000u : 0u) | ((tl + 3 >= elo && tl + 3 < ehi) ? 0x80000000u : 0u);
+}
+// bits 15 / 31 of lo and hi -> bits 0..3
+__device__ __forceinline__ unsigned flags4(unsigned lo, unsigned hi) {
+    return ((lo >> 15) & 1u) | ((lo >> 30) & 2u) | ((hi >> 13) & 4u) | ((hi >> 28) & 8u);
+}
+
+}  // namespace slscan

@@ -13,7 +13,10 @@
 //   pass C  every CTA prefix-sums the counts of the chunks before it and writes its selected
 //           keys at their final position: output is ascending, ties go to the lowest index.
 // Algorithmic DRAM traffic is the code stream (16 B per key and kv head) plus the index list.
+#include <cstdlib>
+
 #include "sl_common.cuh"
+#include "sl_scan.cuh"
 #include "sl_sliced.cuh"
 
 namespace {
@@ -53,7 +56,7 @@ struct ScanArgs {
     unsigned long long* dbg;   // optional [grid][16] phase timestamps (ns)
 };
 
-static unsigned long long* g_dbg_timing = nullptr;   // set by sl_debug_scan_timing (development aid)
+
 
 struct Plan {
     int ctas_per_b, chunk, nbins, S;
@@ -65,7 +68,7 @@ inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
 inline size_t fixed_smem(int KH, int G, int nbins, int S) {
     return align_up((size_t)KH * G * 16, 16) + (size_t)KH * nbins * 4 + (size_t)KH * 2 * 4 +
-           (size_t)KH * S * 3 * 4 + (size_t)KH * 4 * 4 + (size_t)KH * 32 * 4 + 64;
+           (size_t)KH * S * 3 * 4 + (size_t)KH * 4 * 4 + (size_t)KH * 32 * 4 + (size_t)KH * 4 * 4 + 64;
 }
 
 Plan make_plan(int B, long long N, int KH, int G, bool scores_in_global, int nbins = 0) {
@@ -112,9 +115,10 @@ __global__ void __launch_bounds__(NT, 1) scan_topk_kernel(const ScanArgs a) {
     int* s_r = s_tau + KH;                                                            // [KH]
     unsigned* s_task = reinterpret_cast<unsigned*>(s_r + KH);                         // [KH][S][3]
     int* s_base = reinterpret_cast<int*>(s_task + (size_t)KH * S * 3);                // [KH][4]
-    uint32_t* s_planes = reinterpret_cast<uint32_t*>(s_base + KH * 4);                // [KH][2][4][4]
-    unsigned short* sscores = reinterpret_cast<unsigned short*>(
-        smem_raw + (((size_t)((unsigned char*)(s_planes + KH * 32) - smem_raw) + 15) & ~(size_t)15));
+    uint32_t* s_planes = reinterpret_cast<uint32_t*>(                                 // [KH][2][P][4], 16-byte aligned
+        smem_raw + (((size_t)((unsigned char*)(s_base + KH * 4) - smem_raw) + 15) & ~(size_t)15));
+    int* s_pbase = reinterpret_cast<int*>(s_planes + KH * 32);                        // [KH][4]
+    unsigned short* sscores = reinterpret_cast<unsigned short*>(s_pbase + KH * 4);
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int b = blockIdx.x / a.ctas_per_b, c = blockIdx.x % a.ctas_per_b;
@@ -155,6 +159,9 @@ __global__ void __launch_bounds__(NT, 1) scan_topk_kernel(const ScanArgs a) {
     } else if (a.mode != MODE_EMIT_ONLY) {
         // the first tile's loads are in flight while the query codes are staged
         const uint4* base = a.k + (long long)b * a.k_bstride + (long long)t0 * KH;
+        const uint32_t* qb = reinterpret_cast<const uint32_t*>(a.q + (long long)b * KH * G);
+        PlaneWords pw = {{0u, 0u}};
+        if (PT > 0) pw = planes_issue(qb, KH, G, a.layout, warp, NW, lane);   // ahead of the stream's loads
         uint4 cd[U];
         int tile = warp;
 #pragma unroll
@@ -169,53 +176,25 @@ __global__ void __launch_bounds__(NT, 1) scan_topk_kernel(const ScanArgs a) {
         }
         constexpr int PP = PT > 0 ? PT : 1;
         uint32_t M[PP][4], Mp[PP][4];
+        int sbase = 0;
+        const int ssh = sliced_shift(G);
+        // Planes of the group's query codes (one warp per (head, word), straight from global
+        // memory) while the other threads clear the histogram; one barrier, then every lane
+        // copies the planes of its own head into registers.
         if (PT > 0) {
-            // Bit planes of cq (query heads of my kv head with the bit set) and of G - cq, built in
-            // registers: the G query codes come straight from global memory (all loads in flight at
-            // once) and are added bit-sliced, one ripple-carry step per plane -- no shared memory and
-            // no barrier before scoring can start.
-            constexpr int GMAX = PT > 0 ? (1 << PT) - 1 : 1;
-            const int hh = lane % KH;
-            uint4 qv[GMAX];
-#pragma unroll
-            for (int g = 0; g < GMAX; ++g) {
-                if (g < G) {
-                    const int qh = a.layout == SL_GQA_INTERLEAVED ? g * KH + hh : hh * G + g;
-                    qv[g] = a.q[(long long)b * KH * G + qh];
-                }
-            }
-            for (int i = tid; i < KH * nbins; i += NT) shist[i] = 0;
-#pragma unroll
-            for (int j = 0; j < PT; ++j)
-#pragma unroll
-                for (int w = 0; w < 4; ++w) { M[j][w] = 0u; Mp[j][w] = 0u; }
-#pragma unroll
-            for (int g = 0; g < GMAX; ++g) {
-                if (g < G) {
-                    const uint32_t qw[4] = {qv[g].x, qv[g].y, qv[g].z, qv[g].w};
-#pragma unroll
-                    for (int w = 0; w < 4; ++w) {
-                        uint32_t c1 = qw[w], c0 = ~qw[w];
-#pragma unroll
-                        for (int j = 0; j < PT; ++j) {
-                            const uint32_t t1 = M[j][w] & c1, t0_ = Mp[j][w] & c0;
-                            M[j][w] ^= c1; Mp[j][w] ^= c0;
-                            c1 = t1; c0 = t0_;
-                        }
-                    }
-                }
-            }
+            planes_finish<PP>(pw, KH, G, s_planes, s_pbase, warp, NW, lane);
+            stage_planes<PP>(qb, KH, G, a.layout, s_planes, s_pbase, warp, NW, lane, 1);     // KH > 8
         } else {
             for (int i = tid; i < KH * G; i += NT) {
                 const int h = i / G, g = i % G;
                 const int qh = a.layout == SL_GQA_INTERLEAVED ? g * KH + h : h * G + g;
                 sq[i] = a.q[(long long)b * KH * G + qh];
             }
-            for (int i = tid; i < KH * nbins; i += NT) shist[i] = 0;
         }
+        for (int i = tid; i < KH * nbins; i += NT) shist[i] = 0;
         __syncthreads();
+        if (PT > 0) sbase = load_planes<PP>(s_planes, s_pbase, lane % KH, M, Mp);
         SL_STAMP(11)
-        SL_STAMP(12)
         short* so = a.scores_out ? a.scores_out + ((long long)b * N + t0) * KH : nullptr;
         const int full = 128 * G;
         const int khs = 31 - __clz(KH);             // log2(KH) when KH is a power of two (PT > 0)
@@ -228,7 +207,7 @@ __global__ void __launch_bounds__(NT, 1) scan_topk_kernel(const ScanArgs a) {
                 sv[u] = 0;
                 if (i < ncodes) {
                     if (PT > 0) {
-                        sv[u] = sliced_score<PP>(cd[u], M, Mp);
+                        sv[u] = sbase + (sliced_score<PP>(cd[u], M, Mp) << ssh);
                     } else {
                         const uint4* qh = sq + (i % KH) * G;
                         int diff = 0;
@@ -644,15 +623,25 @@ __global__ void __launch_bounds__(NT, 1) scan_topk_kernel(const ScanArgs a) {
 typedef void (*kernel_t)(const ScanArgs);
 
 kernel_t pick_kernel(int G, int KH) {
-    if (32 % KH != 0 || G > 15) return scan_topk_kernel<0>;      // lanes do not keep one head: direct popcounts
-    if (G == 1) return scan_topk_kernel<1>;
-    if (G <= 3) return scan_topk_kernel<2>;
-    if (G <= 7) return scan_topk_kernel<3>;
-    return scan_topk_kernel<4>;
+    if (32 % KH != 0) return scan_topk_kernel<0>;      // lanes do not keep one head: direct popcounts
+    switch (sliced_planes(G)) {
+        case 1: return scan_topk_kernel<1>;
+        case 2: return scan_topk_kernel<2>;
+        case 3: return scan_topk_kernel<3>;
+        case 4: return scan_topk_kernel<4>;
+        default: return scan_topk_kernel<0>;
+    }
+}
+
+// log2 of the coarse bin width of the lean fused kernel: at least 32 fine bins, at most 32 coarse bins
+int coarse_shift(int nbins) {
+    int s = 5;
+    while (((nbins - 1) >> s) + 1 > 32) ++s;
+    return s;
 }
 
 struct WsLayout {
-    size_t sync_off, hist_off, seg_off, score_off, total;
+    size_t sync_off, hist_off, chist_off, seg_off, score_off, total;
 };
 
 WsLayout ws_layout(int B, long long N, int KH, int G, bool with_hist, bool spill, int nbins = 0) {
@@ -661,6 +650,7 @@ WsLayout ws_layout(int B, long long N, int KH, int G, bool with_hist, bool spill
     size_t off = 0;
     w.sync_off = off; off = align_up(off + (size_t)B * 2 * 4, 256);
     w.hist_off = off; if (with_hist) off = align_up(off + (size_t)NCOPY * B * KH * (nbins > 0 ? nbins : 128 * G + 1) * 4, 256);
+    w.chist_off = off; if (with_hist) off = align_up(off + (size_t)NCOPY * B * KH * 32 * 4, 256);
     w.seg_off = off; off = align_up(off + (size_t)B * max_cpb * KH * 16, 256);
     w.score_off = off; if (spill) off = align_up(off + (size_t)B * N * KH * 2, 256);
     w.total = off;
@@ -680,7 +670,7 @@ int check_common(const char* fn, int B, long long N, int KH, int QH) {
 
 int launch(const ScanArgs& a_in, const Plan& p, cudaStream_t s) {
     ScanArgs a = a_in;
-    a.dbg = g_dbg_timing;
+    a.dbg = slscan::g_dbg_timing;
     kernel_t kern = pick_kernel(a.G, a.KH);
     SL_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)p.smem));
     const unsigned grid = (unsigned)(a.B * p.ctas_per_b);
@@ -689,6 +679,8 @@ int launch(const ScanArgs& a_in, const Plan& p, cudaStream_t s) {
 }
 
 }  // namespace
+
+namespace slscan { unsigned long long* g_dbg_timing = nullptr; }
 
 extern "C" size_t sl_scan_topk_workspace_bytes(int B, int64_t N, int KH, int QH) {
     if (B <= 0 || N < 0 || KH <= 0 || QH <= 0 || QH % KH) return 0;
@@ -724,6 +716,34 @@ extern "C" int sl_scan_topk(const uint32_t* d_q_codes, const uint32_t* d_k_codes
                w.total);
     SL_REQUIRE(sl::aligned16(d_workspace), SL_EALIGN, "sl_scan_topk: workspace not 16-byte aligned");
     unsigned char* ws = static_cast<unsigned char*>(d_workspace);
+    static const bool lean_on = [] { const char* e = getenv("SL_SCAN_LEAN"); return !(e && e[0] == '0'); }();
+    if (lean_on && p.cooperative && !p.spill && slscan::fused_covers(KH, G) && p.chunk < (1 << 21) &&
+        (long long)NCOPY * B * KH * p.nbins < (1ll << 30)) {
+        // the common decode shape: the lean kernel (same results, a fraction of the instructions)
+        slscan::FusedArgs f = {};
+        f.q = reinterpret_cast<const uint4*>(d_q_codes);
+        f.k = reinterpret_cast<const uint4*>(d_k_codes);
+        f.k_bstride = k_batch_stride / 4;
+        f.B = B; f.KH = KH; f.G = G; f.layout = gqa_layout; f.N = (int)N;
+        f.k_budget = k;
+        f.s_end = (int)std::min<int64_t>(sink, N);
+        f.r_start = (int)std::max<int64_t>(f.s_end, N - recent);
+        f.idx = d_idx; f.cap = idx_capacity; f.cnt = d_cnt;
+        f.scores_out = d_scores_out;
+        f.hist = reinterpret_cast<unsigned*>(ws + w.hist_off);
+        f.chist = reinterpret_cast<unsigned*>(ws + w.chist_off);
+        f.seg = reinterpret_cast<unsigned long long*>(ws + w.seg_off);
+        f.sync = reinterpret_cast<unsigned*>(ws + w.sync_off);
+        f.status = d_status;
+        f.ctas_per_b = p.ctas_per_b; f.chunk = p.chunk; f.nbins = p.nbins; f.S = p.S;
+        f.cws = coarse_shift(p.nbins);
+        const int roww = (p.chunk >> 1) + ((4 - (p.chunk >> 1)) & 31);
+        f.rowh = 2 * roww;
+        const size_t score_off = align_up(slscan::fused_fixed_smem(KH, p.nbins, p.S), 16);
+        f.score_off = (int)score_off;
+        const size_t smem = score_off + (size_t)(p.chunk + 64) * KH * 2;
+        if (smem <= (size_t)SMEM_BUDGET + 16 * 1024) return slscan::launch_fused(f, smem, s);
+    }
     ScanArgs a = {};
     a.q = reinterpret_cast<const uint4*>(d_q_codes);
     a.k = reinterpret_cast<const uint4*>(d_k_codes);
@@ -861,4 +881,4 @@ extern "C" int sl_topk_from_scores(const int16_t* d_scores, int B, int64_t N, in
 
 // Development aid, not part of the public header: when set to a device buffer of grid*16 uint64,
 // thread 0 of every CTA of the scan kernels stores %globaltimer at its phase boundaries.
-extern "C" void sl_debug_scan_timing(void* d_buf) { g_dbg_timing = static_cast<unsigned long long*>(d_buf); }
+extern "C" void sl_debug_scan_timing(void* d_buf) { slscan::g_dbg_timing = static_cast<unsigned long long*>(d_buf); }
