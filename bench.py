@@ -63,9 +63,14 @@ class ClockSampler:
     def __enter__(self):
         try:
             self.p = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
-                                       "-lms", "100", "-i", str(self.idx)], stdout=self.f, stderr=subprocess.DEVNULL)
+                                       "-lms", "20", "-i", str(self.idx)], stdout=self.f, stderr=subprocess.DEVNULL)
         except OSError:
             self.p = None
+        # nvidia-smi needs a few hundred ms to start: wait for its first line so that the samples
+        # that follow fall inside the timed region
+        t_end = time.time() + 3.0
+        while self.p is not None and time.time() < t_end and os.path.getsize(self.f.name) == 0:
+            time.sleep(0.02)
         return self
 
     def __exit__(self, *a):
@@ -365,6 +370,113 @@ def run_ours(args, cfg):
         dist.destroy_process_group()
 
 
+def run_sharded(args, cfg):
+    """Sequence-sharded layer-step (config 4: 1M-token context): every rank owns n/world keys of
+    `layers` rotating layers, a step is one layer-step through sharded_decode_attention (local scan +
+    histogram, all-gather, emission, local attention, all-gather of (o, lse), merge). Launched under
+    torchrun; with one rank it times the unsharded kernels on the same global shape."""
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the retrieval path has no CPU fallback")
+    torch.cuda.set_device(local)
+    device = torch.device("cuda", local)
+    import torch.distributed as dist
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+    from spotlight_b200 import ops
+    from spotlight_b200.sharded import shard_bounds, sharded_decode_attention
+    from spotlight_b200.workloads import torch_dtype
+    dt = torch_dtype(cfg.dtype)
+    n, B, QH, KH = cfg.context, cfg.batch, cfg.q_heads, cfg.kv_heads
+    L = max(2, min(args.layers or 4, 8))                       # rotating layers: working set >> L2
+    lo, hi = shard_bounds(n, world, rank)
+    nl = hi - lo
+    kb = budget(n, cfg.mask_out, cfg.min_remain)
+    g = torch.Generator(device=device).manual_seed(cfg.seed + rank)
+    codes, ks, vs = [], [], []
+    for _ in range(L):
+        codes.append(torch.randint(0, 2 ** 31, (B, nl, KH, 4), generator=g, device=device, dtype=torch.int64).to(torch.uint32))
+        ks.append(torch.randn((B, nl, KH, HEAD_DIM), generator=g, device=device).to(dt))
+        vs.append(torch.randn((B, nl, KH, HEAD_DIM), generator=g, device=device).to(dt))
+    gq = torch.Generator().manual_seed(cfg.seed)                 # the query is the same on every rank
+    q_rot = torch.randn((B, QH, HEAD_DIM), generator=gq).to(dt).to(device)
+    q_codes = torch.randint(0, 2 ** 31, (B, QH, 4), generator=gq, dtype=torch.int64).to(torch.uint32).to(device)
+
+    def layer_step(layer):
+        if world > 1:
+            return sharded_decode_attention(q_rot, q_codes, codes[layer], ks[layer], vs[layer], lo, n, kb,
+                                            cfg.sink, cfg.recent, ops.GQA_BLOCKED)
+        idx, cnt = ops.scan_topk(q_codes, codes[layer], kb, cfg.sink, cfg.recent, ops.GQA_BLOCKED)
+        return ops.sparse_attn_decode(q_rot, ks[layer], vs[layer], idx, cnt, ops.GQA_BLOCKED)
+
+    def step():
+        out = None
+        for layer in range(L):
+            out = layer_step(layer)
+        return out
+
+    use_graph = not args.no_graph
+    graph = None
+    for _ in range(2):
+        step()
+    torch.cuda.synchronize(device)
+    if use_graph:
+        try:
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                out = step()
+        except RuntimeError as e:
+            print(f"# graph capture failed ({e}); timing eager launches", file=sys.stderr)
+            graph, use_graph = None, False
+            torch.cuda.synchronize(device)
+
+    class Runner:
+        def replay(self):
+            if graph is not None:
+                graph.replay()
+            else:
+                step()
+
+    with ClockSampler(local) as clocks:
+        ms_step = time_graph(Runner(), args.steps, args.warmup, device, dist if world > 1 else None)
+    ops.check_status(device)
+    clk = clocks.summary()
+    if world > 1:
+        t = torch.tensor([ms_step], device=device, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms_step = float(t.item())
+    if rank == 0:
+        us_layer = ms_step * 1e3 / L
+        peak, peak_kind = peaks()
+        by = B * n * KH * 16 + kb * B * KH * HEAD_DIM * 2 * 2            # codes + attended K/V rows, whole job
+        line = {
+            "metric": "decode_attn_us_per_layer_seq_sharded", "value": us_layer, "unit": UNIT, "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": False,
+            "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": f"{cfg.name}: sequence-sharded decode attention, batch {B}, {QH}/{KH} heads, context {n} "
+                                   f"over {world} rank(s), mask_out {cfg.mask_out}, sink {cfg.sink}, recent {cfg.recent}",
+                       "context": n, "keys_per_rank": nl, "rotating_layers": L,
+                       "l2": "inputs larger than L2 (layers rotate)"},
+            "tokens_per_s": B / (us_layer * 1e-6 * 48) if cfg.name == "cfg4" else None,
+            "cuda_graph": use_graph,
+            "path": {"algorithmic_bytes_per_layer": by, "gbs": by / (us_layer * 1e-6) / 1e9,
+                     "frac_of_aggregate_peak": by / (us_layer * 1e-6) / 1e9 / (peak * world), "peak_kind": peak_kind},
+            "clocks": clk,
+        }
+        print(json.dumps(line), flush=True)
+    # A captured graph holds NCCL work: release it before the process group goes away, and leave
+    # without the group's teardown (a hang there would only cost time, the numbers are out).
+    graph = None
+    torch.cuda.synchronize(device)
+    if world > 1:
+        dist.barrier()
+        torch.cuda.synchronize(device)
+        sys.stdout.flush()
+        os._exit(0)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -378,6 +490,8 @@ def main():
     ap.add_argument("--mask-out", type=float, default=None)
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--sharded", action="store_true",
+                    help="sequence-sharded layer-step across the ranks of a torchrun launch (config 4)")
     args = ap.parse_args()
     if args.impl == "ours":
         args.warmup = max(args.warmup, 3)
@@ -389,6 +503,8 @@ def main():
         cfg = dataclasses.replace(cfg, **over)
     if args.impl == "reference":
         run_reference(args, cfg)
+    elif args.sharded:
+        run_sharded(args, cfg)
     else:
         run_ours(args, cfg)
 

@@ -9,6 +9,7 @@
 #include <cstdlib>
 
 #include "sl_common.cuh"
+#include "sl_mma.cuh"
 
 namespace sl {
 int launch_hash_encode_mma(const void* x, long long xs_b, int B, long long T, int H, const sl_hash_params* hp,
@@ -143,29 +144,37 @@ __device__ __forceinline__ void sign_pack(const HashJob& J, const RowInfo* rinfo
     }
 }
 
-// One layer with compile-time widths: thread (ks, cg) owns columns [cg*CPT, +CPT) and the input
-// rows ks, ks + KS, ...; its NLOAD 16-byte weight loads are issued by `fetch` long before `mac`.
+// One layer with compile-time widths. The head's weight matrix is copied into shared memory by
+// 16-byte cp.async (issued before the kernel waits for its predecessor); thread (ks, cg) then owns
+// columns [cg*CPT, +CPT) and the input rows ks, ks + KS, ... and walks them in a ROLLED loop: the
+// kernel runs once per decode step with a cold instruction cache, so its cost is the number of
+// distinct instructions it executes, and an unrolled multiply-accumulate over register-held
+// weights cost more in instruction fetch than in arithmetic. The order of the additions is the
+// same as before (k ascending per thread, then the k-splits pairwise in finish_layer).
 template <typename T, int DIN, int DOUT>
 struct Layer {
     static constexpr int CPT = 16 / sizeof(T), NCG = DOUT / CPT, KS = HT / NCG, NLOAD = DIN / KS;
-    uint4 w[NLOAD];
-    __device__ __forceinline__ void fetch(const void* wbase, int h) {
-        const T* W = reinterpret_cast<const T*>(wbase) + (long long)h * DIN * DOUT;
-        const int cg = threadIdx.x % NCG, ks = threadIdx.x / NCG;
-#pragma unroll
-        for (int j = 0; j < NLOAD; ++j) w[j] = sl::ld_gather_v4(W + (ks + j * KS) * DOUT + cg * CPT);
+    static constexpr int BYTES = DIN * DOUT * (int)sizeof(T);
+    static __device__ __forceinline__ void fetch(const void* wbase, int h, unsigned char* wsm) {
+        const unsigned char* W = reinterpret_cast<const unsigned char*>(wbase) + (size_t)h * BYTES;
+        const unsigned dst = (unsigned)__cvta_generic_to_shared(wsm);
+#pragma unroll 4
+        for (int i = threadIdx.x * 16; i < BYTES; i += HT * 16) cp_async16(dst + i, W + i);
+        cp_async_commit();
     }
     template <int R>
-    __device__ __forceinline__ void mac(const float* xin, float* red) {
+    static __device__ __forceinline__ void mac(const unsigned char* wsm, const float* xin, float* red) {
         const int cg = threadIdx.x % NCG, ks = threadIdx.x / NCG;
         float acc[R][CPT];
 #pragma unroll
         for (int r = 0; r < R; ++r)
 #pragma unroll
             for (int c = 0; c < CPT; ++c) acc[r][c] = 0.0f;
-#pragma unroll
+        const unsigned char* wp = wsm + ((size_t)ks * DOUT + cg * CPT) * sizeof(T);
+#pragma unroll 2
         for (int j = 0; j < NLOAD; ++j) {
-            const T* wv = reinterpret_cast<const T*>(&w[j]);
+            const uint4 wq = *reinterpret_cast<const uint4*>(wp + (size_t)j * KS * DOUT * sizeof(T));
+            const T* wv = reinterpret_cast<const T*>(&wq);
             float wf[CPT];
 #pragma unroll
             for (int c = 0; c < CPT; ++c) wf[c] = sl::VT<T>::to_f(wv[c]);
@@ -187,13 +196,17 @@ struct Layer {
 };
 
 // Fixed shapes 128 -> 128 (NL = 1) and 128 -> DH -> 128 (NL = 2) in 2-byte types: every weight
-// load of the whole MLP is in flight before the input rows are even staged.
+// copy of the whole MLP is in flight before the input rows are even staged.
 template <typename T, int R, int NL, int DH>
 __global__ void __launch_bounds__(HT) hash_kernel_fixed(const HashArgs args) {
+    using L0 = Layer<T, 128, NL == 1 ? 128 : DH>;
+    using L1 = Layer<T, NL == 1 ? 128 : DH, 128>;
     extern __shared__ __align__(16) unsigned char smem_raw[];
     float* xa = reinterpret_cast<float*>(smem_raw);            // [R][MAXD]
     float* xb = xa + R * MAXD;                                 // [R][MAXD]
     float* red = xb + R * MAXD;                                // [KS][R][dout]
+    unsigned char* w0 = reinterpret_cast<unsigned char*>(red + HT * R * 8);
+    unsigned char* w1 = w0 + L0::BYTES;
     __shared__ RowInfo rinfo[R];
     const int hy = blockIdx.y;
     const HashJob& J = hy < args.heads0 ? args.job[0] : args.job[1];
@@ -201,17 +214,19 @@ __global__ void __launch_bounds__(HT) hash_kernel_fixed(const HashArgs args) {
     sl::pdl_trigger();
     if (hy >= args.heads) { prefetch_codes(args); sl::pdl_wait(); return; }
     if ((long long)blockIdx.x >= J.row_tiles) { sl::pdl_wait(); return; }
-    Layer<T, 128, NL == 1 ? 128 : DH> l0;
-    Layer<T, NL == 1 ? 128 : DH, 128> l1;
-    l0.fetch(J.hp.d_w[0], h);
-    if (NL == 2) l1.fetch(J.hp.d_w[1], h);
+    L0::fetch(J.hp.d_w[0], h, w0);
+    if (NL == 2) L1::fetch(J.hp.d_w[1], h, w1);
     sl::pdl_wait();                 // weights are nobody's output; everything below may be
     stage_rows<T, R>(J, h, (long long)blockIdx.x * R, rinfo, xa, xb);
-    l0.template mac<R>(xa, red);
-    finish_layer<T, R>(J, h, 0, NL == 1 ? 128 : DH, decltype(l0)::KS, red, xa, xb);
+    if (NL == 2) cp_async_wait<1>(); else cp_async_wait<0>();
+    __syncthreads();
+    L0::template mac<R>(w0, xa, red);
+    finish_layer<T, R>(J, h, 0, NL == 1 ? 128 : DH, L0::KS, red, xa, xb);
     if (NL == 2) {
-        l1.template mac<R>(xb, red);
-        finish_layer<T, R>(J, h, 1, 128, decltype(l1)::KS, red, xb, xa);
+        cp_async_wait<0>();
+        __syncthreads();
+        L1::template mac<R>(w1, xb, red);
+        finish_layer<T, R>(J, h, 1, 128, L1::KS, red, xb, xa);
     }
     sign_pack<R>(J, rinfo, NL == 2 ? xa : xb);
 }
@@ -286,16 +301,16 @@ int check_params(const char* fn, const sl_hash_params* p, int dtype) {
     return SL_OK;
 }
 
-size_t hash_smem(const sl_hash_params* a, const sl_hash_params* b, int R) {
+size_t hash_smem(int R) {
     // red = KS*R*dout floats with KS*ncg = HT  =>  HT*R*CPT floats at most; CPT <= 8
-    (void)a; (void)b;
     return (size_t)2 * R * MAXD * 4 + (size_t)HT * R * 8 * 4;
 }
 
 typedef void (*hash_kernel_t)(const HashArgs);
 
 template <typename T, int R>
-hash_kernel_t pick_kernel(const HashArgs& args) {
+hash_kernel_t pick_kernel(const HashArgs& args, size_t* weight_smem) {
+    *weight_smem = 0;
     // the fixed-shape kernels need both jobs to share one of the shapes below
     const sl_hash_params& p = args.job[0].hp;
     bool same = true;
@@ -304,16 +319,17 @@ hash_kernel_t pick_kernel(const HashArgs& args) {
         same = q.n_layers == p.n_layers;
         for (int i = 0; same && i <= p.n_layers; ++i) same = q.dims[i] == p.dims[i];
     }
-    if (sizeof(T) == 2 && same) {
-        if (p.n_layers == 1) return hash_kernel_fixed<T, R, 1, 128>;
-        if (p.n_layers == 2 && p.dims[1] == 128) return hash_kernel_fixed<T, R, 2, 128>;
-        if (p.n_layers == 2 && p.dims[1] == 256) return hash_kernel_fixed<T, R, 2, 256>;
+    if (sizeof(T) == 2 && same) {      // the head's weights live in shared memory
+        if (p.n_layers == 1) { *weight_smem = 128 * 128 * 2; return hash_kernel_fixed<T, R, 1, 128>; }
+        if (p.n_layers == 2 && p.dims[1] == 128) { *weight_smem = 2 * 128 * 128 * 2; return hash_kernel_fixed<T, R, 2, 128>; }
+        if (p.n_layers == 2 && p.dims[1] == 256) { *weight_smem = 2 * 128 * 256 * 2; return hash_kernel_fixed<T, R, 2, 256>; }
     }
     return hash_kernel_generic<T, R>;
 }
 
 template <typename T>
 int launch_T(const HashArgs& args, int total_heads, long long max_tiles, int R, size_t smem, cudaStream_t s) {
+    size_t wsm = 0;
     unsigned pf_rows = 0;
     if (args.pf_base != nullptr && args.pf_bytes > 0) {     // fill the SMs the hash leaves idle
         const long long busy = max_tiles * total_heads, sms = sl::sm_count();
@@ -322,11 +338,12 @@ int launch_T(const HashArgs& args, int total_heads, long long max_tiles, int R, 
     dim3 grid((unsigned)max_tiles, (unsigned)total_heads + pf_rows);
     hash_kernel_t kern = nullptr;
     switch (R) {
-        case 1: kern = pick_kernel<T, 1>(args); break;
-        case 2: kern = pick_kernel<T, 2>(args); break;
-        case 4: kern = pick_kernel<T, 4>(args); break;
-        default: kern = pick_kernel<T, 8>(args); break;
+        case 1: kern = pick_kernel<T, 1>(args, &wsm); break;
+        case 2: kern = pick_kernel<T, 2>(args, &wsm); break;
+        case 4: kern = pick_kernel<T, 4>(args, &wsm); break;
+        default: kern = pick_kernel<T, 8>(args, &wsm); break;
     }
+    smem += wsm;
     SL_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     SL_CUDA_OK(sl::launch_kernel(kern, grid, dim3(HT), smem, s, false, args));
     return SL_OK;
@@ -344,7 +361,7 @@ int launch(const HashArgs& args, int dtype, int total_heads, long long rows_max,
     }
     SL_REQUIRE(max_tiles <= 0x7fffffffLL && total_heads <= 65535, SL_ESHAPE, "hash: grid too large");
     if (max_tiles == 0) return SL_OK;
-    const size_t smem = hash_smem(nullptr, nullptr, R);
+    const size_t smem = hash_smem(R);
     switch (dtype) {
         case SL_BF16: return launch_T<__nv_bfloat16>(a, total_heads, max_tiles, R, smem, s);
         case SL_F16: return launch_T<__half>(a, total_heads, max_tiles, R, smem, s);

@@ -208,152 +208,173 @@ __global__ void __launch_bounds__(NT, 1) scan_fused_kernel(const FusedArgs a) {
     __syncthreads();
     SL_STAMP(3)
 
-    // ------------------------------------------------------------------ B: own counts, publish, poll
+    // ------------------------------------------------------------------ B/C: count, publish, poll, emit
     // A task is (head, sub-range of the chunk). A lane tests four consecutive keys of one head per
     // 8-byte load: adding (0x7fff - tau) to a 16-bit score sets bit 15 iff score > tau, adding
     // (0x8000 - tau) iff score >= tau, two scores per 32-bit add.
+    // The walk over the tasks runs twice through the SAME instructions: pass 0 counts the chunk's
+    // {> tau, == tau} keys (then publishes them and polls every chunk's word), pass 1 writes the
+    // attended keys at their final positions. One loop body for both keeps the second pass's
+    // set-up and loop control in the instruction cache.
     const int S = a.S, ntasks = KH * S;
     const int sub = ((len + S - 1) / S + 127) & ~127;
     const int mlo = max(t0, a.s_end) - t0, mhi = min(t1, a.r_start) - t0;     // the chunk's keys outside both windows
+    constexpr int RUN = 20;
 #pragma unroll 1
-    for (int task = warp; task < ntasks; task += NW) {
-        const int h = task & (KH - 1), s = task >> (31 - __clz(KH));
-        const int elo = max(min(len, s * sub), mlo), ehi = min(min(len, (s + 1) * sub), mhi);
-        const int tau = s_tau[h];
-        const unsigned short* row = sscores + h * rowh;
-        const unsigned cgt = (unsigned)(0x7fff - tau) * 0x10001u, cge = (unsigned)(0x8000 - tau) * 0x10001u;
-        int gtM = 0, geM = 0;
+    for (int pass_ = 0; pass_ < 2; ++pass_) {
+        int pass;
+        asm volatile("mov.u32 %0, %1;" : "=r"(pass) : "r"(pass_));        // opaque: one copy of the loop below
 #pragma unroll 1
-        for (int g0 = elo & ~3; g0 < ehi; g0 += 128) {
-            const int tl = g0 + 4 * lane;
-            uint2 x = make_uint2(0u, 0u);
-            if (tl < ehi) x = *reinterpret_cast<const uint2*>(row + tl);
-            unsigned vlo = 0x80008000u, vhi = 0x80008000u;
-            if (tl < elo || tl + 3 >= ehi) edge_masks(tl, elo, ehi, vlo, vhi);
-            gtM += __popc(((x.x + cgt) & vlo) | (((x.y + cgt) & vhi) >> 1));
-            geM += __popc(((x.x + cge) & vlo) | (((x.y + cge) & vhi) >> 1));
+        for (int task = warp; task < ntasks; task += NW) {
+            const int h = task & (KH - 1), s = task >> (31 - __clz(KH));
+            const int lo = min(len, s * sub), hi = min(len, (s + 1) * sub);
+            const int elo = max(lo, mlo), ehi = min(hi, mhi);
+            const int tau = s_tau[h];
+            const unsigned short* row = sscores + h * rowh;
+            const unsigned cgt = (unsigned)(0x7fff - tau) * 0x10001u, cge = (unsigned)(0x8000 - tau) * 0x10001u;
+            int gtM = 0, geM = 0;
+            // pass 1 only: ranks of this task's first key among the attended keys / the threshold ties
+            int rM = 0, selM = 0, eq_before = 0, out_base = 0;
+            int* oi = a.idx + ((size_t)b * KH + h) * a.cap;
+            if (pass) {
+                rM = s_pre[h * 4 + 2]; selM = s_pre[h * 4 + 3];
+                int gt_before = s_pre[h * 4 + 0];
+                eq_before = s_pre[h * 4 + 1];
+#pragma unroll 1
+                for (int s2 = 0; s2 < s; ++s2) { gt_before += s_cnt[(s2 * KH + h) * 2]; eq_before += s_cnt[(s2 * KH + h) * 2 + 1]; }
+                out_base = a.s_end + gt_before + min(eq_before, rM);
+            }
+            // A lane walks RUN consecutive keys per trip (five 8-byte loads; the odd number of 8-byte
+            // units between lanes keeps the loads free of bank conflicts) and keeps one flag bit per
+            // key. Pass 1 ranks the lanes with one packed warp scan per trip and lets every lane
+            // write its own attended keys in order.
+#pragma unroll 1
+            for (int g0 = elo & ~3; g0 < ehi; g0 += 32 * RUN) {
+                const int r0 = g0 + lane * RUN;
+                unsigned Gf = 0, Ef = 0;                               // bit i: key r0 + i is > tau / == tau
+#pragma unroll
+                for (int j = 0; j < RUN / 4; ++j) {
+                    const int tl = r0 + 4 * j;
+                    uint2 x = make_uint2(0u, 0u);
+                    if (tl < ehi) x = *reinterpret_cast<const uint2*>(row + tl);
+                    const unsigned gb = flags4(x.x + cgt, x.y + cgt);
+                    const unsigned eb = flags4(x.x + cge, x.y + cge);
+                    Gf |= gb << (4 * j);
+                    Ef |= eb << (4 * j);
+                }
+                {   // keys of the run inside [elo, ehi)
+                    const int lc = min(max(elo - r0, 0), RUN), hc = min(max(ehi - r0, 0), RUN);
+                    const unsigned vm = ((1u << hc) - 1u) & ~((1u << lc) - 1u);
+                    Gf &= vm;
+                    Ef &= vm & ~Gf;
+                }
+                const int ng = __popc(Gf), ne = __popc(Ef);
+                if (!pass) { gtM += ng; geM += ne; continue; }
+                const unsigned packed = (unsigned)ng | ((unsigned)ne << 16);
+                const unsigned inc = (unsigned)prefix_sum((int)packed, lane);
+                const unsigned tot = __shfl_sync(0xffffffffu, inc, 31), exc = inc - packed;
+                const int tot_e = (int)(tot >> 16);
+                unsigned sel = Gf;
+                int below = (int)(exc & 0xffffu), tot_sel = (int)(tot & 0xffffu);
+                if (eq_before + tot_e <= rM) {                          // every tie of this trip is inside the quota
+                    sel |= Ef;
+                    below += (int)(exc >> 16);
+                    tot_sel += tot_e;
+                } else if (eq_before < rM) {                            // the quota runs out inside this trip
+                    int rank = eq_before + (int)(exc >> 16);
+                    unsigned e = Ef, tk = 0;
+                    while (e && rank < rM) { const unsigned bit = e & (0u - e); tk |= bit; e ^= bit; ++rank; }
+                    sel |= tk;
+                    const int nt = __popc(tk), inc2 = prefix_sum(nt, lane);
+                    below += inc2 - nt;
+                    tot_sel += __shfl_sync(0xffffffffu, inc2, 31);
+                }
+                int pos = out_base + below;
+                const int kbase = t0 + r0;
+                while (sel) {
+                    const int i = __ffs((int)sel) - 1;
+                    sel &= sel - 1u;
+                    if (pos < a.cap) oi[pos] = kbase + i;
+                    ++pos;
+                }
+                out_base += tot_sel;
+                eq_before += tot_e;
+            }
+            if (!pass) {
+                gtM = __reduce_add_sync(0xffffffffu, gtM);
+                geM = __reduce_add_sync(0xffffffffu, geM);
+                if (lane == 0) { s_cnt[task * 2] = gtM; s_cnt[task * 2 + 1] = geM; }
+            } else {
+                // always-kept keys of this sub-range: the sink at its own index, the recent window at the end
+                for (int t = t0 + lo + lane; t < min(t0 + hi, a.s_end); t += 32)
+                    if (t < a.cap) oi[t] = t;
+                for (int t = max(t0 + lo, a.r_start) + lane; t < t0 + hi; t += 32) {
+                    const int pos = a.s_end + selM + (t - a.r_start);
+                    if (pos < a.cap) oi[pos] = t;
+                }
+            }
         }
-        gtM = __reduce_add_sync(0xffffffffu, gtM);
-        geM = __reduce_add_sync(0xffffffffu, geM);
-        if (lane == 0) { s_cnt[task * 2] = gtM; s_cnt[task * 2 + 1] = geM - gtM; }
-    }
-    __syncthreads();
-    SL_STAMP(10)
-    if (tid < KH) {
-        // flag | > tau | == tau | == tau inside the sink, 21 bits each: one atomic 64-bit store
-        unsigned long long gt = 0, eq = 0, eqs = 0;
+        if (pass) break;
+        __syncthreads();
+        SL_STAMP(10)
+        if (tid < KH) {
+            // flag | > tau | == tau | == tau inside the sink, 21 bits each: one atomic 64-bit store
+            unsigned long long gt = 0, eq = 0, eqs = 0;
 #pragma unroll 1
-        for (int s = 0; s < S; ++s) { gt += s_cnt[(s * KH + tid) * 2]; eq += s_cnt[(s * KH + tid) * 2 + 1]; }
-        if (t0 < a.s_end) {
-            const int tau = s_tau[tid];
+            for (int s = 0; s < S; ++s) { gt += s_cnt[(s * KH + tid) * 2]; eq += s_cnt[(s * KH + tid) * 2 + 1]; }
+            if (t0 < a.s_end) {
+                const int tau = s_tau[tid];
 #pragma unroll 1
-            for (int t = t0; t < min(t1, a.s_end); ++t) eqs += (int)sscores[tid * rowh + (t - t0)] == tau;
+                for (int t = t0; t < min(t1, a.s_end); ++t) eqs += (int)sscores[tid * rowh + (t - t0)] == tau;
+            }
+            st_relaxed_u64(seg_b + tid * cpb + c, (1ull << 63) | (gt << 42) | (eq << 21) | eqs);
         }
-        st_relaxed_u64(seg_b + tid * cpb + c, (1ull << 63) | (gt << 42) | (eq << 21) | eqs);
-    }
-    __syncthreads();                 // nobody spins on memory while this CTA still has to publish
+        __syncthreads();                 // nobody spins on memory while this CTA still has to publish
 #pragma unroll 1
-    for (int h = warp; h < KH; h += NW) {
-        // Every chunk's word is polled until its flag shows (bounded): no second grid barrier, and
-        // a CTA that gets past this knows that all CTAs have finished with the histograms.
-        int pre_gt = 0, pre_eq = 0, tot_gt = 0, tot_eq = 0, tot_eqS = 0;
-        const unsigned long long* sp = seg_b + h * cpb;
-        bool ok = true;
+        for (int h = warp; h < KH; h += NW) {
+            // Every chunk's word is polled until its flag shows (bounded): no second grid barrier, and
+            // a CTA that gets past this knows that all CTAs have finished with the histograms.
+            int pre_gt = 0, pre_eq = 0, tot_gt = 0, tot_eq = 0, tot_eqS = 0;
+            const unsigned long long* sp = seg_b + h * cpb;
+            bool ok = true;
 #pragma unroll 1
-        for (int cc0 = 0; cc0 < cpb; cc0 += 32 * 5) {
-            unsigned long long w[5];
-            unsigned it = 0;
-            for (;;) {                               // all loads of a round in flight together
-                bool all = true;
+            for (int cc0 = 0; cc0 < cpb; cc0 += 32 * 5) {
+                unsigned long long w[5];
+                unsigned it = 0;
+                for (;;) {                               // all loads of a round in flight together
+                    bool all = true;
+#pragma unroll
+                    for (int j = 0; j < 5; ++j) {
+                        const int cc = cc0 + j * 32 + lane;
+                        w[j] = cc < cpb ? ld_relaxed_u64(sp + cc) : (1ull << 63);
+                    }
+#pragma unroll
+                    for (int j = 0; j < 5; ++j) all = all && (w[j] >> 63);
+                    if (__all_sync(0xffffffffu, all)) break;
+                    if (++it > 1000000u) { ok = false; break; }
+                    __nanosleep(200);
+                }
 #pragma unroll
                 for (int j = 0; j < 5; ++j) {
                     const int cc = cc0 + j * 32 + lane;
-                    w[j] = cc < cpb ? ld_relaxed_u64(sp + cc) : (1ull << 63);
+                    const int gt = (int)((w[j] >> 42) & 0x1fffffu), eq = (int)((w[j] >> 21) & 0x1fffffu);
+                    tot_gt += gt; tot_eq += eq; tot_eqS += (int)(w[j] & 0x1fffffu);
+                    if (cc < c) { pre_gt += gt; pre_eq += eq; }
                 }
-#pragma unroll
-                for (int j = 0; j < 5; ++j) all = all && (w[j] >> 63);
-                if (__all_sync(0xffffffffu, all)) break;
-                if (++it > 1000000u) { ok = false; break; }
-                __nanosleep(200);
             }
-#pragma unroll
-            for (int j = 0; j < 5; ++j) {
-                const int cc = cc0 + j * 32 + lane;
-                const int gt = (int)((w[j] >> 42) & 0x1fffffu), eq = (int)((w[j] >> 21) & 0x1fffffu);
-                tot_gt += gt; tot_eq += eq; tot_eqS += (int)(w[j] & 0x1fffffu);
-                if (cc < c) { pre_gt += gt; pre_eq += eq; }
+            if (!ok && a.status) atomicExch(a.status, 1);
+            pre_gt = __reduce_add_sync(0xffffffffu, pre_gt); pre_eq = __reduce_add_sync(0xffffffffu, pre_eq);
+            tot_gt = __reduce_add_sync(0xffffffffu, tot_gt); tot_eq = __reduce_add_sync(0xffffffffu, tot_eq);
+            tot_eqS = __reduce_add_sync(0xffffffffu, tot_eqS);
+            const int rM = max(s_r[h] - tot_eqS, 0);
+            const int selM = tot_gt + min(tot_eq, rM);
+            if (lane == 0) {
+                s_pre[h * 4 + 0] = pre_gt; s_pre[h * 4 + 1] = pre_eq; s_pre[h * 4 + 2] = rM; s_pre[h * 4 + 3] = selM;
+                if (c == 0) a.cnt[b * KH + h] = a.s_end + selM + (N - a.r_start);
             }
         }
-        if (!ok && a.status) atomicExch(a.status, 1);
-        pre_gt = __reduce_add_sync(0xffffffffu, pre_gt); pre_eq = __reduce_add_sync(0xffffffffu, pre_eq);
-        tot_gt = __reduce_add_sync(0xffffffffu, tot_gt); tot_eq = __reduce_add_sync(0xffffffffu, tot_eq);
-        tot_eqS = __reduce_add_sync(0xffffffffu, tot_eqS);
-        const int rM = max(s_r[h] - tot_eqS, 0);
-        const int selM = tot_gt + min(tot_eq, rM);
-        if (lane == 0) {
-            s_pre[h * 4 + 0] = pre_gt; s_pre[h * 4 + 1] = pre_eq; s_pre[h * 4 + 2] = rM; s_pre[h * 4 + 3] = selM;
-            if (c == 0) a.cnt[b * KH + h] = a.s_end + selM + (N - a.r_start);
-        }
-    }
-    __syncthreads();
-    SL_STAMP(5)
-
-    // ------------------------------------------------------------------ C: ordered emission
-#pragma unroll 1
-    for (int task = warp; task < ntasks; task += NW) {
-        const int h = task & (KH - 1), s = task >> (31 - __clz(KH));
-        const int lo = min(len, s * sub), hi = min(len, (s + 1) * sub);
-        const int elo = max(lo, mlo), ehi = min(hi, mhi);
-        const int tau = s_tau[h], rM = s_pre[h * 4 + 2], selM = s_pre[h * 4 + 3];
-        int gt_before = s_pre[h * 4 + 0], eq_before = s_pre[h * 4 + 1];
-        for (int s2 = 0; s2 < s; ++s2) { gt_before += s_cnt[(s2 * KH + h) * 2]; eq_before += s_cnt[(s2 * KH + h) * 2 + 1]; }
-        int* oi = a.idx + ((size_t)b * KH + h) * a.cap;
-        const unsigned short* row = sscores + h * rowh;
-        const unsigned cgt = (unsigned)(0x7fff - tau) * 0x10001u, cge = (unsigned)(0x8000 - tau) * 0x10001u;
-        int out_base = a.s_end + gt_before + min(eq_before, rM);
-        const unsigned lt = (1u << lane) - 1u;
-        if (task == 0) { SL_STAMP(12) }
-#pragma unroll 1
-        for (int g0 = elo & ~3; g0 < ehi; g0 += 128) {
-            const int tl = g0 + 4 * lane;
-            uint2 x = make_uint2(0u, 0u);
-            if (tl < ehi) x = *reinterpret_cast<const uint2*>(row + tl);
-            unsigned vlo = 0x80008000u, vhi = 0x80008000u;
-            if (tl < elo || tl + 3 >= ehi) edge_masks(tl, elo, ehi, vlo, vhi);
-            const unsigned gb = flags4((x.x + cgt) & vlo, (x.y + cgt) & vhi);      // bit i: key tl + i is > tau
-            const unsigned eb = flags4((x.x + cge) & vlo, (x.y + cge) & vhi) & ~gb;  //        ...   is == tau
-            unsigned sb = gb;
-            // Ranks come from ballots (one per key slot of a lane), not from a shuffle scan: keys are
-            // ordered lane-major, so what precedes a key is every slot of the lower lanes plus the
-            // lower slots of its own lane.
-            if (eq_before < rM) {                                                   // tie quota not used up (warp-uniform)
-                const unsigned e0 = __ballot_sync(0xffffffffu, eb & 1u), e1 = __ballot_sync(0xffffffffu, eb & 2u);
-                const unsigned e2 = __ballot_sync(0xffffffffu, eb & 4u), e3 = __ballot_sync(0xffffffffu, eb & 8u);
-                const int ex = eq_before + __popc(e0 & lt) + __popc(e1 & lt) + __popc(e2 & lt) + __popc(e3 & lt);
-#pragma unroll
-                for (int i = 0; i < 4; ++i)
-                    if (((eb >> i) & 1u) && ex + __popc(eb & ((1u << i) - 1u)) < rM) sb |= 1u << i;
-                eq_before += __popc(e0) + __popc(e1) + __popc(e2) + __popc(e3);
-            }
-            const unsigned s0 = __ballot_sync(0xffffffffu, sb & 1u), s1 = __ballot_sync(0xffffffffu, sb & 2u);
-            const unsigned s2 = __ballot_sync(0xffffffffu, sb & 4u), s3 = __ballot_sync(0xffffffffu, sb & 8u);
-            const int ex = out_base + __popc(s0 & lt) + __popc(s1 & lt) + __popc(s2 & lt) + __popc(s3 & lt);
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                const int pos = ex + __popc(sb & ((1u << i) - 1u));
-                if (((sb >> i) & 1u) && pos < a.cap) oi[pos] = t0 + tl + i;
-            }
-            out_base += __popc(s0) + __popc(s1) + __popc(s2) + __popc(s3);
-            if (task == 0 && g0 == (elo & ~3)) { SL_STAMP(14) }
-        }
-        if (task == 0) { SL_STAMP(9) }
-        // always-kept keys of this sub-range: the sink at its own index, the recent window at the end
-        for (int t = t0 + lo + lane; t < min(t0 + hi, a.s_end); t += 32)
-            if (t < a.cap) oi[t] = t;
-        for (int t = max(t0 + lo, a.r_start) + lane; t < t0 + hi; t += 32) {
-            const int pos = a.s_end + selM + (t - a.r_start);
-            if (pos < a.cap) oi[pos] = t;
-        }
+        __syncthreads();
+        SL_STAMP(5)
     }
 
     SL_STAMP(6)

@@ -681,6 +681,7 @@ int launch(const ScanArgs& a_in, const Plan& p, cudaStream_t s) {
 }  // namespace
 
 namespace slscan { unsigned long long* g_dbg_timing = nullptr; }
+static int g_lean = -1;    // 1: the decode shapes go to the lean fused kernel (default; SL_SCAN_LEAN=0 turns it off)
 
 extern "C" size_t sl_scan_topk_workspace_bytes(int B, int64_t N, int KH, int QH) {
     if (B <= 0 || N < 0 || KH <= 0 || QH <= 0 || QH % KH) return 0;
@@ -716,8 +717,11 @@ extern "C" int sl_scan_topk(const uint32_t* d_q_codes, const uint32_t* d_k_codes
                w.total);
     SL_REQUIRE(sl::aligned16(d_workspace), SL_EALIGN, "sl_scan_topk: workspace not 16-byte aligned");
     unsigned char* ws = static_cast<unsigned char*>(d_workspace);
-    static const bool lean_on = [] { const char* e = getenv("SL_SCAN_LEAN"); return !(e && e[0] == '0'); }();
-    if (lean_on && p.cooperative && !p.spill && slscan::fused_covers(KH, G) && p.chunk < (1 << 21) &&
+    if (g_lean < 0) {
+        const char* e = getenv("SL_SCAN_LEAN");
+        g_lean = (e && e[0] == '0') ? 0 : 1;
+    }
+    if (g_lean && p.cooperative && !p.spill && slscan::fused_covers(KH, G) && p.chunk < (1 << 21) &&
         (long long)NCOPY * B * KH * p.nbins < (1ll << 30)) {
         // the common decode shape: the lean kernel (same results, a fraction of the instructions)
         slscan::FusedArgs f = {};
@@ -881,4 +885,8 @@ extern "C" int sl_topk_from_scores(const int16_t* d_scores, int B, int64_t N, in
 
 // Development aid, not part of the public header: when set to a device buffer of grid*16 uint64,
 // thread 0 of every CTA of the scan kernels stores %globaltimer at its phase boundaries.
+// Development switch, not part of the public header: routes sl_scan_topk through the general
+// kernel (0) or lets it pick the lean fused kernel where that applies (1, the default).
+extern "C" void sl_debug_set_scan_lean(int on) { g_lean = on ? 1 : 0; }
+
 extern "C" void sl_debug_scan_timing(void* d_buf) { slscan::g_dbg_timing = static_cast<unsigned long long*>(d_buf); }

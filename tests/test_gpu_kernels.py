@@ -101,8 +101,11 @@ SCAN_CASES = [
     (2, 40000, 4, 28, 0, 4, 64, False),        # window only
     (1, 300, 4, 4, 1000, 4, 64, False),        # k >= N
     (1, 9000, 8, 40, 180, 100, 300, True),     # wide windows, G = 5
-    (1, 2048, 2, 24, 64, 4, 64, False),        # G = 12: four bit planes
-    (1, 1500, 2, 40, 64, 4, 64, True),         # G = 20: direct popcount path
+    (1, 2048, 2, 24, 64, 4, 64, False),        # G = 12: three bit planes (even group: halved)
+    (1, 1500, 2, 40, 64, 4, 64, True),         # G = 20: four bit planes
+    (1, 1500, 2, 18, 64, 4, 64, True),         # G = 9: four bit planes (odd group)
+    (1, 1500, 2, 34, 64, 4, 64, True),         # G = 17: direct popcount path
+    (2, 2500, 4, 64, 64, 4, 64, False),        # G = 16
     (160, 700, 4, 8, 30, 4, 64, True),         # more batch rows than SMs: one CTA per row, no grid barrier
     (150, 20000, 8, 8, 100, 4, 64, False),     # the same with scores spilled to global memory
 ]
@@ -123,6 +126,36 @@ def test_scan_topk_bit_exact(ops, B, N, KH, QH, k, sink, recent, low, layout):
         idx, cnt, scores = ops.scan_topk(qd, cd[:, :N], k, sink, recent, layout, return_scores=True)
         np.testing.assert_array_equal(scores.cpu().numpy(), scores_ref)
         check_selection(idx, cnt, ref_idx, ref_cnt)
+    ops.check_status()
+
+
+GENERAL_CASES = [c for c in SCAN_CASES if c[0] < 100 and c[0] * c[1] * c[2] <= 1100000][::2]
+
+
+@pytest.mark.parametrize("B,N,KH,QH,k,sink,recent,low", GENERAL_CASES)
+def test_scan_topk_general_kernel(ops, B, N, KH, QH, k, sink, recent, low):
+    """sl_scan_topk sends the common decode shapes to its lean kernel; the general kernel must give
+    the same answer on them (it is what other shapes, the spill path and the sharded halves use)."""
+    import ctypes
+    from spotlight_b200 import _lib
+    setter = _lib.lib.sl_debug_set_scan_lean
+    setter.argtypes, setter.restype = [ctypes.c_int], None
+    g = torch.Generator().manual_seed(B * 977 + N)
+    q = rand_codes(g, (B, QH, 4), low)
+    cache = rand_codes(g, (B, N, KH, 4), low)
+    scores_ref = O.match_count(np_u32(q)[:, None], np_u32(cache), O.BLOCKED)
+    ref_idx, ref_cnt = O.select(scores_ref, k, sink, recent)
+    setter(0)
+    try:
+        for _ in range(2):
+            idx, cnt, scores = ops.scan_topk(q.to(DEV), cache.to(DEV), k, sink, recent, O.BLOCKED, return_scores=True)
+            np.testing.assert_array_equal(scores.cpu().numpy(), scores_ref)
+            check_selection(idx, cnt, ref_idx, ref_cnt)
+        setter(1)                                        # and the lean kernel on the workspace the general one left
+        idx, cnt = ops.scan_topk(q.to(DEV), cache.to(DEV), k, sink, recent, O.BLOCKED)
+        check_selection(idx, cnt, ref_idx, ref_cnt)
+    finally:
+        setter(1)
     ops.check_status()
 
 
