@@ -53,6 +53,7 @@ struct ScanArgs {
     unsigned* sync;            // [B,2]
     int* status;
     int ctas_per_b, chunk, nbins, S, mode, R, rank, ncopy;
+    int stage;                 // copy this chunk's share of gscores into shared memory first
     unsigned long long* dbg;   // optional [grid][16] phase timestamps (ns)
 };
 
@@ -62,6 +63,7 @@ struct Plan {
     int ctas_per_b, chunk, nbins, S;
     size_t smem;
     bool spill, cooperative;
+    bool stage;     // scores are given in global memory and the chunk's share fits in shared memory: copy it in first
 };
 
 inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
@@ -88,8 +90,21 @@ Plan make_plan(int B, long long N, int KH, int G, bool scores_in_global, int nbi
     const size_t fixed = fixed_smem(KH, G, p.nbins, p.S);
     const size_t sc = (size_t)(p.chunk + 64) * KH * 2;      // transposed rows, padded to 4 (mod 32) words
     p.spill = scores_in_global || fixed + sc > (size_t)SMEM_BUDGET;
+    p.stage = false;
     p.smem = fixed + (p.spill ? 0 : sc);
     p.cooperative = p.ctas_per_b > 1;
+    return p;
+}
+
+// The modes that are fed with scores (from-scores, emit-only) walk them twice; from shared memory
+// that is several times faster than from global memory, so a chunk that fits is copied in first.
+Plan make_plan_given_scores(int B, long long N, int KH, int G, int nbins = 0) {
+    Plan p = make_plan(B, N, KH, G, true, nbins);
+    const size_t sc = (size_t)(p.chunk + 64) * KH * 2;
+    if (p.smem + sc <= (size_t)SMEM_BUDGET) {
+        p.stage = true;
+        p.smem += sc;
+    }
     return p;
 }
 
@@ -127,7 +142,7 @@ __global__ void __launch_bounds__(NT, 1) scan_topk_kernel(const ScanArgs a) {
     // Scores live either in shared memory, TRANSPOSED as [head][local key] with a row stride of
     // 4 (mod 32) words so that the interleaved writes of pass A spread over the banks, or in
     // global memory as [key][head] (spill of huge chunks, and the modes fed with scores).
-    const bool fast = a.gscores == nullptr;
+    const bool fast = a.gscores == nullptr || a.stage;
     const int roww = (a.chunk >> 1) + ((4 - (a.chunk >> 1)) & 31);
     const int rowh = 2 * roww;
     unsigned short* sc = fast ? sscores : a.gscores + ((long long)b * N + t0) * KH;
@@ -146,14 +161,21 @@ __global__ void __launch_bounds__(NT, 1) scan_topk_kernel(const ScanArgs a) {
     sl::pdl_trigger();
     sl::pdl_wait();                 // codes, q codes and the workspace all come from earlier kernels
 
+    if (a.mode == MODE_EMIT_ONLY && a.stage) {
+        const unsigned short* gs = a.gscores + ((long long)b * N + t0) * KH;
+        for (int i = tid; i < ncodes; i += NT) sscores[(i % KH) * rowh + i / KH] = gs[i];
+        __syncthreads();
+    }
     // ---------------------------------------------------------------- pass A: scan + histogram
     if (a.mode == MODE_FROM_SCORES) {
         // scores are given (global memory): histogram them, then select as in the fused mode
         for (int i = tid; i < KH * nbins; i += NT) shist[i] = 0;
         __syncthreads();
+        const unsigned short* gs = a.gscores + ((long long)b * N + t0) * KH;
         for (int i = tid; i < ncodes; i += NT) {
-            const int s = min(max((int)(short)sc[i], 0), nbins - 1);
+            const int s = min(max((int)(short)gs[i], 0), nbins - 1);
             atomicAdd(&shist[(i % KH) * nbins + s], 1u);
+            if (a.stage) sscores[(i % KH) * rowh + i / KH] = (unsigned short)s;
         }
         __syncthreads();
     } else if (a.mode != MODE_EMIT_ONLY) {
@@ -814,7 +836,7 @@ extern "C" int sl_select_emit(const int16_t* d_scores, const uint32_t* d_hist_al
         return SL_OK;
     }
     const int G = QH / KH;
-    const Plan p = make_plan(B, N_local, KH, G, true);
+    const Plan p = make_plan_given_scores(B, N_local, KH, G);
     const WsLayout w = ws_layout(B, N_local, KH, G, false, false);
     SL_REQUIRE(workspace_bytes >= w.total, SL_EWORKSPACE, "sl_select_emit: workspace %zu < required %zu", workspace_bytes,
                w.total);
@@ -837,7 +859,7 @@ extern "C" int sl_select_emit(const int16_t* d_scores, const uint32_t* d_hist_al
     a.sync = reinterpret_cast<unsigned*>(ws + w.sync_off);
     a.status = d_status;
     a.ctas_per_b = p.ctas_per_b; a.chunk = p.chunk; a.nbins = p.nbins; a.S = p.S;
-    a.mode = MODE_EMIT_ONLY; a.R = R; a.rank = rank; a.ncopy = 1;
+    a.mode = MODE_EMIT_ONLY; a.R = R; a.rank = rank; a.ncopy = 1; a.stage = p.stage ? 1 : 0;
     return launch(a, p, s);
 }
 
@@ -862,7 +884,7 @@ extern "C" int sl_topk_from_scores(const int16_t* d_scores, int B, int64_t N, in
         SL_CUDA_OK(cudaMemsetAsync(d_cnt, 0, (size_t)B * KH * 4, s));
         return SL_OK;
     }
-    const Plan p = make_plan(B, N, KH, 1, true, max_score + 1);
+    const Plan p = make_plan_given_scores(B, N, KH, 1, max_score + 1);
     const WsLayout w = ws_layout(B, N, KH, 1, true, false, max_score + 1);
     SL_REQUIRE(workspace_bytes >= w.total, SL_EWORKSPACE, "sl_topk_from_scores: workspace %zu < required %zu",
                workspace_bytes, w.total);
@@ -879,7 +901,7 @@ extern "C" int sl_topk_from_scores(const int16_t* d_scores, int B, int64_t N, in
     a.sync = reinterpret_cast<unsigned*>(ws + w.sync_off);
     a.status = d_status;
     a.ctas_per_b = p.ctas_per_b; a.chunk = p.chunk; a.nbins = p.nbins; a.S = p.S;
-    a.mode = MODE_FROM_SCORES; a.R = 1; a.rank = 0; a.ncopy = NCOPY;
+    a.mode = MODE_FROM_SCORES; a.R = 1; a.rank = 0; a.ncopy = NCOPY; a.stage = p.stage ? 1 : 0;
     return launch(a, p, s);
 }
 

@@ -15,9 +15,28 @@ namespace {
 //   score = base + (sum_j 2^j sum_w popc(X_{j,w})) << sh.
 // The 4*P words are added vertically with carry-save adders (LOP3), leaving one word per power
 // of two: P + 2 popcounts per key. G = 4 needs 2 planes, G = 7 three, G = 8 three.
-#define SL_FA(a, b, c, s, cy) { const uint32_t t_ = (a) ^ (b); s = t_ ^ (c); cy = ((a) & (b)) | ((c) & t_); }
+// Every step below is ONE three-input logic instruction, written as lop3 so that the compiler
+// cannot split it: select (k ? m : m'), the sum bit of a full adder (a ^ b ^ c) and its carry
+// (majority). The truth tables are the values of the expression for a = 0xF0, b = 0xCC, c = 0xAA.
+__device__ __forceinline__ uint32_t lop3_select(uint32_t k, uint32_t m, uint32_t mp) {
+    uint32_t r;
+    asm("lop3.b32 %0, %1, %2, %3, 0xCA;" : "=r"(r) : "r"(k), "r"(m), "r"(mp));
+    return r;
+}
+__device__ __forceinline__ uint32_t lop3_xor3(uint32_t a, uint32_t b, uint32_t c) {
+    uint32_t r;
+    asm("lop3.b32 %0, %1, %2, %3, 0x96;" : "=r"(r) : "r"(a), "r"(b), "r"(c));
+    return r;
+}
+__device__ __forceinline__ uint32_t lop3_maj(uint32_t a, uint32_t b, uint32_t c) {
+    uint32_t r;
+    asm("lop3.b32 %0, %1, %2, %3, 0xE8;" : "=r"(r) : "r"(a), "r"(b), "r"(c));
+    return r;
+}
+#define SL_FA(a, b, c, s, cy) { s = lop3_xor3(a, b, c); cy = lop3_maj(a, b, c); }
 #define SL_HA(a, b, s, cy) { s = (a) ^ (b); cy = (a) & (b); }
 
+// sum_j 2^j sum_w popc(select(k_w, M_{j,w}, M'_{j,w})): the caller adds the base and shifts.
 template <int P>
 __device__ __forceinline__ int sliced_score(const uint4 k, const uint32_t (&M)[P][4], const uint32_t (&Mp)[P][4]) {
     const uint32_t kw[4] = {k.x, k.y, k.z, k.w};
@@ -25,46 +44,45 @@ __device__ __forceinline__ int sliced_score(const uint4 k, const uint32_t (&M)[P
 #pragma unroll
     for (int j = 0; j < P; ++j)
 #pragma unroll
-        for (int w = 0; w < 4; ++w) X[j][w] = (kw[w] & M[j][w]) | (~kw[w] & Mp[j][w]);
+        for (int w = 0; w < 4; ++w) X[j][w] = lop3_select(kw[w], M[j][w], Mp[j][w]);
     uint32_t s1, c1, c2, L0;
     SL_FA(X[0][0], X[0][1], X[0][2], s1, c1)
     SL_HA(s1, X[0][3], L0, c2)
-    int score = __popc(L0);
+    const int p0 = __popc(L0);
     if constexpr (P == 1) {
         uint32_t L1, L2;
         SL_HA(c1, c2, L1, L2)
-        score += 2 * __popc(L1) + 4 * __popc(L2);
+        return p0 + 2 * (__popc(L1) + 2 * __popc(L2));
     } else {
         uint32_t s, sp, d1, d2, d3, L1;
         SL_FA(X[1][0], X[1][1], X[1][2], s, d1)
         SL_FA(X[1][3], c1, c2, sp, d2)
         SL_HA(s, sp, L1, d3)
-        score += 2 * __popc(L1);
+        const int p1 = __popc(L1);
         if constexpr (P == 2) {
             uint32_t L2, L3;
             SL_FA(d1, d2, d3, L2, L3)
-            score += 4 * __popc(L2) + 8 * __popc(L3);
+            return p0 + 2 * (p1 + 2 * (__popc(L2) + 2 * __popc(L3)));
         } else {
             uint32_t e1, e2, e3, L2;
             SL_FA(X[2][0], X[2][1], X[2][2], s, e1)
             SL_FA(X[2][3], d1, d2, sp, e2)
             SL_FA(s, sp, d3, L2, e3)
-            score += 4 * __popc(L2);
+            const int p2 = __popc(L2);
             if constexpr (P == 3) {
                 uint32_t L3, L4;
                 SL_FA(e1, e2, e3, L3, L4)
-                score += 8 * __popc(L3) + 16 * __popc(L4);
+                return p0 + 2 * (p1 + 2 * (p2 + 2 * (__popc(L3) + 2 * __popc(L4))));
             } else {
                 uint32_t f1, f2, f3, L3, L4, L5;
                 SL_FA(X[3][0], X[3][1], X[3][2], s, f1)
                 SL_FA(X[3][3], e1, e2, sp, f2)
                 SL_FA(s, sp, e3, L3, f3)
                 SL_FA(f1, f2, f3, L4, L5)
-                score += 8 * __popc(L3) + 16 * __popc(L4) + 32 * __popc(L5);
+                return p0 + 2 * (p1 + 2 * (p2 + 2 * (__popc(L3) + 2 * (__popc(L4) + 2 * __popc(L5)))));
             }
         }
     }
-    return score;
 }
 
 
