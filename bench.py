@@ -36,10 +36,11 @@ from spotlight_b200.workloads import CONFIGS, HEAD_DIM, budget, make_hash_params
 
 METRIC = "decode_attn_us_per_layer_128k_llama3_8b_shape"
 UNIT = "us/layer"
-# DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) from the ncu captures
-# summarised under profiles/ (scan_topk_headline.md, sparse_attn_headline.md; same per-launch size as the
-# benchmark's launches, captured at 90 % pruning); None where no capture exists.
-NCU_TRAFFIC = {"scan_topk": 16.92e6, "sparse_attn": 54.78e6, "decode_prepare": None}
+# DRAM bytes per launch (dram bytes read + written) from the ncu captures summarised under profiles/
+# (scan_fused_headline.md, sparse_attn_headline.md, decode_prepare_headline.md; same per-launch size as
+# the benchmark's launches, captured at 90 % pruning). decode_prepare's figure includes the 16.8 MB of
+# the code cache it prefetches into L2 for the scan that follows.
+NCU_TRAFFIC = {"scan_topk": 16.85e6, "sparse_attn": 54.76e6, "decode_prepare": 22.08e6}
 
 
 def peaks():
@@ -172,7 +173,8 @@ def run_reference(args, cfg):
 
 
 def workload_config(cfg):
-    return {"workload": f"{cfg.name}: Llama-3-8B-shaped decode attention, batch {cfg.batch}, {cfg.layers} layers, "
+    shape = "Llama-3-8B-shaped " if (cfg.q_heads, cfg.kv_heads) == (32, 8) else ""
+    return {"workload": f"{cfg.name}: {shape}decode attention, batch {cfg.batch}, {cfg.layers} layers, "
                         f"{cfg.q_heads}/{cfg.kv_heads} heads, context {cfg.context}, {cfg.hash} hash {list(cfg.mlp_dims)}, "
                         f"mask_out {cfg.mask_out}, sink {cfg.sink}, recent {cfg.recent}",
             "context": cfg.context, "batch_per_gpu": cfg.batch, "layers": cfg.layers, "mask_out": cfg.mask_out,

@@ -74,9 +74,10 @@ int sl_hamming_scores_u8(const uint8_t* d_q, const uint8_t* d_k, uint8_t* d_out,
 
 /* Workspace protocol for the fused scan + top-k. The workspace must be zero-filled once with
  * sl_workspace_init (or cudaMemset) before its first use; every successful call leaves it
- * zeroed again FOR THE SAME (B, KH, QH): the internal layout depends on those three, so a
- * workspace is bound to one shape (N may change freely) and must be re-initialised before it is
- * used with another. After SL_ETIMEOUT / a non-zero status word it must be re-initialised too. */
+ * ready for the next call WITH THE SAME (B, KH, QH): the internal layout depends on those
+ * three, so a workspace is bound to one shape (N may change freely) and must be re-initialised
+ * before it is used with another. After SL_ETIMEOUT / a non-zero status word it must be
+ * re-initialised too. One workspace serves one call at a time (calls on one stream are fine). */
 size_t sl_scan_topk_workspace_bytes(int B, int64_t N, int KH, int QH);
 int sl_workspace_init(void* d_workspace, size_t bytes, void* stream);
 
@@ -149,6 +150,8 @@ typedef struct {
  *   d_q_codes [B,QH,4] (out)
  *   d_code_cache [B,*,KH,4], d_k_cache / d_v_cache [B,*,KH,128] with batch strides in ELEMENTS
  *   (uint32 words resp. values); row `pos` of each is written. Caches may be NULL to skip.
+ *   With a code cache the launch also asks L2 for code rows 0..pos-1 of every batch element (at
+ *   most 64 MB), which the sl_scan_topk of the same decode step streams next.
  * Replaces, for one decode token, check_and_apply_qk_rope (spotlight/modifiers/modify_llama.py:
  * 68-80) + hash_fn + sign (spotlight_generation.py:13-20) + pack_cuda_func
  * (spotlight/kernel/__init__.py:23-24) + KVHash.update / KVCache.update
