@@ -406,10 +406,16 @@ def run_sharded(args, cfg):
     q_rot = torch.randn((B, QH, HEAD_DIM), generator=gq).to(dt).to(device)
     q_codes = torch.randint(0, 2 ** 31, (B, QH, 4), generator=gq, dtype=torch.int64).to(torch.uint32).to(device)
 
+    exchange = None
+    if world > 1 and args.peer:
+        from spotlight_b200.sharded import PeerExchange
+        G = QH // KH
+        exchange = (PeerExchange(B * KH * (128 * G + 1) * 4, device), PeerExchange(B * QH * 129 * 4, device))
+
     def layer_step(layer):
         if world > 1:
             return sharded_decode_attention(q_rot, q_codes, codes[layer], ks[layer], vs[layer], lo, n, kb,
-                                            cfg.sink, cfg.recent, ops.GQA_BLOCKED)
+                                            cfg.sink, cfg.recent, ops.GQA_BLOCKED, exchange=exchange)
         idx, cnt = ops.scan_topk(q_codes, codes[layer], kb, cfg.sink, cfg.recent, ops.GQA_BLOCKED)
         return ops.sparse_attn_decode(q_rot, ks[layer], vs[layer], idx, cnt, ops.GQA_BLOCKED)
 
@@ -444,6 +450,9 @@ def run_sharded(args, cfg):
     with ClockSampler(local) as clocks:
         ms_step = time_graph(Runner(), args.steps, args.warmup, device, dist if world > 1 else None)
     ops.check_status(device)
+    if exchange:
+        for e in exchange:
+            e.check_status()
     clk = clocks.summary()
     if world > 1:
         t = torch.tensor([ms_step], device=device, dtype=torch.float64)
@@ -460,6 +469,7 @@ def run_sharded(args, cfg):
             "config": {"workload": f"{cfg.name}: sequence-sharded decode attention, batch {B}, {QH}/{KH} heads, context {n} "
                                    f"over {world} rank(s), mask_out {cfg.mask_out}, sink {cfg.sink}, recent {cfg.recent}",
                        "context": n, "keys_per_rank": nl, "rotating_layers": L,
+                       "exchange": "peer memory" if exchange else ("nccl" if world > 1 else "none"),
                        "l2": "inputs larger than L2 (layers rotate)"},
             "tokens_per_s": B / (us_layer * 1e-6 * 48) if cfg.name == "cfg4" else None,
             "cuda_graph": use_graph,
@@ -492,6 +502,8 @@ def main():
     ap.add_argument("--mask-out", type=float, default=None)
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--peer", action="store_true",
+                    help="with --sharded: exchange over peer memory (sl_peer_allgather) instead of NCCL all-gathers")
     ap.add_argument("--sharded", action="store_true",
                     help="sequence-sharded layer-step across the ranks of a torchrun launch (config 4)")
     args = ap.parse_args()

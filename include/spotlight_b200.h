@@ -239,6 +239,31 @@ int sl_gather_rows(const void* d_cache, int64_t batch_stride, int elem_bytes,
                    const int32_t* d_idx, int idx_capacity, int B, int KH, int budget,
                    void* d_out, void* stream);
 
+/* ---- exchange between the GPUs of one node over peer memory (sequence-sharded contexts) ----
+ * No reference counterpart: the reference has no sequence parallelism (its only collectives are
+ * in training, train.py:250-260). A sequence-sharded decode step all-gathers two KB-sized
+ * messages per layer (score histograms, attention partials); these entry points do that with one
+ * kernel per exchange over CUDA-IPC peer mappings instead of a collective library.
+ *   sl_peer_buffer_bytes  size of one rank's exchange buffer for R ranks and a slot of slot_stride bytes
+ *   sl_peer_alloc / sl_peer_free     the buffer (cudaMalloc, zero-filled); one per rank and exchange
+ *   sl_peer_export                   64-byte IPC handle of a buffer, to be sent to the other ranks
+ *   sl_peer_open / sl_peer_close     map / unmap another rank's buffer from its handle
+ *   sl_peer_allgather                this rank's message (bytes % 16 == 0, <= slot_stride) -> slot `rank`
+ *                                    of every buffer in peer_bufs[0..R) (host array, own buffer at index
+ *                                    `rank`); returns in stream order once all R slots of the OWN buffer
+ *                                    hold this round's messages. Every rank must call it for every round,
+ *                                    in the same order; a buffer may be used again only after another
+ *                                    exchange (or any other synchronisation of all ranks) has completed.
+ *                                    The wait is bounded (about a second): *d_status = 3 when it ran out. */
+size_t sl_peer_buffer_bytes(int R, size_t slot_stride);
+int sl_peer_alloc(size_t bytes, void** d_ptr);
+int sl_peer_free(void* d_ptr);
+int sl_peer_export(const void* d_ptr, unsigned char* handle64);
+int sl_peer_open(const unsigned char* handle64, void** d_ptr);
+int sl_peer_close(void* d_ptr);
+int sl_peer_allgather(const void* d_src, size_t bytes, void* const* peer_bufs, int rank, int R,
+                      size_t slot_stride, int32_t* d_status, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -34,23 +34,92 @@ def _all_gather(t: torch.Tensor, group) -> torch.Tensor:
     return out
 
 
+class PeerExchange:
+    """All-gather of one fixed-size message per rank over peer memory (sl_peer_allgather): every
+    rank owns a buffer of `world` slots that its peers map through CUDA IPC, one kernel per exchange
+    stores the message into every rank's buffer and waits (bounded) for the others. Same result as
+    `_all_gather`, without a collective library on the critical path; the handles travel once, at
+    construction, through torch.distributed. The ranks must be GPUs of one node."""
+
+    def __init__(self, nbytes: int, device: torch.device, group=None):
+        import ctypes as C
+        from ._lib import check, lib
+        self._C, self._lib, self._check = C, lib, check
+        self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
+        self.nbytes = int(nbytes)
+        assert self.nbytes % 16 == 0, "messages are sent in 16-byte units"
+        self.device = device
+        total = lib.sl_peer_buffer_bytes(self.world, self.nbytes)
+        own = C.c_void_p()
+        check(lib.sl_peer_alloc(total, C.byref(own)))
+        self._own = own.value
+        handle = C.create_string_buffer(64)
+        check(lib.sl_peer_export(self._own, handle))
+        handles = [None] * self.world
+        dist.all_gather_object(handles, bytes(handle.raw), group=group)
+        self._bufs = (C.c_void_p * self.world)()
+        self._opened = []
+        for r in range(self.world):
+            if r == self.rank:
+                self._bufs[r] = self._own
+            else:
+                ptr = C.c_void_p()
+                check(lib.sl_peer_open(C.create_string_buffer(handles[r], 64), C.byref(ptr)))
+                self._bufs[r] = ptr.value
+                self._opened.append(ptr.value)
+        self.status = torch.zeros(1, dtype=torch.int32, device=device)
+        dist.barrier(group)                      # every buffer is mapped everywhere before the first store
+
+    def _slots(self, dtype: torch.dtype, shape) -> torch.Tensor:
+        """The own buffer's slots as a tensor [world, *shape] (no copy)."""
+        class _Raw:
+            pass
+        raw = _Raw()
+        raw.__cuda_array_interface__ = {"shape": (self.world * self.nbytes,), "typestr": "|u1",
+                                        "data": (self._own, False), "version": 3}
+        flat = torch.as_tensor(raw, device=self.device)
+        return flat.view(dtype).view(self.world, *shape)
+
+    def all_gather(self, t: torch.Tensor) -> torch.Tensor:
+        t = t.contiguous()
+        assert t.numel() * t.element_size() == self.nbytes, "message size is fixed at construction"
+        stream = torch.cuda.current_stream(self.device).cuda_stream
+        self._check(self._lib.sl_peer_allgather(t.data_ptr(), self.nbytes, self._bufs, self.rank, self.world,
+                                                self.nbytes, self.status.data_ptr(), stream))
+        return self._slots(t.dtype, t.shape)
+
+    def check_status(self):
+        code = int(self.status.item())
+        if code:
+            raise RuntimeError(f"peer exchange gave up waiting for another rank (status {code})")
+
+    def close(self):
+        for p in self._opened:
+            self._lib.sl_peer_close(p)
+        self._opened = []
+        if self._own:
+            self._lib.sl_peer_free(self._own)
+            self._own = None
+
+
 def sharded_decode_attention(q_rot: torch.Tensor, q_codes: torch.Tensor, codes_local: torch.Tensor,
                              k_local: torch.Tensor, v_local: torch.Tensor, tok_offset: int, n_global: int,
                              k_budget: int, sink: int = 4, recent: int = 64, layout: int = 1, group=None,
-                             backend=None, return_selection: bool = False):
+                             backend=None, return_selection: bool = False, exchange=None):
     """One layer-step on this rank. q_rot [B,QH,128], q_codes uint32 [B,QH,4] (identical on all
     ranks); codes_local [B,n_local,KH,4], k_local / v_local [B,n_local,KH,128]: this rank's keys
     [tok_offset, tok_offset + n_local). Returns the merged output [B,QH,128] (identical on all
-    ranks) and, on request, this rank's attended LOCAL indices and counts."""
+    ranks) and, on request, this rank's attended LOCAL indices and counts. `exchange`: a pair of
+    PeerExchange objects (histograms, partials) to use instead of the group's all-gathers."""
     if backend is None:
         from . import ops as backend
     rank, world = dist.get_rank(group), dist.get_world_size(group)
     QH = q_rot.shape[1]
     scores, hist = backend.scan_hist(q_codes, codes_local, layout)
-    hist_all = _all_gather(hist, group)
+    hist_all = exchange[0].all_gather(hist) if exchange else _all_gather(hist, group)
     idx, cnt = backend.select_emit(scores, hist_all, rank, tok_offset, n_global, QH, k_budget, sink, recent)
     o, lse = backend.sparse_attn_decode(q_rot, k_local, v_local, idx, cnt, layout, return_lse=True)
     packed = torch.cat([o.float(), lse[..., None]], dim=-1)          # one message: [B,QH,129]
-    parts = _all_gather(packed, group)
+    parts = exchange[1].all_gather(packed) if exchange else _all_gather(packed, group)
     out = backend.merge_lse(parts[..., :128].contiguous(), parts[..., 128].contiguous(), q_rot.dtype)
     return (out, idx, cnt) if return_selection else out

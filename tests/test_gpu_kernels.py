@@ -482,3 +482,33 @@ def test_lru_with_host_backing_store(ops):
         assert torch.equal(ops.sparse_attn_decode(q, kd, vd, idx, cnt), ops.sparse_attn_decode(q, table.k, table.v, slots, cnt))
         assert int(table.status.item()) == 0
     assert table.stats[..., 1].sum().item() == 0 and table.stats[..., 0].sum().item() == B * KH * keep
+
+
+def test_peer_allgather_single_rank(ops):
+    """The peer-memory all-gather with one rank: the message lands in the own slot, the epoch
+    advances, nothing waits. (Two and more ranks: tests/test_gpu_multi.py.)"""
+    import ctypes as C
+    from spotlight_b200._lib import check, lib
+    nbytes = 4096
+    buf = C.c_void_p()
+    check(lib.sl_peer_alloc(lib.sl_peer_buffer_bytes(1, nbytes), C.byref(buf)))
+    try:
+        bufs = (C.c_void_p * 1)(buf.value)
+        status = torch.zeros(1, dtype=torch.int32, device=DEV)
+        stream = torch.cuda.current_stream().cuda_stream
+        for rnd in range(3):
+            msg = torch.arange(nbytes // 4, dtype=torch.int32, device=DEV) + rnd
+            check(lib.sl_peer_allgather(msg.data_ptr(), nbytes, bufs, 0, 1, nbytes, status.data_ptr(), stream))
+            torch.cuda.synchronize()
+
+            class Raw:
+                pass
+            raw = Raw()
+            raw.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (buf.value, False), "version": 3}
+            got = torch.as_tensor(raw, device=DEV).view(torch.int32).clone()
+            torch.testing.assert_close(got, msg, rtol=0, atol=0)
+        assert int(status.item()) == 0
+        with pytest.raises(ValueError):
+            check(lib.sl_peer_allgather(msg.data_ptr(), 24, bufs, 0, 1, nbytes, status.data_ptr(), stream))
+    finally:
+        check(lib.sl_peer_free(buf))

@@ -30,7 +30,7 @@ def _inputs(n, B, KH, QH):
     return q, q_codes, codes, k, v
 
 
-def _worker(rank, world, port, n, keep, ret):
+def _worker(rank, world, port, n, keep, ret, peer=False):
     import torch.distributed as dist
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
@@ -42,23 +42,35 @@ def _worker(rank, world, port, n, keep, ret):
         from spotlight_b200.sharded import shard_bounds, sharded_decode_attention
         q, q_codes, codes, k, v = _inputs(n, 1, 8, 40)
         lo, hi = shard_bounds(n, world, rank)
-        out, idx, cnt = sharded_decode_attention(
-            q.to(dev), q_codes.to(dev), codes[:, lo:hi].contiguous().to(dev), k[:, lo:hi].contiguous().to(dev),
-            v[:, lo:hi].contiguous().to(dev), lo, n, keep, 4, 64, O.BLOCKED, return_selection=True)
+        exchange = None
+        if peer:            # the two all-gathers over peer memory instead of NCCL
+            from spotlight_b200.sharded import PeerExchange
+            exchange = (PeerExchange(1 * 8 * (128 * 5 + 1) * 4, dev), PeerExchange(1 * 40 * 129 * 4, dev))
+        args = (q.to(dev), q_codes.to(dev), codes[:, lo:hi].contiguous().to(dev), k[:, lo:hi].contiguous().to(dev),
+                v[:, lo:hi].contiguous().to(dev), lo, n, keep, 4, 64, O.BLOCKED)
+        for _ in range(3 if peer else 1):            # several rounds: the exchange buffers are reused
+            out, idx, cnt = sharded_decode_attention(*args, return_selection=True, exchange=exchange)
         torch.cuda.synchronize(dev)
         ops.check_status(dev)
+        if exchange:
+            for e in exchange:
+                e.check_status()
+            dist.barrier()
+            for e in exchange:
+                e.close()
         ret[rank] = (out.float().cpu().numpy(), idx.cpu().numpy() + lo, cnt.cpu().numpy())
     finally:
         dist.destroy_process_group()
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs at least two GPUs")
-def test_sequence_sharded_attention_over_nccl():
+@pytest.mark.parametrize("peer", [False, True], ids=["nccl", "peer-memory"])
+def test_sequence_sharded_attention_over_nccl(peer):
     import torch.multiprocessing as mp
     world = min(torch.cuda.device_count(), 4)
     n, keep = 200000, 4000
     ret = mp.Manager().dict()
-    mp.spawn(_worker, args=(world, _free_port(), n, keep, ret), nprocs=world, join=True)
+    mp.spawn(_worker, args=(world, _free_port(), n, keep, ret, peer), nprocs=world, join=True)
     q, q_codes, codes, k, v = _inputs(n, 1, 8, 40)
     scores = O.match_count(q_codes.view(torch.int32).numpy().view(np.uint32)[:, None],
                            codes.view(torch.int32).numpy().view(np.uint32), O.BLOCKED)
