@@ -408,9 +408,8 @@ def run_sharded(args, cfg):
 
     exchange = None
     if world > 1 and args.peer:
-        from spotlight_b200.sharded import PeerExchange
-        G = QH // KH
-        exchange = (PeerExchange(B * KH * (128 * G + 1) * 4, device), PeerExchange(B * QH * 129 * 4, device))
+        from spotlight_b200.sharded import make_peer_exchange
+        exchange = make_peer_exchange(B, KH, QH, device, fused_scan=not args.no_fused_scan)
 
     def layer_step(layer):
         if world > 1:
@@ -469,7 +468,8 @@ def run_sharded(args, cfg):
             "config": {"workload": f"{cfg.name}: sequence-sharded decode attention, batch {B}, {QH}/{KH} heads, context {n} "
                                    f"over {world} rank(s), mask_out {cfg.mask_out}, sink {cfg.sink}, recent {cfg.recent}",
                        "context": n, "keys_per_rank": nl, "rotating_layers": L,
-                       "exchange": "peer memory" if exchange else ("nccl" if world > 1 else "none"),
+                       "exchange": ("peer memory, fused scan" if exchange and len(exchange) > 2 else "peer memory") if exchange
+                       else ("nccl" if world > 1 else "none"),
                        "l2": "inputs larger than L2 (layers rotate)"},
             "tokens_per_s": B / (us_layer * 1e-6 * 48) if cfg.name == "cfg4" else None,
             "cuda_graph": use_graph,
@@ -504,6 +504,8 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--peer", action="store_true",
                     help="with --sharded: exchange over peer memory (sl_peer_allgather) instead of NCCL all-gathers")
+    ap.add_argument("--no-fused-scan", action="store_true",
+                    help="with --peer: keep sl_scan_hist + exchange + sl_select_emit instead of the one-launch form")
     ap.add_argument("--sharded", action="store_true",
                     help="sequence-sharded layer-step across the ranks of a torchrun launch (config 4)")
     args = ap.parse_args()

@@ -263,6 +263,30 @@ int sl_peer_open(const unsigned char* handle64, void** d_ptr);
 int sl_peer_close(void* d_ptr);
 int sl_peer_allgather(const void* d_src, size_t bytes, void* const* peer_bufs, int rank, int R,
                       size_t slot_stride, int32_t* d_status, void* stream);
+/* The exchange of attention partials and their merge in one launch: this rank's partial output
+ * d_o [rows,128] (`dtype`) and d_lse [rows] go to every rank as [rows][129] floats, and d_out
+ * [rows,128] receives the log-sum-exp merge of all R partials (the arithmetic of sl_merge_lse).
+ * slot_stride >= rows*129*4; the same calling rules as sl_peer_allgather. */
+int sl_peer_merge_lse(const void* d_o, const float* d_lse, int dtype, int64_t rows, void* const* peer_bufs,
+                      int rank, int R, size_t slot_stride, void* d_out, int32_t* d_status, void* stream);
+
+/* Fused form of sl_scan_hist + histogram all-gather + sl_select_emit for a sequence shard: one
+ * cooperative launch per rank that scans the local codes, stores the merged local histograms into
+ * every rank's exchange buffer (peer stores), waits (bounded, *d_status = 3 when it ran out) for
+ * the other ranks' histograms and writes this rank's share of the global selection: the k highest
+ * scores of the WHOLE context with ties to the lowest GLOBAL index, plus the parts of the sink and
+ * of the recent window that fall into [tok_offset, tok_offset + N_local). d_idx holds LOCAL indices.
+ * peer_bufs[0..R): exchange buffers of sl_peer_buffer_bytes(R, slot_stride) bytes each (own one at
+ * index `rank`), slot_stride >= sl_scan_topk_sharded_slot_bytes(B, KH, QH), used for nothing else.
+ * All R ranks must call it for every step with grids of the same shape, and must all pass another
+ * exchange (e.g. the attention partials) before the next call. Shapes the fused kernel does not
+ * cover return SL_ESHAPE: use sl_scan_hist + sl_select_emit then. No reference counterpart. */
+size_t sl_scan_topk_sharded_slot_bytes(int B, int KH, int QH);
+int sl_scan_topk_sharded(const uint32_t* d_q_codes, const uint32_t* d_k_codes, int64_t k_batch_stride, int B,
+                         int64_t N_local, int64_t tok_offset, int64_t N_global, int KH, int QH,
+                         int gqa_layout, int k, int sink, int recent, int32_t* d_idx, int idx_capacity,
+                         int32_t* d_cnt, void* d_workspace, size_t workspace_bytes, void* const* peer_bufs,
+                         int rank, int R, size_t slot_stride, int32_t* d_status, void* stream);
 
 #ifdef __cplusplus
 }

@@ -48,6 +48,9 @@ SIGNATURES = {
     "sl_merge_lse": (_I, [_P, _P, _I, _L, _I, _P, _P]),
     "sl_lru_update": (_I, [_P, _I, _P, _I, _I, _P, _P, _L, _I, _P, _P, _I, _P, _L, _P, _P, _I, _P, _P, _P, _P]),
     "sl_gather_rows": (_I, [_P, _L, _I, _P, _I, _I, _I, _I, _P, _P]),
+    "sl_scan_topk_sharded_slot_bytes": (_Z, [_I, _I, _I]),
+    "sl_scan_topk_sharded": (_I, [_P, _P, _L, _I, _L, _L, _L, _I, _I, _I, _I, _I, _I, _P, _I, _P, _P, _Z, C.POINTER(_P),
+                                  _I, _I, _Z, _P, _P]),
     "sl_peer_buffer_bytes": (_Z, [_I, _Z]),
     "sl_peer_alloc": (_I, [_Z, C.POINTER(_P)]),
     "sl_peer_free": (_I, [_P]),
@@ -55,6 +58,7 @@ SIGNATURES = {
     "sl_peer_open": (_I, [C.c_char_p, C.POINTER(_P)]),
     "sl_peer_close": (_I, [_P]),
     "sl_peer_allgather": (_I, [_P, _Z, C.POINTER(_P), _I, _I, _Z, _P, _P]),
+    "sl_peer_merge_lse": (_I, [_P, _P, _I, _L, C.POINTER(_P), _I, _I, _Z, _P, _P, _P]),
 }
 
 

@@ -67,7 +67,118 @@ __global__ void __launch_bounds__(PT) peer_allgather_kernel(const PeerArgs a) {
     __syncthreads();
 }
 
+// The second exchange of a sharded step in one launch: pack this rank's partial (o rounded to the
+// run dtype as sl_sparse_attn_decode leaves it, lse in fp32) as rows*129 floats, all-gather it
+// as above ([rows][128] floats, then lse [rows]), and merge the R partials by log-sum-exp into
+// out [rows][128].
+template <typename T>
+__global__ void __launch_bounds__(PT) peer_merge_lse_kernel(const PeerArgs a, const T* __restrict__ o,
+                                                            const float* __restrict__ lse, int rows, T* __restrict__ out) {
+    __shared__ unsigned s_epoch;
+    sl::pdl_trigger();
+    sl::pdl_wait();
+    const int tid = threadIdx.x;
+    // message: o as [rows][128] floats (16-byte stores), then lse [rows]
+    for (int i = tid; i < rows * 32; i += PT) {
+        const T* src = o + i * 4;
+        const float4 v = make_float4(sl::VT<T>::to_f(src[0]), sl::VT<T>::to_f(src[1]), sl::VT<T>::to_f(src[2]), sl::VT<T>::to_f(src[3]));
+        for (int r = 0; r < a.R; ++r)
+            reinterpret_cast<float4*>(a.base[r] + (unsigned long long)a.rank * a.slot_stride)[i] = v;
+    }
+    for (int i = tid; i < rows; i += PT) {
+        const float v = lse[i];
+        for (int r = 0; r < a.R; ++r)
+            reinterpret_cast<float*>(a.base[r] + (unsigned long long)a.rank * a.slot_stride)[rows * 128 + i] = v;
+    }
+    __syncthreads();
+    if (tid == 0) {
+        unsigned* epoch = reinterpret_cast<unsigned*>(a.base[a.rank] + a.flags_off) + a.R;
+        const unsigned e = *epoch + 1u;
+        *epoch = e;
+        s_epoch = e;
+        __threadfence_system();
+        for (int r = 0; r < a.R; ++r) {
+            unsigned* pf = reinterpret_cast<unsigned*>(a.base[r] + a.flags_off) + a.rank;
+            asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(pf), "r"(e) : "memory");
+        }
+    }
+    __syncthreads();
+    if (tid < a.R) {
+        const unsigned e = s_epoch;
+        const unsigned* lf = reinterpret_cast<const unsigned*>(a.base[a.rank] + a.flags_off) + tid;
+        unsigned v = 0, it = 0;
+        for (;;) {
+            asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(lf) : "memory");
+            if ((int)(v - e) >= 0) break;
+            if (++it > 400000u) {
+                if (a.status) atomicExch(a.status, 3);
+                break;
+            }
+            __nanosleep(100);
+        }
+    }
+    __syncthreads();
+    const float* own = reinterpret_cast<const float*>(a.base[a.rank]);
+    const long long sstr = (long long)(a.slot_stride >> 2);
+    for (int e = tid; e < rows * 128; e += PT) {
+        const int row = e >> 7;
+        float M = -INFINITY;
+        for (int r = 0; r < a.R; ++r) M = fmaxf(M, __ldcg(own + r * sstr + rows * 128 + row));
+        float L = 0.0f, O = 0.0f;
+        if (M != -INFINITY) {
+            for (int r = 0; r < a.R; ++r) {
+                const float w = expf(__ldcg(own + r * sstr + rows * 128 + row) - M);
+                L += w;
+                O += w * __ldcg(own + r * sstr + e);
+            }
+        }
+        out[e] = sl::VT<T>::from_f(L > 0.0f ? O / L : 0.0f);
+    }
+}
+
+int fill_args(PeerArgs& a, void* const* peer_bufs, int rank, int R, size_t slot_stride, int32_t* d_status, const char* fn) {
+    SL_REQUIRE(peer_bufs, SL_EINVAL, "%s: null pointer", fn);
+    SL_REQUIRE(R >= 1 && R <= MAX_RANKS && rank >= 0 && rank < R, SL_EINVAL, "%s: bad rank %d of %d", fn, rank, R);
+    SL_REQUIRE(slot_stride % 16 == 0, SL_ESHAPE, "%s: slot stride must be a multiple of 16 bytes", fn);
+    for (int r = 0; r < R; ++r) {
+        SL_REQUIRE(peer_bufs[r] != nullptr && sl::aligned16(peer_bufs[r]), SL_EINVAL, "%s: bad buffer of rank %d", fn, r);
+        a.base[r] = static_cast<unsigned char*>(peer_bufs[r]);
+    }
+    a.R = R; a.rank = rank;
+    a.slot_stride = slot_stride;
+    a.flags_off = (unsigned long long)R * slot_stride;
+    a.status = d_status;
+    return SL_OK;
+}
+
 }  // namespace
+
+extern "C" int sl_peer_merge_lse(const void* d_o, const float* d_lse, int dtype, int64_t rows, void* const* peer_bufs,
+                                 int rank, int R, size_t slot_stride, void* d_out, int32_t* d_status, void* stream) {
+    SL_REQUIRE(d_o && d_lse && d_out, SL_EINVAL, "sl_peer_merge_lse: null pointer");
+    SL_REQUIRE(rows > 0 && rows <= (1 << 20), SL_ESHAPE, "sl_peer_merge_lse: bad row count");
+    SL_REQUIRE((size_t)rows * 129 * 4 <= slot_stride, SL_ESHAPE, "sl_peer_merge_lse: slot of %zu bytes < %lld rows x 129 floats",
+               slot_stride, (long long)rows);
+    PeerArgs a = {};
+    if (int rc = fill_args(a, peer_bufs, rank, R, slot_stride, d_status, "sl_peer_merge_lse")) return rc;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    switch (dtype) {
+        case SL_BF16:
+            SL_CUDA_OK(sl::launch_kernel(peer_merge_lse_kernel<__nv_bfloat16>, dim3(1), dim3(PT), 0, s, false, a,
+                                         static_cast<const __nv_bfloat16*>(d_o), d_lse, (int)rows, static_cast<__nv_bfloat16*>(d_out)));
+            break;
+        case SL_F16:
+            SL_CUDA_OK(sl::launch_kernel(peer_merge_lse_kernel<__half>, dim3(1), dim3(PT), 0, s, false, a,
+                                         static_cast<const __half*>(d_o), d_lse, (int)rows, static_cast<__half*>(d_out)));
+            break;
+        case SL_F32:
+            SL_CUDA_OK(sl::launch_kernel(peer_merge_lse_kernel<float>, dim3(1), dim3(PT), 0, s, false, a,
+                                         static_cast<const float*>(d_o), d_lse, (int)rows, static_cast<float*>(d_out)));
+            break;
+        default: return sl::fail(SL_EINVAL, "sl_peer_merge_lse: unsupported dtype %d", dtype);
+    }
+    return SL_OK;
+}
 
 extern "C" int sl_peer_alloc(size_t bytes, void** d_ptr) {
     SL_REQUIRE(d_ptr != nullptr && bytes > 0, SL_EINVAL, "sl_peer_alloc: bad arguments");

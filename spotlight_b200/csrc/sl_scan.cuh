@@ -31,11 +31,18 @@ struct FusedArgs {
     int rowh;                  // row stride of the score rows in shared memory (halfwords)
     int score_off;             // byte offset of the score rows in shared memory
     unsigned long long* dbg;   // optional [grid][16] phase stamps (development aid)
+    // sequence shards (R > 0): N, s_end, r_start, idx are local to this rank's keys; the merged local
+    // histograms travel to every rank's exchange buffer and the threshold comes from all R of them
+    unsigned char* peer[8];    // exchange buffer of every rank: [R slots][R flags][epoch][arrivals]
+    int R, rank;
+    unsigned long long slot_stride, pflags_off;
+    int kk;                    // min(k, global number of keys)
 };
 
 bool fused_covers(int KH, int G);
 size_t fused_fixed_smem(int KH, int nbins, int S);
 int launch_fused(const FusedArgs& a, size_t smem, cudaStream_t s);
+size_t shard_message_bytes(int B, int KH, int nbins, int cws);   // one rank's histogram message, padded to 16 bytes
 extern unsigned long long* g_dbg_timing;   // set by sl_debug_scan_timing
 
 __device__ __forceinline__ void touch(const void* p) {   // warms the TLB for a page used later

@@ -22,7 +22,13 @@ namespace {
 
 using namespace slscan;
 
-template <int PT>
+// SHARD: this rank holds a contiguous part of a longer context. After the grid barrier the CTAs
+// merge the copies of the local histograms and store them into slot `rank` of every rank's exchange
+// buffer (plain peer stores over NVLink) and fence at system scope; the last CTA to arrive writes
+// this launch's epoch into flag `rank` of every buffer; then all CTAs wait (bounded) until the R
+// flags of the own buffer carry the epoch. The threshold is then searched over the R slots, and the ties
+// that belong to lower ranks (lower key indices) are taken off this rank's tie quota.
+template <int PT, bool SHARD>
 __global__ void __launch_bounds__(NT, 1) scan_fused_kernel(const FusedArgs a) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     const int KH = a.KH, nbins = a.nbins, N = a.N, cpb = a.ctas_per_b;
@@ -143,10 +149,63 @@ __global__ void __launch_bounds__(NT, 1) scan_fused_kernel(const FusedArgs a) {
     SL_STAMP(1)
     sl::grid_barrier(a.sync + 2 * b, (unsigned)cpb, a.status);
     SL_STAMP(2)
+    const int W = KH * nbins + KH * NC;                          // words of one batch row's message
+    if (SHARD) {
+        unsigned* own_words = reinterpret_cast<unsigned*>(a.peer[a.rank] + a.pflags_off);   // [R flags][epoch][arrivals]
+        const unsigned target = __ldcg(own_words + a.R) + 1u;        // this launch's epoch
+#pragma unroll 1
+        for (int i = c * NT + tid; i < W; i += cpb * NT) {
+            unsigned v = 0;
+            if (i < KH * nbins) {
+#pragma unroll
+                for (int cp = 0; cp < NCOPY; ++cp) v += __ldcg(hist_b + cp * hslice + i);
+            } else {
+#pragma unroll
+                for (int cp = 0; cp < NCOPY; ++cp) v += __ldcg(chist_b + cp * cslice + (i - KH * nbins));
+            }
+            for (int r = 0; r < a.R; ++r)
+                reinterpret_cast<unsigned*>(a.peer[r] + (unsigned long long)a.rank * a.slot_stride)[b * W + i] = v;
+        }
+        __syncthreads();
+        if (tid == 0) {
+            // the last CTA of this rank to get here publishes the epoch on every rank: its fence and
+            // the arrival counter order every CTA's peer stores before the flags
+            __threadfence_system();
+            const unsigned old = atomicAdd(own_words + a.R + 1, 1u);
+            if (old == gridDim.x - 1u) {
+                own_words[a.R + 1] = 0;
+                __threadfence_system();
+                for (int r = 0; r < a.R; ++r) {
+                    unsigned* pf = reinterpret_cast<unsigned*>(a.peer[r] + a.pflags_off) + a.rank;
+                    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(pf), "r"(target) : "memory");
+                }
+            }
+        }
+        if (tid < a.R) {
+            const unsigned* lf = own_words + tid;
+            unsigned v = 0, it = 0;
+            for (;;) {
+                asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(lf) : "memory");
+                if ((int)(v - target) >= 0) break;
+                if (++it > 400000u) {    // about a second: give up, tell the host, finish with what is there
+                    if (a.status) atomicExch(a.status, 3);
+                    break;
+                }
+                __nanosleep(100);
+            }
+        }
+        __syncthreads();
+    }
+    // the histograms the threshold is searched in: the copies of the workspace, or the ranks' slots
+    const int nsl = SHARD ? a.R : NCOPY;
+    const unsigned* Fb = SHARD ? reinterpret_cast<const unsigned*>(a.peer[a.rank]) + b * W : hist_b;
+    const unsigned* Cb = SHARD ? Fb + KH * nbins : chist_b;
+    const long long fstr = SHARD ? (long long)(a.slot_stride >> 2) : (long long)hslice;
+    const long long cstr = SHARD ? (long long)(a.slot_stride >> 2) : (long long)cslice;
 
     // ------------------------------------------------------------------ B: threshold per head
     {
-        const int kk = min(a.k_budget, N);
+        const int kk = SHARD ? a.kk : min(a.k_budget, N);
         const int FPL = 1 << (a.cws - 5);                    // fine bins per lane in the second step
 #pragma unroll 1
         for (int h = warp; h < KH; h += NW) {
@@ -154,8 +213,8 @@ __global__ void __launch_bounds__(NT, 1) scan_fused_kernel(const FusedArgs a) {
             if (kk > 0) {
                 unsigned cv = 0;
                 if (lane < NC) {
-#pragma unroll
-                    for (int cp = 0; cp < NCOPY; ++cp) cv += __ldcg(chist_b + cp * cslice + h * NC + lane);
+#pragma unroll 4
+                    for (int sl_ = 0; sl_ < nsl; ++sl_) cv += __ldcg(Cb + sl_ * cstr + h * NC + lane);
                 }
                 const unsigned suf = suffix_sum(cv, lane);
                 const unsigned ball = __ballot_sync(0xffffffffu, suf >= (unsigned)kk);
@@ -164,20 +223,21 @@ __global__ void __launch_bounds__(NT, 1) scan_fused_kernel(const FusedArgs a) {
                 } else {
                     const int L = 31 - __clz(ball);
                     const unsigned above = __shfl_sync(0xffffffffu, suf - cv, L);    // keys in coarse bins above L
-                    const unsigned* F = hist_b + h * nbins;
+                    const unsigned* F = Fb + h * nbins;
                     const int f0 = (L << a.cws) + lane * FPL;
                     unsigned fv0 = 0, fv1 = 0, fs = 0;
                     if (FPL <= 2) {
-#pragma unroll
-                        for (int cp = 0; cp < NCOPY; ++cp) {
-                            if (f0 < nbins) fv0 += __ldcg(F + cp * hslice + f0);
-                            if (FPL == 2 && f0 + 1 < nbins) fv1 += __ldcg(F + cp * hslice + f0 + 1);
+#pragma unroll 4
+                        for (int sl_ = 0; sl_ < nsl; ++sl_) {
+                            if (f0 < nbins) fv0 += __ldcg(F + sl_ * fstr + f0);
+                            if (FPL == 2 && f0 + 1 < nbins) fv1 += __ldcg(F + sl_ * fstr + f0 + 1);
                         }
                         fs = fv0 + fv1;
                     } else {
 #pragma unroll 1
-                        for (int t = 0; t < FPL * NCOPY; ++t)
-                            if (f0 + (t >> 2) < nbins) fs += __ldcg(F + (t & (NCOPY - 1)) * hslice + f0 + (t >> 2));
+                        for (int t = 0; t < FPL; ++t)
+                            for (int sl_ = 0; sl_ < nsl; ++sl_)
+                                if (f0 + t < nbins) fs += __ldcg(F + sl_ * fstr + f0 + t);
                     }
                     const unsigned fsuf = suffix_sum(fs, lane);
                     const unsigned ball2 = __ballot_sync(0xffffffffu, above + fsuf >= (unsigned)kk);
@@ -192,7 +252,7 @@ __global__ void __launch_bounds__(NT, 1) scan_fused_kernel(const FusedArgs a) {
                                 v = t ? fv1 : fv0;
                             } else if (f0 + t < nbins) {
 #pragma unroll 1
-                                for (int cp = 0; cp < NCOPY; ++cp) v += __ldcg(F + cp * hslice + f0 + t);
+                                for (int sl_ = 0; sl_ < nsl; ++sl_) v += __ldcg(F + sl_ * fstr + f0 + t);
                             }
                             if (cum + v >= (unsigned)kk) { tau_l = f0 + t; gt_l = (int)cum; break; }
                             cum += v;
@@ -200,6 +260,11 @@ __global__ void __launch_bounds__(NT, 1) scan_fused_kernel(const FusedArgs a) {
                     }
                     tau = __shfl_sync(0xffffffffu, tau_l, L2);
                     r = kk - __shfl_sync(0xffffffffu, gt_l, L2);
+                    if (SHARD) {        // threshold ties on lower ranks come first in key order
+                        int e_lower = lane < a.rank ? (int)__ldcg(F + lane * fstr + tau) : 0;
+                        e_lower = __reduce_add_sync(0xffffffffu, e_lower);
+                        r = max(r - e_lower, 0);
+                    }
                 }
             }
             if (lane == 0) { s_tau[h] = tau; s_r[h] = r; }
@@ -386,6 +451,10 @@ __global__ void __launch_bounds__(NT, 1) scan_fused_kernel(const FusedArgs a) {
 #pragma unroll 1
         for (int i = c * NT + tid; i < NCOPY * ctot; i += cpb * NT) chist_b[(i / ctot) * cslice + i % ctot] = 0;
         __syncthreads();
+        if (SHARD && blockIdx.x == 0 && tid == 0) {      // every CTA read the epoch before the grid barrier
+            unsigned* epoch_w = reinterpret_cast<unsigned*>(a.peer[a.rank] + a.pflags_off) + a.R;
+            *epoch_w = __ldcg(epoch_w) + 1u;
+        }
         if (tid == 0) {
             unsigned* sync = a.sync + 2 * b;
             __threadfence();
@@ -401,12 +470,13 @@ __global__ void __launch_bounds__(NT, 1) scan_fused_kernel(const FusedArgs a) {
 
 typedef void (*fused_kernel_t)(const FusedArgs);
 
+template <bool SHARD>
 fused_kernel_t pick(int P) {
     switch (P) {
-        case 1: return scan_fused_kernel<1>;
-        case 2: return scan_fused_kernel<2>;
-        case 3: return scan_fused_kernel<3>;
-        default: return scan_fused_kernel<4>;
+        case 1: return scan_fused_kernel<1, SHARD>;
+        case 2: return scan_fused_kernel<2, SHARD>;
+        case 3: return scan_fused_kernel<3, SHARD>;
+        default: return scan_fused_kernel<4, SHARD>;
     }
 }
 
@@ -421,10 +491,15 @@ size_t fused_fixed_smem(int KH, int nbins, int S) {
            (size_t)KH * nbins * 4;
 }
 
+size_t shard_message_bytes(int B, int KH, int nbins, int cws) {
+    const int NC = ((nbins - 1) >> cws) + 1;
+    return ((size_t)B * (KH * nbins + KH * NC) * 4 + 15) / 16 * 16;
+}
+
 int launch_fused(const FusedArgs& a_in, size_t smem, cudaStream_t s) {
     FusedArgs a = a_in;
     a.dbg = g_dbg_timing;
-    fused_kernel_t kern = pick(sliced_planes(a.G));
+    fused_kernel_t kern = a.R > 0 ? pick<true>(sliced_planes(a.G)) : pick<false>(sliced_planes(a.G));
     SL_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     SL_CUDA_OK(sl::launch_kernel(kern, dim3((unsigned)(a.B * a.ctas_per_b)), dim3(NT), smem, s, true, a));
     return SL_OK;

@@ -816,6 +816,78 @@ extern "C" int sl_scan_hist(const uint32_t* d_q_codes, const uint32_t* d_k_codes
     return launch(a, p, static_cast<cudaStream_t>(stream));
 }
 
+extern "C" size_t sl_scan_topk_sharded_slot_bytes(int B, int KH, int QH) {
+    if (B <= 0 || KH <= 0 || QH <= 0 || QH % KH) return 0;
+    const int nbins = 128 * (QH / KH) + 1;
+    return slscan::shard_message_bytes(B, KH, nbins, coarse_shift(nbins));
+}
+
+extern "C" int sl_scan_topk_sharded(const uint32_t* d_q_codes, const uint32_t* d_k_codes, int64_t k_batch_stride, int B,
+                                    int64_t N_local, int64_t tok_offset, int64_t N_global, int KH, int QH,
+                                    int gqa_layout, int k, int sink, int recent, int32_t* d_idx, int idx_capacity,
+                                    int32_t* d_cnt, void* d_workspace, size_t workspace_bytes, void* const* peer_bufs,
+                                    int rank, int R, size_t slot_stride, int32_t* d_status, void* stream) {
+    SL_REQUIRE(d_q_codes && d_k_codes && d_idx && d_cnt && d_workspace && peer_bufs, SL_EINVAL,
+               "sl_scan_topk_sharded: null pointer");
+    if (int rc = check_common("sl_scan_topk_sharded", B, N_local, KH, QH)) return rc;
+    SL_REQUIRE(gqa_layout == SL_GQA_INTERLEAVED || gqa_layout == SL_GQA_BLOCKED, SL_EINVAL,
+               "sl_scan_topk_sharded: unknown gqa_layout %d", gqa_layout);
+    SL_REQUIRE(R >= 1 && R <= 8 && rank >= 0 && rank < R, SL_EINVAL, "sl_scan_topk_sharded: bad rank %d of %d", rank, R);
+    SL_REQUIRE(tok_offset >= 0 && tok_offset + N_local <= N_global, SL_ESHAPE, "sl_scan_topk_sharded: shard outside the context");
+    SL_REQUIRE(k >= 0 && sink >= 0 && recent >= 0, SL_EINVAL, "sl_scan_topk_sharded: negative k/sink/recent");
+    SL_REQUIRE(sl::aligned16(d_q_codes) && sl::aligned16(d_k_codes) && k_batch_stride % 4 == 0, SL_EALIGN,
+               "sl_scan_topk_sharded: codes must be 16-byte aligned");
+    SL_REQUIRE(k_batch_stride >= N_local * KH * 4, SL_ESHAPE, "sl_scan_topk_sharded: batch stride shorter than a batch row");
+    const int G = QH / KH;
+    const Plan p = make_plan(B, N_local, KH, G, false);
+    // the fused form needs every rank to run the lean kernel; other shapes use sl_scan_hist + sl_select_emit
+    SL_REQUIRE(p.cooperative && !p.spill && slscan::fused_covers(KH, G) && p.chunk < (1 << 21), SL_ESHAPE,
+               "sl_scan_topk_sharded: shape not covered by the fused kernel");
+    const WsLayout w = ws_layout(B, N_local, KH, G, true, false);
+    SL_REQUIRE(workspace_bytes >= w.total, SL_EWORKSPACE, "sl_scan_topk_sharded: workspace %zu < required %zu",
+               workspace_bytes, w.total);
+    const size_t msg = slscan::shard_message_bytes(B, KH, p.nbins, coarse_shift(p.nbins));
+    SL_REQUIRE(slot_stride >= msg && slot_stride % 16 == 0, SL_ESHAPE, "sl_scan_topk_sharded: slot of %zu bytes < message of %zu",
+               slot_stride, msg);
+    const int64_t s_end_g = std::min<int64_t>(sink, N_global);
+    const int64_t r_start_g = std::max<int64_t>(s_end_g, N_global - recent);
+    const int64_t s_end = std::min<int64_t>(std::max<int64_t>(s_end_g - tok_offset, 0), N_local);
+    const int64_t r_start = std::min<int64_t>(std::max<int64_t>(r_start_g - tok_offset, s_end), N_local);
+    const int64_t need = std::min<int64_t>(N_local, (int64_t)k + s_end + (N_local - r_start));
+    SL_REQUIRE(idx_capacity >= need, SL_ESHAPE, "sl_scan_topk_sharded: idx_capacity %d < %lld", idx_capacity, (long long)need);
+    unsigned char* ws = static_cast<unsigned char*>(d_workspace);
+    slscan::FusedArgs f = {};
+    f.q = reinterpret_cast<const uint4*>(d_q_codes);
+    f.k = reinterpret_cast<const uint4*>(d_k_codes);
+    f.k_bstride = k_batch_stride / 4;
+    f.B = B; f.KH = KH; f.G = G; f.layout = gqa_layout; f.N = (int)N_local;
+    f.k_budget = k;
+    f.kk = (int)std::min<int64_t>(k, N_global);
+    f.s_end = (int)s_end; f.r_start = (int)r_start;
+    f.idx = d_idx; f.cap = idx_capacity; f.cnt = d_cnt;
+    f.hist = reinterpret_cast<unsigned*>(ws + w.hist_off);
+    f.chist = reinterpret_cast<unsigned*>(ws + w.chist_off);
+    f.seg = reinterpret_cast<unsigned long long*>(ws + w.seg_off);
+    f.sync = reinterpret_cast<unsigned*>(ws + w.sync_off);
+    f.status = d_status;
+    f.ctas_per_b = p.ctas_per_b; f.chunk = p.chunk; f.nbins = p.nbins; f.S = p.S;
+    f.cws = coarse_shift(p.nbins);
+    const int roww = (p.chunk >> 1) + ((4 - (p.chunk >> 1)) & 31);
+    f.rowh = 2 * roww;
+    const size_t score_off = align_up(slscan::fused_fixed_smem(KH, p.nbins, p.S), 16);
+    f.score_off = (int)score_off;
+    const size_t smem = score_off + (size_t)(p.chunk + 64) * KH * 2;
+    SL_REQUIRE(smem <= (size_t)SMEM_BUDGET + 16 * 1024, SL_ESHAPE, "sl_scan_topk_sharded: chunk does not fit in shared memory");
+    for (int r = 0; r < R; ++r) {
+        SL_REQUIRE(peer_bufs[r] != nullptr && sl::aligned16(peer_bufs[r]), SL_EINVAL, "sl_scan_topk_sharded: bad buffer of rank %d", r);
+        f.peer[r] = static_cast<unsigned char*>(peer_bufs[r]);
+    }
+    f.R = R; f.rank = rank;
+    f.slot_stride = slot_stride;
+    f.pflags_off = (unsigned long long)R * slot_stride;
+    return slscan::launch_fused(f, smem, static_cast<cudaStream_t>(stream));
+}
+
 extern "C" size_t sl_select_emit_workspace_bytes(int B, int64_t N_local, int KH, int QH) {
     if (B <= 0 || N_local < 0 || KH <= 0 || QH <= 0 || QH % KH) return 0;
     return ws_layout(B, N_local, KH, QH / KH, false, false).total;

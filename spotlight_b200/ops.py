@@ -221,6 +221,38 @@ def scan_topk(q_codes: torch.Tensor, k_codes: torch.Tensor, k: int, sink: int = 
     return (idx, cnt, scores) if return_scores else (idx, cnt)
 
 
+def scan_topk_sharded(q_codes: torch.Tensor, k_codes: torch.Tensor, peer, tok_offset: int, n_global: int, k: int,
+                      sink: int = 4, recent: int = 64, layout: int = GQA_BLOCKED):
+    """One rank's share of the global selection in ONE launch (see sl_scan_topk_sharded): local scan,
+    histogram exchange through the peer buffer `peer` (sharded.PeerBuffer sized with
+    scan_sharded_slot_bytes), emission of LOCAL indices. Raises ValueError when the fused kernel does
+    not cover the shape."""
+    if q_codes.dim() == 4:
+        q_codes = q_codes[:, 0]
+    B, QH, _ = q_codes.shape
+    _, N, KH, _ = k_codes.shape
+    dev = _cuda(q_codes, k_codes)
+    q_codes = q_codes.contiguous()
+    kb = _rows_view(k_codes, 4)
+    s_end = min(sink, n_global)
+    r_start = max(s_end, n_global - recent)
+    forced = max(0, min(s_end - tok_offset, N)) + max(0, tok_offset + N - max(r_start, tok_offset))
+    cap = max(1, min(N, k + forced))
+    idx = torch.empty((B, KH, cap), dtype=torch.int32, device=dev)
+    cnt = torch.empty((B, KH), dtype=torch.int32, device=dev)
+    need = lib.sl_scan_topk_workspace_bytes(B, N, KH, QH)
+    ws, status = workspaces.get("scan", dev, need, (B, KH, QH))
+    check(lib.sl_scan_topk_sharded(q_codes.data_ptr(), k_codes.data_ptr(), kb, B, N, tok_offset, n_global, KH, QH, layout,
+                                   k, sink, recent, idx.data_ptr(), cap, cnt.data_ptr(), ws.data_ptr(), ws.numel(),
+                                   peer.bufs, peer.rank, peer.world, peer.nbytes, status.data_ptr(), _stream()))
+    _count()
+    return idx, cnt
+
+
+def scan_sharded_slot_bytes(B: int, KH: int, QH: int) -> int:
+    return int(lib.sl_scan_topk_sharded_slot_bytes(B, KH, QH))
+
+
 def topk_from_scores(scores: torch.Tensor, k: int, max_score: int, sink: int = 0, recent: int = 0):
     """scores int16 [B,N,KH] in [0,max_score] -> (idx int32 [B,KH,cap] ascending, cnt int32 [B,KH])."""
     B, N, KH = scores.shape

@@ -34,12 +34,10 @@ def _all_gather(t: torch.Tensor, group) -> torch.Tensor:
     return out
 
 
-class PeerExchange:
-    """All-gather of one fixed-size message per rank over peer memory (sl_peer_allgather): every
-    rank owns a buffer of `world` slots that its peers map through CUDA IPC, one kernel per exchange
-    stores the message into every rank's buffer and waits (bounded) for the others. Same result as
-    `_all_gather`, without a collective library on the critical path; the handles travel once, at
-    construction, through torch.distributed. The ranks must be GPUs of one node."""
+class PeerBuffer:
+    """One rank's exchange buffer ([world slots of nbytes][flags][epoch]) mapped into every rank of
+    the group through CUDA IPC; the handles travel once, here, through torch.distributed. The ranks
+    must be GPUs of one node. `bufs[r]` is rank r's buffer as seen from this process."""
 
     def __init__(self, nbytes: int, device: torch.device, group=None):
         import ctypes as C
@@ -57,36 +55,18 @@ class PeerExchange:
         check(lib.sl_peer_export(self._own, handle))
         handles = [None] * self.world
         dist.all_gather_object(handles, bytes(handle.raw), group=group)
-        self._bufs = (C.c_void_p * self.world)()
+        self.bufs = (C.c_void_p * self.world)()
         self._opened = []
         for r in range(self.world):
             if r == self.rank:
-                self._bufs[r] = self._own
+                self.bufs[r] = self._own
             else:
                 ptr = C.c_void_p()
                 check(lib.sl_peer_open(C.create_string_buffer(handles[r], 64), C.byref(ptr)))
-                self._bufs[r] = ptr.value
+                self.bufs[r] = ptr.value
                 self._opened.append(ptr.value)
         self.status = torch.zeros(1, dtype=torch.int32, device=device)
         dist.barrier(group)                      # every buffer is mapped everywhere before the first store
-
-    def _slots(self, dtype: torch.dtype, shape) -> torch.Tensor:
-        """The own buffer's slots as a tensor [world, *shape] (no copy)."""
-        class _Raw:
-            pass
-        raw = _Raw()
-        raw.__cuda_array_interface__ = {"shape": (self.world * self.nbytes,), "typestr": "|u1",
-                                        "data": (self._own, False), "version": 3}
-        flat = torch.as_tensor(raw, device=self.device)
-        return flat.view(dtype).view(self.world, *shape)
-
-    def all_gather(self, t: torch.Tensor) -> torch.Tensor:
-        t = t.contiguous()
-        assert t.numel() * t.element_size() == self.nbytes, "message size is fixed at construction"
-        stream = torch.cuda.current_stream(self.device).cuda_stream
-        self._check(self._lib.sl_peer_allgather(t.data_ptr(), self.nbytes, self._bufs, self.rank, self.world,
-                                                self.nbytes, self.status.data_ptr(), stream))
-        return self._slots(t.dtype, t.shape)
 
     def check_status(self):
         code = int(self.status.item())
@@ -102,6 +82,55 @@ class PeerExchange:
             self._own = None
 
 
+class PeerExchange(PeerBuffer):
+    """All-gather of one fixed-size message per rank over peer memory (sl_peer_allgather): one
+    kernel per exchange stores the message into every rank's buffer and waits (bounded) for the
+    others. Same result as `_all_gather`, without a collective library on the critical path."""
+
+    def _slots(self, dtype: torch.dtype, shape) -> torch.Tensor:
+        """The own buffer's slots as a tensor [world, *shape] (no copy)."""
+        class _Raw:
+            pass
+        raw = _Raw()
+        raw.__cuda_array_interface__ = {"shape": (self.world * self.nbytes,), "typestr": "|u1",
+                                        "data": (self._own, False), "version": 3}
+        flat = torch.as_tensor(raw, device=self.device)
+        return flat.view(dtype).view(self.world, *shape)
+
+    def all_gather(self, t: torch.Tensor) -> torch.Tensor:
+        t = t.contiguous()
+        assert t.numel() * t.element_size() == self.nbytes, "message size is fixed at construction"
+        stream = torch.cuda.current_stream(self.device).cuda_stream
+        self._check(self._lib.sl_peer_allgather(t.data_ptr(), self.nbytes, self.bufs, self.rank, self.world,
+                                                self.nbytes, self.status.data_ptr(), stream))
+        return self._slots(t.dtype, t.shape)
+
+
+    def merge_lse(self, o: torch.Tensor, lse: torch.Tensor) -> torch.Tensor:
+        """This rank's partial (o [...,128], lse [...]) -> the merge of all ranks' partials, one launch
+        (pack, exchange, log-sum-exp merge: sl_peer_merge_lse)."""
+        from .ops import _dt
+        o, lse = o.contiguous(), lse.contiguous()
+        assert lse.dtype == torch.float32
+        rows = o.numel() // 128
+        assert rows * 129 * 4 <= self.nbytes, "partials do not fit the slot"
+        out = torch.empty_like(o)
+        stream = torch.cuda.current_stream(self.device).cuda_stream
+        self._check(self._lib.sl_peer_merge_lse(o.data_ptr(), lse.data_ptr(), _dt(o), rows, self.bufs, self.rank,
+                                                self.world, self.nbytes, out.data_ptr(), self.status.data_ptr(), stream))
+        return out
+
+
+def make_peer_exchange(B: int, KH: int, QH: int, device: torch.device, group=None, fused_scan: bool = True):
+    """The peer buffers of a sequence-sharded step: (histograms, partials[, fused-scan buffer])."""
+    from . import ops
+    G = QH // KH
+    ex = [PeerExchange(B * KH * (128 * G + 1) * 4, device, group), PeerExchange(B * QH * 129 * 4, device, group)]
+    if fused_scan:
+        ex.append(PeerBuffer(ops.scan_sharded_slot_bytes(B, KH, QH), device, group))
+    return tuple(ex)
+
+
 def sharded_decode_attention(q_rot: torch.Tensor, q_codes: torch.Tensor, codes_local: torch.Tensor,
                              k_local: torch.Tensor, v_local: torch.Tensor, tok_offset: int, n_global: int,
                              k_budget: int, sink: int = 4, recent: int = 64, layout: int = 1, group=None,
@@ -109,17 +138,27 @@ def sharded_decode_attention(q_rot: torch.Tensor, q_codes: torch.Tensor, codes_l
     """One layer-step on this rank. q_rot [B,QH,128], q_codes uint32 [B,QH,4] (identical on all
     ranks); codes_local [B,n_local,KH,4], k_local / v_local [B,n_local,KH,128]: this rank's keys
     [tok_offset, tok_offset + n_local). Returns the merged output [B,QH,128] (identical on all
-    ranks) and, on request, this rank's attended LOCAL indices and counts. `exchange`: a pair of
-    PeerExchange objects (histograms, partials) to use instead of the group's all-gathers."""
+    ranks) and, on request, this rank's attended LOCAL indices and counts. `exchange`: the tuple of
+    make_peer_exchange (histograms, partials[, fused-scan buffer]) to use peer memory instead of the
+    group's all-gathers; with the third buffer the scan, the histogram exchange and the emission are
+    one launch (sl_scan_topk_sharded)."""
     if backend is None:
         from . import ops as backend
     rank, world = dist.get_rank(group), dist.get_world_size(group)
     QH = q_rot.shape[1]
-    scores, hist = backend.scan_hist(q_codes, codes_local, layout)
-    hist_all = exchange[0].all_gather(hist) if exchange else _all_gather(hist, group)
-    idx, cnt = backend.select_emit(scores, hist_all, rank, tok_offset, n_global, QH, k_budget, sink, recent)
+    if exchange and len(exchange) > 2:
+        # one launch: local scan, histograms to the peers, wait for theirs, emit
+        idx, cnt = backend.scan_topk_sharded(q_codes, codes_local, exchange[2], tok_offset, n_global, k_budget,
+                                             sink, recent, layout)
+    else:
+        scores, hist = backend.scan_hist(q_codes, codes_local, layout)
+        hist_all = exchange[0].all_gather(hist) if exchange else _all_gather(hist, group)
+        idx, cnt = backend.select_emit(scores, hist_all, rank, tok_offset, n_global, QH, k_budget, sink, recent)
     o, lse = backend.sparse_attn_decode(q_rot, k_local, v_local, idx, cnt, layout, return_lse=True)
-    packed = torch.cat([o.float(), lse[..., None]], dim=-1)          # one message: [B,QH,129]
-    parts = exchange[1].all_gather(packed) if exchange else _all_gather(packed, group)
-    out = backend.merge_lse(parts[..., :128].contiguous(), parts[..., 128].contiguous(), q_rot.dtype)
+    if exchange:
+        out = exchange[1].merge_lse(o, lse)                          # pack + exchange + merge in one launch
+    else:
+        packed = torch.cat([o.float(), lse[..., None]], dim=-1)      # one message: [B,QH,129]
+        parts = _all_gather(packed, group)
+        out = backend.merge_lse(parts[..., :128].contiguous(), parts[..., 128].contiguous(), q_rot.dtype)
     return (out, idx, cnt) if return_selection else out

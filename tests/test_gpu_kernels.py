@@ -512,3 +512,36 @@ def test_peer_allgather_single_rank(ops):
             check(lib.sl_peer_allgather(msg.data_ptr(), 24, bufs, 0, 1, nbytes, status.data_ptr(), stream))
     finally:
         check(lib.sl_peer_free(buf))
+
+
+@pytest.mark.parametrize("B,N,KH,QH,k", [(1, 131072, 8, 32, 13108), (2, 60000, 4, 28, 1200), (1, 40000, 8, 40, 800)])
+def test_scan_topk_sharded_single_rank(ops, B, N, KH, QH, k):
+    """The one-launch sharded scan with a world of one rank (histograms go through the rank's own
+    exchange buffer) must reproduce sl_scan_topk; run three times: epochs advance, buffers are reused."""
+    import ctypes as C
+    from spotlight_b200._lib import check, lib
+
+    class Peer:
+        pass
+    peer = Peer()
+    peer.rank, peer.world = 0, 1
+    peer.nbytes = ops.scan_sharded_slot_bytes(B, KH, QH)
+    own = C.c_void_p()
+    check(lib.sl_peer_alloc(lib.sl_peer_buffer_bytes(1, peer.nbytes), C.byref(own)))
+    peer.bufs = (C.c_void_p * 1)(own.value)
+    try:
+        g = torch.Generator().manual_seed(N + KH)
+        q = rand_codes(g, (B, QH, 4), True).to(DEV)
+        cache = rand_codes(g, (B, N, KH, 4), True).to(DEV)
+        ref_idx, ref_cnt = ops.scan_topk(q, cache, k, 4, 64, O.BLOCKED)
+        for _ in range(3):
+            idx, cnt = ops.scan_topk_sharded(q, cache, peer, 0, N, k, 4, 64, O.BLOCKED)
+            torch.testing.assert_close(cnt, ref_cnt, rtol=0, atol=0)
+            for b in range(B):
+                for h in range(KH):
+                    c = int(cnt[b, h])
+                    torch.testing.assert_close(idx[b, h, :c], ref_idx[b, h, :c], rtol=0, atol=0)
+        ops.check_status()
+    finally:
+        torch.cuda.synchronize()
+        check(lib.sl_peer_free(own))

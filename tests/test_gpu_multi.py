@@ -43,9 +43,9 @@ def _worker(rank, world, port, n, keep, ret, peer=False):
         q, q_codes, codes, k, v = _inputs(n, 1, 8, 40)
         lo, hi = shard_bounds(n, world, rank)
         exchange = None
-        if peer:            # the two all-gathers over peer memory instead of NCCL
-            from spotlight_b200.sharded import PeerExchange
-            exchange = (PeerExchange(1 * 8 * (128 * 5 + 1) * 4, dev), PeerExchange(1 * 40 * 129 * 4, dev))
+        if peer:            # the exchanges over peer memory instead of NCCL; "fused": scan + exchange + emit in one launch
+            from spotlight_b200.sharded import make_peer_exchange
+            exchange = make_peer_exchange(1, 8, 40, dev, fused_scan=(peer == "fused"))
         args = (q.to(dev), q_codes.to(dev), codes[:, lo:hi].contiguous().to(dev), k[:, lo:hi].contiguous().to(dev),
                 v[:, lo:hi].contiguous().to(dev), lo, n, keep, 4, 64, O.BLOCKED)
         for _ in range(3 if peer else 1):            # several rounds: the exchange buffers are reused
@@ -64,7 +64,7 @@ def _worker(rank, world, port, n, keep, ret, peer=False):
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs at least two GPUs")
-@pytest.mark.parametrize("peer", [False, True], ids=["nccl", "peer-memory"])
+@pytest.mark.parametrize("peer", [False, True, "fused"], ids=["nccl", "peer-memory", "peer-memory-fused-scan"])
 def test_sequence_sharded_attention_over_nccl(peer):
     import torch.multiprocessing as mp
     world = min(torch.cuda.device_count(), 4)
