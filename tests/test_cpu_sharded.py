@@ -76,6 +76,28 @@ class CpuBackend:
         return ((o_parts * w[..., None]).sum(0) / w.sum(0)[..., None]).to(dtype)
 
 
+class CpuExchange:
+    """The surface of sharded.PeerExchange / PeerBuffer served by gloo, so that the driver's
+    peer-memory branches (one-launch scan, one-launch partial merge) run on the CPU."""
+
+    def all_gather(self, t):
+        from spotlight_b200.sharded import _all_gather
+        return _all_gather(t, None)
+
+    def merge_lse(self, o, lse):
+        parts = self.all_gather(torch.cat([o.float(), lse[..., None].float()], dim=-1))
+        return CpuBackend.merge_lse(parts[..., :128].contiguous(), parts[..., 128].contiguous(), o.dtype)
+
+
+def _scan_topk_sharded(q_codes, codes_local, peer, tok_offset, n_global, k, sink, recent, layout):
+    scores, hist = CpuBackend.scan_hist(q_codes, codes_local, layout)
+    hist_all = peer.all_gather(hist)
+    return CpuBackend.select_emit(scores, hist_all, dist.get_rank(), tok_offset, n_global, q_codes.shape[1], k, sink, recent)
+
+
+CpuBackend.scan_topk_sharded = staticmethod(_scan_topk_sharded)
+
+
 def _free_port():
     with socket.socket() as s:
         s.bind(("127.0.0.1", 0))
@@ -97,7 +119,7 @@ def _make(n, B, KH, QH, seed, low_entropy):
     return q, q_codes.to(torch.int32).view(torch.uint32), codes.to(torch.int32).view(torch.uint32), k, v
 
 
-def _worker(rank, world, port, n, keep, low_entropy, ret):
+def _worker(rank, world, port, n, keep, low_entropy, ret, peer_branches=False):
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
     dist.init_process_group("gloo", rank=rank, world_size=world)
@@ -107,17 +129,20 @@ def _worker(rank, world, port, n, keep, low_entropy, ret):
         q, q_codes, codes, k, v = _make(n, B, KH, QH, 5, low_entropy)   # every rank builds the same global tensors
         lo, hi = shard_bounds(n, world, rank)
         out, idx, cnt = sharded_decode_attention(q, q_codes, codes[:, lo:hi], k[:, lo:hi], v[:, lo:hi], lo, n, keep,
-                                                 4, 64, O.BLOCKED, backend=CpuBackend, return_selection=True)
+                                                 4, 64, O.BLOCKED, backend=CpuBackend, return_selection=True,
+                                                 exchange=(CpuExchange(), CpuExchange(), CpuExchange()) if peer_branches else None)
         ret[rank] = (out.numpy(), idx.numpy() + lo, cnt.numpy())
     finally:
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("world,n,keep,low", [(2, 700, 60, True), (2, 90, 20, False), (3, 1000, 100, True), (2, 70, 5, True)])
-def test_sequence_sharded_driver_equals_unsharded(world, n, keep, low):
+@pytest.mark.parametrize("world,n,keep,low,peer_branches",
+                         [(2, 700, 60, True, False), (2, 90, 20, False, False), (3, 1000, 100, True, False),
+                          (2, 70, 5, True, False), (2, 700, 60, True, True), (3, 500, 40, False, True)])
+def test_sequence_sharded_driver_equals_unsharded(world, n, keep, low, peer_branches):
     mgr = mp.Manager()
     ret = mgr.dict()
-    mp.spawn(_worker, args=(world, _free_port(), n, keep, low, ret), nprocs=world, join=True)
+    mp.spawn(_worker, args=(world, _free_port(), n, keep, low, ret, peer_branches), nprocs=world, join=True)
     B, KH, QH = 2, 2, 6
     q, q_codes, codes, k, v = _make(n, B, KH, QH, 5, low)
     scores = O.match_count(q_codes.view(torch.int32).numpy().view(np.uint32)[:, None],
