@@ -184,7 +184,7 @@ def workload_config(cfg):
 # ------------------------------------------------------------------------------------------
 # GPU arm
 # ------------------------------------------------------------------------------------------
-def build_session(cfg, device):
+def build_session(cfg, device, lru=False):
     from spotlight_b200 import ops
     from spotlight_b200.session import DecodeSession, SessionConfig
     from spotlight_b200.workloads import apply_rope, rope_tables, torch_dtype
@@ -197,8 +197,9 @@ def build_session(cfg, device):
         pk = pq if cfg.q_heads == cfg.kv_heads else make_hash_params(cfg.hash, cfg.kv_heads, cfg.mlp_dims, gen, dt)
         hq.append(ops.HashParams.from_dict(pq, device, cfg.mlp_residue))
         hk.append(ops.HashParams.from_dict(pk, device, cfg.mlp_residue))
+    lru_slots = 2 * (budget(n, cfg.mask_out, cfg.min_remain) + cfg.sink + cfg.recent) if lru else 0
     scfg = SessionConfig(cfg.batch, cfg.q_heads, cfg.kv_heads, cfg.layers, n, dt, cfg.mask_out, cfg.min_remain,
-                         cfg.sink, cfg.recent)
+                         cfg.sink, cfg.recent, lru_slots=lru_slots)
     s = DecodeSession(scfg, hq, hk, device)
     dgen = torch.Generator(device=device).manual_seed(cfg.seed)
     ch = torch.randperm(HEAD_DIM, generator=gen)[:4].to(device)
@@ -262,7 +263,7 @@ def run_ours(args, cfg):
         dist = dist_
     from spotlight_b200 import ops
 
-    s, code_build_ms = build_session(cfg, device)
+    s, code_build_ms = build_session(cfg, device, lru=args.lru)
     n, L = cfg.context, cfg.layers
     pos = n - 1
 
@@ -292,7 +293,7 @@ def run_ours(args, cfg):
     with ClockSampler(local) as clocks:
         ms_step = time_graph(g_all if use_graph else Eager(), args.steps, args.warmup, device, dist)
         stage_ms = {}
-        for stage in ("prepare", "scan", "attn"):
+        for stage in ("prepare", "scan", "attn") + (("lru",) if args.lru else ()):
             g = s.capture(pos, stage) if use_graph else Eager(stage)
             stage_ms[stage] = time_graph(g, max(3, args.steps // 2), 3, device) / L
         # end to end: pinned host inputs in, outputs back, one host sync per token
@@ -335,6 +336,8 @@ def run_ours(args, cfg):
         "sparse_attn": {"bytes": by_attn, "us": stage_ms["attn"] * 1e3},
         "decode_prepare": {"bytes": wbytes, "us": stage_ms["prepare"] * 1e3},
     }
+    if args.lru:     # stage 3: bytes of the slot tables it walks (rows only move on misses; none in a replayed step)
+        kern["lru_update"] = {"bytes": cfg.batch * cfg.kv_heads * s.cfg.lru_slots * 8, "us": stage_ms["lru"] * 1e3}
     for k_, d in kern.items():
         d["gbs"] = d["bytes"] / (d["us"] * 1e-6) / 1e9
         d["frac"] = d["gbs"] / peak
@@ -348,7 +351,8 @@ def run_ours(args, cfg):
         "e2e": {"value": max(ms_e2e, wall_e2e) * 1e3 / L, "unit": UNIT,
                 "h2d_bytes_per_step": s.host_bytes_per_step[0], "d2h_bytes_per_step": s.host_bytes_per_step[1],
                 "device_ms_per_step": ms_e2e, "wall_ms_per_step": wall_e2e},
-        "gpu_launches": 4 * L * args.steps,
+        "gpu_launches": (5 if args.lru else 4) * L * args.steps,
+        "lru_stage": bool(args.lru),
         "cuda_graph": use_graph,
         "roofline": {"bound": "hbm", "kernel": dom, "achieved": kern[dom]["gbs"], "peak": peak, "unit": "GB/s",
                      "frac": kern[dom]["frac"], "traffic": NCU_TRAFFIC[dom], "peak_kind": peak_kind,
@@ -502,6 +506,8 @@ def main():
     ap.add_argument("--mask-out", type=float, default=None)
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--lru", action="store_true",
+                    help="include stage 3: update an LRU-resident K/V buffer every layer-step and attend over it")
     ap.add_argument("--peer", action="store_true",
                     help="with --sharded: exchange over peer memory (sl_peer_allgather) instead of NCCL all-gathers")
     ap.add_argument("--no-fused-scan", action="store_true",

@@ -217,7 +217,7 @@ extern "C" int sl_peer_close(void* d_ptr) {
 
 extern "C" size_t sl_peer_buffer_bytes(int R, size_t slot_stride) {
     if (R <= 0 || R > MAX_RANKS) return 0;
-    return (size_t)R * slot_stride + (size_t)(R + 1) * 4 + 60;
+    return (size_t)R * slot_stride + 8192;      // slots, then 8 KB of flag and epoch words
 }
 
 extern "C" int sl_peer_allgather(const void* d_src, size_t bytes, void* const* peer_bufs, int rank, int R,

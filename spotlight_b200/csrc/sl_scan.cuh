@@ -9,6 +9,7 @@ constexpr int NT = 512;            // threads per CTA
 constexpr int NW = NT / 32;
 constexpr int U = 8;               // 16-byte loads in flight per thread
 constexpr int NCOPY = 4;           // copies of the global histograms in the workspace
+constexpr int SHARD_EPOCH_WORD = 2040;   // the flag area of an exchange buffer is 8 KB: [R][B] flags, epoch here
 
 struct FusedArgs {
     const uint4* q;            // [B,QH] codes
@@ -33,7 +34,7 @@ struct FusedArgs {
     unsigned long long* dbg;   // optional [grid][16] phase stamps (development aid)
     // sequence shards (R > 0): N, s_end, r_start, idx are local to this rank's keys; the merged local
     // histograms travel to every rank's exchange buffer and the threshold comes from all R of them
-    unsigned char* peer[8];    // exchange buffer of every rank: [R slots][R flags][epoch][arrivals]
+    unsigned char* peer[8];    // exchange buffer of every rank: [R slots][flags [R][B] ... epoch]
     int R, rank;
     unsigned long long slot_stride, pflags_off;
     int kk;                    // min(k, global number of keys)

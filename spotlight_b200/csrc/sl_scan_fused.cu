@@ -24,9 +24,9 @@ using namespace slscan;
 
 // SHARD: this rank holds a contiguous part of a longer context. After the grid barrier the CTAs
 // merge the copies of the local histograms and store them into slot `rank` of every rank's exchange
-// buffer (plain peer stores over NVLink) and fence at system scope; the last CTA to arrive writes
-// this launch's epoch into flag `rank` of every buffer; then all CTAs wait (bounded) until the R
-// flags of the own buffer carry the epoch. The threshold is then searched over the R slots, and the ties
+// buffer (plain peer stores over NVLink; one CTA per batch row does it), fences at system scope and
+// writes this launch's epoch into the row's flag `rank` of every buffer; then the row's CTAs wait
+// (bounded) until the R flags of the row in the own buffer carry the epoch. The threshold is then searched over the R slots, and the ties
 // that belong to lower ranks (lower key indices) are taken off this rank's tie quota.
 template <int PT, bool SHARD>
 __global__ void __launch_bounds__(NT, 1) scan_fused_kernel(const FusedArgs a) {
@@ -151,38 +151,45 @@ __global__ void __launch_bounds__(NT, 1) scan_fused_kernel(const FusedArgs a) {
     SL_STAMP(2)
     const int W = KH * nbins + KH * NC;                          // words of one batch row's message
     if (SHARD) {
-        unsigned* own_words = reinterpret_cast<unsigned*>(a.peer[a.rank] + a.pflags_off);   // [R flags][epoch][arrivals]
-        const unsigned target = __ldcg(own_words + a.R) + 1u;        // this launch's epoch
-#pragma unroll 1
-        for (int i = c * NT + tid; i < W; i += cpb * NT) {
-            unsigned v = 0;
-            if (i < KH * nbins) {
+        // own buffer: [R slots][flags [R][B]] ... [epoch at word SHARD_EPOCH_WORD of the flag area]
+        unsigned* own_words = reinterpret_cast<unsigned*>(a.peer[a.rank] + a.pflags_off);
+        const unsigned target = __ldcg(own_words + SHARD_EPOCH_WORD) + 1u;        // this launch's epoch
+        if (c == 0) {
+            // One CTA per batch row carries the row's message (a few thousand words) to every rank and
+            // then publishes the epoch in the row's flag on every rank. A system-scope fence costs
+            // about 2.5 us on this machine, so exactly one is executed on the sending side.
+            for (int i0 = tid; i0 < W; i0 += NT * 4) {
+                unsigned v[4] = {0u, 0u, 0u, 0u};
 #pragma unroll
-                for (int cp = 0; cp < NCOPY; ++cp) v += __ldcg(hist_b + cp * hslice + i);
-            } else {
+                for (int j = 0; j < 4; ++j) {                // all loads of four rounds in flight together
+                    const int i = i0 + j * NT;
+                    if (i < KH * nbins) {
 #pragma unroll
-                for (int cp = 0; cp < NCOPY; ++cp) v += __ldcg(chist_b + cp * cslice + (i - KH * nbins));
+                        for (int cp = 0; cp < NCOPY; ++cp) v[j] += __ldcg(hist_b + cp * hslice + i);
+                    } else if (i < W) {
+#pragma unroll
+                        for (int cp = 0; cp < NCOPY; ++cp) v[j] += __ldcg(chist_b + cp * cslice + (i - KH * nbins));
+                    }
+                }
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const int i = i0 + j * NT;
+                    if (i < W)
+                        for (int r = 0; r < a.R; ++r)
+                            reinterpret_cast<unsigned*>(a.peer[r] + (unsigned long long)a.rank * a.slot_stride)[b * W + i] = v[j];
+                }
             }
-            for (int r = 0; r < a.R; ++r)
-                reinterpret_cast<unsigned*>(a.peer[r] + (unsigned long long)a.rank * a.slot_stride)[b * W + i] = v;
-        }
-        __syncthreads();
-        if (tid == 0) {
-            // the last CTA of this rank to get here publishes the epoch on every rank: its fence and
-            // the arrival counter order every CTA's peer stores before the flags
-            __threadfence_system();
-            const unsigned old = atomicAdd(own_words + a.R + 1, 1u);
-            if (old == gridDim.x - 1u) {
-                own_words[a.R + 1] = 0;
-                __threadfence_system();
+            __syncthreads();
+            if (tid == 0) {
+                __threadfence_system();      // the CTA's peer stores (ordered before this by the barrier) first
                 for (int r = 0; r < a.R; ++r) {
-                    unsigned* pf = reinterpret_cast<unsigned*>(a.peer[r] + a.pflags_off) + a.rank;
-                    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(pf), "r"(target) : "memory");
+                    unsigned* pf = reinterpret_cast<unsigned*>(a.peer[r] + a.pflags_off) + a.rank * a.B + b;
+                    asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(pf), "r"(target) : "memory");
                 }
             }
         }
         if (tid < a.R) {
-            const unsigned* lf = own_words + tid;
+            const unsigned* lf = own_words + tid * a.B + b;
             unsigned v = 0, it = 0;
             for (;;) {
                 asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(lf) : "memory");
@@ -191,7 +198,7 @@ __global__ void __launch_bounds__(NT, 1) scan_fused_kernel(const FusedArgs a) {
                     if (a.status) atomicExch(a.status, 3);
                     break;
                 }
-                __nanosleep(100);
+                __nanosleep(64);
             }
         }
         __syncthreads();
@@ -451,8 +458,8 @@ __global__ void __launch_bounds__(NT, 1) scan_fused_kernel(const FusedArgs a) {
 #pragma unroll 1
         for (int i = c * NT + tid; i < NCOPY * ctot; i += cpb * NT) chist_b[(i / ctot) * cslice + i % ctot] = 0;
         __syncthreads();
-        if (SHARD && blockIdx.x == 0 && tid == 0) {      // every CTA read the epoch before the grid barrier
-            unsigned* epoch_w = reinterpret_cast<unsigned*>(a.peer[a.rank] + a.pflags_off) + a.R;
+        if (SHARD && blockIdx.x == 0 && tid == 0) {      // every CTA read the epoch before it went on to emit
+            unsigned* epoch_w = reinterpret_cast<unsigned*>(a.peer[a.rank] + a.pflags_off) + SHARD_EPOCH_WORD;
             *epoch_w = __ldcg(epoch_w) + 1u;
         }
         if (tid == 0) {

@@ -36,6 +36,7 @@ class SessionConfig:
     recent: int = 64
     layout: int = GQA_BLOCKED
     fix_layers: tuple = ()             # layers that attend to every key
+    lru_slots: int = 0                 # > 0: attend over an LRU-resident K/V buffer of this many slots per (row, kv head)
 
 
 class DecodeSession:
@@ -62,6 +63,12 @@ class DecodeSession:
         cap = min(C, budget(C, cfg.mask_out, cfg.min_remain) + cfg.sink + cfg.recent + 1)
         self.idx = torch.empty((B, KH, cap), dtype=torch.int32, device=dev)
         self.cnt = torch.zeros((B, KH), dtype=torch.int32, device=dev)
+        # stage 3 (optional): the attended keys are made resident in a per-layer LRU buffer and the
+        # attention reads that buffer through the slots the update returns
+        self.lru = None
+        if cfg.lru_slots > 0:
+            self.lru = [ops.LruTable(B, KH, C, cfg.lru_slots, dt, dev) for _ in range(L)]
+            self.slots = torch.empty_like(self.idx)
         self._graphs = {}
         self._host = None
 
@@ -99,9 +106,16 @@ class DecodeSession:
                 raise NotImplementedError("dense layers are served by the attention hook, not the session")
             ops.scan_topk(self.q_codes, self.codes[layer][:, :n], budget(n, c.mask_out, c.min_remain), c.sink,
                           c.recent, c.layout, idx=self.idx, cnt=self.cnt)
+        if self.lru is not None and stage in (None, "lru"):
+            ops.lru_update(self.lru[layer], self.idx, self.cnt, self.k_cache[layer][:, :n], self.v_cache[layer][:, :n],
+                           slots_out=self.slots)
         if stage in (None, "attn"):
-            ops.sparse_attn_decode(self.q_rot, self.k_cache[layer][:, :n], self.v_cache[layer][:, :n], self.idx,
-                                   self.cnt, c.layout, out=self.out[layer])
+            if self.lru is not None:
+                ops.sparse_attn_decode(self.q_rot, self.lru[layer].k, self.lru[layer].v, self.slots, self.cnt, c.layout,
+                                       out=self.out[layer])
+            else:
+                ops.sparse_attn_decode(self.q_rot, self.k_cache[layer][:, :n], self.v_cache[layer][:, :n], self.idx,
+                                       self.cnt, c.layout, out=self.out[layer])
 
     def step(self, pos: int, stage: Optional[str] = None):
         for layer in range(self.cfg.layers):
