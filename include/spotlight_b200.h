@@ -150,8 +150,8 @@ typedef struct {
  *   d_q_codes [B,QH,4] (out)
  *   d_code_cache [B,*,KH,4], d_k_cache / d_v_cache [B,*,KH,128] with batch strides in ELEMENTS
  *   (uint32 words resp. values); row `pos` of each is written. Caches may be NULL to skip.
- *   With a code cache the launch also asks L2 for code rows 0..pos-1 of every batch element (at
- *   most 64 MB), which the sl_scan_topk of the same decode step streams next.
+ *   With a code cache of at most 24 MB (rows 0..pos-1 of all batch elements) the launch also asks
+ *   L2 for those rows, which the sl_scan_topk of the same decode step streams next.
  * Replaces, for one decode token, check_and_apply_qk_rope (spotlight/modifiers/modify_llama.py:
  * 68-80) + hash_fn + sign (spotlight_generation.py:13-20) + pack_cuda_func
  * (spotlight/kernel/__init__.py:23-24) + KVHash.update / KVCache.update
