@@ -184,7 +184,7 @@ def workload_config(cfg):
 # ------------------------------------------------------------------------------------------
 # GPU arm
 # ------------------------------------------------------------------------------------------
-def build_session(cfg, device, lru=False):
+def build_session(cfg, device, lru=False, extra_capacity=0):
     from spotlight_b200 import ops
     from spotlight_b200.session import DecodeSession, SessionConfig
     from spotlight_b200.workloads import apply_rope, rope_tables, torch_dtype
@@ -198,8 +198,8 @@ def build_session(cfg, device, lru=False):
         hq.append(ops.HashParams.from_dict(pq, device, cfg.mlp_residue))
         hk.append(ops.HashParams.from_dict(pk, device, cfg.mlp_residue))
     lru_slots = 2 * (budget(n, cfg.mask_out, cfg.min_remain) + cfg.sink + cfg.recent) if lru else 0
-    scfg = SessionConfig(cfg.batch, cfg.q_heads, cfg.kv_heads, cfg.layers, n, dt, cfg.mask_out, cfg.min_remain,
-                         cfg.sink, cfg.recent, lru_slots=lru_slots)
+    scfg = SessionConfig(cfg.batch, cfg.q_heads, cfg.kv_heads, cfg.layers, n + extra_capacity, dt, cfg.mask_out,
+                         cfg.min_remain, cfg.sink, cfg.recent, lru_slots=lru_slots)
     s = DecodeSession(scfg, hq, hk, device)
     dgen = torch.Generator(device=device).manual_seed(cfg.seed)
     ch = torch.randperm(HEAD_DIM, generator=gen)[:4].to(device)
@@ -376,6 +376,56 @@ def run_ours(args, cfg):
         dist.destroy_process_group()
 
 
+def run_decode_loop(args, cfg):
+    """Config 1 as the reference runs it: a prefilled context, then `--decode-steps` consecutive decode
+    tokens, each appended at the next position (the scan grows by one key per token). Launches are
+    issued eagerly, one position after the other (positions are host arguments of the C ABI, so
+    every token needs its own launches); the time is the device time of the whole loop."""
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the retrieval path has no CPU fallback")
+    device = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+    torch.cuda.set_device(device)
+    from spotlight_b200 import ops
+    T = args.decode_steps
+    s, code_build_ms = build_session(cfg, device, extra_capacity=T + 1)
+    n0, L = cfg.context, cfg.layers
+    dt = s.cfg.dtype
+    g = torch.Generator(device=device).manual_seed(cfg.seed + 7)
+    for t in range(3):                                  # warm-up tokens (they stay in the cache)
+        s.set_position(n0 + t, cfg.rope_theta)
+        s.step(n0 + t)
+    torch.cuda.synchronize(device)
+    launches0 = ops.launch_count
+    with ClockSampler(device.index or 0) as clocks:
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t_wall = time.perf_counter()
+        e0.record()
+        for t in range(3, T):
+            pos = n0 + t
+            s.q_in.copy_(torch.randn(s.q_in.shape, generator=g, device=device).to(dt))   # this token's q/k/v
+            s.k_in.copy_(torch.randn(s.k_in.shape, generator=g, device=device).to(dt))
+            s.v_in.copy_(torch.randn(s.v_in.shape, generator=g, device=device).to(dt))
+            s.set_position(pos, cfg.rope_theta)
+            s.step(pos)
+        e1.record()
+        torch.cuda.synchronize(device)
+        wall_ms = (time.perf_counter() - t_wall) * 1e3
+    ops.check_status(device)
+    ms = e0.elapsed_time(e1)
+    tokens = T - 3
+    line = {
+        "metric": "decode_loop_us_per_layer", "value": ms * 1e3 / tokens / L, "unit": UNIT, "n_gpus": 1,
+        "steps": tokens, "warmup": 3, "ms_per_step": ms / tokens, "higher_is_better": False, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": dict(workload_config(cfg), decode_steps=tokens, first_position=n0 + 3, launches="eager, one position per token"),
+        "tokens_per_s": cfg.batch * tokens / (ms * 1e-3), "wall_ms_per_step": wall_ms / tokens,
+        "gpu_launches": ops.launch_count - launches0, "cuda_graph": False,
+        "code_build_ms_per_layer": code_build_ms, "clocks": clocks.summary(),
+        "checksum": float(s.out.float().abs().sum()),
+    }
+    print(json.dumps(line), flush=True)
+
+
 def run_sharded(args, cfg):
     """Sequence-sharded layer-step (config 4: 1M-token context): every rank owns n/world keys of
     `layers` rotating layers, a step is one layer-step through sharded_decode_attention (local scan +
@@ -506,6 +556,9 @@ def main():
     ap.add_argument("--mask-out", type=float, default=None)
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--decode-steps", type=int, default=0,
+                    help="run this many consecutive decode tokens at advancing positions (config 1: 256) instead of "
+                         "replaying one position")
     ap.add_argument("--lru", action="store_true",
                     help="include stage 3: update an LRU-resident K/V buffer every layer-step and attend over it")
     ap.add_argument("--peer", action="store_true",
@@ -525,6 +578,8 @@ def main():
         cfg = dataclasses.replace(cfg, **over)
     if args.impl == "reference":
         run_reference(args, cfg)
+    elif args.decode_steps:
+        run_decode_loop(args, cfg)
     elif args.sharded:
         run_sharded(args, cfg)
     else:

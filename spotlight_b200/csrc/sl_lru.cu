@@ -12,7 +12,7 @@
 //           the resident buffer performs the same arithmetic as attention over the full cache.
 // The reference has no such stage; the policy is specified here and restated in the CPU checker.
 // One CTA of 1024 threads per (b, kv head); victim selection is a histogram select over ages
-// (no sort), ordered compaction by warp ballots.
+// (no sort); the ordered assignments use bitmaps and block scans.
 #include "sl_common.cuh"
 
 namespace {
@@ -31,34 +31,51 @@ struct LruArgs {
     int* slots_out; int* stats; int* status;
 };
 
-// exclusive ranks of two flags over the block, in thread order; totals returned through tot0/tot1
-__device__ __forceinline__ void block_rank2(bool f0, bool f1, int (*wt)[2], int& r0, int& r1, int& tot0, int& tot1) {
+// exclusive prefix of one value per thread over the block (thread order) and the block total
+__device__ __forceinline__ int block_exclusive_scan(int v, int* wsum, int& total) {
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const unsigned lt = (1u << lane) - 1u;
-    const unsigned b0 = __ballot_sync(0xffffffffu, f0), b1 = __ballot_sync(0xffffffffu, f1);
-    if (lane == 0) { wt[warp][0] = __popc(b0); wt[warp][1] = __popc(b1); }
-    __syncthreads();
-    int p0 = 0, p1 = 0, t0 = 0, t1 = 0;
-    for (int w = 0; w < LW; ++w) {
-        const int a0 = wt[w][0], a1 = wt[w][1];
-        if (w < warp) { p0 += a0; p1 += a1; }
-        t0 += a0; t1 += a1;
+    int inc = v;
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+        const int t = __shfl_up_sync(0xffffffffu, inc, d);
+        if (lane >= d) inc += t;
     }
-    r0 = p0 + __popc(b0 & lt);
-    r1 = p1 + __popc(b1 & lt);
-    tot0 = t0; tot1 = t1;
+    if (lane == 31) wsum[warp] = inc;
     __syncthreads();
+    int wv = wsum[lane];                      // LW == 32 warps: one value per lane
+    int winc = wv;
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+        const int t = __shfl_up_sync(0xffffffffu, winc, d);
+        if (lane >= d) winc += t;
+    }
+    total = __shfl_sync(0xffffffffu, winc, 31);
+    const int before = __shfl_sync(0xffffffffu, winc - wv, warp);
+    __syncthreads();
+    return before + inc - v;
 }
 
+// Ranks come from bitmaps, not from ordered loops: a flag per slot (or list entry) is packed into
+// 32-bit words by warp ballots, one block scan over the words' popcounts gives every word its
+// prefix, and every element finds its own rank with one more popcount. The kernel has a fixed,
+// small number of block barriers whatever C and n are.
 __global__ void __launch_bounds__(LT) lru_update_kernel(const LruArgs a) {
     extern __shared__ int smem_i[];
+    const int cw = (a.C + 31) >> 5, nw = (a.cap + 31) >> 5;      // bitmap words over slots / list entries
     int* victims = smem_i;                 // [cap] slot taken by the r-th miss
-    int* misstok = smem_i + a.cap;         // [cap] key of the r-th miss
+    int* misstok = victims + a.cap;        // [cap] key of the r-th miss
+    unsigned* m_gt = reinterpret_cast<unsigned*>(misstok + a.cap);   // [cw] slots older than tau
+    unsigned* m_eq = m_gt + cw;            // [cw] slots of age tau
+    int* p_gt = reinterpret_cast<int*>(m_eq + cw);                   // [cw] prefixes of the two bitmaps
+    int* p_eq = p_gt + cw;
+    unsigned* m_miss = reinterpret_cast<unsigned*>(p_eq + cw);       // [nw] list entries that missed
+    int* p_miss = reinterpret_cast<int*>(m_miss + nw);               // [nw]
+    unsigned short* age16 = reinterpret_cast<unsigned short*>(p_miss + nw);   // [C]
     __shared__ unsigned hist[NBIN];
-    __shared__ int wt[LW][2];
+    __shared__ int wsum[LW];
     __shared__ int s_hits, s_tau, s_r;
 
-    const int h = blockIdx.x, b = blockIdx.y, tid = threadIdx.x, lane = tid & 31;
+    const int h = blockIdx.x, b = blockIdx.y, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const long long bh = (long long)b * a.KH + h;
     const int n = min(a.cnt[bh], a.cap);
     const int* list = a.idx + bh * a.cap;
@@ -67,6 +84,7 @@ __global__ void __launch_bounds__(LT) lru_update_kernel(const LruArgs a) {
     int* s2t = a.slot2tok + bh * a.C;
     int* lu = a.last_used + bh * a.C;
     const int t = a.step;
+    const unsigned lt = (1u << lane) - 1u;
 
     if (tid == 0) s_hits = 0;
     for (int i = tid; i < NBIN; i += LT) hist[i] = 0;
@@ -76,86 +94,143 @@ __global__ void __launch_bounds__(LT) lru_update_kernel(const LruArgs a) {
         return;
     }
 
-    // ---- hits: stamp their slots
+    // ---- hits: stamp their slots; misses go into a bitmap (eight entries per thread and round, so
+    // that the two dependent loads of an entry cost one trip to memory per round, not per entry)
     int myhits = 0;
-    for (int j = tid; j < n; j += LT) {
-        const int s = t2s[list[j]];
-        if (s >= 0) { lu[s] = t; ++myhits; }
-        out[j] = s;
+    for (int j0 = warp * 32; j0 < nw * 32; j0 += LT * 8) {
+        int tok[8], sl_[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            const int j = j0 + u * LT + lane;
+            tok[u] = j < n ? __ldg(list + j) : -1;
+        }
+#pragma unroll
+        for (int u = 0; u < 8; ++u) sl_[u] = tok[u] >= 0 ? t2s[tok[u]] : -1;
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            const int j = j0 + u * LT + lane;
+            if (tok[u] >= 0) {
+                if (sl_[u] >= 0) { lu[sl_[u]] = t; ++myhits; }
+                out[j] = sl_[u];
+            }
+            const unsigned mb = __ballot_sync(0xffffffffu, tok[u] >= 0 && sl_[u] < 0);
+            if (lane == 0 && (j0 + u * LT) < nw * 32) m_miss[(j0 + u * LT) >> 5] = mb;
+        }
     }
     myhits = __reduce_add_sync(0xffffffffu, myhits);
     if (lane == 0 && myhits) atomicAdd(&s_hits, myhits);
     __syncthreads();
     const int m = n - s_hits;              // misses = victims needed
+    if (m == 0) {                           // everything was resident: nothing to evict or copy
+        if (tid == 0 && a.stats) { a.stats[bh * 2] = s_hits; a.stats[bh * 2 + 1] = 0; }
+        return;
+    }
 
-    // ---- age histogram of the slots not used in this step
-    for (int s = tid; s < a.C; s += LT) {
-        const int l = lu[s];
-        const int age = l < 0 ? AGE_MAX + 1 : min(t - l, AGE_MAX);
-        if (age > 0) atomicAdd(&hist[age], 1u);
+    // ---- ages of the slots not used in this step: kept in shared memory, histogrammed
+    for (int s0 = tid; s0 < a.C; s0 += LT * 8) {
+        int l[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) l[u] = s0 + u * LT < a.C ? lu[s0 + u * LT] : t;
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            if (s0 + u * LT < a.C) {
+                const int age = l[u] < 0 ? AGE_MAX + 1 : min(t - l[u], AGE_MAX);
+                age16[s0 + u * LT] = (unsigned short)age;
+                if (age > 0) atomicAdd(&hist[age], 1u);
+            }
+        }
     }
     __syncthreads();
     if (tid < 32) {                         // oldest first: largest age with a cumulative count >= m
         int tau = NBIN, r = 0;
-        if (m > 0) {
-            const int BW = (NBIN + 31) >> 5;
-            const int blo = lane * BW, bhi = min(NBIN, blo + BW);
-            unsigned bs = 0;
-            for (int i = blo; i < bhi; ++i) bs += hist[i];
-            unsigned suf = bs;
+        const int BW = (NBIN + 31) >> 5;
+        const int blo = lane * BW, bhi = min(NBIN, blo + BW);
+        unsigned bs = 0;
+        for (int i = blo; i < bhi; ++i) bs += hist[i];
+        unsigned suf = bs;
 #pragma unroll
-            for (int d = 1; d < 32; d <<= 1) {
-                const unsigned v = __shfl_down_sync(0xffffffffu, suf, d);
-                if (lane + d < 32) suf += v;
-            }
-            const unsigned ball = __ballot_sync(0xffffffffu, suf >= (unsigned)m);
-            if (ball == 0u && lane == 0 && a.status) atomicExch(a.status, 4);   // table state is inconsistent
-            const int L = ball ? 31 - __clz(ball) : 0;   // a consistent table always has n - hits evictable slots
-            int tau_l = 0, gt_l = 0;
-            if (lane == L) {
-                unsigned cum = suf - bs;
-                for (int i = bhi - 1; i >= blo; --i) {
-                    const unsigned v = hist[i];
-                    if (cum + v >= (unsigned)m) { tau_l = i; gt_l = (int)cum; break; }
-                    cum += v;
-                }
-            }
-            tau = __shfl_sync(0xffffffffu, tau_l, L);
-            r = m - __shfl_sync(0xffffffffu, gt_l, L);
+        for (int d = 1; d < 32; d <<= 1) {
+            const unsigned v = __shfl_down_sync(0xffffffffu, suf, d);
+            if (lane + d < 32) suf += v;
         }
+        const unsigned ball = __ballot_sync(0xffffffffu, suf >= (unsigned)m);
+        if (ball == 0u && lane == 0 && a.status) atomicExch(a.status, 4);   // table state is inconsistent
+        const int L = ball ? 31 - __clz(ball) : 0;   // a consistent table always has n - hits evictable slots
+        int tau_l = 0, gt_l = 0;
+        if (lane == L) {
+            unsigned cum = suf - bs;
+            for (int i = bhi - 1; i >= blo; --i) {
+                const unsigned v = hist[i];
+                if (cum + v >= (unsigned)m) { tau_l = i; gt_l = (int)cum; break; }
+                cum += v;
+            }
+        }
+        tau = __shfl_sync(0xffffffffu, tau_l, L);
+        r = m - __shfl_sync(0xffffffffu, gt_l, L);
         if (lane == 0) { s_tau = tau; s_r = r; }
     }
     __syncthreads();
     const int tau = s_tau, r = s_r;
 
-    // ---- victims in slot order: every slot older than tau, then the first r slots of age tau
-    int gt_before = 0, eq_before = 0;
-    for (int s0 = 0; s0 < a.C && m > 0; s0 += LT) {
-        const int s = s0 + tid;
-        int age = 0;
-        if (s < a.C) {
-            const int l = lu[s];
-            age = l < 0 ? AGE_MAX + 1 : min(t - l, AGE_MAX);
+    // ---- victim bitmaps: every slot older than tau, and the slots of age tau (the first r are taken)
+    for (int w = warp; w < cw; w += LW) {
+        const int s = w * 32 + lane;
+        const int age = s < a.C ? (int)age16[s] : 0;
+        const unsigned g = __ballot_sync(0xffffffffu, age > tau);
+        const unsigned e = __ballot_sync(0xffffffffu, age == tau && age > 0);
+        if (lane == 0) { m_gt[w] = g; m_eq[w] = e; }
+    }
+    __syncthreads();
+    // prefixes of the word popcounts: thread i owns words [i*WPT, (i+1)*WPT)
+    {
+        const int WPT = (cw + LT - 1) / LT;
+        int cg = 0, ce = 0;
+        for (int k = 0; k < WPT; ++k) {
+            const int w = tid * WPT + k;
+            if (w < cw) { cg += __popc(m_gt[w]); ce += __popc(m_eq[w]); }
         }
-        const bool isgt = age > tau, iseq = age == tau && age > 0;
-        int rg, re, tg, te;
-        block_rank2(isgt, iseq, wt, rg, re, tg, te);
-        const int eqr = eq_before + re;
-        if (isgt || (iseq && eqr < r)) victims[gt_before + rg + min(eqr, r)] = s;
-        gt_before += tg;
-        eq_before += te;
+        int tg, te;
+        int pg = block_exclusive_scan(cg, wsum, tg);
+        int pe = block_exclusive_scan(ce, wsum, te);
+        for (int k = 0; k < WPT; ++k) {
+            const int w = tid * WPT + k;
+            if (w < cw) {
+                p_gt[w] = pg; p_eq[w] = pe;
+                pg += __popc(m_gt[w]); pe += __popc(m_eq[w]);
+            }
+        }
+    }
+    __syncthreads();
+    // victims in slot order: a taken slot's position is (older slots before it) + (taken ties before it)
+    for (int w = warp; w < cw; w += LW) {
+        const unsigned g = m_gt[w], e = m_eq[w];
+        const int gb = p_gt[w] + __popc(g & lt), eb = p_eq[w] + __popc(e & lt);
+        const bool isg = (g >> lane) & 1u, ise = (e >> lane) & 1u;
+        if (isg || (ise && eb < r)) victims[gb + min(eb, r)] = w * 32 + lane;
+    }
+    // ranks of the misses in list order
+    {
+        const int WPT = (nw + LT - 1) / LT;
+        int cm = 0;
+        for (int k = 0; k < WPT; ++k) {
+            const int w = tid * WPT + k;
+            if (w < nw) cm += __popc(m_miss[w]);
+        }
+        int tm;
+        int pm = block_exclusive_scan(cm, wsum, tm);
+        for (int k = 0; k < WPT; ++k) {
+            const int w = tid * WPT + k;
+            if (w < nw) { p_miss[w] = pm; pm += __popc(m_miss[w]); }
+        }
     }
     __syncthreads();
 
     // ---- misses in list order take the victims in that order
-    int miss_before = 0;
-    for (int j0 = 0; j0 < n && m > 0; j0 += LT) {
-        const int j = j0 + tid;
-        const bool miss = j < n && out[j] < 0;
-        int rm, dummy, tm, td;
-        block_rank2(miss, false, wt, rm, dummy, tm, td);
-        if (miss) {
-            const int rank = miss_before + rm;
+    for (int w = warp; w < nw; w += LW) {
+        const unsigned mm = m_miss[w];
+        if ((mm >> lane) & 1u) {
+            const int j = w * 32 + lane;
+            const int rank = p_miss[w] + __popc(mm & lt);
             const int v = victims[rank], tok = list[j];
             const int old = s2t[v];
             if (old >= 0) t2s[old] = -1;
@@ -165,7 +240,6 @@ __global__ void __launch_bounds__(LT) lru_update_kernel(const LruArgs a) {
             out[j] = v;
             misstok[rank] = tok;
         }
-        miss_before += tm;
     }
     __syncthreads();
 
@@ -203,9 +277,10 @@ extern "C" int sl_lru_update(const int32_t* d_idx, int idx_capacity, const int32
     SL_REQUIRE(sl::aligned16(k_backing) && sl::aligned16(v_backing) && sl::aligned16(d_k_resident) &&
                    sl::aligned16(d_v_resident) && (backing_batch_stride * elem_bytes) % 16 == 0,
                SL_EALIGN, "sl_lru_update: K/V buffers must be 16-byte aligned");
-    const size_t smem = (size_t)idx_capacity * 2 * sizeof(int);
-    SL_REQUIRE(smem <= 200 * 1024, SL_ESHAPE, "sl_lru_update: idx_capacity %d too large for the shared-memory victim list",
-               idx_capacity);
+    const size_t cw = ((size_t)C + 31) / 32, nw = ((size_t)idx_capacity + 31) / 32;
+    const size_t smem = (size_t)idx_capacity * 2 * sizeof(int) + cw * 16 + nw * 8 + (size_t)C * 2 + 16;
+    SL_REQUIRE(smem <= 220 * 1024, SL_ESHAPE, "sl_lru_update: idx_capacity %d / %d slots too large for shared memory",
+               idx_capacity, C);
     LruArgs a;
     a.idx = d_idx; a.cap = idx_capacity; a.cnt = d_cnt;
     a.B = B; a.KH = KH; a.C = C; a.step = step; a.row_bytes = 128 * elem_bytes;

@@ -424,7 +424,7 @@ __global__ void __launch_bounds__(NT, 1) scan_fused_kernel(const FusedArgs a) {
                     for (int j = 0; j < 5; ++j) all = all && (w[j] >> 63);
                     if (__all_sync(0xffffffffu, all)) break;
                     if (++it > 1000000u) { ok = false; break; }
-                    __nanosleep(200);
+                    __nanosleep(32);
                 }
 #pragma unroll
                 for (int j = 0; j < 5; ++j) {
