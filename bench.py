@@ -406,7 +406,10 @@ def run_decode_loop(args, cfg):
             s.k_in.copy_(torch.randn(s.k_in.shape, generator=g, device=device).to(dt))
             s.v_in.copy_(torch.randn(s.v_in.shape, generator=g, device=device).to(dt))
             s.set_position(pos, cfg.rope_theta)
-            s.step(pos)
+            if args.python_loop:
+                s.step(pos)
+            else:
+                s.step_native(pos)
         e1.record()
         torch.cuda.synchronize(device)
         wall_ms = (time.perf_counter() - t_wall) * 1e3
@@ -417,7 +420,8 @@ def run_decode_loop(args, cfg):
         "metric": "decode_loop_us_per_layer", "value": ms * 1e3 / tokens / L, "unit": UNIT, "n_gpus": 1,
         "steps": tokens, "warmup": 3, "ms_per_step": ms / tokens, "higher_is_better": False, "scaling": "weak",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": dict(workload_config(cfg), decode_steps=tokens, first_position=n0 + 3, launches="eager, one position per token"),
+        "config": dict(workload_config(cfg), decode_steps=tokens, first_position=n0 + 3,
+                       launches="eager, one position per token, layer loop in " + ("Python" if args.python_loop else "the library (sl_decode_step)")),
         "tokens_per_s": cfg.batch * tokens / (ms * 1e-3), "wall_ms_per_step": wall_ms / tokens,
         "gpu_launches": ops.launch_count - launches0, "cuda_graph": False,
         "code_build_ms_per_layer": code_build_ms, "clocks": clocks.summary(),
@@ -559,6 +563,8 @@ def main():
     ap.add_argument("--decode-steps", type=int, default=0,
                     help="run this many consecutive decode tokens at advancing positions (config 1: 256) instead of "
                          "replaying one position")
+    ap.add_argument("--python-loop", action="store_true",
+                    help="with --decode-steps: keep the layer loop in Python (three calls per layer) instead of sl_decode_step")
     ap.add_argument("--lru", action="store_true",
                     help="include stage 3: update an LRU-resident K/V buffer every layer-step and attend over it")
     ap.add_argument("--peer", action="store_true",

@@ -239,6 +239,38 @@ int sl_gather_rows(const void* d_cache, int64_t batch_stride, int elem_bytes,
                    const int32_t* d_idx, int idx_capacity, int B, int KH, int budget,
                    void* d_out, void* stream);
 
+/* One decode token through all layers, with the layer loop in native code: per layer
+ * sl_decode_prepare (token `pos` appended) -> sl_scan_topk over keys 0..pos with the reference's
+ * budget rule k = max(min(n, min_remain), n - int(n * mask_out)), n = pos + 1
+ * (spotlight/modifiers/spotlight_generation.py:162-164) -> sl_sparse_attn_decode.
+ * Replaces the per-layer Python of the attention hook for callers that own the layer loop
+ * (spotlight/modifiers/spotlight_generation.py:109-226 runs once per layer and token).
+ * Pointer tables are HOST arrays of `layers` device pointers; d_k / d_v tables (or entries) may be
+ * NULL when the token's key/value are already in the caches. The scratch buffers are shared by all
+ * layers (the launches are in stream order); workspaces as for the single entry points. */
+typedef struct {
+    int B, QH, KH, layers, dtype, gqa_layout;
+    int sink, recent, min_remain;
+    double mask_out;
+    int64_t code_batch_stride, kv_batch_stride;      /* uint32 words / elements, as in sl_decode_prepare */
+    const void* const* d_q;                          /* [layers] -> [B,QH,128] */
+    const void* const* d_k;                          /* [layers] -> [B,KH,128] */
+    const void* const* d_v;
+    const sl_hash_params* hash_q;                    /* [layers] */
+    const sl_hash_params* hash_k;
+    uint32_t* const* d_code_cache;                   /* [layers] -> [B,*,KH,4] */
+    void* const* d_k_cache;                          /* [layers] -> [B,*,KH,128] */
+    void* const* d_v_cache;
+    void* const* d_out;                              /* [layers] -> [B,QH,128] */
+    const void* d_cos; const void* d_sin;            /* [128] for position pos, or NULL */
+    void* d_q_rot; uint32_t* d_q_codes;              /* scratch [B,QH,128], [B,QH,4] */
+    int32_t* d_idx; int idx_capacity; int32_t* d_cnt;
+    void* d_scan_workspace; size_t scan_workspace_bytes;
+    void* d_attn_workspace; size_t attn_workspace_bytes;
+    int32_t* d_status;
+} sl_decode_step_args;
+int sl_decode_step(const sl_decode_step_args* args, int64_t pos, void* stream);
+
 /* ---- exchange between the GPUs of one node over peer memory (sequence-sharded contexts) ----
  * No reference counterpart: the reference has no sequence parallelism (its only collectives are
  * in training, train.py:250-260). A sequence-sharded decode step all-gathers two KB-sized

@@ -23,6 +23,20 @@ class HashParamsStruct(C.Structure):
 
 _P, _I, _L, _Z = C.c_void_p, C.c_int, C.c_int64, C.c_size_t
 _HP = C.POINTER(HashParamsStruct)
+_PP = C.POINTER(C.c_void_p)
+
+
+class DecodeStepArgs(C.Structure):
+    """sl_decode_step_args of include/spotlight_b200.h."""
+    _fields_ = [("B", _I), ("QH", _I), ("KH", _I), ("layers", _I), ("dtype", _I), ("gqa_layout", _I),
+                ("sink", _I), ("recent", _I), ("min_remain", _I), ("mask_out", C.c_double),
+                ("code_batch_stride", _L), ("kv_batch_stride", _L),
+                ("d_q", _PP), ("d_k", _PP), ("d_v", _PP), ("hash_q", _HP), ("hash_k", _HP),
+                ("d_code_cache", _PP), ("d_k_cache", _PP), ("d_v_cache", _PP), ("d_out", _PP),
+                ("d_cos", _P), ("d_sin", _P), ("d_q_rot", _P), ("d_q_codes", _P),
+                ("d_idx", _P), ("idx_capacity", _I), ("d_cnt", _P),
+                ("d_scan_workspace", _P), ("scan_workspace_bytes", _Z),
+                ("d_attn_workspace", _P), ("attn_workspace_bytes", _Z), ("d_status", _P)]
 
 # name -> (restype, argtypes); must list every symbol of include/spotlight_b200.h
 SIGNATURES = {
@@ -48,6 +62,7 @@ SIGNATURES = {
     "sl_merge_lse": (_I, [_P, _P, _I, _L, _I, _P, _P]),
     "sl_lru_update": (_I, [_P, _I, _P, _I, _I, _P, _P, _L, _I, _P, _P, _I, _P, _L, _P, _P, _I, _P, _P, _P, _P]),
     "sl_gather_rows": (_I, [_P, _L, _I, _P, _I, _I, _I, _I, _P, _P]),
+    "sl_decode_step": (_I, [C.POINTER(DecodeStepArgs), _L, _P]),
     "sl_scan_topk_sharded_slot_bytes": (_Z, [_I, _I, _I]),
     "sl_scan_topk_sharded": (_I, [_P, _P, _L, _I, _L, _L, _L, _I, _I, _I, _I, _I, _I, _P, _I, _P, _P, _Z, C.POINTER(_P),
                                   _I, _I, _Z, _P, _P]),

@@ -1,5 +1,7 @@
 // Error plumbing, version and workspace helpers of the C ABI.
 #include <cstdlib>
+#include <mutex>
+#include <unordered_map>
 
 #include "sl_common.cuh"
 
@@ -38,6 +40,23 @@ bool l2_prefetch_enabled() {
         g_l2pf = (e && e[0] == '0') ? 0 : 1;
     }
     return g_l2pf != 0;
+}
+
+// cudaFuncSetAttribute costs a microsecond or two; a decode loop launches thousands of kernels per
+// second, so the largest dynamic shared-memory size set per (device, kernel) is remembered.
+cudaError_t ensure_dyn_smem(const void* func, size_t bytes) {
+    static std::mutex mu;
+    static std::unordered_map<unsigned long long, size_t> seen;
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
+    const unsigned long long key = (unsigned long long)reinterpret_cast<uintptr_t>(func) * 64ull + (unsigned)dev;
+    std::lock_guard<std::mutex> lock(mu);
+    auto it = seen.find(key);
+    if (it != seen.end() && it->second >= bytes) return cudaSuccess;
+    e = cudaFuncSetAttribute(func, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+    if (e == cudaSuccess) seen[key] = bytes;
+    return e;
 }
 
 int sm_count() {

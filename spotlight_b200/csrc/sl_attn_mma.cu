@@ -269,12 +269,8 @@ int attn_mma_splits(int B, int KH, int cap) {
 
 int launch_attn_mma(const AttnArgs& a, int G, cudaStream_t s) {
     dim3 grid((unsigned)a.splits, (unsigned)a.KH, (unsigned)a.B);
-    static bool attr_set = false;
-    if (!attr_set) {
-        SL_CUDA_OK(cudaFuncSetAttribute(sparse_attn_mma_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, RING_BYTES));
-        SL_CUDA_OK(cudaFuncSetAttribute(sparse_attn_mma_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, RING_BYTES));
-        attr_set = true;
-    }
+    SL_CUDA_OK(ensure_dyn_smem(reinterpret_cast<const void*>(G > 8 ? sparse_attn_mma_kernel<true> : sparse_attn_mma_kernel<false>),
+                               RING_BYTES));
     if (G > 8) SL_CUDA_OK(launch_kernel(sparse_attn_mma_kernel<true>, grid, dim3(MT), RING_BYTES, s, false, a, G));
     else SL_CUDA_OK(launch_kernel(sparse_attn_mma_kernel<false>, grid, dim3(MT), RING_BYTES, s, false, a, G));
     if (a.splits > 1) return launch_attn_merge(a, G, SL_BF16, s);

@@ -17,6 +17,7 @@ namespace sl {
 char* err_buf();
 int fail(int code, const char* fmt, ...);
 int sm_count();          // SMs of the current device (cached per device)
+cudaError_t ensure_dyn_smem(const void* func, size_t bytes);   // opt-in to `bytes` of dynamic shared memory, once
 bool pdl_enabled();      // programmatic dependent launch on (default) / off (SL_PDL=0 or sl_set_pdl)
 bool l2_prefetch_enabled();   // the decode-step hash warms L2 with the code cache (SL_L2_PREFETCH=0: off)
 

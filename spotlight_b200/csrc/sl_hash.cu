@@ -344,7 +344,7 @@ int launch_T(const HashArgs& args, int total_heads, long long max_tiles, int R, 
         default: kern = pick_kernel<T, 8>(args, &wsm); break;
     }
     smem += wsm;
-    SL_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    SL_CUDA_OK(sl::ensure_dyn_smem(reinterpret_cast<const void*>(kern), smem));
     SL_CUDA_OK(sl::launch_kernel(kern, grid, dim3(HT), smem, s, false, args));
     return SL_OK;
 }

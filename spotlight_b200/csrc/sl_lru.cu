@@ -289,7 +289,7 @@ extern "C" int sl_lru_update(const int32_t* d_idx, int idx_capacity, const int32
     a.k_res = static_cast<unsigned char*>(d_k_resident); a.v_res = static_cast<unsigned char*>(d_v_resident);
     a.tok2slot = d_tok2slot; a.n_max = n_max; a.slot2tok = d_slot2tok; a.last_used = d_last_used;
     a.slots_out = d_slots_out; a.stats = d_stats; a.status = d_status;
-    SL_CUDA_OK(cudaFuncSetAttribute(lru_update_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    SL_CUDA_OK(sl::ensure_dyn_smem(reinterpret_cast<const void*>(lru_update_kernel), smem));
     dim3 grid((unsigned)KH, (unsigned)B);
     lru_update_kernel<<<grid, LT, smem, static_cast<cudaStream_t>(stream)>>>(a);
     SL_CUDA_OK(cudaGetLastError());

@@ -507,7 +507,7 @@ int launch_fused(const FusedArgs& a_in, size_t smem, cudaStream_t s) {
     FusedArgs a = a_in;
     a.dbg = g_dbg_timing;
     fused_kernel_t kern = a.R > 0 ? pick<true>(sliced_planes(a.G)) : pick<false>(sliced_planes(a.G));
-    SL_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    SL_CUDA_OK(sl::ensure_dyn_smem(reinterpret_cast<const void*>(kern), smem));
     SL_CUDA_OK(sl::launch_kernel(kern, dim3((unsigned)(a.B * a.ctas_per_b)), dim3(NT), smem, s, true, a));
     return SL_OK;
 }

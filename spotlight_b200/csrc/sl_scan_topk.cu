@@ -694,7 +694,7 @@ int launch(const ScanArgs& a_in, const Plan& p, cudaStream_t s) {
     ScanArgs a = a_in;
     a.dbg = slscan::g_dbg_timing;
     kernel_t kern = pick_kernel(a.G, a.KH);
-    SL_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)p.smem));
+    SL_CUDA_OK(sl::ensure_dyn_smem(reinterpret_cast<const void*>(kern), p.smem));
     const unsigned grid = (unsigned)(a.B * p.ctas_per_b);
     SL_CUDA_OK(sl::launch_kernel(kern, dim3(grid), dim3(NT), p.smem, s, p.cooperative, a));
     return SL_OK;

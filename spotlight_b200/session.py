@@ -121,6 +121,46 @@ class DecodeSession:
         for layer in range(self.cfg.layers):
             self.layer_step(layer, pos, stage)
 
+    def step_native(self, pos: int):
+        """`step(pos)` with the layer loop in the library (sl_decode_step): one call per token instead
+        of three per layer, for decode loops at advancing positions that cannot replay a graph."""
+        import ctypes as C
+        from . import _lib
+        c = self.cfg
+        assert self.lru is None and not c.fix_layers
+        if getattr(self, "_native", None) is None:
+            L = c.layers
+            arr = lambda ts: (C.c_void_p * L)(*[t.data_ptr() for t in ts])
+            a = _lib.DecodeStepArgs()
+            a.B, a.QH, a.KH, a.layers = c.batch, c.q_heads, c.kv_heads, L
+            a.dtype, a.gqa_layout = ops._dt(self.q_in), c.layout
+            a.sink, a.recent, a.min_remain, a.mask_out = c.sink, c.recent, c.min_remain, c.mask_out
+            a.code_batch_stride = self.codes[0].stride(0)
+            a.kv_batch_stride = self.k_cache[0].stride(0)
+            keep = {"q": arr([self.q_in[l] for l in range(L)]), "k": arr([self.k_in[l] for l in range(L)]),
+                    "v": arr([self.v_in[l] for l in range(L)]), "codes": arr(self.codes), "kc": arr(self.k_cache),
+                    "vc": arr(self.v_cache), "out": arr([self.out[l] for l in range(L)]),
+                    "hq": (_lib.HashParamsStruct * L)(*[h.struct for h in self.hash_q]),
+                    "hk": (_lib.HashParamsStruct * L)(*[h.struct for h in self.hash_k])}
+            a.d_q, a.d_k, a.d_v = keep["q"], keep["k"], keep["v"]
+            a.hash_q, a.hash_k = keep["hq"], keep["hk"]
+            a.d_code_cache, a.d_k_cache, a.d_v_cache, a.d_out = keep["codes"], keep["kc"], keep["vc"], keep["out"]
+            a.d_cos, a.d_sin = self.cos.data_ptr(), self.sin.data_ptr()
+            a.d_q_rot, a.d_q_codes = self.q_rot.data_ptr(), self.q_codes.data_ptr()
+            a.d_idx, a.idx_capacity, a.d_cnt = self.idx.data_ptr(), self.idx.shape[2], self.cnt.data_ptr()
+            shape = (c.batch, c.kv_heads, c.q_heads)
+            sw, status = ops.workspaces.get("scan", self.device, _lib.lib.sl_scan_topk_workspace_bytes(
+                c.batch, c.capacity, c.kv_heads, c.q_heads), shape)
+            aw, _ = ops.workspaces.get("attn", self.device, _lib.lib.sl_sparse_attn_workspace_bytes(
+                c.batch, c.kv_heads, c.q_heads), shape)
+            a.d_scan_workspace, a.scan_workspace_bytes = sw.data_ptr(), sw.numel()
+            a.d_attn_workspace, a.attn_workspace_bytes = aw.data_ptr(), aw.numel()
+            a.d_status = status.data_ptr()
+            self._native = (a, keep, sw, aw, status)
+        _lib.check(_lib.lib.sl_decode_step(C.byref(self._native[0]), pos,
+                                           torch.cuda.current_stream(self.device).cuda_stream))
+        ops.launch_count += 4 * c.layers
+
     # ------------------------------------------------------------------ graphs
     def capture(self, pos: int, stage: Optional[str] = None, host_io: bool = False) -> torch.cuda.CUDAGraph:
         """Capture `step(pos)` (optionally one stage only, optionally with the pinned-host copies)

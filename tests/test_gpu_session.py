@@ -1,0 +1,74 @@
+"""DecodeSession (the layer loop a caller owns) on the GPU: the Python loop, the native loop
+(sl_decode_step) and a replayed CUDA graph must agree bit for bit over consecutive tokens, and a
+layer-step must equal the single ops applied by hand."""
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+DEV = torch.device("cuda", 0) if torch.cuda.is_available() else None
+
+
+def _session(seed=3, layers=3, B=2, QH=8, KH=4, n=2500, extra=8, mask_out=0.9):
+    from spotlight_b200 import ops
+    from spotlight_b200.session import DecodeSession, SessionConfig
+    from spotlight_b200.workloads import make_hash_params
+    g = torch.Generator().manual_seed(seed)
+    dt = torch.bfloat16
+    hq = [ops.HashParams.from_dict(make_hash_params("mlp", QH, (128, 256, 128), g, dt, mlp_scale=0.05), DEV) for _ in range(layers)]
+    hk = [ops.HashParams.from_dict(make_hash_params("mlp", KH, (128, 256, 128), g, dt, mlp_scale=0.05), DEV) for _ in range(layers)]
+    s = DecodeSession(SessionConfig(B, QH, KH, layers, n + extra, dt, mask_out), hq, hk, DEV)
+    for layer in range(layers):
+        k = torch.randn((B, n, KH, 128), generator=g).to(dt).to(DEV)
+        v = torch.randn((B, n, KH, 128), generator=g).to(dt).to(DEV)
+        s.load_context(layer, k, v)
+    return s, g, n
+
+
+def _token(s, g):
+    for t in (s.q_in, s.k_in, s.v_in):
+        t.copy_(torch.randn(t.shape, generator=g).to(t.dtype))
+
+
+def test_native_loop_and_graph_equal_the_python_loop():
+    from spotlight_b200 import ops
+    a, ga, n = _session()
+    b, gb, _ = _session()
+    for step in range(4):                      # consecutive tokens: every one is appended, the scan grows
+        pos = n + step
+        _token(a, ga)
+        _token(b, gb)
+        a.set_position(pos, 500000.0)
+        b.set_position(pos, 500000.0)
+        a.step(pos)
+        b.step_native(pos)
+        torch.cuda.synchronize()
+        assert torch.equal(a.out, b.out), f"token {step}: native loop differs from the Python loop"
+        for layer in range(a.cfg.layers):
+            assert torch.equal(a.codes[layer][:, : pos + 1], b.codes[layer][:, : pos + 1])
+            assert torch.equal(a.k_cache[layer][:, pos], b.k_cache[layer][:, pos])
+    ref = a.out.clone()
+    graph = a.capture(n + 3)                   # same position again: appends rewrite the same row
+    graph.replay()
+    torch.cuda.synchronize()
+    assert torch.equal(a.out, ref)
+    ops.check_status()
+
+
+def test_layer_step_equals_the_single_ops():
+    from spotlight_b200 import ops
+    from spotlight_b200.workloads import budget
+    s, g, n = _session(seed=5, layers=1)
+    _token(s, g)
+    s.set_position(n, 500000.0)
+    q, k, v = s.q_in[0].clone(), s.k_in[0].clone(), s.v_in[0].clone()
+    s.step(n)
+    codes, kc, vc = s.codes[0].clone(), s.k_cache[0].clone(), s.v_cache[0].clone()   # token n already appended
+    q_rot, q_codes = ops.decode_prepare(q, k, v, s.hash_q[0], s.hash_k[0], n, codes, kc, vc, s.cos, s.sin)
+    idx, cnt = ops.scan_topk(q_codes, codes[:, : n + 1], budget(n + 1, s.cfg.mask_out), 4, 64)
+    out = ops.sparse_attn_decode(q_rot, kc[:, : n + 1], vc[:, : n + 1], idx, cnt)
+    torch.cuda.synchronize()
+    assert torch.equal(out, s.out[0])
+    assert np.array_equal(cnt.cpu().numpy(), s.cnt.cpu().numpy())
+    ops.check_status()
