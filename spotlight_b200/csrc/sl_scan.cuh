@@ -31,6 +31,7 @@ struct FusedArgs {
     int cws;                   // log2 of the coarse bin width: NC = ((nbins - 1) >> cws) + 1 <= 32
     int rowh;                  // row stride of the score rows in shared memory (halfwords)
     int score_off;             // byte offset of the score rows in shared memory
+    int trip_off, trips_per_warp;   // per-warp trip records ({flags, flags, counts below, totals} per lane): byte offset, records per warp
     unsigned long long* dbg;   // optional [grid][16] phase stamps (development aid)
     // sequence shards (R > 0): N, s_end, r_start, idx are local to this rank's keys; the merged local
     // histograms travel to every rank's exchange buffer and the threshold comes from all R of them
@@ -43,6 +44,7 @@ struct FusedArgs {
 bool fused_covers(int KH, int G);
 size_t fused_fixed_smem(int KH, int nbins, int S);
 int launch_fused(const FusedArgs& a, size_t smem, cudaStream_t s);
+size_t fused_plan_smem(FusedArgs& f, int KH, int nbins, int S, int chunk);   // fills the shared-memory offsets, returns the total
 size_t shard_message_bytes(int B, int KH, int nbins, int cws);   // one rank's histogram message, padded to 16 bytes
 extern unsigned long long* g_dbg_timing;   // set by sl_debug_scan_timing
 

@@ -281,47 +281,30 @@ __global__ void __launch_bounds__(NT, 1) scan_fused_kernel(const FusedArgs a) {
     SL_STAMP(3)
 
     // ------------------------------------------------------------------ B/C: count, publish, poll, emit
-    // A task is (head, sub-range of the chunk). A lane tests four consecutive keys of one head per
-    // 8-byte load: adding (0x7fff - tau) to a 16-bit score sets bit 15 iff score > tau, adding
-    // (0x8000 - tau) iff score >= tau, two scores per 32-bit add.
-    // The walk over the tasks runs twice through the SAME instructions: pass 0 counts the chunk's
-    // {> tau, == tau} keys (then publishes them and polls every chunk's word), pass 1 writes the
-    // attended keys at their final positions. One loop body for both keeps the second pass's
-    // set-up and loop control in the instruction cache.
+    // A task is (head, sub-range of the chunk). A lane walks RUN consecutive keys per trip (five
+    // 8-byte loads; the odd number of 8-byte units between lanes keeps them free of bank conflicts)
+    // and keeps one flag bit per key: adding (0x7fff - tau) to a 16-bit score sets bit 15 iff
+    // score > tau, adding (0x8000 - tau) iff score >= tau, two scores per 32-bit add.
+    // Everything that does not depend on the other chunks happens BEFORE their counts are polled:
+    // flags, per-lane counts and one packed warp scan per trip are kept in shared memory, so that
+    // after the poll only the tie decision and the writes remain.
     const int S = a.S, ntasks = KH * S;
     const int sub = ((len + S - 1) / S + 127) & ~127;
     const int mlo = max(t0, a.s_end) - t0, mhi = min(t1, a.r_start) - t0;     // the chunk's keys outside both windows
     constexpr int RUN = 20;
-#pragma unroll 1
-    for (int pass_ = 0; pass_ < 2; ++pass_) {
-        int pass;
-        asm volatile("mov.u32 %0, %1;" : "=r"(pass) : "r"(pass_));        // opaque: one copy of the loop below
+    uint4* s_trip = reinterpret_cast<uint4*>(smem_raw + a.trip_off) + warp * (a.trips_per_warp * 32) + lane;
+    {
+        int slot = 0;
 #pragma unroll 1
         for (int task = warp; task < ntasks; task += NW) {
             const int h = task & (KH - 1), s = task >> (31 - __clz(KH));
-            const int lo = min(len, s * sub), hi = min(len, (s + 1) * sub);
-            const int elo = max(lo, mlo), ehi = min(hi, mhi);
+            const int elo = max(min(len, s * sub), mlo), ehi = min(min(len, (s + 1) * sub), mhi);
             const int tau = s_tau[h];
             const unsigned short* row = sscores + h * rowh;
             const unsigned cgt = (unsigned)(0x7fff - tau) * 0x10001u, cge = (unsigned)(0x8000 - tau) * 0x10001u;
-            int gtM = 0, geM = 0;
-            // pass 1 only: ranks of this task's first key among the attended keys / the threshold ties
-            int rM = 0, selM = 0, eq_before = 0, out_base = 0;
-            int* oi = a.idx + ((size_t)b * KH + h) * a.cap;
-            if (pass) {
-                rM = s_pre[h * 4 + 2]; selM = s_pre[h * 4 + 3];
-                int gt_before = s_pre[h * 4 + 0];
-                eq_before = s_pre[h * 4 + 1];
+            unsigned task_tot = 0;                                     // > tau | == tau << 16 of the task
 #pragma unroll 1
-                for (int s2 = 0; s2 < s; ++s2) { gt_before += s_cnt[(s2 * KH + h) * 2]; eq_before += s_cnt[(s2 * KH + h) * 2 + 1]; }
-                out_base = a.s_end + gt_before + min(eq_before, rM);
-            }
-            // A lane walks RUN consecutive keys per trip (five 8-byte loads; the odd number of 8-byte
-            // units between lanes keeps the loads free of bank conflicts) and keeps one flag bit per
-            // key. Pass 1 ranks the lanes with one packed warp scan per trip and lets every lane
-            // write its own attended keys in order.
-#pragma unroll 1
-            for (int g0 = elo & ~3; g0 < ehi; g0 += 32 * RUN) {
+            for (int g0 = elo & ~3; g0 < ehi; g0 += 32 * RUN, ++slot) {
                 const int r0 = g0 + lane * RUN;
                 unsigned Gf = 0, Ef = 0;                               // bit i: key r0 + i is > tau / == tau
 #pragma unroll
@@ -329,10 +312,8 @@ __global__ void __launch_bounds__(NT, 1) scan_fused_kernel(const FusedArgs a) {
                     const int tl = r0 + 4 * j;
                     uint2 x = make_uint2(0u, 0u);
                     if (tl < ehi) x = *reinterpret_cast<const uint2*>(row + tl);
-                    const unsigned gb = flags4(x.x + cgt, x.y + cgt);
-                    const unsigned eb = flags4(x.x + cge, x.y + cge);
-                    Gf |= gb << (4 * j);
-                    Ef |= eb << (4 * j);
+                    Gf |= flags4(x.x + cgt, x.y + cgt) << (4 * j);
+                    Ef |= flags4(x.x + cge, x.y + cge) << (4 * j);
                 }
                 {   // keys of the run inside [elo, ehi)
                     const int lc = min(max(elo - r0, 0), RUN), hc = min(max(ehi - r0, 0), RUN);
@@ -340,53 +321,16 @@ __global__ void __launch_bounds__(NT, 1) scan_fused_kernel(const FusedArgs a) {
                     Gf &= vm;
                     Ef &= vm & ~Gf;
                 }
-                const int ng = __popc(Gf), ne = __popc(Ef);
-                if (!pass) { gtM += ng; geM += ne; continue; }
-                const unsigned packed = (unsigned)ng | ((unsigned)ne << 16);
+                const unsigned packed = (unsigned)__popc(Gf) | ((unsigned)__popc(Ef) << 16);
                 const unsigned inc = (unsigned)prefix_sum((int)packed, lane);
-                const unsigned tot = __shfl_sync(0xffffffffu, inc, 31), exc = inc - packed;
-                const int tot_e = (int)(tot >> 16);
-                unsigned sel = Gf;
-                int below = (int)(exc & 0xffffu), tot_sel = (int)(tot & 0xffffu);
-                if (eq_before + tot_e <= rM) {                          // every tie of this trip is inside the quota
-                    sel |= Ef;
-                    below += (int)(exc >> 16);
-                    tot_sel += tot_e;
-                } else if (eq_before < rM) {                            // the quota runs out inside this trip
-                    int rank = eq_before + (int)(exc >> 16);
-                    unsigned e = Ef, tk = 0;
-                    while (e && rank < rM) { const unsigned bit = e & (0u - e); tk |= bit; e ^= bit; ++rank; }
-                    sel |= tk;
-                    const int nt = __popc(tk), inc2 = prefix_sum(nt, lane);
-                    below += inc2 - nt;
-                    tot_sel += __shfl_sync(0xffffffffu, inc2, 31);
-                }
-                int pos = out_base + below;
-                const int kbase = t0 + r0;
-                while (sel) {
-                    const int i = __ffs((int)sel) - 1;
-                    sel &= sel - 1u;
-                    if (pos < a.cap) oi[pos] = kbase + i;
-                    ++pos;
-                }
-                out_base += tot_sel;
-                eq_before += tot_e;
+                const unsigned tot = __shfl_sync(0xffffffffu, inc, 31);
+                s_trip[slot * 32] = make_uint4(Gf, Ef, inc - packed, tot);
+                task_tot += tot;                                       // at most chunk < 65536 keys per field
             }
-            if (!pass) {
-                gtM = __reduce_add_sync(0xffffffffu, gtM);
-                geM = __reduce_add_sync(0xffffffffu, geM);
-                if (lane == 0) { s_cnt[task * 2] = gtM; s_cnt[task * 2 + 1] = geM; }
-            } else {
-                // always-kept keys of this sub-range: the sink at its own index, the recent window at the end
-                for (int t = t0 + lo + lane; t < min(t0 + hi, a.s_end); t += 32)
-                    if (t < a.cap) oi[t] = t;
-                for (int t = max(t0 + lo, a.r_start) + lane; t < t0 + hi; t += 32) {
-                    const int pos = a.s_end + selM + (t - a.r_start);
-                    if (pos < a.cap) oi[pos] = t;
-                }
-            }
+            if (lane == 0) { s_cnt[task * 2] = (int)(task_tot & 0xffffu); s_cnt[task * 2 + 1] = (int)(task_tot >> 16); }
         }
-        if (pass) break;
+    }
+    {
         __syncthreads();
         SL_STAMP(10)
         if (tid < KH) {
@@ -448,6 +392,59 @@ __global__ void __launch_bounds__(NT, 1) scan_fused_kernel(const FusedArgs a) {
         __syncthreads();
         SL_STAMP(5)
     }
+    {
+        int slot = 0;
+#pragma unroll 1
+        for (int task = warp; task < ntasks; task += NW) {
+            const int h = task & (KH - 1), s = task >> (31 - __clz(KH));
+            const int lo = min(len, s * sub), hi = min(len, (s + 1) * sub);
+            const int elo = max(lo, mlo), ehi = min(hi, mhi);
+            const int rM = s_pre[h * 4 + 2], selM = s_pre[h * 4 + 3];
+            int gt_before = s_pre[h * 4 + 0], eq_before = s_pre[h * 4 + 1];
+#pragma unroll 1
+            for (int s2 = 0; s2 < s; ++s2) { gt_before += s_cnt[(s2 * KH + h) * 2]; eq_before += s_cnt[(s2 * KH + h) * 2 + 1]; }
+            int out_base = a.s_end + gt_before + min(eq_before, rM);
+            int* oi = a.idx + ((size_t)b * KH + h) * a.cap;
+#pragma unroll 1
+            for (int g0 = elo & ~3; g0 < ehi; g0 += 32 * RUN, ++slot) {
+                const uint4 st = s_trip[slot * 32];                    // {> tau flags, == tau flags, counts below, totals}
+                const unsigned Ef = st.y, exc = st.z, tot = st.w;
+                const int tot_e = (int)(tot >> 16);
+                unsigned sel = st.x;
+                int below = (int)(exc & 0xffffu), tot_sel = (int)(tot & 0xffffu);
+                if (eq_before + tot_e <= rM) {                          // every tie of this trip is inside the quota
+                    sel |= Ef;
+                    below += (int)(exc >> 16);
+                    tot_sel += tot_e;
+                } else if (eq_before < rM) {                            // the quota runs out inside this trip
+                    int rank = eq_before + (int)(exc >> 16);
+                    unsigned e = Ef, tk = 0;
+                    while (e && rank < rM) { const unsigned bit = e & (0u - e); tk |= bit; e ^= bit; ++rank; }
+                    sel |= tk;
+                    const int nt = __popc(tk), inc2 = prefix_sum(nt, lane);
+                    below += inc2 - nt;
+                    tot_sel += __shfl_sync(0xffffffffu, inc2, 31);
+                }
+                int pos = out_base + below;
+                const int kbase = t0 + g0 + lane * RUN;
+                while (sel) {
+                    const int i = __ffs((int)sel) - 1;
+                    sel &= sel - 1u;
+                    if (pos < a.cap) oi[pos] = kbase + i;
+                    ++pos;
+                }
+                out_base += tot_sel;
+                eq_before += tot_e;
+            }
+            // always-kept keys of this sub-range: the sink at its own index, the recent window at the end
+            for (int t = t0 + lo + lane; t < min(t0 + hi, a.s_end); t += 32)
+                if (t < a.cap) oi[t] = t;
+            for (int t = max(t0 + lo, a.r_start) + lane; t < t0 + hi; t += 32) {
+                const int pos = a.s_end + selM + (t - a.r_start);
+                if (pos < a.cap) oi[pos] = t;
+            }
+        }
+    }
 
     SL_STAMP(6)
     // ------------------------------------------------------------------ leave the workspace zeroed
@@ -496,6 +493,19 @@ bool fused_covers(int KH, int G) { return KH <= 32 && (KH & (KH - 1)) == 0 && sl
 size_t fused_fixed_smem(int KH, int nbins, int S) {
     return (size_t)KH * 32 * 4 + (size_t)KH * 4 * 4 + (size_t)KH * 2 * 4 + (size_t)KH * S * 2 * 4 + (size_t)KH * 4 * 4 +
            (size_t)KH * nbins * 4;
+}
+
+size_t fused_plan_smem(FusedArgs& f, int KH, int nbins, int S, int chunk) {
+    size_t off = (fused_fixed_smem(KH, nbins, S) + 15) / 16 * 16;
+    f.score_off = (int)off;
+    off = (off + (size_t)(chunk + 64) * KH * 2 + 15) / 16 * 16;
+    const int tasks_per_warp = (KH * S + NW - 1) / NW;
+    const int sub = (((chunk + S - 1) / S) + 127) & ~127;              // the longest sub-range a task can get
+    const int trips = (sub + 3 + 32 * 20 - 1) / (32 * 20) + 1;         // trips of 640 keys, one spare
+    f.trips_per_warp = tasks_per_warp * trips;
+    f.trip_off = (int)off;
+    off += (size_t)NW * f.trips_per_warp * 32 * 16;
+    return off;
 }
 
 size_t shard_message_bytes(int B, int KH, int nbins, int cws) {

@@ -765,10 +765,8 @@ extern "C" int sl_scan_topk(const uint32_t* d_q_codes, const uint32_t* d_k_codes
         f.cws = coarse_shift(p.nbins);
         const int roww = (p.chunk >> 1) + ((4 - (p.chunk >> 1)) & 31);
         f.rowh = 2 * roww;
-        const size_t score_off = align_up(slscan::fused_fixed_smem(KH, p.nbins, p.S), 16);
-        f.score_off = (int)score_off;
-        const size_t smem = score_off + (size_t)(p.chunk + 64) * KH * 2;
-        if (smem <= (size_t)SMEM_BUDGET + 16 * 1024) return slscan::launch_fused(f, smem, s);
+        const size_t smem = slscan::fused_plan_smem(f, KH, p.nbins, p.S, p.chunk);
+        if (smem <= (size_t)SMEM_BUDGET + 24 * 1024) return slscan::launch_fused(f, smem, s);
     }
     ScanArgs a = {};
     a.q = reinterpret_cast<const uint4*>(d_q_codes);
@@ -875,10 +873,8 @@ extern "C" int sl_scan_topk_sharded(const uint32_t* d_q_codes, const uint32_t* d
     f.cws = coarse_shift(p.nbins);
     const int roww = (p.chunk >> 1) + ((4 - (p.chunk >> 1)) & 31);
     f.rowh = 2 * roww;
-    const size_t score_off = align_up(slscan::fused_fixed_smem(KH, p.nbins, p.S), 16);
-    f.score_off = (int)score_off;
-    const size_t smem = score_off + (size_t)(p.chunk + 64) * KH * 2;
-    SL_REQUIRE(smem <= (size_t)SMEM_BUDGET + 16 * 1024, SL_ESHAPE, "sl_scan_topk_sharded: chunk does not fit in shared memory");
+    const size_t smem = slscan::fused_plan_smem(f, KH, p.nbins, p.S, p.chunk);
+    SL_REQUIRE(smem <= (size_t)SMEM_BUDGET + 24 * 1024, SL_ESHAPE, "sl_scan_topk_sharded: chunk does not fit in shared memory");
     for (int r = 0; r < R; ++r) {
         SL_REQUIRE(peer_bufs[r] != nullptr && sl::aligned16(peer_bufs[r]), SL_EINVAL, "sl_scan_topk_sharded: bad buffer of rank %d", r);
         f.peer[r] = static_cast<unsigned char*>(peer_bufs[r]);
