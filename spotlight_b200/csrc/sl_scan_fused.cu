@@ -10,11 +10,12 @@
 //      histogram and to a coarse one (<= 32 bins per head)
 //   -- the only grid barrier (bounded) --
 //   B  threshold per head: one warp reads the coarse bins (one per lane), then the fine bins of
-//      the coarse bin that holds the threshold; count own {> tau, == tau} keys; publish them as
-//      one flagged 64-bit word per (head, chunk); poll all chunks' words (bounded)
+//      the coarse bin that holds the threshold; flag, count and rank the own {> tau, == tau} keys
+//      (kept in shared memory); publish the counts as one flagged 64-bit word per (head, chunk);
+//      poll all chunks' words (bounded)
 //   C  write the attended keys at their final positions: ascending, ties to the lowest index.
-// The kernel is written for a small instruction footprint: its phases run once per launch, so
-// their cost is the instruction fetch, not the arithmetic.
+// The kernel is written for a small instruction footprint: its phases run once per launch, and
+// code that is not in the instruction cache runs at a third of the resident rate.
 #include "sl_scan.cuh"
 #include "sl_sliced.cuh"
 
@@ -22,12 +23,13 @@ namespace {
 
 using namespace slscan;
 
-// SHARD: this rank holds a contiguous part of a longer context. After the grid barrier the CTAs
-// merge the copies of the local histograms and store them into slot `rank` of every rank's exchange
-// buffer (plain peer stores over NVLink; one CTA per batch row does it), fences at system scope and
-// writes this launch's epoch into the row's flag `rank` of every buffer; then the row's CTAs wait
-// (bounded) until the R flags of the row in the own buffer carry the epoch. The threshold is then searched over the R slots, and the ties
-// that belong to lower ranks (lower key indices) are taken off this rank's tie quota.
+// SHARD: this rank holds a contiguous part of a longer context. After the grid barrier one CTA per
+// batch row merges the copies of the row's local histograms and stores them into slot `rank` of
+// every rank's exchange buffer (plain peer stores over NVLink), fences at system scope and writes
+// this launch's epoch into the row's flag `rank` of every buffer; then the row's CTAs wait
+// (bounded) until the R flags of the row in the own buffer carry the epoch. The threshold is then
+// searched over the R slots, and the ties that belong to lower ranks (lower key indices) are taken
+// off this rank's tie quota.
 template <int PT, bool SHARD>
 __global__ void __launch_bounds__(NT, 1) scan_fused_kernel(const FusedArgs a) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
