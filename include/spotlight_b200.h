@@ -48,6 +48,17 @@ const char* sl_last_error_string(void);
  * points (the reference sets a DeviceGuard per call, spotlight/kernel/attn_k4_q28.cu:116). */
 int sl_set_device(int device);
 
+/* Process-wide switches, for measurements and tests; the defaults are what the decode path is tuned
+ * for. Takes effect for launches made after the call. No reference counterpart.
+ *   SL_OPT_PDL          1 (default): decode-path kernels are launched with programmatic stream
+ *                       serialisation, so a kernel's prologue overlaps its predecessor's tail; 0: plain launches
+ *   SL_OPT_L2_PREFETCH  1 (default): sl_decode_prepare asks L2 for the code cache that the
+ *                       sl_scan_topk of the same step streams next (caches of at most 24 MB); 0: off
+ *   SL_OPT_SCAN_KERNEL  which kernel sl_scan_topk uses where several apply (results are identical):
+ *                       1 (default) the one-barrier kernel, 2 the flagged-word kernel, 0 the general kernel */
+typedef enum { SL_OPT_PDL = 0, SL_OPT_L2_PREFETCH = 1, SL_OPT_SCAN_KERNEL = 2 } sl_option;
+int sl_configure(int option, int value);
+
 /* Sign-bit packing: bit j of output byte i  <=>  x[8*i + j] > 0 (LSB first). Read as uint32
  * words on a little-endian machine this is the 32-bit packing of the reference.
  * Replaces packbits (spotlight/kernel/packbits.cu:28-63), pack_dx_u32_func

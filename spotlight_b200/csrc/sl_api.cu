@@ -6,7 +6,6 @@
 #include "sl_common.cuh"
 
 namespace sl {
-void set_pdl(int on);
 
 static thread_local char g_err[512] = "";
 
@@ -20,27 +19,10 @@ int fail(int code, const char* fmt, ...) {
     return code;
 }
 
-static int g_pdl = -1;
+static int g_pdl = 1, g_l2pf = 1;
 
-bool pdl_enabled() {
-    if (g_pdl < 0) {
-        const char* e = getenv("SL_PDL");
-        g_pdl = (e && e[0] == '0') ? 0 : 1;
-    }
-    return g_pdl != 0;
-}
-
-void set_pdl(int on) { g_pdl = on ? 1 : 0; }
-
-static int g_l2pf = -1;
-
-bool l2_prefetch_enabled() {
-    if (g_l2pf < 0) {
-        const char* e = getenv("SL_L2_PREFETCH");
-        g_l2pf = (e && e[0] == '0') ? 0 : 1;
-    }
-    return g_l2pf != 0;
-}
+bool pdl_enabled() { return g_pdl != 0; }
+bool l2_prefetch_enabled() { return g_l2pf != 0; }
 
 // cudaFuncSetAttribute costs a microsecond or two; a decode loop launches thousands of kernels per
 // second, so the largest dynamic shared-memory size set per (device, kernel) is remembered.
@@ -88,6 +70,16 @@ extern "C" int sl_workspace_init(void* d_workspace, size_t bytes, void* stream) 
     return SL_OK;
 }
 
-// Development switch, not part of the public header: turns programmatic dependent launch of the
-// decode-path kernels on or off (default on; the environment variable SL_PDL=0 turns it off).
-extern "C" void sl_debug_set_pdl(int on) { sl::set_pdl(on); }
+namespace slscan { void set_scan_kernel(int v); }
+
+extern "C" int sl_configure(int option, int value) {
+    switch (option) {
+        case SL_OPT_PDL: sl::g_pdl = value ? 1 : 0; return SL_OK;
+        case SL_OPT_L2_PREFETCH: sl::g_l2pf = value ? 1 : 0; return SL_OK;
+        case SL_OPT_SCAN_KERNEL:
+            SL_REQUIRE(value >= 0 && value <= 2, SL_EINVAL, "sl_configure: SL_OPT_SCAN_KERNEL takes 0, 1 or 2");
+            slscan::set_scan_kernel(value);
+            return SL_OK;
+        default: return sl::fail(SL_EINVAL, "sl_configure: unknown option %d", option);
+    }
+}

@@ -18,8 +18,8 @@ char* err_buf();
 int fail(int code, const char* fmt, ...);
 int sm_count();          // SMs of the current device (cached per device)
 cudaError_t ensure_dyn_smem(const void* func, size_t bytes);   // opt-in to `bytes` of dynamic shared memory, once
-bool pdl_enabled();      // programmatic dependent launch on (default) / off (SL_PDL=0 or sl_set_pdl)
-bool l2_prefetch_enabled();   // the decode-step hash warms L2 with the code cache (SL_L2_PREFETCH=0: off)
+bool pdl_enabled();      // programmatic dependent launch on (default) / off (sl_configure)
+bool l2_prefetch_enabled();   // the decode-step hash warms L2 with the code cache (sl_configure)
 
 #define SL_CUDA_OK(expr)                                                                    \
     do {                                                                                    \
@@ -117,8 +117,8 @@ template <> struct VT<float> {
 // A bounded grid-wide barrier over `n_ctas` co-resident CTAs. `counter` counts arrivals and
 // only grows during a launch (target of the j-th barrier is (j+1)*n_ctas). Thread 0 fences
 // (ordering the CTA's earlier global writes, which the bar.sync made visible to it), arrives
-// with a relaxed add and polls with relaxed loads; data published before the barrier must be
-// read with L2-coherent loads (__ldcg) after it. Measured on B200: ~1.2 us, against ~1.5 us
+// with a relaxed add, polls with relaxed loads and fences again once the poll has succeeded; data
+// published before the barrier is read with L2-coherent loads (__ldcg) after it. Measured on B200: ~1.2 us, against ~1.5 us
 // for the release-add / acquire-poll form. Gives up after `limit` polls, sets *status and
 // returns false; callers carry on with bounded work.
 __device__ __forceinline__ bool grid_barrier(unsigned* counter, unsigned target, int* status,
@@ -135,6 +135,7 @@ __device__ __forceinline__ bool grid_barrier(unsigned* counter, unsigned target,
             if (v >= target) break;
             if (++it > limit) { ok = 0; break; }
         }
+        __threadfence();     // acquire side: the CTA's later reads are ordered after the successful poll
         if (!ok && status) atomicExch(status, 1);
         ok_s = ok;
     }

@@ -41,12 +41,58 @@ struct FusedArgs {
     int kk;                    // min(k, global number of keys)
 };
 
+// ---- the one-barrier kernel of the decode step (sl_scan_lean.cu) ----
+constexpr int LEAN_CWS = 3;        // log2 of the coarse bin width: 8 scores
+constexpr int LEAN_MAX_WIN = 96;   // always-kept keys (sink + recent) it handles, three per lane
+constexpr int LEAN_CPL_MAX = 5;    // chunks per lane in the trip for the chunks' counts; coarse bins per lane
+
+struct LeanArgs {
+    const uint4* q;            // [B,QH] codes
+    const uint4* k;            // code stream
+    long long k_bstride;       // batch stride in codes
+    int B, KH, G, layout, N;
+    int k_budget;
+    int s_end, r_start;        // forced ranges: [0,s_end) and [r_start,N)
+    int* idx;
+    int cap;
+    int* cnt;
+    short* scores_out;         // optional [B,N,KH]
+    unsigned* sync;            // [B,2] barrier arrivals, finished CTAs
+    unsigned* epoch;           // [B] launches completed on this workspace (parity picks the coarse buffer)
+    unsigned* chist;           // [2][NCOPY][B][KH][NC] coarse histograms
+    unsigned* pub;             // [B*ctas_per_b][KH][prow/2] counts per score of every chunk, 16-bit pairs
+    unsigned short* pubc;      // [B*ctas_per_b][KH][NC] keys of the chunk above each coarse bin
+    unsigned short* wsc;       // [B][KH][LEAN_MAX_WIN] scores of the always-kept keys
+    int* status;
+    int ctas_per_b, chunk, nbins, S;
+    int NC;                    // coarse bins per head
+    int prow;                  // 16-bit words per published row: 8 * NC
+    int rowh;                  // row stride of the score rows in shared memory (halfwords)
+    int hist_off, score_off;   // byte offsets of the histogram rows and of the score rows in shared memory
+    unsigned long long* dbg;   // optional [grid][16] phase stamps (profiling builds only)
+};
+
+bool lean_covers(int KH, int G, int ctas_per_b, int chunk, int nwin);
+int lean_prow(int nbins);
+int lean_nc(int nbins);
+size_t lean_plan_smem(LeanArgs& f, int KH, int nbins, int S, int chunk);   // fills the offsets, returns the total
+int launch_lean(const LeanArgs& a, size_t smem, cudaStream_t s);
+
 bool fused_covers(int KH, int G);
 size_t fused_fixed_smem(int KH, int nbins, int S);
 int launch_fused(const FusedArgs& a, size_t smem, cudaStream_t s);
 size_t fused_plan_smem(FusedArgs& f, int KH, int nbins, int S, int chunk);   // fills the shared-memory offsets, returns the total
 size_t shard_message_bytes(int B, int KH, int nbins, int cws);   // one rank's histogram message, padded to 16 bytes
-extern unsigned long long* g_dbg_timing;   // set by sl_debug_scan_timing
+// Phase stamps exist only in profiling builds (-DSL_SCAN_TIMING): thread 0 of every CTA stores the SM
+// cycle counter at its phase boundaries into the buffer given to sl_profile_scan_timing.
+#ifdef SL_SCAN_TIMING
+extern unsigned long long* g_dbg_timing;
+#define SL_STAMP(i) if (a.dbg && threadIdx.x == 0) a.dbg[blockIdx.x * 16 + (i)] = (unsigned long long)clock64();
+#define SL_STAMP_BUF slscan::g_dbg_timing
+#else
+#define SL_STAMP(i)
+#define SL_STAMP_BUF nullptr
+#endif
 
 __device__ __forceinline__ void touch(const void* p) {   // warms the TLB for a page used later
     unsigned v;

@@ -55,12 +55,6 @@ __global__ void __launch_bounds__(NT, 1) scan_fused_kernel(const FusedArgs a) {
     unsigned long long* seg_b = a.seg + (size_t)b * KH * cpb;
     sl::pdl_trigger();
     sl::pdl_wait();
-#define SL_STAMP(i) if (a.dbg && tid == 0) a.dbg[blockIdx.x * 16 + (i)] = (unsigned long long)clock64();
-    if (a.dbg && tid == 0) {
-        unsigned long long t_;
-        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_));
-        a.dbg[blockIdx.x * 16 + 15] = t_;
-    }
     SL_STAMP(0)
 
     // ------------------------------------------------------------------ A: scan + histogram
@@ -517,7 +511,7 @@ size_t shard_message_bytes(int B, int KH, int nbins, int cws) {
 
 int launch_fused(const FusedArgs& a_in, size_t smem, cudaStream_t s) {
     FusedArgs a = a_in;
-    a.dbg = g_dbg_timing;
+    a.dbg = SL_STAMP_BUF;
     fused_kernel_t kern = a.R > 0 ? pick<true>(sliced_planes(a.G)) : pick<false>(sliced_planes(a.G));
     SL_CUDA_OK(sl::ensure_dyn_smem(reinterpret_cast<const void*>(kern), smem));
     SL_CUDA_OK(sl::launch_kernel(kern, dim3((unsigned)(a.B * a.ctas_per_b)), dim3(NT), smem, s, true, a));

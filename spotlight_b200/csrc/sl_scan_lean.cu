@@ -1,0 +1,519 @@
+// The decode step's fused Hamming scan + exact top-k + sink/recent window for the common shapes
+// (several CTAs per batch row, a chunk's scores fit in shared memory, kv heads divide the warp, the
+// bit-sliced scorer covers the group size). One cooperative launch with ONE grid-wide dependency:
+// everything a CTA needs from the other chunks after the barrier is published before it, so the
+// tail is two trips to L2 and one pass over the chunk's scores.
+//
+//   A  the chunk is cut into S contiguous sub-ranges, each streamed by its own group of warps
+//      (8 x 16-byte loads in flight per thread); the bit-sliced scorer leaves the 16-bit scores in
+//      shared memory ([head][key], bank-spread) and counts them in a histogram per (sub-range, head)
+//   P  one pass over the histograms: the chunk's counts per score (sub-ranges added up) go to global
+//      memory as 16-bit words, 16 bytes per coarse bin (8 scores) and thread; the coarse bins' counts
+//      are added to a small global histogram; per head one warp turns them into "keys of this chunk
+//      above coarse bin c" and publishes that too; the scores of the chunk's sink / recent keys go
+//      beside them
+//   -- the only grid barrier (bounded) --
+//   T  one warp per head: the global coarse bins give the 8 scores that hold the threshold (trip 1);
+//      every chunk's 8 counts there and its count above them (trip 2, one chunk per lane and round)
+//      give the threshold itself, the tie quota, and -- from the same registers -- how many selected
+//      keys and threshold ties lie in the chunks before this one
+//   E  one pass over the chunk's scores: flags, one packed warp scan per 640 keys, the attended
+//      keys written at their final positions (ascending, ties to the lowest index, sink and recent
+//      window included).
+// The coarse histogram is double-buffered by launch parity (a device-side launch counter in the
+// workspace): a launch adds into one buffer and clears the other, so nothing has to be cleared
+// between the threshold search and the end of the launch and no second grid-wide wait exists.
+#include "sl_scan.cuh"
+#include "sl_sliced.cuh"
+
+namespace {
+
+using namespace slscan;
+
+__device__ __forceinline__ uint4 ldcg_v4(const void* p) {
+    uint4 r;
+    asm volatile("ld.global.cg.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w) : "l"(p));
+    return r;
+}
+__device__ __forceinline__ unsigned ldcg_u32(const void* p) {
+    unsigned r;
+    asm volatile("ld.global.cg.u32 %0, [%1];" : "=r"(r) : "l"(p));
+    return r;
+}
+__device__ __forceinline__ unsigned ldcg_u16(const void* p) {
+    unsigned short r;
+    asm volatile("ld.global.cg.u16 %0, [%1];" : "=h"(r) : "l"(p));
+    return r;
+}
+
+template <int PT>
+__global__ void __launch_bounds__(NT, 1) scan_lean_kernel(const LeanArgs a) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    const int KH = a.KH, nbins = a.nbins, nb1 = (nbins + 4) & ~3, N = a.N, cpb = a.ctas_per_b, S = a.S;   // rows of nb1 words: 16-byte aligned, R[nbins..] = 0
+    uint32_t* s_planes = reinterpret_cast<uint32_t*>(smem_raw);                 // [KH][2][PT][4]
+    int* s_pbase = reinterpret_cast<int*>(s_planes + KH * 32);                    // [KH][4]
+    int* s_tau = s_pbase + KH * 4;                                                // [KH]
+    int* s_pre = s_tau + KH;                                                      // [KH][4] {> tau before, == tau before, rM, selM}
+    unsigned short* s_win = reinterpret_cast<unsigned short*>(s_pre + KH * 4);    // [KH][LEAN_MAX_WIN]
+    unsigned* s_coarse = reinterpret_cast<unsigned*>(s_win + KH * LEAN_MAX_WIN);  // [KH][NC]
+    unsigned* shist = reinterpret_cast<unsigned*>(smem_raw + a.hist_off);         // [S][KH][nb1]
+    unsigned short* sscores = reinterpret_cast<unsigned short*>(smem_raw + a.score_off);
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int b = blockIdx.x / cpb, c = blockIdx.x - b * cpb;
+    const int t0 = min(N, c * a.chunk), t1 = min(N, t0 + a.chunk);
+    const int len = t1 - t0, ncodes = len * KH;
+    const int rowh = a.rowh;                                                      // row stride of sscores (halfwords)
+    const int khs = 31 - __clz(KH);
+    const int sub = ((len + S - 1) / S + 127) & ~127;                             // keys per sub-range
+    const int NC = a.NC, cslice = a.B * KH * NC;
+    const int nwin = a.s_end + (N - a.r_start);                                   // always-kept keys of the row
+    sl::pdl_trigger();
+    sl::pdl_wait();
+    SL_STAMP(0)
+    const unsigned par = __ldcg(a.epoch + b) & 1u;                                // this launch's coarse buffer
+    unsigned* chist_b = a.chist + (size_t)par * NCOPY * cslice + b * KH * NC;
+
+    // ------------------------------------------------------------------ A: scan + histograms
+    {
+        const uint4* base0 = a.k + (size_t)b * a.k_bstride + (size_t)t0 * KH;
+        const uint32_t* qb = reinterpret_cast<const uint32_t*>(a.q + (size_t)b * KH * a.G);
+        const PlaneWords pw = planes_issue(qb, KH, a.G, a.layout, warp, NW, lane);   // ahead of the stream's loads
+        // group g of warps streams sub-range g of the chunk
+        const int wpg = NW / S, grp = warp / wpg, wig = warp - grp * wpg;
+        const int gbeg = min(ncodes, grp * sub * KH), gend = min(ncodes, (grp + 1) * sub * KH);
+        const uint4* base = base0 + gbeg;
+        const int gcodes = gend - gbeg;
+        uint4 cd[U];
+        int tile = wig;
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int i = tile * (32 * U) + u * 32 + lane;
+            if (i < gcodes) cd[u] = sl::ld_stream_v4(base + i);
+        }
+        if (tid == NT - 32) {            // pages the later phases store to
+            touch(a.idx + (size_t)b * KH * a.cap);
+            touch(a.cnt + b * KH);
+            touch(a.pub + (size_t)blockIdx.x * KH * (a.prow >> 1));
+            touch(a.pubc + (size_t)blockIdx.x * KH * a.NC);
+        }
+        for (int i = tid; i < S * KH * (nb1 >> 2); i += NT) reinterpret_cast<uint4*>(shist)[i] = make_uint4(0u, 0u, 0u, 0u);
+        {   // last launch's coarse buffer: cleared here, added to by the next launch
+            unsigned* other = a.chist + (size_t)(par ^ 1u) * NCOPY * cslice + b * KH * NC;
+            const int ctot = KH * NC;
+            for (int i = c * NT + tid; i < NCOPY * ctot; i += cpb * NT) other[(i / ctot) * cslice + i % ctot] = 0;
+        }
+        planes_finish<PT>(pw, KH, a.G, s_planes, s_pbase, warp, NW, lane);
+        stage_planes<PT>(qb, KH, a.G, a.layout, s_planes, s_pbase, warp, NW, lane, 1);   // KH > 8
+        __syncthreads();
+        uint32_t M[PT][4], Mp[PT][4];
+        const int hh = lane & (KH - 1);                       // this lane's head (KH is a power of two <= 32)
+        const int sbase = load_planes<PT>(s_planes, s_pbase, hh, M, Mp);
+        const int ssh = sliced_shift(a.G);
+        unsigned short* srow = sscores + hh * rowh + (gbeg >> khs);
+        unsigned* hrow = shist + (grp * KH + hh) * nb1;
+        short* so = a.scores_out ? a.scores_out + ((size_t)b * N + t0) * KH + gbeg : nullptr;
+        SL_STAMP(1)
+#pragma unroll 1
+        while (tile * (32 * U) < gcodes) {
+            const int i0 = tile * (32 * U) + lane;
+            int sv[U];
+#pragma unroll
+            for (int u = 0; u < U; ++u) sv[u] = sbase + (sliced_score<PT>(cd[u], M, Mp) << ssh);
+            tile += wpg;
+#pragma unroll
+            for (int u = 0; u < U; ++u) {       // next tile's loads before the stores of this one
+                const int i = tile * (32 * U) + u * 32 + lane;
+                if (i < gcodes) cd[u] = sl::ld_stream_v4(base + i);
+            }
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                const int i = i0 + u * 32;
+                if (i < gcodes) {
+                    srow[i >> khs] = (unsigned short)sv[u];
+                    atomicAdd(hrow + sv[u], 1u);
+                    if (so) so[i] = (short)sv[u];
+                }
+            }
+        }
+        __syncthreads();
+    }
+    SL_STAMP(2)
+
+    // ------------------------------------------------------------------ P: suffix sums, publish
+    {
+        // scores of the always-kept keys this chunk owns (the other CTAs correct their counts with them)
+        for (int j = tid; j < KH * nwin; j += NT) {
+            const int h = j / nwin, wj = j - h * nwin;
+            const int t = wj < a.s_end ? wj : a.r_start + (wj - a.s_end);
+            if (t >= t0 && t < t1) a.wsc[((size_t)b * KH + h) * LEAN_MAX_WIN + wj] = sscores[h * rowh + (t - t0)];
+        }
+        // one thread per (head, coarse bin): the chunk's 8 counts of the bin as 16-bit words (zero beyond
+        // the last score), their sum into shared memory and -- if not zero -- into the global coarse bins
+        unsigned* dstc = chist_b + (c & (NCOPY - 1)) * cslice;
+        uint4* pub = reinterpret_cast<uint4*>(a.pub + (size_t)blockIdx.x * KH * (a.prow >> 1));
+        const int nc8 = a.prow >> 3;                          // 16-byte groups per published row (>= NC)
+#pragma unroll 1
+        for (int t = tid; t < KH * nc8; t += NT) {
+            const int h = t / nc8, cb = t - h * nc8;
+            unsigned v[8] = {0u, 0u, 0u, 0u, 0u, 0u, 0u, 0u};
+            if (cb < NC) {
+                const uint4* R = reinterpret_cast<const uint4*>(shist + h * nb1 + (cb << LEAN_CWS));
+                for (int s = 0; s < S; ++s) {
+                    const uint4 x = R[s * KH * (nb1 >> 2)];
+                    v[0] += x.x; v[1] += x.y; v[2] += x.z; v[3] += x.w;
+                    if ((cb << LEAN_CWS) + 4 < nb1) {
+                        const uint4 y = R[s * KH * (nb1 >> 2) + 1];
+                        v[4] += y.x; v[5] += y.y; v[6] += y.z; v[7] += y.w;
+                    }
+                }
+                const unsigned cs = ((v[0] + v[1]) + (v[2] + v[3])) + ((v[4] + v[5]) + (v[6] + v[7]));
+                s_coarse[h * NC + cb] = cs;
+                if (cs) atomicAdd(dstc + h * NC + cb, cs);
+            }
+            pub[t] = make_uint4(v[0] | (v[1] << 16), v[2] | (v[3] << 16), v[4] | (v[5] << 16), v[6] | (v[7] << 16));
+        }
+        __syncthreads();
+        SL_STAMP(7)
+        // per head: keys of this chunk above each coarse bin
+        const int CPL = (NC + 31) >> 5;
+#pragma unroll 1
+        for (int h = warp; h < KH; h += NW) {
+            unsigned cv[LEAN_CPL_MAX], sum = 0;
+#pragma unroll
+            for (int i = 0; i < LEAN_CPL_MAX; ++i) {
+                const int cb = lane * CPL + i;
+                cv[i] = (i < CPL && cb < NC) ? s_coarse[h * NC + cb] : 0u;
+                sum += cv[i];
+            }
+            unsigned above = suffix_sum(sum, lane) - sum;
+            unsigned short* pc = a.pubc + ((size_t)blockIdx.x * KH + h) * NC;
+#pragma unroll
+            for (int i = LEAN_CPL_MAX - 1; i >= 0; --i) {
+                const int cb = lane * CPL + i;
+                if (i < CPL && cb < NC) pc[cb] = (unsigned short)above;
+                above += cv[i];
+            }
+        }
+    }
+    SL_STAMP(3)
+    sl::grid_barrier(a.sync + 2 * b, (unsigned)cpb, a.status);
+    SL_STAMP(4)
+
+    // ------------------------------------------------------------------ T: threshold, quota, counts before this chunk
+    {
+        const int kk = min(a.k_budget, N);
+        const int CPL = (NC + 31) >> 5;                      // coarse bins per lane, consecutive
+#pragma unroll 1
+        for (int h = warp; h < KH; h += NW) {
+            // always-kept keys of the row: their scores, loaded with the first trip
+            unsigned wv[LEAN_MAX_WIN / 32];
+#pragma unroll
+            for (int i = 0; i < LEAN_MAX_WIN / 32; ++i) {
+                const int wj = lane + 32 * i;
+                wv[i] = wj < nwin ? ldcg_u16(a.wsc + ((size_t)b * KH + h) * LEAN_MAX_WIN + wj) : 0xffffu;
+            }
+            int tau = nbins, pre_gt = 0, pre_eq = 0, rM = 0, selM = 0;
+            if (kk > 0) {
+                // trip 1: global coarse bins -> the 8 scores [Lb, Lb + 8) that hold the threshold
+                unsigned cv[LEAN_CPL_MAX];
+                unsigned csum = 0;
+#pragma unroll
+                for (int i = 0; i < LEAN_CPL_MAX; ++i) {
+                    const int cb = lane * CPL + i;
+                    cv[i] = 0u;
+                    if (i < CPL && cb < NC) {
+#pragma unroll
+                        for (int cp = 0; cp < NCOPY; ++cp) cv[i] += __ldcg(chist_b + cp * cslice + h * NC + cb);
+                    }
+                    csum += cv[i];
+                }
+                const unsigned suf = suffix_sum(csum, lane);
+                const unsigned ball = __ballot_sync(0xffffffffu, suf >= (unsigned)kk);   // not empty: the row holds N >= kk keys
+                const int Ll = 31 - __clz(ball | 1u);
+                int Lc_l = 0;
+                {
+                    unsigned above = suf - csum;
+#pragma unroll
+                    for (int i = LEAN_CPL_MAX - 1; i >= 0; --i) {
+                        if (above < (unsigned)kk && above + cv[i] >= (unsigned)kk) Lc_l = lane * CPL + i;
+                        above += cv[i];
+                    }
+                }
+                const int Lc = __shfl_sync(0xffffffffu, Lc_l, Ll), Lb = Lc << LEAN_CWS;
+                SL_STAMP(8)
+                // trip 2: every chunk's 8 counts at Lb .. Lb + 7 and its count above them, chunk = lane + 32 j
+                uint4 raw[LEAN_CPL_MAX];
+                unsigned abv[LEAN_CPL_MAX];
+#pragma unroll
+                for (int j = 0; j < LEAN_CPL_MAX; ++j) {
+                    const int cc = lane + 32 * j;
+                    raw[j] = make_uint4(0u, 0u, 0u, 0u);
+                    abv[j] = 0u;
+                    if (cc < cpb) {
+                        const size_t rowi = (size_t)(b * cpb + cc) * KH + h;
+                        raw[j] = __ldcg(reinterpret_cast<const uint4*>(a.pub + rowi * (a.prow >> 1)) + Lc);
+                        abv[j] = __ldcg(a.pubc + rowi * NC + Lc);
+                    }
+                }
+                SL_STAMP(9)
+                int acc[8], accA = 0;
+#pragma unroll
+                for (int i = 0; i < 8; ++i) acc[i] = 0;
+#pragma unroll
+                for (int j = 0; j < LEAN_CPL_MAX; ++j) {
+                    acc[0] += (int)(raw[j].x & 0xffffu); acc[1] += (int)(raw[j].x >> 16);
+                    acc[2] += (int)(raw[j].y & 0xffffu); acc[3] += (int)(raw[j].y >> 16);
+                    acc[4] += (int)(raw[j].z & 0xffffu); acc[5] += (int)(raw[j].z >> 16);
+                    acc[6] += (int)(raw[j].w & 0xffffu); acc[7] += (int)(raw[j].w >> 16);
+                    accA += (int)abv[j];
+                }
+                // sums over the lanes: afterwards lane l holds the row's count at score Lb + (l & 7)
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    acc[i] += __shfl_xor_sync(0xffffffffu, acc[i], 16);
+                    acc[i] += __shfl_xor_sync(0xffffffffu, acc[i], 8);
+                }
+#pragma unroll
+                for (int wd = 4; wd >= 1; wd >>= 1) {
+                    const bool up = (lane & wd) != 0;
+#pragma unroll
+                    for (int i = 0; i < wd; ++i) {
+                        const int send = up ? acc[i] : acc[i + wd];
+                        const int recv = __shfl_xor_sync(0xffffffffu, send, wd);
+                        acc[i] = (up ? acc[i + wd] : acc[i]) + recv;
+                    }
+                }
+                accA = __reduce_add_sync(0xffffffffu, accA);
+                // suffix over the 8 scores: mine = keys of the row with score >= Lb + (l & 7)
+                int mine = acc[0];
+#pragma unroll
+                for (int d = 1; d < 8; d <<= 1) {
+                    const int t = __shfl_down_sync(0xffffffffu, mine, d);
+                    if ((lane & 7) + d < 8) mine += t;
+                }
+                mine += accA;
+                SL_STAMP(10)
+                const unsigned ball2 = __ballot_sync(0xffffffffu, mine >= kk) & 0xffu;   // not empty by the choice of Lb
+                const int ls = 31 - __clz(ball2 | 1u);
+                tau = Lb + ls;
+                const int ge_tot = __shfl_sync(0xffffffffu, mine, ls);
+                const int gt_next = __shfl_sync(0xffffffffu, mine, (ls + 1) & 7);
+                const int gt_tot = ls == 7 ? accA : gt_next;
+                const int r = kk - gt_tot;
+                // keys above / at the threshold in the chunks before this one
+#pragma unroll
+                for (int j = 0; j < LEAN_CPL_MAX; ++j) {
+                    if (lane + 32 * j < c) {
+                        const unsigned w[4] = {raw[j].x, raw[j].y, raw[j].z, raw[j].w};
+                        int gt = (int)abv[j], eq = 0;
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) {
+                            const int v = (int)((i & 1) ? (w[i >> 1] >> 16) : (w[i >> 1] & 0xffffu));
+                            gt += i > ls ? v : 0;
+                            eq += i == ls ? v : 0;
+                        }
+                        pre_gt += gt;
+                        pre_eq += eq;
+                    }
+                }
+                pre_gt = __reduce_add_sync(0xffffffffu, pre_gt);
+                pre_eq = __reduce_add_sync(0xffffffffu, pre_eq);
+                // always-kept keys: threshold ties inside the sink come off the quota; all of them leave the totals
+                int eq_sink = 0, gt_win = 0, eq_win = 0;
+#pragma unroll
+                for (int i = 0; i < LEAN_MAX_WIN / 32; ++i) {
+                    const int wj = lane + 32 * i;
+                    const bool in = wj < nwin;
+                    const int v = (int)wv[i];
+                    gt_win += __popc(__ballot_sync(0xffffffffu, in && v > tau));
+                    eq_win += __popc(__ballot_sync(0xffffffffu, in && v == tau));
+                    eq_sink += __popc(__ballot_sync(0xffffffffu, in && wj < a.s_end && v == tau));
+                }
+                rM = max(r - eq_sink, 0);
+                selM = (gt_tot - gt_win) + min((ge_tot - gt_tot) - eq_win, rM);
+            }
+#pragma unroll
+            for (int i = 0; i < LEAN_MAX_WIN / 32; ++i) s_win[h * LEAN_MAX_WIN + lane + 32 * i] = (unsigned short)wv[i];
+            if (lane == 0) {
+                s_tau[h] = tau;
+                s_pre[h * 4 + 0] = pre_gt; s_pre[h * 4 + 1] = pre_eq; s_pre[h * 4 + 2] = rM; s_pre[h * 4 + 3] = selM;
+                if (c == 0) a.cnt[b * KH + h] = a.s_end + selM + (N - a.r_start);
+            }
+        }
+    }
+    __syncthreads();
+    SL_STAMP(5)
+
+    // ------------------------------------------------------------------ E: flags, ranks, writes
+    // A task is (head, sub-range). A lane walks RUN consecutive keys per trip (five 8-byte loads; the
+    // odd number of 8-byte units between lanes keeps them free of bank conflicts) and keeps one flag
+    // bit per key: adding (0x7fff - tau) to a 16-bit score sets bit 15 iff score > tau, adding
+    // (0x8000 - tau) iff score >= tau, two scores per 32-bit add.
+    {
+        const int ntasks = KH * S;
+        const int mlo = max(t0, a.s_end) - t0, mhi = min(t1, a.r_start) - t0;     // the chunk's keys outside both windows
+        constexpr int RUN = 20;
+#pragma unroll 1
+        for (int task = warp; task < ntasks; task += NW) {
+            const int h = task & (KH - 1), s = task >> khs;
+            const int lo = min(len, s * sub), hi = min(len, (s + 1) * sub);
+            const int elo = max(lo, mlo), ehi = min(hi, mhi);
+            const int tau = s_tau[h];
+            const int rM = s_pre[h * 4 + 2], selM = s_pre[h * 4 + 3];
+            // selected keys / ties before this sub-range: earlier chunks, earlier sub-ranges of this chunk,
+            // less the always-kept keys among them (they are written at their own positions)
+            int gt_before = s_pre[h * 4 + 0], eq_before = s_pre[h * 4 + 1];
+            {
+                // earlier sub-ranges of this chunk: their keys above the threshold (summed from the counts) and at it
+                const int v0 = (min(tau, nbins) + 4) & ~3;              // first 4-aligned score above the threshold ...
+                for (int s2 = 0; s2 < s; ++s2) {
+                    const unsigned* R = shist + (s2 * KH + h) * nb1;
+                    unsigned part = 0;
+                    for (int v = v0 + 4 * lane; v < nb1; v += 128) {
+                        const uint4 x = *reinterpret_cast<const uint4*>(R + v);
+                        part += (x.x + x.y) + (x.z + x.w);
+                    }
+                    if (lane == 0)                                       // ... and the up to three scores between
+                        for (int v = min(tau, nbins) + 1; v < min(v0, nb1); ++v) part += R[v];
+                    gt_before += (int)__reduce_add_sync(0xffffffffu, part);
+                    eq_before += (int)R[min(tau, nbins)];
+                }
+                const int e0 = t0 + lo;
+#pragma unroll
+                for (int i = 0; i < LEAN_MAX_WIN / 32; ++i) {
+                    const int wj = lane + 32 * i;
+                    const int t = wj < a.s_end ? wj : a.r_start + (wj - a.s_end);
+                    const bool in = wj < nwin && t < e0;
+                    const int v = (int)s_win[h * LEAN_MAX_WIN + wj];
+                    gt_before -= __popc(__ballot_sync(0xffffffffu, in && v > tau));
+                    eq_before -= __popc(__ballot_sync(0xffffffffu, in && v == tau));
+                }
+            }
+            int out_base = a.s_end + gt_before + min(eq_before, rM);
+            int* oi = a.idx + ((size_t)b * KH + h) * a.cap;
+            const unsigned short* row = sscores + h * rowh;
+            const unsigned cgt = (unsigned)(0x7fff - tau) * 0x10001u, cge = (unsigned)(0x8000 - tau) * 0x10001u;
+#pragma unroll 1
+            for (int g0 = elo & ~3; g0 < ehi; g0 += 32 * RUN) {
+                const int r0 = g0 + lane * RUN;
+                unsigned Gf = 0, Ef = 0;                               // bit i: key r0 + i is > tau / == tau
+#pragma unroll
+                for (int j = 0; j < RUN / 4; ++j) {
+                    const int tl = r0 + 4 * j;
+                    uint2 x = make_uint2(0u, 0u);
+                    if (tl < ehi) x = *reinterpret_cast<const uint2*>(row + tl);
+                    Gf |= flags4(x.x + cgt, x.y + cgt) << (4 * j);
+                    Ef |= flags4(x.x + cge, x.y + cge) << (4 * j);
+                }
+                {   // keys of the run inside [elo, ehi)
+                    const int lc = min(max(elo - r0, 0), RUN), hc = min(max(ehi - r0, 0), RUN);
+                    const unsigned vm = ((1u << hc) - 1u) & ~((1u << lc) - 1u);
+                    Gf &= vm;
+                    Ef &= vm & ~Gf;
+                }
+                const unsigned packed = (unsigned)__popc(Gf) | ((unsigned)__popc(Ef) << 16);
+                const unsigned inc = (unsigned)prefix_sum((int)packed, lane);
+                const unsigned tot = __shfl_sync(0xffffffffu, inc, 31);
+                const unsigned exc = inc - packed;
+                const int tot_e = (int)(tot >> 16);
+                unsigned sel = Gf;
+                int below = (int)(exc & 0xffffu), tot_sel = (int)(tot & 0xffffu);
+                if (eq_before + tot_e <= rM) {                          // every tie of this trip is inside the quota
+                    sel |= Ef;
+                    below += (int)(exc >> 16);
+                    tot_sel += tot_e;
+                } else if (eq_before < rM) {                            // the quota runs out inside this trip
+                    int rank = eq_before + (int)(exc >> 16);
+                    unsigned e = Ef, tk = 0;
+                    while (e && rank < rM) { const unsigned bit = e & (0u - e); tk |= bit; e ^= bit; ++rank; }
+                    sel |= tk;
+                    const int nt = __popc(tk), inc2 = prefix_sum(nt, lane);
+                    below += inc2 - nt;
+                    tot_sel += __shfl_sync(0xffffffffu, inc2, 31);
+                }
+                int pos = out_base + below;
+                const int kbase = t0 + r0;
+                while (sel) {
+                    const int i = __ffs((int)sel) - 1;
+                    sel &= sel - 1u;
+                    if (pos < a.cap) oi[pos] = kbase + i;
+                    ++pos;
+                }
+                out_base += tot_sel;
+                eq_before += tot_e;
+            }
+            // always-kept keys of this sub-range: the sink at its own index, the recent window at the end
+            for (int t = t0 + lo + lane; t < min(t0 + hi, a.s_end); t += 32)
+                if (t < a.cap) oi[t] = t;
+            for (int t = max(t0 + lo, a.r_start) + lane; t < t0 + hi; t += 32) {
+                const int pos = a.s_end + selM + (t - a.r_start);
+                if (pos < a.cap) oi[pos] = t;
+            }
+        }
+    }
+    SL_STAMP(6)
+
+    // ------------------------------------------------------------------ the last CTA of the row re-arms the barrier
+    __syncthreads();
+    if (tid == 0) {
+        unsigned* sync = a.sync + 2 * b;
+        __threadfence();
+        const unsigned old = atomicAdd(&sync[1], 1u);
+        if (old == (unsigned)cpb - 1u) {
+            sync[0] = 0;
+            sync[1] = 0;
+            a.epoch[b] = __ldcg(a.epoch + b) + 1u;           // the next launch takes the other coarse buffer
+            __threadfence();
+        }
+    }
+}
+
+typedef void (*lean_kernel_t)(const LeanArgs);
+
+lean_kernel_t pick(int P) {
+    switch (P) {
+        case 1: return scan_lean_kernel<1>;
+        case 2: return scan_lean_kernel<2>;
+        case 3: return scan_lean_kernel<3>;
+        default: return scan_lean_kernel<4>;
+    }
+}
+
+inline size_t up16(size_t v) { return (v + 15) / 16 * 16; }
+
+}  // namespace
+
+namespace slscan {
+
+int lean_prow(int nbins) { return (nbins + 7) / 8 * 8; }
+int lean_nc(int nbins) { return ((nbins - 1) >> LEAN_CWS) + 1; }
+
+// What the one-barrier kernel covers beyond fused_covers(): at most LEAN_MAX_WIN always-kept keys,
+// 16-bit counts per chunk, one trip for the chunks' counts, at most LEAN_CPL_MAX coarse bins per lane.
+bool lean_covers(int KH, int G, int ctas_per_b, int chunk, int nwin) {
+    return fused_covers(KH, G) && ctas_per_b > 1 && ctas_per_b <= 32 * LEAN_CPL_MAX && chunk < 65536 &&
+           nwin <= LEAN_MAX_WIN && lean_nc(128 * G + 1) <= 32 * LEAN_CPL_MAX;
+}
+
+size_t lean_plan_smem(LeanArgs& f, int KH, int nbins, int S, int chunk) {
+    size_t off = (size_t)KH * 32 * 4 + (size_t)KH * 4 * 4 + (size_t)KH * 4 + (size_t)KH * 4 * 4 +
+                 (size_t)KH * LEAN_MAX_WIN * 2 + (size_t)KH * lean_nc(nbins) * 4;
+    off = up16(off);
+    f.hist_off = (int)off;
+    off = up16(off + (size_t)S * KH * ((nbins + 4) & ~3) * 4);
+    f.score_off = (int)off;
+    off = up16(off + (size_t)(chunk + 64) * KH * 2);
+    return off;
+}
+
+int launch_lean(const LeanArgs& a_in, size_t smem, cudaStream_t s) {
+    LeanArgs a = a_in;
+    a.dbg = SL_STAMP_BUF;
+    lean_kernel_t kern = pick(sliced_planes(a.G));
+    SL_CUDA_OK(sl::ensure_dyn_smem(reinterpret_cast<const void*>(kern), smem));
+    SL_CUDA_OK(sl::launch_kernel(kern, dim3((unsigned)(a.B * a.ctas_per_b)), dim3(NT), smem, s, true, a));
+    return SL_OK;
+}
+
+}  // namespace slscan

@@ -151,12 +151,6 @@ __global__ void __launch_bounds__(NT, 1) scan_topk_kernel(const ScanArgs a) {
     unsigned* sync = a.sync ? a.sync + 2 * b : nullptr;
     const bool multi = a.ctas_per_b > 1;
     unsigned barriers = 0;
-#define SL_STAMP(i)                                                                         \
-    if (a.dbg && tid == 0) {                                                                \
-        unsigned long long t_;                                                              \
-        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_));                              \
-        a.dbg[blockIdx.x * 16 + (i)] = t_;                                                   \
-    }
     SL_STAMP(0)
     sl::pdl_trigger();
     sl::pdl_wait();                 // codes, q codes and the workspace all come from earlier kernels
@@ -664,6 +658,7 @@ int coarse_shift(int nbins) {
 
 struct WsLayout {
     size_t sync_off, hist_off, chist_off, seg_off, score_off, total;
+    size_t epoch_off, chist2_off, pub_off, pubc_off, wsc_off;     // the one-barrier kernel's own areas
 };
 
 WsLayout ws_layout(int B, long long N, int KH, int G, bool with_hist, bool spill, int nbins = 0) {
@@ -675,6 +670,15 @@ WsLayout ws_layout(int B, long long N, int KH, int G, bool with_hist, bool spill
     w.chist_off = off; if (with_hist) off = align_up(off + (size_t)NCOPY * B * KH * 32 * 4, 256);
     w.seg_off = off; off = align_up(off + (size_t)B * max_cpb * KH * 16, 256);
     w.score_off = off; if (spill) off = align_up(off + (size_t)B * N * KH * 2, 256);
+    w.epoch_off = w.chist2_off = w.pub_off = w.pubc_off = w.wsc_off = off;
+    if (with_hist && nbins <= 0) {
+        const int nb = 128 * G + 1;
+        w.epoch_off = off; off = align_up(off + (size_t)B * 4, 256);
+        w.chist2_off = off; off = align_up(off + (size_t)2 * NCOPY * B * KH * slscan::lean_nc(nb) * 4, 256);
+        w.pub_off = off; off = align_up(off + (size_t)std::max(B, sl::sm_count()) * KH * slscan::lean_prow(nb) * 2, 256);
+        w.pubc_off = off; off = align_up(off + (size_t)std::max(B, sl::sm_count()) * KH * slscan::lean_nc(nb) * 2, 256);
+        w.wsc_off = off; off = align_up(off + (size_t)B * KH * slscan::LEAN_MAX_WIN * 2, 256);
+    }
     w.total = off;
     return w;
 }
@@ -692,7 +696,7 @@ int check_common(const char* fn, int B, long long N, int KH, int QH) {
 
 int launch(const ScanArgs& a_in, const Plan& p, cudaStream_t s) {
     ScanArgs a = a_in;
-    a.dbg = slscan::g_dbg_timing;
+    a.dbg = SL_STAMP_BUF;
     kernel_t kern = pick_kernel(a.G, a.KH);
     SL_CUDA_OK(sl::ensure_dyn_smem(reinterpret_cast<const void*>(kern), p.smem));
     const unsigned grid = (unsigned)(a.B * p.ctas_per_b);
@@ -702,8 +706,10 @@ int launch(const ScanArgs& a_in, const Plan& p, cudaStream_t s) {
 
 }  // namespace
 
+#ifdef SL_SCAN_TIMING
 namespace slscan { unsigned long long* g_dbg_timing = nullptr; }
-static int g_lean = -1;    // 1: the decode shapes go to the lean fused kernel (default; SL_SCAN_LEAN=0 turns it off)
+#endif
+static int g_lean = 1;     // 1: one-barrier kernel where it applies (default); 2: the flagged-word kernel; 0: the general kernel
 
 extern "C" size_t sl_scan_topk_workspace_bytes(int B, int64_t N, int KH, int QH) {
     if (B <= 0 || N < 0 || KH <= 0 || QH <= 0 || QH % KH) return 0;
@@ -739,13 +745,39 @@ extern "C" int sl_scan_topk(const uint32_t* d_q_codes, const uint32_t* d_k_codes
                w.total);
     SL_REQUIRE(sl::aligned16(d_workspace), SL_EALIGN, "sl_scan_topk: workspace not 16-byte aligned");
     unsigned char* ws = static_cast<unsigned char*>(d_workspace);
-    if (g_lean < 0) {
-        const char* e = getenv("SL_SCAN_LEAN");
-        g_lean = (e && e[0] == '0') ? 0 : 1;
+    const int s_end0 = (int)std::min<int64_t>(sink, N);
+    const int nwin0 = s_end0 + (int)(N - std::max<int64_t>(s_end0, N - recent));
+    if (g_lean == 1 && p.cooperative && !p.spill && B * p.ctas_per_b <= sl::sm_count() &&
+        slscan::lean_covers(KH, G, p.ctas_per_b, p.chunk, nwin0)) {
+        // the common decode shape: one barrier, everything the tail needs published before it
+        slscan::LeanArgs f = {};
+        f.q = reinterpret_cast<const uint4*>(d_q_codes);
+        f.k = reinterpret_cast<const uint4*>(d_k_codes);
+        f.k_bstride = k_batch_stride / 4;
+        f.B = B; f.KH = KH; f.G = G; f.layout = gqa_layout; f.N = (int)N;
+        f.k_budget = k;
+        f.s_end = s_end0;
+        f.r_start = (int)std::max<int64_t>(f.s_end, N - recent);
+        f.idx = d_idx; f.cap = idx_capacity; f.cnt = d_cnt;
+        f.scores_out = d_scores_out;
+        f.sync = reinterpret_cast<unsigned*>(ws + w.sync_off);
+        f.epoch = reinterpret_cast<unsigned*>(ws + w.epoch_off);
+        f.chist = reinterpret_cast<unsigned*>(ws + w.chist2_off);
+        f.pub = reinterpret_cast<unsigned*>(ws + w.pub_off);
+        f.pubc = reinterpret_cast<unsigned short*>(ws + w.pubc_off);
+        f.wsc = reinterpret_cast<unsigned short*>(ws + w.wsc_off);
+        f.status = d_status;
+        f.ctas_per_b = p.ctas_per_b; f.chunk = p.chunk; f.nbins = p.nbins; f.S = p.S;
+        f.NC = slscan::lean_nc(p.nbins);
+        f.prow = slscan::lean_prow(p.nbins);
+        const int roww = (p.chunk >> 1) + ((4 - (p.chunk >> 1)) & 31);
+        f.rowh = 2 * roww;
+        const size_t smem = slscan::lean_plan_smem(f, KH, p.nbins, p.S, p.chunk);
+        if (smem <= (size_t)SMEM_BUDGET + 24 * 1024) return slscan::launch_lean(f, smem, s);
     }
     if (g_lean && p.cooperative && !p.spill && slscan::fused_covers(KH, G) && p.chunk < (1 << 21) &&
         (long long)NCOPY * B * KH * p.nbins < (1ll << 30)) {
-        // the common decode shape: the lean kernel (same results, a fraction of the instructions)
+        // the two-phase kernel with flagged words (also the form the sequence shards use)
         slscan::FusedArgs f = {};
         f.q = reinterpret_cast<const uint4*>(d_q_codes);
         f.k = reinterpret_cast<const uint4*>(d_k_codes);
@@ -974,10 +1006,10 @@ extern "C" int sl_topk_from_scores(const int16_t* d_scores, int B, int64_t N, in
     return launch(a, p, s);
 }
 
-// Development aid, not part of the public header: when set to a device buffer of grid*16 uint64,
-// thread 0 of every CTA of the scan kernels stores %globaltimer at its phase boundaries.
-// Development switch, not part of the public header: routes sl_scan_topk through the general
-// kernel (0) or lets it pick the lean fused kernel where that applies (1, the default).
-extern "C" void sl_debug_set_scan_lean(int on) { g_lean = on ? 1 : 0; }
+namespace slscan { void set_scan_kernel(int v) { g_lean = v; } }
 
-extern "C" void sl_debug_scan_timing(void* d_buf) { slscan::g_dbg_timing = static_cast<unsigned long long*>(d_buf); }
+#ifdef SL_SCAN_TIMING
+// Profiling builds only (not in the public header): thread 0 of every CTA of the scan kernels stores
+// the SM cycle counter at its phase boundaries into d_buf [grid][16] uint64.
+extern "C" void sl_profile_scan_timing(void* d_buf) { slscan::g_dbg_timing = static_cast<unsigned long long*>(d_buf); }
+#endif

@@ -122,7 +122,7 @@ def test_scan_topk_bit_exact(ops, B, N, KH, QH, k, sink, recent, low, layout):
     qd, cd = q.to(DEV), cache.to(DEV)
     scores_ref = O.match_count(np_u32(q)[:, None], np_u32(cache)[:, :N], layout)
     ref_idx, ref_cnt = O.select(scores_ref, k, sink, recent)
-    for _ in range(2):                                   # second call reuses the self-cleaned workspace
+    for _ in range(3):                                   # later calls reuse the workspace the kernel left behind
         idx, cnt, scores = ops.scan_topk(qd, cd[:, :N], k, sink, recent, layout, return_scores=True)
         np.testing.assert_array_equal(scores.cpu().numpy(), scores_ref)
         check_selection(idx, cnt, ref_idx, ref_cnt)
@@ -134,28 +134,47 @@ GENERAL_CASES = [c for c in SCAN_CASES if c[0] < 100 and c[0] * c[1] * c[2] <= 1
 
 @pytest.mark.parametrize("B,N,KH,QH,k,sink,recent,low", GENERAL_CASES)
 def test_scan_topk_general_kernel(ops, B, N, KH, QH, k, sink, recent, low):
-    """sl_scan_topk sends the common decode shapes to its lean kernel; the general kernel must give
-    the same answer on them (it is what other shapes, the spill path and the sharded halves use)."""
-    import ctypes
+    """sl_scan_topk sends the common decode shapes to its one-barrier kernel; the general kernel (other
+    shapes, the spill path, the sharded halves) and the flagged-word kernel (the sequence shards' fused
+    form) must give the same answer on them, also when they take turns on one workspace."""
     from spotlight_b200 import _lib
-    setter = _lib.lib.sl_debug_set_scan_lean
-    setter.argtypes, setter.restype = [ctypes.c_int], None
+
+    def setter(mode):
+        _lib.check(_lib.lib.sl_configure(_lib.SL_OPT_SCAN_KERNEL, mode))
     g = torch.Generator().manual_seed(B * 977 + N)
     q = rand_codes(g, (B, QH, 4), low)
     cache = rand_codes(g, (B, N, KH, 4), low)
     scores_ref = O.match_count(np_u32(q)[:, None], np_u32(cache), O.BLOCKED)
     ref_idx, ref_cnt = O.select(scores_ref, k, sink, recent)
-    setter(0)
     try:
-        for _ in range(2):
-            idx, cnt, scores = ops.scan_topk(q.to(DEV), cache.to(DEV), k, sink, recent, O.BLOCKED, return_scores=True)
-            np.testing.assert_array_equal(scores.cpu().numpy(), scores_ref)
-            check_selection(idx, cnt, ref_idx, ref_cnt)
-        setter(1)                                        # and the lean kernel on the workspace the general one left
-        idx, cnt = ops.scan_topk(q.to(DEV), cache.to(DEV), k, sink, recent, O.BLOCKED)
-        check_selection(idx, cnt, ref_idx, ref_cnt)
+        for mode in (0, 2, 1, 0, 1, 2, 1):               # 0 general, 2 flagged words, 1 one barrier (default)
+            setter(mode)
+            for _ in range(2):
+                idx, cnt, scores = ops.scan_topk(q.to(DEV), cache.to(DEV), k, sink, recent, O.BLOCKED, return_scores=True)
+                np.testing.assert_array_equal(scores.cpu().numpy(), scores_ref)
+                check_selection(idx, cnt, ref_idx, ref_cnt)
     finally:
         setter(1)
+    ops.check_status()
+
+
+@pytest.mark.parametrize("B,KH,QH,N0,sink,recent", [(1, 8, 32, 40000, 4, 64), (2, 4, 28, 9000, 4, 64), (1, 8, 8, 520, 4, 64),
+                                                   (1, 2, 2, 3000, 1, 95), (4, 1, 4, 20000, 7, 30), (1, 16, 32, 30000, 0, 5),
+                                                   (1, 8, 64, 12000, 4, 64), (3, 32, 32, 5000, 4, 64)])
+def test_scan_topk_growing_context(ops, B, KH, QH, N0, sink, recent):
+    """A decode loop: the context grows by one key per call on ONE workspace (the chunking, and with it
+    the kernel that serves the call, changes along the way), low-entropy codes so that the threshold
+    bin is crowded with ties, some of them inside the sink and the recent window."""
+    g = torch.Generator().manual_seed(N0 + KH)
+    q = rand_codes(g, (B, QH, 4), True)
+    cache = rand_codes(g, (B, N0 + 40, KH, 4), True)
+    qd, cd = q.to(DEV), cache.to(DEV)
+    for step, N in enumerate(list(range(N0, N0 + 6)) + [N0 // 2, N0 + 33, 300, N0 + 40]):
+        k = max(min(N, 20), N - int(N * 0.9))
+        scores_ref = O.match_count(np_u32(q)[:, None], np_u32(cache)[:, :N], O.BLOCKED)
+        ref_idx, ref_cnt = O.select(scores_ref, k, sink, recent)
+        idx, cnt = ops.scan_topk(qd, cd[:, :N], k, sink, recent, O.BLOCKED)
+        check_selection(idx, cnt, ref_idx, ref_cnt)
     ops.check_status()
 
 
