@@ -59,21 +59,20 @@ struct LeanArgs {
     short* scores_out;         // optional [B,N,KH]
     unsigned* sync;            // [B,2] barrier arrivals, finished CTAs
     unsigned* epoch;           // [B] launches completed on this workspace (parity picks the coarse buffer)
-    unsigned* chist;           // [2][NCOPY][B][KH][NC] coarse histograms
-    unsigned* pub;             // [B*ctas_per_b][KH][prow/2] counts per score of every chunk, 16-bit pairs
-    unsigned short* pubc;      // [B*ctas_per_b][KH][NC] keys of the chunk above each coarse bin
+    unsigned* chist;           // [2][B][KH][NC] coarse histograms (one per launch parity)
+    uint4* pub;                // [B][KH][NC][ctas_per_b] every chunk's counts of each coarse bin's 8 scores, 16 bits each
+    unsigned short* puba;      // [B][KH][NC][ctas_per_b] every chunk's keys above each coarse bin
+    unsigned nc_magic;         // ceil(2^32 / NC): i / NC == __umulhi(i, nc_magic) for i < 2^16
     unsigned short* wsc;       // [B][KH][LEAN_MAX_WIN] scores of the always-kept keys
     int* status;
     int ctas_per_b, chunk, nbins, S;
     int NC;                    // coarse bins per head
-    int prow;                  // 16-bit words per published row: 8 * NC
     int rowh;                  // row stride of the score rows in shared memory (halfwords)
     int hist_off, score_off;   // byte offsets of the histogram rows and of the score rows in shared memory
     unsigned long long* dbg;   // optional [grid][16] phase stamps (profiling builds only)
 };
 
 bool lean_covers(int KH, int G, int ctas_per_b, int chunk, int nwin);
-int lean_prow(int nbins);
 int lean_nc(int nbins);
 size_t lean_plan_smem(LeanArgs& f, int KH, int nbins, int S, int chunk);   // fills the offsets, returns the total
 int launch_lean(const LeanArgs& a, size_t smem, cudaStream_t s);

@@ -7,22 +7,21 @@
 //   A  the chunk is cut into S contiguous sub-ranges, each streamed by its own group of warps
 //      (8 x 16-byte loads in flight per thread); the bit-sliced scorer leaves the 16-bit scores in
 //      shared memory ([head][key], bank-spread) and counts them in a histogram per (sub-range, head)
-//   P  one pass over the histograms: the chunk's counts per score (sub-ranges added up) go to global
-//      memory as 16-bit words, 16 bytes per coarse bin (8 scores) and thread; the coarse bins' counts
-//      are added to a small global histogram; per head one warp turns them into "keys of this chunk
-//      above coarse bin c" and publishes that too; the scores of the chunk's sink / recent keys go
-//      beside them
+//   P  per (head, coarse bin of 8 scores): the chunk's 8 counts go to global memory as one 16-byte
+//      record and the chunk's number of keys above the bin as a 16-bit word beside it, both laid out
+//      [head][coarse bin][chunk] so that all chunks' entries for one bin are contiguous; the bins'
+//      counts are added to a small global histogram; the scores of the chunk's sink / recent keys follow
 //   -- the only grid barrier (bounded) --
 //   T  one warp per head: the global coarse bins give the 8 scores that hold the threshold (trip 1);
-//      every chunk's 8 counts there and its count above them (trip 2, one chunk per lane and round)
-//      give the threshold itself, the tie quota, and -- from the same registers -- how many selected
-//      keys and threshold ties lie in the chunks before this one
+//      all chunks' entries for that bin (trip 2: coalesced, one chunk per lane and round) give the
+//      threshold itself, the tie quota, and -- from the same registers -- how many selected keys and
+//      threshold ties lie in the chunks before this one
 //   E  one pass over the chunk's scores: flags, one packed warp scan per 640 keys, the attended
 //      keys written at their final positions (ascending, ties to the lowest index, sink and recent
 //      window included).
 // The coarse histogram is double-buffered by launch parity (a device-side launch counter in the
-// workspace): a launch adds into one buffer and clears the other, so nothing has to be cleared
-// between the threshold search and the end of the launch and no second grid-wide wait exists.
+// workspace, advanced by the last CTA to finish): a launch adds into one buffer and clears the
+// other, so nothing has to be cleared while others may still read it and no second grid-wide wait exists.
 #include "sl_scan.cuh"
 #include "sl_sliced.cuh"
 
@@ -72,7 +71,7 @@ __global__ void __launch_bounds__(NT, 1) scan_lean_kernel(const LeanArgs a) {
     sl::pdl_wait();
     SL_STAMP(0)
     const unsigned par = __ldcg(a.epoch + b) & 1u;                                // this launch's coarse buffer
-    unsigned* chist_b = a.chist + (size_t)par * NCOPY * cslice + b * KH * NC;
+    unsigned* chist_b = a.chist + (size_t)par * cslice + b * KH * NC;
 
     // ------------------------------------------------------------------ A: scan + histograms
     {
@@ -94,14 +93,13 @@ __global__ void __launch_bounds__(NT, 1) scan_lean_kernel(const LeanArgs a) {
         if (tid == NT - 32) {            // pages the later phases store to
             touch(a.idx + (size_t)b * KH * a.cap);
             touch(a.cnt + b * KH);
-            touch(a.pub + (size_t)blockIdx.x * KH * (a.prow >> 1));
-            touch(a.pubc + (size_t)blockIdx.x * KH * a.NC);
+            touch(a.pub + (size_t)b * KH * NC * cpb + c);
+            touch(a.puba + (size_t)b * KH * NC * cpb + c);
         }
         for (int i = tid; i < S * KH * (nb1 >> 2); i += NT) reinterpret_cast<uint4*>(shist)[i] = make_uint4(0u, 0u, 0u, 0u);
         {   // last launch's coarse buffer: cleared here, added to by the next launch
-            unsigned* other = a.chist + (size_t)(par ^ 1u) * NCOPY * cslice + b * KH * NC;
-            const int ctot = KH * NC;
-            for (int i = c * NT + tid; i < NCOPY * ctot; i += cpb * NT) other[(i / ctot) * cslice + i % ctot] = 0;
+            unsigned* other = a.chist + (size_t)(par ^ 1u) * cslice + b * KH * NC;
+            for (int i = c * NT + tid; i < KH * NC; i += cpb * NT) other[i] = 0;
         }
         planes_finish<PT>(pw, KH, a.G, s_planes, s_pbase, warp, NW, lane);
         stage_planes<PT>(qb, KH, a.G, a.layout, s_planes, s_pbase, warp, NW, lane, 1);   // KH > 8
@@ -143,39 +141,37 @@ __global__ void __launch_bounds__(NT, 1) scan_lean_kernel(const LeanArgs a) {
     // ------------------------------------------------------------------ P: suffix sums, publish
     {
         // scores of the always-kept keys this chunk owns (the other CTAs correct their counts with them)
-        for (int j = tid; j < KH * nwin; j += NT) {
-            const int h = j / nwin, wj = j - h * nwin;
-            const int t = wj < a.s_end ? wj : a.r_start + (wj - a.s_end);
-            if (t >= t0 && t < t1) a.wsc[((size_t)b * KH + h) * LEAN_MAX_WIN + wj] = sscores[h * rowh + (t - t0)];
-        }
-        // one thread per (head, coarse bin): the chunk's 8 counts of the bin as 16-bit words (zero beyond
-        // the last score), their sum into shared memory and -- if not zero -- into the global coarse bins
-        unsigned* dstc = chist_b + (c & (NCOPY - 1)) * cslice;
-        uint4* pub = reinterpret_cast<uint4*>(a.pub + (size_t)blockIdx.x * KH * (a.prow >> 1));
-        const int nc8 = a.prow >> 3;                          // 16-byte groups per published row (>= NC)
-#pragma unroll 1
-        for (int t = tid; t < KH * nc8; t += NT) {
-            const int h = t / nc8, cb = t - h * nc8;
-            unsigned v[8] = {0u, 0u, 0u, 0u, 0u, 0u, 0u, 0u};
-            if (cb < NC) {
-                const uint4* R = reinterpret_cast<const uint4*>(shist + h * nb1 + (cb << LEAN_CWS));
-                for (int s = 0; s < S; ++s) {
-                    const uint4 x = R[s * KH * (nb1 >> 2)];
-                    v[0] += x.x; v[1] += x.y; v[2] += x.z; v[3] += x.w;
-                    if ((cb << LEAN_CWS) + 4 < nb1) {
-                        const uint4 y = R[s * KH * (nb1 >> 2) + 1];
-                        v[4] += y.x; v[5] += y.y; v[6] += y.z; v[7] += y.w;
-                    }
-                }
-                const unsigned cs = ((v[0] + v[1]) + (v[2] + v[3])) + ((v[4] + v[5]) + (v[6] + v[7]));
-                s_coarse[h * NC + cb] = cs;
-                if (cs) atomicAdd(dstc + h * NC + cb, cs);
+        if (t0 < a.s_end || t1 > a.r_start) {
+            if (tid < nwin) {
+                const int t = tid < a.s_end ? tid : a.r_start + (tid - a.s_end);
+                if (t >= t0 && t < t1)
+                    for (int h = 0; h < KH; ++h) a.wsc[((size_t)b * KH + h) * LEAN_MAX_WIN + tid] = sscores[h * rowh + (t - t0)];
             }
-            pub[t] = make_uint4(v[0] | (v[1] << 16), v[2] | (v[3] << 16), v[4] | (v[5] << 16), v[6] | (v[7] << 16));
+        }
+        // one thread per (head, coarse bin): the 8 counts (sub-ranges added up) as a record, their sum to shared memory
+        const size_t pbase = (size_t)b * KH * NC * cpb + c;
+#pragma unroll 1
+        for (int i = tid; i < KH * NC; i += NT) {
+            const int h = (int)__umulhi((unsigned)i, a.nc_magic), cb = i - h * NC;
+            const uint4* R = reinterpret_cast<const uint4*>(shist + h * nb1 + (cb << LEAN_CWS));
+            const bool two = (cb << LEAN_CWS) + 4 < nb1;
+            unsigned v[8] = {0u, 0u, 0u, 0u, 0u, 0u, 0u, 0u};
+#pragma unroll 2
+            for (int s2 = 0; s2 < S; ++s2) {
+                const uint4 x = R[s2 * KH * (nb1 >> 2)];
+                v[0] += x.x; v[1] += x.y; v[2] += x.z; v[3] += x.w;
+                if (two) {
+                    const uint4 y = R[s2 * KH * (nb1 >> 2) + 1];
+                    v[4] += y.x; v[5] += y.y; v[6] += y.z; v[7] += y.w;
+                }
+            }
+            s_coarse[i] = ((v[0] + v[1]) + (v[2] + v[3])) + ((v[4] + v[5]) + (v[6] + v[7]));
+            a.pub[pbase + (size_t)i * cpb] =
+                make_uint4(v[0] | (v[1] << 16), v[2] | (v[3] << 16), v[4] | (v[5] << 16), v[6] | (v[7] << 16));
         }
         __syncthreads();
         SL_STAMP(7)
-        // per head: keys of this chunk above each coarse bin
+        // per head: keys of this chunk above each coarse bin; the bins' counts join the global ones
         const int CPL = (NC + 31) >> 5;
 #pragma unroll 1
         for (int h = warp; h < KH; h += NW) {
@@ -187,13 +183,16 @@ __global__ void __launch_bounds__(NT, 1) scan_lean_kernel(const LeanArgs a) {
                 sum += cv[i];
             }
             unsigned above = suffix_sum(sum, lane) - sum;
-            unsigned short* pc = a.pubc + ((size_t)blockIdx.x * KH + h) * NC;
+            unsigned short* pa = a.puba + pbase + (size_t)(h * NC + lane * CPL) * cpb;
 #pragma unroll
             for (int i = LEAN_CPL_MAX - 1; i >= 0; --i) {
-                const int cb = lane * CPL + i;
-                if (i < CPL && cb < NC) pc[cb] = (unsigned short)above;
+                if (i < CPL && lane * CPL + i < NC) pa[(size_t)i * cpb] = (unsigned short)above;
                 above += cv[i];
             }
+            unsigned* dst = chist_b + h * NC + lane * CPL;
+#pragma unroll
+            for (int i = 0; i < LEAN_CPL_MAX; ++i)
+                if (cv[i]) atomicAdd(dst + i, cv[i]);
         }
     }
     SL_STAMP(3)
@@ -206,27 +205,26 @@ __global__ void __launch_bounds__(NT, 1) scan_lean_kernel(const LeanArgs a) {
         const int CPL = (NC + 31) >> 5;                      // coarse bins per lane, consecutive
 #pragma unroll 1
         for (int h = warp; h < KH; h += NW) {
-            // always-kept keys of the row: their scores, loaded with the first trip
-            unsigned wv[LEAN_MAX_WIN / 32];
+            unsigned wv[LEAN_MAX_WIN / 32];                      // scores of the row's always-kept keys
 #pragma unroll
-            for (int i = 0; i < LEAN_MAX_WIN / 32; ++i) {
-                const int wj = lane + 32 * i;
-                wv[i] = wj < nwin ? ldcg_u16(a.wsc + ((size_t)b * KH + h) * LEAN_MAX_WIN + wj) : 0xffffu;
-            }
+            for (int i = 0; i < LEAN_MAX_WIN / 32; ++i) wv[i] = 0xffffu;
             int tau = nbins, pre_gt = 0, pre_eq = 0, rM = 0, selM = 0;
             if (kk > 0) {
-                // trip 1: global coarse bins -> the 8 scores [Lb, Lb + 8) that hold the threshold
+                // trip 1: the head's global coarse bins (and the always-kept keys' scores)
                 unsigned cv[LEAN_CPL_MAX];
                 unsigned csum = 0;
+                {
+                    const unsigned* src = chist_b + h * NC + lane * CPL;
 #pragma unroll
-                for (int i = 0; i < LEAN_CPL_MAX; ++i) {
-                    const int cb = lane * CPL + i;
-                    cv[i] = 0u;
-                    if (i < CPL && cb < NC) {
-#pragma unroll
-                        for (int cp = 0; cp < NCOPY; ++cp) cv[i] += __ldcg(chist_b + cp * cslice + h * NC + cb);
+                    for (int i = 0; i < LEAN_CPL_MAX; ++i) {
+                        cv[i] = (i < CPL && lane * CPL + i < NC) ? __ldcg(src + i) : 0u;
+                        csum += cv[i];
                     }
-                    csum += cv[i];
+                }
+#pragma unroll
+                for (int i = 0; i < LEAN_MAX_WIN / 32; ++i) {
+                    const int wj = lane + 32 * i;
+                    if (wj < nwin) wv[i] = ldcg_u16(a.wsc + ((size_t)b * KH + h) * LEAN_MAX_WIN + wj);
                 }
                 const unsigned suf = suffix_sum(csum, lane);
                 const unsigned ball = __ballot_sync(0xffffffffu, suf >= (unsigned)kk);   // not empty: the row holds N >= kk keys
@@ -242,83 +240,59 @@ __global__ void __launch_bounds__(NT, 1) scan_lean_kernel(const LeanArgs a) {
                 }
                 const int Lc = __shfl_sync(0xffffffffu, Lc_l, Ll), Lb = Lc << LEAN_CWS;
                 SL_STAMP(8)
-                // trip 2: every chunk's 8 counts at Lb .. Lb + 7 and its count above them, chunk = lane + 32 j
-                uint4 raw[LEAN_CPL_MAX];
-                unsigned abv[LEAN_CPL_MAX];
+                // every chunk's record of coarse bin Lc and its count above the bin, chunk = lane + 32 j.
+                // Sums of one lane stay below 2^16 per 16-bit field (chunk * LEAN_CPL_MAX < 65536): pairs are added packed.
+                unsigned pk[4] = {0u, 0u, 0u, 0u}, pa = 0u;      // all of the lane's chunks
+                unsigned qk[4] = {0u, 0u, 0u, 0u}, qa = 0u;      // those before this chunk
+                {
+                    const size_t e0 = ((size_t)(b * KH + h) * NC + Lc) * cpb;
+                    uint4 x[LEAN_CPL_MAX];
+                    unsigned y[LEAN_CPL_MAX];
 #pragma unroll
-                for (int j = 0; j < LEAN_CPL_MAX; ++j) {
-                    const int cc = lane + 32 * j;
-                    raw[j] = make_uint4(0u, 0u, 0u, 0u);
-                    abv[j] = 0u;
-                    if (cc < cpb) {
-                        const size_t rowi = (size_t)(b * cpb + cc) * KH + h;
-                        raw[j] = __ldcg(reinterpret_cast<const uint4*>(a.pub + rowi * (a.prow >> 1)) + Lc);
-                        abv[j] = __ldcg(a.pubc + rowi * NC + Lc);
+                    for (int j = 0; j < LEAN_CPL_MAX; ++j) {
+                        const int cc = lane + 32 * j;
+                        x[j] = make_uint4(0u, 0u, 0u, 0u);
+                        y[j] = 0u;
+                        if (cc < cpb) { x[j] = __ldcg(a.pub + e0 + cc); y[j] = __ldcg(a.puba + e0 + cc); }
+                    }
+#pragma unroll
+                    for (int j = 0; j < LEAN_CPL_MAX; ++j) {
+                        pk[0] += x[j].x; pk[1] += x[j].y; pk[2] += x[j].z; pk[3] += x[j].w; pa += y[j];
+                        if (lane + 32 * j < c) { qk[0] += x[j].x; qk[1] += x[j].y; qk[2] += x[j].z; qk[3] += x[j].w; qa += y[j]; }
                     }
                 }
                 SL_STAMP(9)
-                int acc[8], accA = 0;
+                int tot[9];                                   // the row's keys with score >= Lb + i, in every lane
+                tot[8] = __reduce_add_sync(0xffffffffu, (int)pa);
 #pragma unroll
-                for (int i = 0; i < 8; ++i) acc[i] = 0;
-#pragma unroll
-                for (int j = 0; j < LEAN_CPL_MAX; ++j) {
-                    acc[0] += (int)(raw[j].x & 0xffffu); acc[1] += (int)(raw[j].x >> 16);
-                    acc[2] += (int)(raw[j].y & 0xffffu); acc[3] += (int)(raw[j].y >> 16);
-                    acc[4] += (int)(raw[j].z & 0xffffu); acc[5] += (int)(raw[j].z >> 16);
-                    acc[6] += (int)(raw[j].w & 0xffffu); acc[7] += (int)(raw[j].w >> 16);
-                    accA += (int)abv[j];
+                for (int i = 3; i >= 0; --i) {
+                    tot[2 * i + 1] = tot[2 * i + 2] + __reduce_add_sync(0xffffffffu, (int)(pk[i] >> 16));
+                    tot[2 * i] = tot[2 * i + 1] + __reduce_add_sync(0xffffffffu, (int)(pk[i] & 0xffffu));
                 }
-                // sums over the lanes: afterwards lane l holds the row's count at score Lb + (l & 7)
+                SL_STAMP(10)
+                int ls = 0;                                   // tot[0] >= kk > tot[8] by the choice of Lc
+#pragma unroll
+                for (int i = 1; i < 8; ++i) ls += tot[i] >= kk ? 1 : 0;
+                tau = Lb + ls;
+                int ge_tot = 0, gt_tot = 0;
 #pragma unroll
                 for (int i = 0; i < 8; ++i) {
-                    acc[i] += __shfl_xor_sync(0xffffffffu, acc[i], 16);
-                    acc[i] += __shfl_xor_sync(0xffffffffu, acc[i], 8);
+                    ge_tot = i == ls ? tot[i] : ge_tot;
+                    gt_tot = i == ls ? tot[i + 1] : gt_tot;
                 }
-#pragma unroll
-                for (int wd = 4; wd >= 1; wd >>= 1) {
-                    const bool up = (lane & wd) != 0;
-#pragma unroll
-                    for (int i = 0; i < wd; ++i) {
-                        const int send = up ? acc[i] : acc[i + wd];
-                        const int recv = __shfl_xor_sync(0xffffffffu, send, wd);
-                        acc[i] = (up ? acc[i + wd] : acc[i]) + recv;
-                    }
-                }
-                accA = __reduce_add_sync(0xffffffffu, accA);
-                // suffix over the 8 scores: mine = keys of the row with score >= Lb + (l & 7)
-                int mine = acc[0];
-#pragma unroll
-                for (int d = 1; d < 8; d <<= 1) {
-                    const int t = __shfl_down_sync(0xffffffffu, mine, d);
-                    if ((lane & 7) + d < 8) mine += t;
-                }
-                mine += accA;
-                SL_STAMP(10)
-                const unsigned ball2 = __ballot_sync(0xffffffffu, mine >= kk) & 0xffu;   // not empty by the choice of Lb
-                const int ls = 31 - __clz(ball2 | 1u);
-                tau = Lb + ls;
-                const int ge_tot = __shfl_sync(0xffffffffu, mine, ls);
-                const int gt_next = __shfl_sync(0xffffffffu, mine, (ls + 1) & 7);
-                const int gt_tot = ls == 7 ? accA : gt_next;
                 const int r = kk - gt_tot;
-                // keys above / at the threshold in the chunks before this one
+                // keys above / at the threshold in the chunks before this one, from the lane's packed sums
+                {
+                    int gt = (int)qa, eq = 0;
 #pragma unroll
-                for (int j = 0; j < LEAN_CPL_MAX; ++j) {
-                    if (lane + 32 * j < c) {
-                        const unsigned w[4] = {raw[j].x, raw[j].y, raw[j].z, raw[j].w};
-                        int gt = (int)abv[j], eq = 0;
-#pragma unroll
-                        for (int i = 0; i < 8; ++i) {
-                            const int v = (int)((i & 1) ? (w[i >> 1] >> 16) : (w[i >> 1] & 0xffffu));
-                            gt += i > ls ? v : 0;
-                            eq += i == ls ? v : 0;
-                        }
-                        pre_gt += gt;
-                        pre_eq += eq;
+                    for (int i = 0; i < 8; ++i) {
+                        const int v = (int)((i & 1) ? (qk[i >> 1] >> 16) : (qk[i >> 1] & 0xffffu));
+                        gt += i > ls ? v : 0;
+                        eq += i == ls ? v : 0;
                     }
+                    pre_gt = __reduce_add_sync(0xffffffffu, gt);
+                    pre_eq = __reduce_add_sync(0xffffffffu, eq);
                 }
-                pre_gt = __reduce_add_sync(0xffffffffu, pre_gt);
-                pre_eq = __reduce_add_sync(0xffffffffu, pre_eq);
                 // always-kept keys: threshold ties inside the sink come off the quota; all of them leave the totals
                 int eq_sink = 0, gt_win = 0, eq_win = 0;
 #pragma unroll
@@ -454,7 +428,7 @@ __global__ void __launch_bounds__(NT, 1) scan_lean_kernel(const LeanArgs a) {
     }
     SL_STAMP(6)
 
-    // ------------------------------------------------------------------ the last CTA of the row re-arms the barrier
+    // ------------------------------------------------------------------ the last CTA of the row advances the launch counter
     __syncthreads();
     if (tid == 0) {
         unsigned* sync = a.sync + 2 * b;
@@ -486,13 +460,12 @@ inline size_t up16(size_t v) { return (v + 15) / 16 * 16; }
 
 namespace slscan {
 
-int lean_prow(int nbins) { return (nbins + 7) / 8 * 8; }
 int lean_nc(int nbins) { return ((nbins - 1) >> LEAN_CWS) + 1; }
 
 // What the one-barrier kernel covers beyond fused_covers(): at most LEAN_MAX_WIN always-kept keys,
-// 16-bit counts per chunk, one trip for the chunks' counts, at most LEAN_CPL_MAX coarse bins per lane.
+// 16-bit sums per lane over its chunks, one trip for the chunks' records, at most LEAN_CPL_MAX coarse bins per lane.
 bool lean_covers(int KH, int G, int ctas_per_b, int chunk, int nwin) {
-    return fused_covers(KH, G) && ctas_per_b > 1 && ctas_per_b <= 32 * LEAN_CPL_MAX && chunk < 65536 &&
+    return fused_covers(KH, G) && ctas_per_b > 1 && ctas_per_b <= 32 * LEAN_CPL_MAX && chunk * LEAN_CPL_MAX < 65536 &&
            nwin <= LEAN_MAX_WIN && lean_nc(128 * G + 1) <= 32 * LEAN_CPL_MAX;
 }
 

@@ -658,7 +658,7 @@ int coarse_shift(int nbins) {
 
 struct WsLayout {
     size_t sync_off, hist_off, chist_off, seg_off, score_off, total;
-    size_t epoch_off, chist2_off, pub_off, pubc_off, wsc_off;     // the one-barrier kernel's own areas
+    size_t epoch_off, chist2_off, pub_off, puba_off, wsc_off;     // the one-barrier kernel's own areas
 };
 
 WsLayout ws_layout(int B, long long N, int KH, int G, bool with_hist, bool spill, int nbins = 0) {
@@ -670,13 +670,13 @@ WsLayout ws_layout(int B, long long N, int KH, int G, bool with_hist, bool spill
     w.chist_off = off; if (with_hist) off = align_up(off + (size_t)NCOPY * B * KH * 32 * 4, 256);
     w.seg_off = off; off = align_up(off + (size_t)B * max_cpb * KH * 16, 256);
     w.score_off = off; if (spill) off = align_up(off + (size_t)B * N * KH * 2, 256);
-    w.epoch_off = w.chist2_off = w.pub_off = w.pubc_off = w.wsc_off = off;
+    w.epoch_off = w.chist2_off = w.pub_off = w.puba_off = w.wsc_off = off;
     if (with_hist && nbins <= 0) {
         const int nb = 128 * G + 1;
         w.epoch_off = off; off = align_up(off + (size_t)B * 4, 256);
-        w.chist2_off = off; off = align_up(off + (size_t)2 * NCOPY * B * KH * slscan::lean_nc(nb) * 4, 256);
-        w.pub_off = off; off = align_up(off + (size_t)std::max(B, sl::sm_count()) * KH * slscan::lean_prow(nb) * 2, 256);
-        w.pubc_off = off; off = align_up(off + (size_t)std::max(B, sl::sm_count()) * KH * slscan::lean_nc(nb) * 2, 256);
+        w.chist2_off = off; off = align_up(off + (size_t)2 * B * KH * slscan::lean_nc(nb) * 4, 256);
+        w.pub_off = off; off = align_up(off + (size_t)std::max(B, sl::sm_count()) * KH * slscan::lean_nc(nb) * 16, 256);
+        w.puba_off = off; off = align_up(off + (size_t)std::max(B, sl::sm_count()) * KH * slscan::lean_nc(nb) * 2, 256);
         w.wsc_off = off; off = align_up(off + (size_t)B * KH * slscan::LEAN_MAX_WIN * 2, 256);
     }
     w.total = off;
@@ -763,13 +763,13 @@ extern "C" int sl_scan_topk(const uint32_t* d_q_codes, const uint32_t* d_k_codes
         f.sync = reinterpret_cast<unsigned*>(ws + w.sync_off);
         f.epoch = reinterpret_cast<unsigned*>(ws + w.epoch_off);
         f.chist = reinterpret_cast<unsigned*>(ws + w.chist2_off);
-        f.pub = reinterpret_cast<unsigned*>(ws + w.pub_off);
-        f.pubc = reinterpret_cast<unsigned short*>(ws + w.pubc_off);
+        f.pub = reinterpret_cast<uint4*>(ws + w.pub_off);
+        f.puba = reinterpret_cast<unsigned short*>(ws + w.puba_off);
         f.wsc = reinterpret_cast<unsigned short*>(ws + w.wsc_off);
         f.status = d_status;
         f.ctas_per_b = p.ctas_per_b; f.chunk = p.chunk; f.nbins = p.nbins; f.S = p.S;
         f.NC = slscan::lean_nc(p.nbins);
-        f.prow = slscan::lean_prow(p.nbins);
+        f.nc_magic = (unsigned)(((1ull << 32) + f.NC - 1) / f.NC);
         const int roww = (p.chunk >> 1) + ((4 - (p.chunk >> 1)) & 31);
         f.rowh = 2 * roww;
         const size_t smem = slscan::lean_plan_smem(f, KH, p.nbins, p.S, p.chunk);
