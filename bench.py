@@ -184,7 +184,7 @@ def workload_config(cfg):
 # ------------------------------------------------------------------------------------------
 # GPU arm
 # ------------------------------------------------------------------------------------------
-def build_session(cfg, device, lru=False, extra_capacity=0):
+def build_session(cfg, device, lru=False, extra_capacity=0, fused_kv=True):
     from spotlight_b200 import ops
     from spotlight_b200.session import DecodeSession, SessionConfig
     from spotlight_b200.workloads import apply_rope, rope_tables, torch_dtype
@@ -199,7 +199,7 @@ def build_session(cfg, device, lru=False, extra_capacity=0):
         hk.append(ops.HashParams.from_dict(pk, device, cfg.mlp_residue))
     lru_slots = 2 * (budget(n, cfg.mask_out, cfg.min_remain) + cfg.sink + cfg.recent) if lru else 0
     scfg = SessionConfig(cfg.batch, cfg.q_heads, cfg.kv_heads, cfg.layers, n + extra_capacity, dt, cfg.mask_out,
-                         cfg.min_remain, cfg.sink, cfg.recent, lru_slots=lru_slots)
+                         cfg.min_remain, cfg.sink, cfg.recent, lru_slots=lru_slots, fused_kv=fused_kv)
     s = DecodeSession(scfg, hq, hk, device)
     dgen = torch.Generator(device=device).manual_seed(cfg.seed)
     ch = torch.randperm(HEAD_DIM, generator=gen)[:4].to(device)
@@ -263,7 +263,10 @@ def run_ours(args, cfg):
         dist = dist_
     from spotlight_b200 import ops
 
-    s, code_build_ms = build_session(cfg, device, lru=args.lru)
+    if args.attn_warps:
+        from spotlight_b200 import _lib
+        _lib.check(_lib.lib.sl_configure(_lib.SL_OPT_ATTN_WARPS, args.attn_warps))
+    s, code_build_ms = build_session(cfg, device, lru=args.lru, fused_kv=not args.separate_kv)
     n, L = cfg.context, cfg.layers
     pos = n - 1
 
@@ -559,6 +562,8 @@ def main():
     ap.add_argument("--batch", type=int, default=None)
     ap.add_argument("--mask-out", type=float, default=None)
     ap.add_argument("--no-graph", action="store_true")
+    ap.add_argument("--separate-kv", action="store_true", help="two K/V caches per layer instead of one fused cache")
+    ap.add_argument("--attn-warps", type=int, default=0, choices=[0, 4, 8], help="warps per CTA of the attention kernel (0: by shape)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--decode-steps", type=int, default=0,
                     help="run this many consecutive decode tokens at advancing positions (config 1: 256) instead of "

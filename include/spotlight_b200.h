@@ -55,8 +55,9 @@ int sl_set_device(int device);
  *   SL_OPT_L2_PREFETCH  1 (default): sl_decode_prepare asks L2 for the code cache that the
  *                       sl_scan_topk of the same step streams next (caches of at most 24 MB); 0: off
  *   SL_OPT_SCAN_KERNEL  which kernel sl_scan_topk uses where several apply (results are identical):
- *                       1 (default) the one-barrier kernel, 2 the flagged-word kernel, 0 the general kernel */
-typedef enum { SL_OPT_PDL = 0, SL_OPT_L2_PREFETCH = 1, SL_OPT_SCAN_KERNEL = 2 } sl_option;
+ *                       1 (default) the one-barrier kernel, 2 the flagged-word kernel, 0 the general kernel
+ *   SL_OPT_ATTN_WARPS   warps per CTA of the bf16 attention kernel: 0 (default) by shape, 4 or 8 */
+typedef enum { SL_OPT_PDL = 0, SL_OPT_L2_PREFETCH = 1, SL_OPT_SCAN_KERNEL = 2, SL_OPT_ATTN_WARPS = 3 } sl_option;
 int sl_configure(int option, int value);
 
 /* Sign-bit packing: bit j of output byte i  <=>  x[8*i + j] > 0 (LSB first). Read as uint32
@@ -137,6 +138,14 @@ int sl_select_emit(const int16_t* d_scores, const uint32_t* d_hist_all, int R, i
                    int sink, int recent, int32_t* d_idx, int idx_capacity, int32_t* d_cnt,
                    void* d_workspace, size_t workspace_bytes, int32_t* d_status, void* stream);
 
+/* Geometry of a K or V cache, strides in ELEMENTS:
+ *   row of key t, kv head g, batch row b  =  base + b*batch_stride + t*token_stride + g*head_stride.
+ * See sl_sparse_attn_decode_ex for the layouts in use. */
+typedef struct {
+    int64_t batch_stride, token_stride, head_stride;
+    int list_heads_per_kv_head;
+} sl_kv_layout;
+
 /* Hash parameters of one head set (query heads or key heads): an MLP of n_layers layers,
  * layer i: dx = act(x @ W_i + b_i), act = SiLU for i < n_layers-1 else identity,
  * x = dx + x when residue. n_layers = 1 with no bias is the linear hash.
@@ -173,6 +182,15 @@ int sl_decode_prepare(const void* d_q, const void* d_k, const void* d_v, int dty
                       void* d_q_rot, uint32_t* d_q_codes, uint32_t* d_code_cache,
                       int64_t code_batch_stride, void* d_k_cache, void* d_v_cache,
                       int64_t kv_batch_stride, int64_t pos, void* stream);
+/* The same with the cache geometry spelled out (d_k_cache and d_v_cache share it; list_heads_per_kv_head
+ * is not used here): row `pos` of a fused cache [B,N,KH,2,128] is written with d_v_cache = d_k_cache + 128,
+ * token_stride = KH*256, head_stride = 256. */
+int sl_decode_prepare_ex(const void* d_q, const void* d_k, const void* d_v, int dtype, int B, int QH,
+                         int KH, const void* d_cos, const void* d_sin,
+                         const sl_hash_params* hash_q, const sl_hash_params* hash_k,
+                         void* d_q_rot, uint32_t* d_q_codes, uint32_t* d_code_cache,
+                         int64_t code_batch_stride, void* d_k_cache, void* d_v_cache,
+                         const sl_kv_layout* kv, int64_t pos, void* stream);
 
 /* Hash + sign + pack of many rows (code-cache build at prefill):
  * d_x [B,T,H,128] with batch stride x_batch_stride (elements) -> d_codes [B,T,H,4] with batch
@@ -180,6 +198,11 @@ int sl_decode_prepare(const void* d_q, const void* d_k, const void* d_v, int dty
 int sl_hash_encode(const void* d_x, int64_t x_batch_stride, int dtype, int B, int64_t T, int H,
                    const sl_hash_params* hash, uint32_t* d_codes, int64_t code_batch_stride,
                    void* stream);
+/* The same over rows with explicit token / head strides (elements), e.g. the K rows of a fused cache
+ * [B,N,KH,2,128]: x_token_stride = KH*256, x_head_stride = 256. */
+int sl_hash_encode_ex(const void* d_x, int64_t x_batch_stride, int64_t x_token_stride, int64_t x_head_stride,
+                      int dtype, int B, int64_t T, int H, const sl_hash_params* hash, uint32_t* d_codes,
+                      int64_t code_batch_stride, void* stream);
 
 /* Sparse GQA decode attention over the attended keys only:
  *   out[b,qh,:] = softmax_j( q[b,qh] . K[b, idx[b,h,j], h] / sqrt(128) ) V[b, idx[b,h,j], h]
@@ -200,6 +223,24 @@ int sl_sparse_attn_decode(const void* d_q, const void* d_k, const void* d_v, int
                           const int32_t* d_cnt, int B, int KH, int QH, int gqa_layout,
                           void* d_out, float* d_lse, void* d_workspace, size_t workspace_bytes,
                           void* stream);
+
+/* The same attention with the geometry of the caches spelled out (strides in ELEMENTS):
+ * row of key t, kv head g, batch row b  =  base + b*batch_stride + t*token_stride + g*head_stride.
+ *  - the reference's two caches [B,N,KH,128] (spotlight/modifiers/gpu_cache.py:28-36):
+ *    token_stride = KH*128, head_stride = 128;
+ *  - one fused cache [B,N,KH,2,128] with d_v = d_k + 128: token_stride = KH*256, head_stride = 256.
+ *    A key's K and V rows are then one 512-byte piece of memory, which is what the gather wants;
+ *  - batch_stride = 0 lets every batch row read the same cache (the batch aliasing of
+ *    spotlight/modifiers/fake_cache.py:42-49,96-106).
+ * list_heads_per_kv_head = 1 is the per-kv-head selection of the reference's kernels. With a value
+ * m > 1 the KH index lists of a batch row are taken m at a time per kv head of the caches (list head
+ * h reads kv head h / m): KH = QH and m = QH / kv heads gives every QUERY head its own list over
+ * shared K/V, the per-query-head selection of the reference's modifier
+ * (spotlight/modifiers/spotlight_generation.py:128-165) without repeating the caches. */
+int sl_sparse_attn_decode_ex(const void* d_q, const void* d_k, const void* d_v, int dtype, const sl_kv_layout* kv,
+                             const int32_t* d_idx, int idx_capacity, const int32_t* d_cnt, int B, int KH, int QH,
+                             int gqa_layout, void* d_out, float* d_lse, void* d_workspace, size_t workspace_bytes,
+                             void* stream);
 
 /* sl_sparse_attn_decode for callers that may not allocate device memory where they run attention
  * (an engine whose memory pool took all of HBM at start-up; a decode loop in which cudaMalloc and
@@ -264,6 +305,7 @@ typedef struct {
     int sink, recent, min_remain;
     double mask_out;
     int64_t code_batch_stride, kv_batch_stride;      /* uint32 words / elements, as in sl_decode_prepare */
+    int64_t kv_token_stride, kv_head_stride;         /* elements; 0, 0 = the two-cache layout (KH*128, 128) */
     const void* const* d_q;                          /* [layers] -> [B,QH,128] */
     const void* const* d_k;                          /* [layers] -> [B,KH,128] */
     const void* const* d_v;
@@ -281,6 +323,26 @@ typedef struct {
     int32_t* d_status;
 } sl_decode_step_args;
 int sl_decode_step(const sl_decode_step_args* args, int64_t pos, void* stream);
+
+/* sl_decode_step with the position in DEVICE memory, so that ONE captured sequence of launches (a CUDA
+ * graph) serves every token of a decode loop: the token sits at *d_pos, the context is *d_pos + 1 keys,
+ * the budget follows the same rule, evaluated on the device. Replaces the per-token Python of the
+ * reference's generate loop (spotlight/modifiers/spotlight_generation.py:470-495), whose every
+ * iteration rebuilds its launches and synchronises with `.item()`.
+ *   d_pos            int64 word; 0 <= *d_pos < max_context. With advance != 0 the last launch adds 1 to it.
+ *   max_context      what the launches are planned for (grid shapes, idx_capacity >= min(max_context,
+ *                    k(max_context) + sink + recent)); the caches hold at least that many rows
+ *   d_cos_table/d_sin_table  [table_rows,128] of args->dtype: row r holds position table_pos0 + r
+ *                    (NULL, NULL: q/k arrive rotated); args->d_cos / d_sin are ignored
+ * Shapes the one-barrier scan kernel does not cover return SL_ESHAPE: use sl_decode_step per position then. */
+typedef struct {
+    int64_t* d_pos;
+    int64_t max_context;
+    const void* d_cos_table; const void* d_sin_table;
+    int64_t table_pos0, table_rows;
+    int advance;
+} sl_decode_dev;
+int sl_decode_step_dev(const sl_decode_step_args* args, const sl_decode_dev* dev, void* stream);
 
 /* ---- exchange between the GPUs of one node over peer memory (sequence-sharded contexts) ----
  * No reference counterpart: the reference has no sequence parallelism (its only collectives are

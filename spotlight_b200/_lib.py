@@ -14,7 +14,7 @@ LIB_PATH = os.path.join(_HERE, "lib", "libspotlight_b200.so")
 SL_OK, SL_EINVAL, SL_ESHAPE, SL_EALIGN, SL_EWORKSPACE, SL_ECUDA, SL_ETIMEOUT = 0, -1, -2, -3, -4, -5, -6
 SL_BF16, SL_F32, SL_F16, SL_BOOL = 0, 1, 2, 3
 GQA_INTERLEAVED, GQA_BLOCKED = 0, 1
-SL_OPT_PDL, SL_OPT_L2_PREFETCH, SL_OPT_SCAN_KERNEL = 0, 1, 2
+SL_OPT_PDL, SL_OPT_L2_PREFETCH, SL_OPT_SCAN_KERNEL, SL_OPT_ATTN_WARPS = 0, 1, 2, 3
 
 
 class HashParamsStruct(C.Structure):
@@ -31,13 +31,26 @@ class DecodeStepArgs(C.Structure):
     """sl_decode_step_args of include/spotlight_b200.h."""
     _fields_ = [("B", _I), ("QH", _I), ("KH", _I), ("layers", _I), ("dtype", _I), ("gqa_layout", _I),
                 ("sink", _I), ("recent", _I), ("min_remain", _I), ("mask_out", C.c_double),
-                ("code_batch_stride", _L), ("kv_batch_stride", _L),
+                ("code_batch_stride", _L), ("kv_batch_stride", _L), ("kv_token_stride", _L), ("kv_head_stride", _L),
                 ("d_q", _PP), ("d_k", _PP), ("d_v", _PP), ("hash_q", _HP), ("hash_k", _HP),
                 ("d_code_cache", _PP), ("d_k_cache", _PP), ("d_v_cache", _PP), ("d_out", _PP),
                 ("d_cos", _P), ("d_sin", _P), ("d_q_rot", _P), ("d_q_codes", _P),
                 ("d_idx", _P), ("idx_capacity", _I), ("d_cnt", _P),
                 ("d_scan_workspace", _P), ("scan_workspace_bytes", _Z),
                 ("d_attn_workspace", _P), ("attn_workspace_bytes", _Z), ("d_status", _P)]
+
+class KvLayout(C.Structure):
+    """sl_kv_layout of include/spotlight_b200.h (strides in elements)."""
+    _fields_ = [("batch_stride", _L), ("token_stride", _L), ("head_stride", _L), ("list_heads_per_kv_head", _I)]
+
+
+class DecodeDev(C.Structure):
+    """sl_decode_dev of include/spotlight_b200.h."""
+    _fields_ = [("d_pos", _P), ("max_context", _L), ("d_cos_table", _P), ("d_sin_table", _P),
+                ("table_pos0", _L), ("table_rows", _L), ("advance", _I)]
+
+
+_KV = C.POINTER(KvLayout)
 
 # name -> (restype, argtypes); must list every symbol of include/spotlight_b200.h
 SIGNATURES = {
@@ -57,14 +70,18 @@ SIGNATURES = {
     "sl_select_emit_workspace_bytes": (_Z, [_I, _L, _I, _I]),
     "sl_select_emit": (_I, [_P, _P, _I, _I, _I, _L, _L, _L, _I, _I, _I, _I, _I, _P, _I, _P, _P, _Z, _P, _P]),
     "sl_decode_prepare": (_I, [_P, _P, _P, _I, _I, _I, _I, _P, _P, _HP, _HP, _P, _P, _P, _L, _P, _P, _L, _L, _P]),
+    "sl_decode_prepare_ex": (_I, [_P, _P, _P, _I, _I, _I, _I, _P, _P, _HP, _HP, _P, _P, _P, _L, _P, _P, _KV, _L, _P]),
     "sl_hash_encode": (_I, [_P, _L, _I, _I, _L, _I, _HP, _P, _L, _P]),
+    "sl_hash_encode_ex": (_I, [_P, _L, _L, _L, _I, _I, _L, _I, _HP, _P, _L, _P]),
     "sl_sparse_attn_workspace_bytes": (_Z, [_I, _I, _I]),
     "sl_sparse_attn_decode": (_I, [_P, _P, _P, _I, _L, _P, _I, _P, _I, _I, _I, _I, _P, _P, _P, _Z, _P]),
+    "sl_sparse_attn_decode_ex": (_I, [_P, _P, _P, _I, _KV, _P, _I, _P, _I, _I, _I, _I, _P, _P, _P, _Z, _P]),
     "sl_sparse_attn_decode_static": (_I, [_P, _P, _P, _I, _L, _P, _I, _P, _I, _I, _I, _I, _P, _P, _P]),
     "sl_merge_lse": (_I, [_P, _P, _I, _L, _I, _P, _P]),
     "sl_lru_update": (_I, [_P, _I, _P, _I, _I, _P, _P, _L, _I, _P, _P, _I, _P, _L, _P, _P, _I, _P, _P, _P, _P]),
     "sl_gather_rows": (_I, [_P, _L, _I, _P, _I, _I, _I, _I, _P, _P]),
     "sl_decode_step": (_I, [C.POINTER(DecodeStepArgs), _L, _P]),
+    "sl_decode_step_dev": (_I, [C.POINTER(DecodeStepArgs), C.POINTER(DecodeDev), _P]),
     "sl_scan_topk_sharded_slot_bytes": (_Z, [_I, _I, _I]),
     "sl_scan_topk_sharded": (_I, [_P, _P, _L, _I, _L, _L, _L, _I, _I, _I, _I, _I, _I, _P, _I, _P, _P, _Z, C.POINTER(_P),
                                   _I, _I, _Z, _P, _P]),

@@ -71,6 +71,7 @@ extern "C" int sl_workspace_init(void* d_workspace, size_t bytes, void* stream) 
 }
 
 namespace slscan { void set_scan_kernel(int v); }
+namespace sl { void set_attn_warps(int v); }
 
 extern "C" int sl_configure(int option, int value) {
     switch (option) {
@@ -79,6 +80,10 @@ extern "C" int sl_configure(int option, int value) {
         case SL_OPT_SCAN_KERNEL:
             SL_REQUIRE(value >= 0 && value <= 2, SL_EINVAL, "sl_configure: SL_OPT_SCAN_KERNEL takes 0, 1 or 2");
             slscan::set_scan_kernel(value);
+            return SL_OK;
+        case SL_OPT_ATTN_WARPS:
+            SL_REQUIRE(value == 0 || value == 4 || value == 8, SL_EINVAL, "sl_configure: SL_OPT_ATTN_WARPS takes 0, 4 or 8");
+            sl::set_attn_warps(value);
             return SL_OK;
         default: return sl::fail(SL_EINVAL, "sl_configure: unknown option %d", option);
     }

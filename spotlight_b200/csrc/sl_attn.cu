@@ -36,9 +36,10 @@ __global__ void __launch_bounds__(AT, (G * (16 / sizeof(T)) > 32) ? 1 : 2) spars
     const int per = (n + a.splits - 1) / a.splits;
     const int lo = min(n, sp * per), hi = min(n, lo + per);
     const int* list = a.idx + ((long long)b * KH + h) * a.cap;
-    const T* kb = reinterpret_cast<const T*>(a.k) + (long long)b * a.kv_b + (long long)h * 128 + sub * EPL;
-    const T* vb = reinterpret_cast<const T*>(a.v) + (long long)b * a.kv_b + (long long)h * 128 + sub * EPL;
-    const long long row_stride = (long long)KH * 128;
+    const long long hoff = (long long)b * a.kv_b + (long long)(h / a.kv_div) * a.head_stride + sub * EPL;
+    const T* kb = reinterpret_cast<const T*>(a.k) + hoff;
+    const T* vb = reinterpret_cast<const T*>(a.v) + hoff;
+    const long long row_stride = a.tok_stride;
 
     float qf[G][EPL];
 #pragma unroll
@@ -301,23 +302,30 @@ extern "C" size_t sl_sparse_attn_workspace_bytes(int B, int KH, int QH) {
     return (size_t)B * QH * MAX_SPLITS * 130 * 4;
 }
 
-extern "C" int sl_sparse_attn_decode(const void* d_q, const void* d_k, const void* d_v, int dtype,
-                                     int64_t kv_batch_stride, const int32_t* d_idx, int idx_capacity,
-                                     const int32_t* d_cnt, int B, int KH, int QH, int gqa_layout, void* d_out,
-                                     float* d_lse, void* d_workspace, size_t workspace_bytes, void* stream) {
-    SL_REQUIRE(d_q && d_k && d_v && d_idx && d_cnt && d_out && d_workspace, SL_EINVAL, "sl_sparse_attn_decode: null pointer");
+extern "C" int sl_sparse_attn_decode_ex(const void* d_q, const void* d_k, const void* d_v, int dtype, const sl_kv_layout* kv,
+                                        const int32_t* d_idx, int idx_capacity, const int32_t* d_cnt, int B, int KH, int QH,
+                                        int gqa_layout, void* d_out, float* d_lse, void* d_workspace, size_t workspace_bytes,
+                                        void* stream) {
+    SL_REQUIRE(d_q && d_k && d_v && kv && d_idx && d_cnt && d_out && d_workspace, SL_EINVAL, "sl_sparse_attn_decode: null pointer");
     SL_REQUIRE(B > 0 && KH > 0 && QH > 0 && QH % KH == 0 && idx_capacity > 0, SL_ESHAPE, "sl_sparse_attn_decode: bad shape");
     SL_REQUIRE(B <= 65535 && KH <= 65535, SL_ESHAPE, "sl_sparse_attn_decode: B or KH > 65535");
     SL_REQUIRE(gqa_layout == SL_GQA_INTERLEAVED || gqa_layout == SL_GQA_BLOCKED, SL_EINVAL,
                "sl_sparse_attn_decode: unknown gqa_layout %d", gqa_layout);
     SL_REQUIRE(dtype == SL_BF16 || dtype == SL_F32 || dtype == SL_F16, SL_EINVAL, "sl_sparse_attn_decode: unsupported dtype %d", dtype);
+    SL_REQUIRE(kv->list_heads_per_kv_head >= 1 && KH % kv->list_heads_per_kv_head == 0, SL_ESHAPE,
+               "sl_sparse_attn_decode: %d list heads do not divide into groups of %d per kv head", KH, kv->list_heads_per_kv_head);
+    SL_REQUIRE(kv->batch_stride >= 0 && kv->token_stride >= 128 && kv->head_stride >= 128, SL_ESHAPE,
+               "sl_sparse_attn_decode: cache strides must leave room for a 128-value row");
     const int esz = dtype == SL_F32 ? 4 : 2;
-    SL_REQUIRE(sl::aligned16(d_q) && sl::aligned16(d_k) && sl::aligned16(d_v) && (kv_batch_stride * esz) % 16 == 0, SL_EALIGN,
-               "sl_sparse_attn_decode: q/k/v must be 16-byte aligned");
+    SL_REQUIRE(sl::aligned16(d_q) && sl::aligned16(d_k) && sl::aligned16(d_v) && (kv->batch_stride * esz) % 16 == 0 &&
+                   (kv->token_stride * esz) % 16 == 0 && (kv->head_stride * esz) % 16 == 0, SL_EALIGN,
+               "sl_sparse_attn_decode: q/k/v and the cache strides must be 16-byte aligned");
     SL_REQUIRE(workspace_bytes >= sl_sparse_attn_workspace_bytes(B, KH, QH), SL_EWORKSPACE,
                "sl_sparse_attn_decode: workspace %zu < required %zu", workspace_bytes, sl_sparse_attn_workspace_bytes(B, KH, QH));
+    SL_REQUIRE(sl::aligned16(d_workspace), SL_EALIGN, "sl_sparse_attn_decode: workspace not 16-byte aligned");
     AttnArgs a;
-    a.q = d_q; a.k = d_k; a.v = d_v; a.kv_b = kv_batch_stride;
+    a.q = d_q; a.k = d_k; a.v = d_v; a.kv_b = kv->batch_stride;
+    a.tok_stride = kv->token_stride; a.head_stride = kv->head_stride; a.kv_div = kv->list_heads_per_kv_head;
     a.idx = d_idx; a.cap = idx_capacity; a.cnt = d_cnt;
     a.B = B; a.KH = KH; a.layout = gqa_layout;
     a.splits = pick_splits(B, KH, idx_capacity);
@@ -334,6 +342,15 @@ extern "C" int sl_sparse_attn_decode(const void* d_q, const void* d_k, const voi
         case SL_F16: return dispatch_g<__half>(a, G, s);
         default: return dispatch_g<float>(a, G, s);
     }
+}
+
+extern "C" int sl_sparse_attn_decode(const void* d_q, const void* d_k, const void* d_v, int dtype,
+                                     int64_t kv_batch_stride, const int32_t* d_idx, int idx_capacity,
+                                     const int32_t* d_cnt, int B, int KH, int QH, int gqa_layout, void* d_out,
+                                     float* d_lse, void* d_workspace, size_t workspace_bytes, void* stream) {
+    const sl_kv_layout kv = {kv_batch_stride, (int64_t)KH * 128, 128, 1};
+    return sl_sparse_attn_decode_ex(d_q, d_k, d_v, dtype, &kv, d_idx, idx_capacity, d_cnt, B, KH, QH, gqa_layout, d_out,
+                                    d_lse, d_workspace, workspace_bytes, stream);
 }
 
 extern "C" int sl_merge_lse(const float* d_o, const float* d_lse, int R, int64_t rows, int dtype, void* d_out, void* stream) {

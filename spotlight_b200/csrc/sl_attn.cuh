@@ -9,6 +9,9 @@ constexpr int ATTN_MAX_SPLITS = 64;
 struct AttnArgs {
     const void* q; const void* k; const void* v;
     long long kv_b;                // batch stride in elements
+    long long tok_stride;          // elements between the rows of consecutive keys (KH * 128 for [B,N,KH,128])
+    long long head_stride;         // elements between the rows of consecutive kv heads of one key (128)
+    int kv_div;                    // list heads (entries of idx/cnt per batch row) per kv head of the caches (1)
     const int* idx; int cap; const int* cnt;
     int B, KH, layout, splits;
     void* out; float* lse;

@@ -13,7 +13,15 @@
 //               ldmatrix.x4.trans (two 8-wide column tiles of V per instruction).
 //
 // Online softmax in fp32 (exp2 domain). Warps of a CTA merge through shared memory; the CTAs of
-// a (batch row, kv head) leave partials that a small merge kernel combines (sl_attn.cu).
+// a (batch row, kv head) leave partials that a small merge kernel combines (sl_attn.cu): its launch
+// overlaps this kernel's tail (programmatic dependent launch). Letting the last CTA of a
+// (row, head) combine the partials instead (a ticket per pair) measured 1.2 us SLOWER at the
+// headline shape: the combining CTA's fence, ticket and two trips to L2 are a serial tail.
+//
+// Cache geometry is explicit (batch / token / head strides): K and V may be two caches
+// [B, N, KH, 128] or one cache [B, N, KH, 2, 128] in which a key's K and V rows are adjacent, so
+// that one gathered key is ONE 512-byte piece of DRAM instead of two 256-byte ones (measured on
+// B200: no difference in time, 17.25 against 17.31 us at the headline shape).
 #include "sl_attn.cuh"
 #include "sl_mma.cuh"
 
@@ -21,11 +29,8 @@ namespace {
 
 using sl::AttnArgs;
 
-constexpr int MT = 128;            // threads per CTA
-constexpr int MW = MT / 32;        // warps
 constexpr int ST = 3;              // cp.async stages per warp
 constexpr int STAGE_BYTES = 8192;  // 16 K rows + 16 V rows of 256 B
-constexpr int RING_BYTES = MW * ST * STAGE_BYTES;
 constexpr float LOG2E = 1.4426950408889634f;
 constexpr float LN2 = 0.6931471805599453f;
 constexpr float QK_SCALE = 0.08838834764831845f * LOG2E;   // 1/sqrt(128) in the exp2 domain
@@ -33,8 +38,12 @@ constexpr float QK_SCALE = 0.08838834764831845f * LOG2E;   // 1/sqrt(128) in the
 // byte offset of 16-byte chunk c (0..15) of row r (0..15) inside a swizzled 16 x 256 B tile
 __device__ __forceinline__ unsigned swz(int r, int c) { return (unsigned)(r * 256 + (((c & 8) | ((c ^ r) & 7)) << 4)); }
 
-template <bool HI>   // HI: the group has more than 8 query heads (rows 8..15 of the tile are used)
-__global__ void __launch_bounds__(MT, 2) sparse_attn_mma_kernel(const AttnArgs a, const int G) {
+// HI: the group has more than 8 query heads (rows 8..15 of the tile are used).
+// MW warps per CTA: 8 (one CTA per SM) when there are at most as many (batch row, kv head) pairs as
+// SMs -- fewer, fatter CTAs mean fewer partials to combine -- else 4 (two CTAs per SM).
+template <bool HI, int MW>
+__global__ void __launch_bounds__(MW * 32, 8 / MW) sparse_attn_mma_kernel(const AttnArgs a, const int G) {
+    constexpr int MT = MW * 32;
     extern __shared__ __align__(128) unsigned char ring[];          // [MW][ST][K 4 KB | V 4 KB]; reused by the epilogue
     __shared__ float sm_m[MW][16], sm_l[MW][16];
 
@@ -48,9 +57,10 @@ __global__ void __launch_bounds__(MT, 2) sparse_attn_mma_kernel(const AttnArgs a
     const int per = (ntiles + a.splits - 1) / a.splits;
     const int tile_lo = min(ntiles, sp * per), tile_hi = min(ntiles, tile_lo + per);
     const int* list = a.idx + ((long long)b * KH + h) * a.cap;
-    const long long row_stride = (long long)KH * 128;
-    const __nv_bfloat16* kb = reinterpret_cast<const __nv_bfloat16*>(a.k) + (long long)b * a.kv_b + h * 128;
-    const __nv_bfloat16* vb = reinterpret_cast<const __nv_bfloat16*>(a.v) + (long long)b * a.kv_b + h * 128;
+    const long long row_stride = a.tok_stride;
+    const long long hoff = (long long)b * a.kv_b + (long long)(h / a.kv_div) * a.head_stride;
+    const __nv_bfloat16* kb = reinterpret_cast<const __nv_bfloat16*>(a.k) + hoff + (lane & 15) * 8;
+    const __nv_bfloat16* vb = reinterpret_cast<const __nv_bfloat16*>(a.v) + hoff + (lane & 15) * 8;
     const unsigned wring = (unsigned)__cvta_generic_to_shared(ring) + warp * (ST * STAGE_BYTES);
 
     // one tile = list entries [16 t, 16 t + 16); lane l < 16 fetches entry l (clamped to the last one)
@@ -62,7 +72,7 @@ __global__ void __launch_bounds__(MT, 2) sparse_attn_mma_kernel(const AttnArgs a
 #pragma unroll
         for (int it = 0; it < 8; ++it) {
             const int r = 2 * it + (lane >> 4);
-            const long long off = (long long)__shfl_sync(0xffffffffu, tok, r) * row_stride + c * 8;
+            const long long off = (long long)__shfl_sync(0xffffffffu, tok, r) * row_stride;
             cp_async16(sbase + swz(r, c), kb + off);
             cp_async16(sbase + 4096 + swz(r, c), vb + off);
         }
@@ -83,7 +93,7 @@ __global__ void __launch_bounds__(MT, 2) sparse_attn_mma_kernel(const AttnArgs a
     // ---- Q fragments (A operand), natural order
     unsigned qa[8][HI ? 4 : 2];
     {
-        const __nv_bfloat16* qbase = reinterpret_cast<const __nv_bfloat16*>(a.q) + (long long)b * KH * G * 128;
+        const __nv_bfloat16* qbase = reinterpret_cast<const __nv_bfloat16*>(a.q) + (long long)b * KH * G * 128;   // KH * G query heads
 #pragma unroll
         for (int half = 0; half < (HI ? 2 : 1); ++half) {
             const int g = grp + 8 * half;
@@ -257,24 +267,34 @@ __global__ void __launch_bounds__(MT, 2) sparse_attn_mma_kernel(const AttnArgs a
 
 namespace sl {
 
+static int g_attn_warps = 0;        // 0: by shape; 4 / 8: forced (sl_configure, for measurements)
+void set_attn_warps(int v) { g_attn_warps = v; }
+static bool fat_ctas(int B, int KH) { return g_attn_warps ? g_attn_warps == 8 : B * KH <= sm_count(); }
+
 int attn_mma_splits(int B, int KH, int cap) {
-    // two CTAs of four warps per SM, never more CTAs than fit at once; every warp should get
-    // at least one 16-row tile
+    // never more CTAs than fit at once (one of eight warps per SM, or two of four); every warp
+    // should get at least one 16-row tile
     const int ctas = B * KH;
     const int tiles = (cap + 15) / 16;
-    int s = (2 * sm_count()) / ctas;
-    s = std::min(s, std::min(ATTN_MAX_SPLITS, std::max(1, tiles / MW)));
+    const int mw = fat_ctas(B, KH) ? 8 : 4;
+    int s = ((8 / mw) * sm_count()) / ctas;
+    s = std::min(s, std::min(ATTN_MAX_SPLITS, std::max(1, tiles / mw)));
     return std::max(s, 1);
 }
 
-int launch_attn_mma(const AttnArgs& a, int G, cudaStream_t s) {
+template <bool HI, int MW>
+static int launch_one(const AttnArgs& a, int G, cudaStream_t s) {
+    const size_t ring_bytes = (size_t)MW * ST * STAGE_BYTES;
     dim3 grid((unsigned)a.splits, (unsigned)a.KH, (unsigned)a.B);
-    SL_CUDA_OK(ensure_dyn_smem(reinterpret_cast<const void*>(G > 8 ? sparse_attn_mma_kernel<true> : sparse_attn_mma_kernel<false>),
-                               RING_BYTES));
-    if (G > 8) SL_CUDA_OK(launch_kernel(sparse_attn_mma_kernel<true>, grid, dim3(MT), RING_BYTES, s, false, a, G));
-    else SL_CUDA_OK(launch_kernel(sparse_attn_mma_kernel<false>, grid, dim3(MT), RING_BYTES, s, false, a, G));
+    SL_CUDA_OK(ensure_dyn_smem(reinterpret_cast<const void*>(sparse_attn_mma_kernel<HI, MW>), ring_bytes));
+    SL_CUDA_OK(launch_kernel(sparse_attn_mma_kernel<HI, MW>, grid, dim3(MW * 32), ring_bytes, s, false, a, G));
     if (a.splits > 1) return launch_attn_merge(a, G, SL_BF16, s);
     return SL_OK;
+}
+
+int launch_attn_mma(const AttnArgs& a, int G, cudaStream_t s) {
+    if (fat_ctas(a.B, a.KH)) return G > 8 ? launch_one<true, 8>(a, G, s) : launch_one<false, 8>(a, G, s);
+    return G > 8 ? launch_one<true, 4>(a, G, s) : launch_one<false, 4>(a, G, s);
 }
 
 }  // namespace sl

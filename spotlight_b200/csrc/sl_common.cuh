@@ -35,6 +35,23 @@ bool l2_prefetch_enabled();   // the decode-step hash warms L2 with the code cac
 
 static inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
+// ---- entry points with a device-side position (one captured launch serves every decode token) ----
+struct DevPos {
+    const long long* d_pos;        // position of the decode token; the context is *d_pos + 1 keys
+    const void* cos_tab;           // [rows,128] of the run dtype, row r = position tab_pos0 + r (or null: no rotation)
+    const void* sin_tab;
+    long long tab_pos0;
+};
+int scan_topk_impl(const uint32_t* d_q_codes, const uint32_t* d_k_codes, int64_t k_batch_stride, int B, int64_t N,
+                   int KH, int QH, int gqa_layout, int k, int sink, int recent, int32_t* d_idx, int idx_capacity,
+                   int32_t* d_cnt, int16_t* d_scores_out, void* d_workspace, size_t workspace_bytes,
+                   int32_t* d_status, const long long* d_pos, double mask_out, int min_remain, void* stream);
+int decode_prepare_impl(const void* d_q, const void* d_k, const void* d_v, int dtype, int B, int QH, int KH,
+                        const void* d_cos, const void* d_sin, const sl_hash_params* hash_q, const sl_hash_params* hash_k,
+                        void* d_q_rot, uint32_t* d_q_codes, uint32_t* d_code_cache, int64_t code_batch_stride,
+                        void* d_k_cache, void* d_v_cache, const sl_kv_layout* kv, int64_t pos, const DevPos* dp,
+                        void* stream);
+
 // ---- launches ----------------------------------------------------------------------------
 // Kernels of the decode path are launched with programmatic stream serialisation: a kernel may
 // start while its predecessor in the stream drains, does whatever does not depend on it, and

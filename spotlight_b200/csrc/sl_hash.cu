@@ -12,7 +12,7 @@
 #include "sl_mma.cuh"
 
 namespace sl {
-int launch_hash_encode_mma(const void* x, long long xs_b, int B, long long T, int H, const sl_hash_params* hp,
+int launch_hash_encode_mma(const void* x, long long xs_b, long long xs_tok, long long xs_h, int B, long long T, int H, const sl_hash_params* hp,
                            uint32_t* codes, long long cs_b, cudaStream_t s);
 }
 
@@ -23,11 +23,17 @@ constexpr int MAXD = 256;    // largest layer width
 
 struct HashJob {
     const void* x; long long xs_b; long long T; int H; int B;
+    long long xs_tok, xs_h;                          // elements between consecutive tokens / heads of x
     sl_hash_params hp;
     uint32_t* codes; long long cs_b;
     void* x_rot; long long xr_b;
     const void* cosr; const void* sinr;
     const void* v_src; void* v_dst; long long v_b;   // optional value-row append (decode)
+    long long xr_h, v_h;                             // elements between consecutive heads of a row of x_rot / v_dst
+    // position on the device (decode, optional): outputs move by *d_pos rows, cos/sin come from row *d_pos - tab_pos0
+    const long long* d_pos;
+    long long xr_tok, v_tok, code_tok;               // elements (code words) per position of x_rot / v_dst / codes
+    long long tab_pos0;
     long long row_tiles;
 };
 
@@ -39,19 +45,27 @@ struct HashArgs {
     // from HBM overlaps this latency-bound kernel, which leaves most SMs idle.
     int heads;
     const unsigned char* pf_base; long long pf_bstride; long long pf_bytes; int pf_B;
+    const long long* pf_pos; long long pf_row_bytes;      // position on the device: pf_bytes = *pf_pos * pf_row_bytes (capped)
 };
 
 constexpr int PF_PIECE = 2048;                     // bytes per bulk prefetch
 constexpr long long PF_MAX_BYTES = 24ll << 20;     // what HBM delivers in the few us this kernel lasts
 
 __device__ __forceinline__ void prefetch_codes(const HashArgs& args) {
-    const long long per_b = (args.pf_bytes + PF_PIECE - 1) / PF_PIECE;
+    long long bytes = args.pf_bytes;
+    if (args.pf_pos) {
+        // Read before the wait on the preceding kernel, which may be the one that advances the position:
+        // a stale value only makes the prefetch one row short.
+        bytes = min(bytes, __ldcg(args.pf_pos) * args.pf_row_bytes);
+        if (bytes <= 0) return;
+    }
+    const long long per_b = (bytes + PF_PIECE - 1) / PF_PIECE;
     const long long total = per_b * args.pf_B;
     const long long nthreads = (long long)(gridDim.y - args.heads) * gridDim.x * blockDim.x;
     long long p = ((long long)(blockIdx.y - args.heads) * gridDim.x + blockIdx.x) * blockDim.x + threadIdx.x;
     for (; p < total; p += nthreads) {
         const long long b = p / per_b, off = (p % per_b) * PF_PIECE;
-        const unsigned size = (unsigned)min((long long)PF_PIECE, args.pf_bytes - off);
+        const unsigned size = (unsigned)min((long long)PF_PIECE, bytes - off);
         const unsigned char* ptr = args.pf_base + b * args.pf_bstride + off;
         asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(ptr), "r"(size) : "memory");
     }
@@ -60,6 +74,7 @@ __device__ __forceinline__ void prefetch_codes(const HashArgs& args) {
 // Offsets of the R rows of a tile, computed once (integer divisions are kept out of the loops).
 struct RowInfo {
     long long x, xrot, vsrc, vdst, code;
+    long long trow;          // offset of the position's row in the cos / sin tables (0 without a device-side position)
     int valid;
 };
 
@@ -74,11 +89,13 @@ __device__ __forceinline__ void stage_rows(const HashJob& J, int h, long long r0
             long long b = rg, t = 0;
             if (J.T != 1) { b = rg / J.T; t = rg - b * J.T; }
             const long long th = t * J.H + h;
-            ri.x = b * J.xs_b + th * 128;
-            ri.xrot = b * J.xr_b + th * 128;
+            const long long pos = J.d_pos ? __ldcg(J.d_pos) : 0;
+            ri.trow = J.d_pos ? (pos - J.tab_pos0) * 128 : 0;
+            ri.x = b * J.xs_b + t * J.xs_tok + h * J.xs_h;
+            ri.xrot = b * J.xr_b + th * J.xr_h + pos * J.xr_tok;
             ri.vsrc = ((b * J.T + t) * J.H + h) * 128;
-            ri.vdst = b * J.v_b + th * 128;
-            ri.code = b * J.cs_b + th * 4;
+            ri.vdst = b * J.v_b + th * J.v_h + pos * J.v_tok;
+            ri.code = b * J.cs_b + th * 4 + pos * J.code_tok;
         }
         rinfo[tid] = ri;
     }
@@ -100,8 +117,9 @@ __device__ __forceinline__ void stage_rows(const HashJob& J, int h, long long r0
         if (J.cosr) {
             const float other = xb[r * MAXD + (j ^ 64)];
             const float rot = j < 64 ? -other : other;
-            const float c = sl::VT<T>::to_f(reinterpret_cast<const T*>(J.cosr)[j]);
-            const float sn = sl::VT<T>::to_f(reinterpret_cast<const T*>(J.sinr)[j]);
+            const long long trow = rinfo[r].trow;
+            const float c = sl::VT<T>::to_f(reinterpret_cast<const T*>(J.cosr)[trow + j]);
+            const float sn = sl::VT<T>::to_f(reinterpret_cast<const T*>(J.sinr)[trow + j]);
             val = sl::VT<T>::round(__fadd_rn(sl::VT<T>::round(__fmul_rn(val, c)), sl::VT<T>::round(__fmul_rn(rot, sn))));
         }
         if (J.x_rot && rinfo[r].valid) (reinterpret_cast<T*>(J.x_rot) + rinfo[r].xrot)[j] = sl::VT<T>::from_f(val);
@@ -377,8 +395,32 @@ extern "C" int sl_decode_prepare(const void* d_q, const void* d_k, const void* d
                                  const sl_hash_params* hash_k, void* d_q_rot, uint32_t* d_q_codes,
                                  uint32_t* d_code_cache, int64_t code_batch_stride, void* d_k_cache, void* d_v_cache,
                                  int64_t kv_batch_stride, int64_t pos, void* stream) {
+    const sl_kv_layout kv = {kv_batch_stride, (int64_t)KH * 128, 128, 1};
+    return sl::decode_prepare_impl(d_q, d_k, d_v, dtype, B, QH, KH, d_cos, d_sin, hash_q, hash_k, d_q_rot, d_q_codes,
+                                   d_code_cache, code_batch_stride, d_k_cache, d_v_cache, &kv, pos, nullptr, stream);
+}
+
+extern "C" int sl_decode_prepare_ex(const void* d_q, const void* d_k, const void* d_v, int dtype, int B, int QH, int KH,
+                                    const void* d_cos, const void* d_sin, const sl_hash_params* hash_q,
+                                    const sl_hash_params* hash_k, void* d_q_rot, uint32_t* d_q_codes,
+                                    uint32_t* d_code_cache, int64_t code_batch_stride, void* d_k_cache, void* d_v_cache,
+                                    const sl_kv_layout* kv, int64_t pos, void* stream) {
+    SL_REQUIRE(kv != nullptr, SL_EINVAL, "sl_decode_prepare_ex: null cache layout");
+    return sl::decode_prepare_impl(d_q, d_k, d_v, dtype, B, QH, KH, d_cos, d_sin, hash_q, hash_k, d_q_rot, d_q_codes,
+                                   d_code_cache, code_batch_stride, d_k_cache, d_v_cache, kv, pos, nullptr, stream);
+}
+
+// dp == nullptr: the token sits at `pos`, d_cos / d_sin are its [128] rows. Otherwise the position is the
+// device word *dp->d_pos, `pos` is the largest position the caches hold (bounds the prefetch) and the
+// cos / sin rows are looked up in dp's tables.
+int sl::decode_prepare_impl(const void* d_q, const void* d_k, const void* d_v, int dtype, int B, int QH, int KH,
+                            const void* d_cos, const void* d_sin, const sl_hash_params* hash_q,
+                            const sl_hash_params* hash_k, void* d_q_rot, uint32_t* d_q_codes, uint32_t* d_code_cache,
+                            int64_t code_batch_stride, void* d_k_cache, void* d_v_cache, const sl_kv_layout* kv,
+                            int64_t pos, const sl::DevPos* dp, void* stream) {
     SL_REQUIRE(d_q && d_q_codes, SL_EINVAL, "sl_decode_prepare: null query pointer");
     SL_REQUIRE(B > 0 && QH > 0 && KH >= 0 && pos >= 0, SL_ESHAPE, "sl_decode_prepare: bad shape");
+    if (dp) { d_cos = dp->cos_tab; d_sin = dp->sin_tab; }
     SL_REQUIRE((d_cos == nullptr) == (d_sin == nullptr), SL_EINVAL, "sl_decode_prepare: cos and sin must come together");
     if (int rc = check_params("sl_decode_prepare", hash_q, dtype)) return rc;
     const bool with_k = d_k != nullptr && KH > 0;
@@ -386,33 +428,40 @@ extern "C" int sl_decode_prepare(const void* d_q, const void* d_k, const void* d
         if (int rc = check_params("sl_decode_prepare", hash_k, dtype)) return rc;
         SL_REQUIRE(d_code_cache != nullptr, SL_EINVAL, "sl_decode_prepare: key given without a code cache");
         SL_REQUIRE((d_v == nullptr) == (d_v_cache == nullptr), SL_EINVAL, "sl_decode_prepare: value and value cache must come together");
+        SL_REQUIRE(kv->token_stride >= 128 && kv->head_stride >= 128, SL_ESHAPE, "sl_decode_prepare: cache strides must leave room for a 128-value row");
     }
+    const long long pos_host = dp ? 0 : pos;               // rows are offset on the host, or by *d_pos in the kernel
     HashArgs args = {};
     HashJob& q = args.job[0];
-    q.x = d_q; q.xs_b = (long long)QH * 128; q.T = 1; q.H = QH; q.B = B;
+    q.x = d_q; q.xs_b = (long long)QH * 128; q.xs_tok = (long long)QH * 128; q.xs_h = 128; q.T = 1; q.H = QH; q.B = B;
     q.hp = *hash_q;
     q.codes = d_q_codes; q.cs_b = (long long)QH * 4;
-    q.x_rot = d_q_rot; q.xr_b = (long long)QH * 128;
+    q.x_rot = d_q_rot; q.xr_b = (long long)QH * 128; q.xr_h = 128; q.v_h = 128;
     q.cosr = d_cos; q.sinr = d_sin;
+    if (dp) { q.d_pos = dp->d_pos; q.tab_pos0 = dp->tab_pos0; }
     args.heads0 = QH;
     int total = QH;
     if (with_k) {
         HashJob& k = args.job[1];
-        k.x = d_k; k.xs_b = (long long)KH * 128; k.T = 1; k.H = KH; k.B = B;
+        const size_t esz = dtype == SL_F32 ? 4 : 2;
+        k.x = d_k; k.xs_b = (long long)KH * 128; k.xs_tok = (long long)KH * 128; k.xs_h = 128; k.T = 1; k.H = KH; k.B = B;
         k.hp = *hash_k;
-        k.codes = d_code_cache + pos * KH * 4; k.cs_b = code_batch_stride;
+        k.codes = d_code_cache + pos_host * KH * 4; k.cs_b = code_batch_stride;
+        k.xr_h = k.v_h = kv->head_stride;
         if (d_k_cache) {
-            const size_t esz = dtype == SL_F32 ? 4 : 2;
-            k.x_rot = static_cast<unsigned char*>(d_k_cache) + (size_t)pos * KH * 128 * esz;
-            k.xr_b = kv_batch_stride;
+            k.x_rot = static_cast<unsigned char*>(d_k_cache) + (size_t)pos_host * kv->token_stride * esz;
+            k.xr_b = kv->batch_stride;
         }
         if (d_v_cache) {
-            const size_t esz = dtype == SL_F32 ? 4 : 2;
             k.v_src = d_v;
-            k.v_dst = static_cast<unsigned char*>(d_v_cache) + (size_t)pos * KH * 128 * esz;
-            k.v_b = kv_batch_stride;
+            k.v_dst = static_cast<unsigned char*>(d_v_cache) + (size_t)pos_host * kv->token_stride * esz;
+            k.v_b = kv->batch_stride;
         }
         k.cosr = d_cos; k.sinr = d_sin;
+        if (dp) {
+            k.d_pos = dp->d_pos; k.tab_pos0 = dp->tab_pos0;
+            k.xr_tok = k.v_tok = kv->token_stride; k.code_tok = (long long)KH * 4;
+        }
         total += KH;
     }
     if (d_code_cache != nullptr && KH > 0 && pos > 0 && sl::l2_prefetch_enabled() && sl::aligned16(d_code_cache) &&
@@ -424,6 +473,7 @@ extern "C" int sl_decode_prepare(const void* d_q, const void* d_k, const void* d
         if ((long long)pos * KH * 16 * B <= PF_MAX_BYTES) {
             args.pf_bytes = (long long)pos * KH * 16;
             args.pf_B = B;
+            if (dp) { args.pf_pos = dp->d_pos; args.pf_row_bytes = (long long)KH * 16; }
         } else {
             args.pf_base = nullptr;
         }
@@ -433,23 +483,31 @@ extern "C" int sl_decode_prepare(const void* d_q, const void* d_k, const void* d
 
 extern "C" int sl_hash_encode(const void* d_x, int64_t x_batch_stride, int dtype, int B, int64_t T, int H,
                               const sl_hash_params* hash, uint32_t* d_codes, int64_t code_batch_stride, void* stream) {
+    return sl_hash_encode_ex(d_x, x_batch_stride, (int64_t)H * 128, 128, dtype, B, T, H, hash, d_codes, code_batch_stride,
+                             stream);
+}
+
+extern "C" int sl_hash_encode_ex(const void* d_x, int64_t x_batch_stride, int64_t x_token_stride, int64_t x_head_stride,
+                                 int dtype, int B, int64_t T, int H, const sl_hash_params* hash, uint32_t* d_codes,
+                                 int64_t code_batch_stride, void* stream) {
     SL_REQUIRE(d_x && d_codes, SL_EINVAL, "sl_hash_encode: null pointer");
     SL_REQUIRE(B > 0 && T >= 0 && H > 0, SL_ESHAPE, "sl_hash_encode: bad shape");
-    SL_REQUIRE(x_batch_stride >= T * H * 128 && code_batch_stride >= T * H * 4, SL_ESHAPE,
-               "sl_hash_encode: batch stride shorter than a batch row");
+    SL_REQUIRE(x_head_stride >= 128 && x_token_stride >= 128 && code_batch_stride >= T * H * 4, SL_ESHAPE,
+               "sl_hash_encode: strides shorter than a row");
     if (int rc = check_params("sl_hash_encode", hash, dtype)) return rc;
     if (T == 0) return SL_OK;
-    if (dtype == SL_BF16 && (long long)B * T >= 64 && sl::aligned16(d_x) && x_batch_stride % 8 == 0) {
+    if (dtype == SL_BF16 && (long long)B * T >= 64 && sl::aligned16(d_x) && x_batch_stride % 8 == 0 &&
+        x_token_stride % 8 == 0 && x_head_stride % 8 == 0) {
         // many rows: the tensor-core kernel (weights resident in shared memory); 1 = shape not covered
-        const int rc = sl::launch_hash_encode_mma(d_x, x_batch_stride, B, T, H, hash, d_codes, code_batch_stride,
-                                                  static_cast<cudaStream_t>(stream));
+        const int rc = sl::launch_hash_encode_mma(d_x, x_batch_stride, x_token_stride, x_head_stride, B, T, H, hash, d_codes,
+                                                  code_batch_stride, static_cast<cudaStream_t>(stream));
         if (rc <= 0) return rc;
     }
     HashArgs args = {};
     HashJob& j = args.job[0];
-    j.x = d_x; j.xs_b = x_batch_stride; j.T = T; j.H = H; j.B = B;
+    j.x = d_x; j.xs_b = x_batch_stride; j.xs_tok = x_token_stride; j.xs_h = x_head_stride; j.T = T; j.H = H; j.B = B;
     j.hp = *hash;
-    j.codes = d_codes; j.cs_b = code_batch_stride;
+    j.codes = d_codes; j.cs_b = code_batch_stride; j.xr_h = j.v_h = 128;
     args.heads0 = H;
     return launch(args, dtype, H, (long long)B * T, static_cast<cudaStream_t>(stream));
 }

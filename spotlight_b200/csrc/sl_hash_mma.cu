@@ -19,7 +19,7 @@ constexpr int HM_THREADS = 256;
 constexpr int HM_TILE = 128;             // rows per CTA tile = 8 warps x 16 rows
 
 struct HashMmaArgs {
-    const __nv_bfloat16* x; long long xs_b; long long T; int H; int B;
+    const __nv_bfloat16* x; long long xs_b, xs_tok, xs_h; long long T; int H; int B;
     const __nv_bfloat16* w[2]; const __nv_bfloat16* bias[2]; int residue;
     uint32_t* codes; long long cs_b; long long n_tiles;
 };
@@ -80,7 +80,7 @@ __global__ void __launch_bounds__(HM_THREADS, 1) hash_encode_mma_kernel(const Ha
             long long rg = tile * HM_TILE + r;
             if (rg >= rows) rg = rows - 1;
             const long long b = rg / a.T, t = rg - b * a.T;
-            cp_async16(s_x + buf * (HM_TILE * 256) + wz(r, c, 16), a.x + b * a.xs_b + (t * a.H + h) * 128 + c * 8);
+            cp_async16(s_x + buf * (HM_TILE * 256) + wz(r, c, 16), a.x + b * a.xs_b + t * a.xs_tok + h * a.xs_h + c * 8);
         }
     };
 
@@ -214,13 +214,13 @@ int launch_one(const HashMmaArgs& a, cudaStream_t s) {
 namespace sl {
 
 // Returns SL_OK after launching, or 1 when the shape is not one the tensor-core kernel covers.
-int launch_hash_encode_mma(const void* x, long long xs_b, int B, long long T, int H, const sl_hash_params* hp,
+int launch_hash_encode_mma(const void* x, long long xs_b, long long xs_tok, long long xs_h, int B, long long T, int H, const sl_hash_params* hp,
                            uint32_t* codes, long long cs_b, cudaStream_t s) {
     if (hp->dims[0] != 128 || hp->dims[hp->n_layers] != 128 || hp->n_layers > 2) return 1;
     if (hp->n_layers == 2 && hp->dims[1] != 128 && hp->dims[1] != 256) return 1;
     if (H > 65535) return 1;
     HashMmaArgs a = {};
-    a.x = static_cast<const __nv_bfloat16*>(x); a.xs_b = xs_b; a.T = T; a.H = H; a.B = B;
+    a.x = static_cast<const __nv_bfloat16*>(x); a.xs_b = xs_b; a.xs_tok = xs_tok; a.xs_h = xs_h; a.T = T; a.H = H; a.B = B;
     for (int i = 0; i < hp->n_layers; ++i) {
         a.w[i] = static_cast<const __nv_bfloat16*>(hp->d_w[i]);
         a.bias[i] = static_cast<const __nv_bfloat16*>(hp->d_b[i]);

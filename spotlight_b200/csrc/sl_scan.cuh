@@ -69,6 +69,10 @@ struct LeanArgs {
     int NC;                    // coarse bins per head
     int rowh;                  // row stride of the score rows in shared memory (halfwords)
     int hist_off, score_off;   // byte offsets of the histogram rows and of the score rows in shared memory
+    // context length on the device (optional): N above is then the capacity the launch is planned for
+    const long long* d_pos;    // position of the decode token: the context is *d_pos + 1 keys
+    int sink, recent, min_remain;
+    double mask_out;
     unsigned long long* dbg;   // optional [grid][16] phase stamps (profiling builds only)
 };
 

@@ -48,7 +48,7 @@ __device__ __forceinline__ unsigned ldcg_u16(const void* p) {
 template <int PT>
 __global__ void __launch_bounds__(NT, 1) scan_lean_kernel(const LeanArgs a) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
-    const int KH = a.KH, nbins = a.nbins, nb1 = (nbins + 4) & ~3, N = a.N, cpb = a.ctas_per_b, S = a.S;   // rows of nb1 words: 16-byte aligned, R[nbins..] = 0
+    const int KH = a.KH, nbins = a.nbins, nb1 = (nbins + 4) & ~3, cpb = a.ctas_per_b, S = a.S;   // rows of nb1 words: 16-byte aligned, R[nbins..] = 0
     uint32_t* s_planes = reinterpret_cast<uint32_t*>(smem_raw);                 // [KH][2][PT][4]
     int* s_pbase = reinterpret_cast<int*>(s_planes + KH * 32);                    // [KH][4]
     int* s_tau = s_pbase + KH * 4;                                                // [KH]
@@ -60,16 +60,26 @@ __global__ void __launch_bounds__(NT, 1) scan_lean_kernel(const LeanArgs a) {
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int b = blockIdx.x / cpb, c = blockIdx.x - b * cpb;
-    const int t0 = min(N, c * a.chunk), t1 = min(N, t0 + a.chunk);
-    const int len = t1 - t0, ncodes = len * KH;
     const int rowh = a.rowh;                                                      // row stride of sscores (halfwords)
     const int khs = 31 - __clz(KH);
-    const int sub = ((len + S - 1) / S + 127) & ~127;                             // keys per sub-range
     const int NC = a.NC, cslice = a.B * KH * NC;
-    const int nwin = a.s_end + (N - a.r_start);                                   // always-kept keys of the row
     sl::pdl_trigger();
     sl::pdl_wait();
     SL_STAMP(0)
+    // The context length is a launch argument, or -- so that one captured launch serves every token of
+    // a decode loop -- the word *d_pos + 1 with the reference's budget rule evaluated here as Python
+    // evaluates it (doubles): k = max(min(n, min_remain), n - int(n * mask_out)).
+    int N = a.N, s_end = a.s_end, r_start = a.r_start, k_budget = a.k_budget;
+    if (a.d_pos) {
+        N = (int)min((long long)a.N, __ldcg(a.d_pos) + 1);
+        s_end = min(a.sink, N);
+        r_start = max(s_end, N - a.recent);
+        k_budget = max(min(N, a.min_remain), N - (int)((double)N * a.mask_out));
+    }
+    const int t0 = min(N, c * a.chunk), t1 = min(N, t0 + a.chunk);
+    const int len = t1 - t0, ncodes = len * KH;
+    const int sub = ((len + S - 1) / S + 127) & ~127;                             // keys per sub-range
+    const int nwin = s_end + (N - r_start);                                       // always-kept keys of the row
     const unsigned par = __ldcg(a.epoch + b) & 1u;                                // this launch's coarse buffer
     unsigned* chist_b = a.chist + (size_t)par * cslice + b * KH * NC;
 
@@ -141,9 +151,9 @@ __global__ void __launch_bounds__(NT, 1) scan_lean_kernel(const LeanArgs a) {
     // ------------------------------------------------------------------ P: suffix sums, publish
     {
         // scores of the always-kept keys this chunk owns (the other CTAs correct their counts with them)
-        if (t0 < a.s_end || t1 > a.r_start) {
+        if (t0 < s_end || t1 > r_start) {
             if (tid < nwin) {
-                const int t = tid < a.s_end ? tid : a.r_start + (tid - a.s_end);
+                const int t = tid < s_end ? tid : r_start + (tid - s_end);
                 if (t >= t0 && t < t1)
                     for (int h = 0; h < KH; ++h) a.wsc[((size_t)b * KH + h) * LEAN_MAX_WIN + tid] = sscores[h * rowh + (t - t0)];
             }
@@ -201,7 +211,7 @@ __global__ void __launch_bounds__(NT, 1) scan_lean_kernel(const LeanArgs a) {
 
     // ------------------------------------------------------------------ T: threshold, quota, counts before this chunk
     {
-        const int kk = min(a.k_budget, N);
+        const int kk = min(k_budget, N);
         const int CPL = (NC + 31) >> 5;                      // coarse bins per lane, consecutive
 #pragma unroll 1
         for (int h = warp; h < KH; h += NW) {
@@ -302,7 +312,7 @@ __global__ void __launch_bounds__(NT, 1) scan_lean_kernel(const LeanArgs a) {
                     const int v = (int)wv[i];
                     gt_win += __popc(__ballot_sync(0xffffffffu, in && v > tau));
                     eq_win += __popc(__ballot_sync(0xffffffffu, in && v == tau));
-                    eq_sink += __popc(__ballot_sync(0xffffffffu, in && wj < a.s_end && v == tau));
+                    eq_sink += __popc(__ballot_sync(0xffffffffu, in && wj < s_end && v == tau));
                 }
                 rM = max(r - eq_sink, 0);
                 selM = (gt_tot - gt_win) + min((ge_tot - gt_tot) - eq_win, rM);
@@ -312,7 +322,7 @@ __global__ void __launch_bounds__(NT, 1) scan_lean_kernel(const LeanArgs a) {
             if (lane == 0) {
                 s_tau[h] = tau;
                 s_pre[h * 4 + 0] = pre_gt; s_pre[h * 4 + 1] = pre_eq; s_pre[h * 4 + 2] = rM; s_pre[h * 4 + 3] = selM;
-                if (c == 0) a.cnt[b * KH + h] = a.s_end + selM + (N - a.r_start);
+                if (c == 0) a.cnt[b * KH + h] = s_end + selM + (N - r_start);
             }
         }
     }
@@ -326,7 +336,7 @@ __global__ void __launch_bounds__(NT, 1) scan_lean_kernel(const LeanArgs a) {
     // (0x8000 - tau) iff score >= tau, two scores per 32-bit add.
     {
         const int ntasks = KH * S;
-        const int mlo = max(t0, a.s_end) - t0, mhi = min(t1, a.r_start) - t0;     // the chunk's keys outside both windows
+        const int mlo = max(t0, s_end) - t0, mhi = min(t1, r_start) - t0;     // the chunk's keys outside both windows
         constexpr int RUN = 20;
 #pragma unroll 1
         for (int task = warp; task < ntasks; task += NW) {
@@ -357,14 +367,14 @@ __global__ void __launch_bounds__(NT, 1) scan_lean_kernel(const LeanArgs a) {
 #pragma unroll
                 for (int i = 0; i < LEAN_MAX_WIN / 32; ++i) {
                     const int wj = lane + 32 * i;
-                    const int t = wj < a.s_end ? wj : a.r_start + (wj - a.s_end);
+                    const int t = wj < s_end ? wj : r_start + (wj - s_end);
                     const bool in = wj < nwin && t < e0;
                     const int v = (int)s_win[h * LEAN_MAX_WIN + wj];
                     gt_before -= __popc(__ballot_sync(0xffffffffu, in && v > tau));
                     eq_before -= __popc(__ballot_sync(0xffffffffu, in && v == tau));
                 }
             }
-            int out_base = a.s_end + gt_before + min(eq_before, rM);
+            int out_base = s_end + gt_before + min(eq_before, rM);
             int* oi = a.idx + ((size_t)b * KH + h) * a.cap;
             const unsigned short* row = sscores + h * rowh;
             const unsigned cgt = (unsigned)(0x7fff - tau) * 0x10001u, cge = (unsigned)(0x8000 - tau) * 0x10001u;
@@ -418,10 +428,10 @@ __global__ void __launch_bounds__(NT, 1) scan_lean_kernel(const LeanArgs a) {
                 eq_before += tot_e;
             }
             // always-kept keys of this sub-range: the sink at its own index, the recent window at the end
-            for (int t = t0 + lo + lane; t < min(t0 + hi, a.s_end); t += 32)
+            for (int t = t0 + lo + lane; t < min(t0 + hi, s_end); t += 32)
                 if (t < a.cap) oi[t] = t;
-            for (int t = max(t0 + lo, a.r_start) + lane; t < t0 + hi; t += 32) {
-                const int pos = a.s_end + selM + (t - a.r_start);
+            for (int t = max(t0 + lo, r_start) + lane; t < t0 + hi; t += 32) {
+                const int pos = s_end + selM + (t - r_start);
                 if (pos < a.cap) oi[pos] = t;
             }
         }

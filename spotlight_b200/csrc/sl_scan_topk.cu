@@ -722,7 +722,23 @@ extern "C" int sl_scan_topk(const uint32_t* d_q_codes, const uint32_t* d_k_codes
                             int64_t N, int KH, int QH, int gqa_layout, int k, int sink, int recent, int32_t* d_idx,
                             int idx_capacity, int32_t* d_cnt, int16_t* d_scores_out, void* d_workspace,
                             size_t workspace_bytes, int32_t* d_status, void* stream) {
+    return sl::scan_topk_impl(d_q_codes, d_k_codes, k_batch_stride, B, N, KH, QH, gqa_layout, k, sink, recent, d_idx,
+                              idx_capacity, d_cnt, d_scores_out, d_workspace, workspace_bytes, d_status, nullptr, 0.0, 0,
+                              stream);
+}
+
+// d_pos == nullptr: N keys, budget k. Otherwise N is the capacity the launch is planned for, the context
+// is *d_pos + 1 keys and the budget follows the reference's rule from mask_out / min_remain on the device.
+int sl::scan_topk_impl(const uint32_t* d_q_codes, const uint32_t* d_k_codes, int64_t k_batch_stride, int B, int64_t N,
+                       int KH, int QH, int gqa_layout, int k, int sink, int recent, int32_t* d_idx, int idx_capacity,
+                       int32_t* d_cnt, int16_t* d_scores_out, void* d_workspace, size_t workspace_bytes,
+                       int32_t* d_status, const long long* d_pos, double mask_out, int min_remain, void* stream) {
     SL_REQUIRE(d_q_codes && d_k_codes && d_idx && d_cnt && d_workspace, SL_EINVAL, "sl_scan_topk: null pointer");
+    if (d_pos) {
+        SL_REQUIRE(N > 0 && mask_out >= 0.0 && mask_out <= 1.0 && min_remain >= 0, SL_EINVAL,
+                   "sl_scan_topk: bad capacity / mask_out / min_remain for a device-side context length");
+        k = (int)std::max<int64_t>(std::min<int64_t>(N, min_remain), N - (int64_t)((double)N * mask_out));
+    }
     if (int rc = check_common("sl_scan_topk", B, N, KH, QH)) return rc;
     SL_REQUIRE(gqa_layout == SL_GQA_INTERLEAVED || gqa_layout == SL_GQA_BLOCKED, SL_EINVAL,
                "sl_scan_topk: unknown gqa_layout %d", gqa_layout);
@@ -747,8 +763,11 @@ extern "C" int sl_scan_topk(const uint32_t* d_q_codes, const uint32_t* d_k_codes
     unsigned char* ws = static_cast<unsigned char*>(d_workspace);
     const int s_end0 = (int)std::min<int64_t>(sink, N);
     const int nwin0 = s_end0 + (int)(N - std::max<int64_t>(s_end0, N - recent));
-    if (g_lean == 1 && p.cooperative && !p.spill && B * p.ctas_per_b <= sl::sm_count() &&
-        slscan::lean_covers(KH, G, p.ctas_per_b, p.chunk, nwin0)) {
+    const bool lean_ok = p.cooperative && !p.spill && B * p.ctas_per_b <= sl::sm_count() &&
+                         slscan::lean_covers(KH, G, p.ctas_per_b, p.chunk, d_pos ? sink + recent : nwin0);
+    SL_REQUIRE(d_pos == nullptr || lean_ok, SL_ESHAPE,
+               "sl_scan_topk: a device-side context length needs a shape the one-barrier kernel covers");
+    if ((g_lean == 1 || d_pos) && lean_ok) {
         // the common decode shape: one barrier, everything the tail needs published before it
         slscan::LeanArgs f = {};
         f.q = reinterpret_cast<const uint4*>(d_q_codes);
@@ -768,6 +787,7 @@ extern "C" int sl_scan_topk(const uint32_t* d_q_codes, const uint32_t* d_k_codes
         f.wsc = reinterpret_cast<unsigned short*>(ws + w.wsc_off);
         f.status = d_status;
         f.ctas_per_b = p.ctas_per_b; f.chunk = p.chunk; f.nbins = p.nbins; f.S = p.S;
+        f.d_pos = d_pos; f.sink = sink; f.recent = recent; f.min_remain = min_remain; f.mask_out = mask_out;
         f.NC = slscan::lean_nc(p.nbins);
         f.nc_magic = (unsigned)(((1ull << 32) + f.NC - 1) / f.NC);
         const int roww = (p.chunk >> 1) + ((4 - (p.chunk >> 1)) & 31);

@@ -61,6 +61,21 @@ def _rows_view(t: torch.Tensor, inner: int) -> int:
     return t.stride(0) if B > 1 else max(t.stride(0), N * H * D)
 
 
+def _kv_layout(t: torch.Tensor, list_heads_per_kv_head: int = 1) -> "_lib.KvLayout":
+    """Geometry of a cache view [B, N, H, 128]: any batch / token / head strides with unit stride inside
+    a row (two caches [B,N,H,128], the K or V half of a fused cache [B,N,H,2,128], an aliased batch
+    made with ``expand``)."""
+    B, N, H, D = t.shape
+    sb, st, sh, sd = t.stride()
+    if D != 128 or (sd != 1 and D > 1):
+        raise ValueError("expected rows of 128 contiguous values")
+    if N <= 1:
+        st = max(st, H * D)
+    if H <= 1:
+        sh = max(sh, D)
+    return _lib.KvLayout(sb if B > 1 else max(sb, 0), st, sh, list_heads_per_kv_head)
+
+
 # ----------------------------------------------------------------------------- workspaces
 class _Workspaces:
     """Zero-initialised scratch buffers, one per (kind, device, shape); the kernels leave
@@ -329,7 +344,8 @@ def decode_prepare(q: torch.Tensor, k: Optional[torch.Tensor], v: Optional[torch
         q_rot = torch.empty_like(q)
     if q_codes is None:
         q_codes = torch.empty((B, QH, 4), dtype=torch.uint32, device=dev)
-    code_b = kv_b = 0
+    code_b = 0
+    kv = _lib.KvLayout(0, max(KH, 1) * 128, 128, 1)
     if k is not None:
         k = k.contiguous()
         v = None if v is None else v.contiguous()
@@ -338,13 +354,14 @@ def decode_prepare(q: torch.Tensor, k: Optional[torch.Tensor], v: Optional[torch
         code_b = _rows_view(code_cache, 4)
         if k_cache is not None:
             assert pos < k_cache.shape[1], "kv cache is full"
-            kv_b = _rows_view(k_cache, 128)
+            kv = _kv_layout(k_cache)
             if v_cache is not None:
-                assert _rows_view(v_cache, 128) == kv_b
-    check(lib.sl_decode_prepare(q.data_ptr(), _ptr(k), _ptr(v), _dt(q), B, QH, KH, _ptr(cos), _ptr(sin),
-                                hash_q.ref(), hash_k.ref() if hash_k is not None else None, q_rot.data_ptr(),
-                                q_codes.data_ptr(), _ptr(code_cache), code_b, _ptr(k_cache), _ptr(v_cache), kv_b,
-                                pos, _stream()))
+                kv2 = _kv_layout(v_cache)
+                assert (kv2.batch_stride, kv2.token_stride, kv2.head_stride) == (kv.batch_stride, kv.token_stride, kv.head_stride)
+    check(lib.sl_decode_prepare_ex(q.data_ptr(), _ptr(k), _ptr(v), _dt(q), B, QH, KH, _ptr(cos), _ptr(sin),
+                                   hash_q.ref(), hash_k.ref() if hash_k is not None else None, q_rot.data_ptr(),
+                                   q_codes.data_ptr(), _ptr(code_cache), code_b, _ptr(k_cache), _ptr(v_cache), C.byref(kv),
+                                   pos, _stream()))
     _count()
     return q_rot, q_codes
 
@@ -354,11 +371,12 @@ def hash_encode(x: torch.Tensor, params: HashParams, out: Optional[torch.Tensor]
     B, T, H, D = x.shape
     assert D == 128 and H == params.heads
     dev = _cuda(x)
-    xb = _rows_view(x, 128)
+    xl = _kv_layout(x)
     if out is None:
         out = torch.empty((B, T, H, 4), dtype=torch.uint32, device=dev)
     ob = _rows_view(out, 4)
-    check(lib.sl_hash_encode(x.data_ptr(), xb, _dt(x), B, T, H, params.ref(), out.data_ptr(), ob, _stream()))
+    check(lib.sl_hash_encode_ex(x.data_ptr(), xl.batch_stride, xl.token_stride, xl.head_stride, _dt(x), B, T, H,
+                                params.ref(), out.data_ptr(), ob, _stream()))
     _count()
     return out
 
@@ -367,24 +385,30 @@ def hash_encode(x: torch.Tensor, params: HashParams, out: Optional[torch.Tensor]
 def sparse_attn_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, idx: torch.Tensor,
                        cnt: torch.Tensor, layout: int = GQA_BLOCKED, out: Optional[torch.Tensor] = None,
                        return_lse: bool = False):
-    """q [B,QH,128]; k_cache/v_cache [B,N,KH,128] (views of a larger cache are fine);
-    idx int32 [B,KH,cap], cnt int32 [B,KH] -> out [B,QH,128] (+ lse float [B,QH])."""
+    """q [B,QH,128]; k_cache/v_cache [B,N,KVH,128] views with any batch / token / head strides (two
+    caches, the halves of a fused [B,N,KVH,2,128] cache, an ``expand``-ed batch);
+    idx int32 [B,LH,cap], cnt int32 [B,LH] -> out [B,QH,128] (+ lse float [B,QH]).
+    LH = KVH is the per-kv-head selection; LH = QH (a multiple of KVH) gives every query head its own
+    list over the shared K/V (query head j reads kv head j // (QH / KVH))."""
     B, QH, D = q.shape
-    _, _, KH, _ = k_cache.shape
+    KVH = k_cache.shape[2]
+    LH = idx.shape[1]
     assert D == 128 and k_cache.dtype == q.dtype and v_cache.dtype == q.dtype
+    assert LH % KVH == 0 and QH % LH == 0, "index lists must be per kv head or per query head"
     dev = _cuda(q, k_cache, v_cache, idx, cnt)
     q = q.contiguous()
-    kvb = _rows_view(k_cache, 128)
-    assert _rows_view(v_cache, 128) == kvb
+    kv = _kv_layout(k_cache, LH // KVH)
+    kv2 = _kv_layout(v_cache)
+    assert (kv2.batch_stride, kv2.token_stride, kv2.head_stride) == (kv.batch_stride, kv.token_stride, kv.head_stride)
     assert idx.is_contiguous() and cnt.is_contiguous() and idx.dtype == torch.int32 and cnt.dtype == torch.int32
     if out is None:
         out = torch.empty_like(q)
     lse = torch.empty((B, QH), dtype=torch.float32, device=dev) if return_lse else None
-    need = lib.sl_sparse_attn_workspace_bytes(B, KH, QH)
-    ws, _ = workspaces.get("attn", dev, need, (B, KH, QH))
-    check(lib.sl_sparse_attn_decode(q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), _dt(q), kvb,
-                                    idx.data_ptr(), idx.shape[2], cnt.data_ptr(), B, KH, QH, layout,
-                                    out.data_ptr(), _ptr(lse), ws.data_ptr(), ws.numel(), _stream()))
+    need = lib.sl_sparse_attn_workspace_bytes(B, LH, QH)
+    ws, _ = workspaces.get("attn", dev, need, (B, LH, QH))
+    check(lib.sl_sparse_attn_decode_ex(q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), _dt(q), C.byref(kv),
+                                       idx.data_ptr(), idx.shape[2], cnt.data_ptr(), B, LH, QH, layout,
+                                       out.data_ptr(), _ptr(lse), ws.data_ptr(), ws.numel(), _stream()))
     _count()
     return (out, lse) if return_lse else out
 

@@ -37,6 +37,7 @@ class SessionConfig:
     layout: int = GQA_BLOCKED
     fix_layers: tuple = ()             # layers that attend to every key
     lru_slots: int = 0                 # > 0: attend over an LRU-resident K/V buffer of this many slots per (row, kv head)
+    fused_kv: bool = True              # one cache [B,C,KH,2,128] per layer (a key's K and V rows adjacent) instead of two
 
 
 class DecodeSession:
@@ -47,8 +48,15 @@ class DecodeSession:
         B, QH, KH, L, C = cfg.batch, cfg.q_heads, cfg.kv_heads, cfg.layers, cfg.capacity
         dev, dt = self.device, cfg.dtype
         self.hash_q, self.hash_k = hash_q, hash_k
-        self.k_cache = [torch.empty((B, C, KH, 128), dtype=dt, device=dev) for _ in range(L)]
-        self.v_cache = [torch.empty((B, C, KH, 128), dtype=dt, device=dev) for _ in range(L)]
+        if cfg.fused_kv and cfg.lru_slots == 0:
+            # a gathered key is then ONE 512-byte piece of memory: k_cache / v_cache are strided views
+            self.kv_cache = [torch.empty((B, C, KH, 2, 128), dtype=dt, device=dev) for _ in range(L)]
+            self.k_cache = [kv[:, :, :, 0] for kv in self.kv_cache]
+            self.v_cache = [kv[:, :, :, 1] for kv in self.kv_cache]
+        else:
+            self.kv_cache = None
+            self.k_cache = [torch.empty((B, C, KH, 128), dtype=dt, device=dev) for _ in range(L)]
+            self.v_cache = [torch.empty((B, C, KH, 128), dtype=dt, device=dev) for _ in range(L)]
         self.codes = [torch.empty((B, C, KH, 4), dtype=torch.uint32, device=dev) for _ in range(L)]
         self.length = 0
         # one token's inputs and outputs for all layers
@@ -71,6 +79,10 @@ class DecodeSession:
             self.slots = torch.empty_like(self.idx)
         self._graphs = {}
         self._host = None
+        # device-side position: one captured step serves every token (see step_dev)
+        self.pos_dev = torch.zeros((1,), dtype=torch.int64, device=dev)
+        self.cos_tab = self.sin_tab = None
+        self.tab_pos0 = 0
 
     # ------------------------------------------------------------------ cache filling
     def load_context(self, layer: int, k: torch.Tensor, v: torch.Tensor, start: int = 0, codes: bool = True):
@@ -90,6 +102,16 @@ class DecodeSession:
         emb = torch.cat([f, f])
         self.cos.copy_(emb.cos().to(self.cfg.dtype))
         self.sin.copy_(emb.sin().to(self.cfg.dtype))
+
+    def set_position_table(self, pos0: int, count: int, theta: float):
+        """RoPE rows of positions [pos0, pos0 + count) on the device, computed as set_position computes
+        one row, for decode loops whose position lives in device memory (step_dev)."""
+        inv = 1.0 / (theta ** (torch.arange(0, 128, 2, dtype=torch.float32) / 128))
+        f = torch.arange(pos0, pos0 + count, dtype=torch.float32)[:, None] * inv[None, :]
+        emb = torch.cat([f, f], dim=-1)
+        self.cos_tab = emb.cos().to(self.cfg.dtype).to(self.device)
+        self.sin_tab = emb.sin().to(self.cfg.dtype).to(self.device)
+        self.tab_pos0 = pos0
 
     # ------------------------------------------------------------------ one token
     def layer_step(self, layer: int, pos: int, stage: Optional[str] = None):
@@ -121,9 +143,7 @@ class DecodeSession:
         for layer in range(self.cfg.layers):
             self.layer_step(layer, pos, stage)
 
-    def step_native(self, pos: int):
-        """`step(pos)` with the layer loop in the library (sl_decode_step): one call per token instead
-        of three per layer, for decode loops at advancing positions that cannot replay a graph."""
+    def _native_args(self):
         import ctypes as C
         from . import _lib
         c = self.cfg
@@ -136,7 +156,8 @@ class DecodeSession:
             a.dtype, a.gqa_layout = ops._dt(self.q_in), c.layout
             a.sink, a.recent, a.min_remain, a.mask_out = c.sink, c.recent, c.min_remain, c.mask_out
             a.code_batch_stride = self.codes[0].stride(0)
-            a.kv_batch_stride = self.k_cache[0].stride(0)
+            kv = ops._kv_layout(self.k_cache[0])
+            a.kv_batch_stride, a.kv_token_stride, a.kv_head_stride = kv.batch_stride, kv.token_stride, kv.head_stride
             keep = {"q": arr([self.q_in[l] for l in range(L)]), "k": arr([self.k_in[l] for l in range(L)]),
                     "v": arr([self.v_in[l] for l in range(L)]), "codes": arr(self.codes), "kc": arr(self.k_cache),
                     "vc": arr(self.v_cache), "out": arr([self.out[l] for l in range(L)]),
@@ -157,9 +178,66 @@ class DecodeSession:
             a.d_attn_workspace, a.attn_workspace_bytes = aw.data_ptr(), aw.numel()
             a.d_status = status.data_ptr()
             self._native = (a, keep, sw, aw, status)
-        _lib.check(_lib.lib.sl_decode_step(C.byref(self._native[0]), pos,
+        return self._native[0]
+
+    def step_native(self, pos: int):
+        """`step(pos)` with the layer loop in the library (sl_decode_step): one call per token instead
+        of three per layer."""
+        import ctypes as C
+        from . import _lib
+        _lib.check(_lib.lib.sl_decode_step(C.byref(self._native_args()), pos,
                                            torch.cuda.current_stream(self.device).cuda_stream))
-        ops.launch_count += 4 * c.layers
+        ops.launch_count += 3 * self.cfg.layers
+
+    def step_dev(self, max_context: Optional[int] = None, advance: bool = True):
+        """One token at the position held in `self.pos_dev` (device memory): the launches depend on no
+        host-side position, so a captured graph of this call serves every token of a decode loop
+        (capture_dev). Needs set_position_table to cover the positions that will be visited."""
+        import ctypes as C
+        from . import _lib
+        assert self.cos_tab is not None, "call set_position_table first"
+        d = _lib.DecodeDev()
+        d.d_pos = self.pos_dev.data_ptr()
+        d.max_context = int(max_context or self.cfg.capacity)
+        d.d_cos_table, d.d_sin_table = self.cos_tab.data_ptr(), self.sin_tab.data_ptr()
+        d.table_pos0, d.table_rows = self.tab_pos0, self.cos_tab.shape[0]
+        d.advance = int(advance)
+        _lib.check(_lib.lib.sl_decode_step_dev(C.byref(self._native_args()), C.byref(d),
+                                               torch.cuda.current_stream(self.device).cuda_stream))
+        ops.launch_count += 3 * self.cfg.layers + int(advance)
+
+    def capture_dev(self, host_io: bool = False, max_context: Optional[int] = None) -> torch.cuda.CUDAGraph:
+        """One CUDA graph for every token: step_dev (which advances the device-side position at its end),
+        optionally with the pinned-host copies of the token's inputs and outputs around it. The warm-up
+        run outside the capture executes one token: set `pos_dev` afterwards."""
+        key = ("dev", host_io, max_context)
+        if key in self._graphs:
+            return self._graphs[key]
+        if host_io:
+            self._ensure_host()
+
+        def run():
+            if host_io:
+                self.q_in.copy_(self._host["q"], non_blocking=True)
+                self.k_in.copy_(self._host["k"], non_blocking=True)
+                self.v_in.copy_(self._host["v"], non_blocking=True)
+            self.step_dev(max_context)
+            if host_io:
+                self._host["out"].copy_(self.out, non_blocking=True)
+
+        saved = self.pos_dev.clone()
+        s = torch.cuda.Stream(device=self.device)
+        s.wait_stream(torch.cuda.current_stream(self.device))
+        with torch.cuda.stream(s):
+            run()
+        torch.cuda.current_stream(self.device).wait_stream(s)
+        torch.cuda.synchronize(self.device)
+        self.pos_dev.copy_(saved)
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            run()
+        self._graphs[key] = g
+        return g
 
     # ------------------------------------------------------------------ graphs
     def capture(self, pos: int, stage: Optional[str] = None, host_io: bool = False) -> torch.cuda.CUDAGraph:

@@ -364,6 +364,50 @@ def test_sparse_attention(ops, B, N, KH, QH, keep, dtype, tol, layout):
     assert torch.equal(out, out2)                                             # deterministic, workspace self-cleans
 
 
+@pytest.mark.parametrize("B,N,KH,QH,keep", [(1, 30000, 8, 32, 3000), (2, 5000, 4, 28, 600), (9, 3000, 32, 32, 200)])
+def test_sparse_attention_cache_geometries(ops, B, N, KH, QH, keep):
+    """The same attention over two caches [B,N,KH,128], over the halves of one fused cache
+    [B,N,KH,2,128] (a key's K and V rows adjacent) and over a batch aliased with expand (every row reads
+    batch row 0, spotlight/modifiers/fake_cache.py:42-49,96-106): identical bits, and the checker's values."""
+    q, k, v, g = _attn_inputs(B, N, KH, QH, torch.bfloat16, N + B)
+    idx = np.zeros((B, KH, keep), np.int32)
+    for b in range(B):
+        for h in range(KH):
+            idx[b, h] = np.sort(torch.randperm(N, generator=g)[:keep].numpy())
+    cnt = np.full((B, KH), keep, np.int32)
+    qd, idx_d, cnt_d = q.to(DEV), torch.from_numpy(idx).to(DEV), torch.from_numpy(cnt).to(DEV)
+    kd, vd = k.to(DEV), v.to(DEV)
+    two = ops.sparse_attn_decode(qd, kd, vd, idx_d, cnt_d)
+    fused = torch.empty((B, N + 3, KH, 2, 128), dtype=torch.bfloat16, device=DEV)
+    fused[:, :N, :, 0], fused[:, :N, :, 1] = kd, vd
+    one = ops.sparse_attn_decode(qd, fused[:, :N, :, 0], fused[:, :N, :, 1], idx_d, cnt_d)
+    assert torch.equal(one, two)
+    ref = O.sparse_attention(q, k, v, idx, cnt, O.BLOCKED)
+    assert (one.float().cpu() - ref).abs().max().item() <= 2e-2
+    # aliased batch: all rows read row 0's cache
+    alias = ops.sparse_attn_decode(qd, kd[:1].expand(B, -1, -1, -1), vd[:1].expand(B, -1, -1, -1), idx_d, cnt_d)
+    ref_alias = O.sparse_attention(q, k[:1].expand(B, -1, -1, -1), v[:1].expand(B, -1, -1, -1), idx, cnt, O.BLOCKED)
+    assert (alias.float().cpu() - ref_alias).abs().max().item() <= 2e-2
+
+
+@pytest.mark.parametrize("B,N,KH,QH,keep", [(1, 6000, 2, 8, 500), (2, 3000, 4, 28, 100)])
+def test_sparse_attention_per_query_head_lists(ops, B, N, KH, QH, keep):
+    """Every query head with its own index list over the shared K/V caches (the per-query-head
+    selection of the reference's modifier, spotlight_generation.py:128-165): equals attention with
+    the caches repeated per query head as repeat_kv does."""
+    q, k, v, g = _attn_inputs(B, N, KH, QH, torch.bfloat16, N + QH)
+    G = QH // KH
+    idx = np.zeros((B, QH, keep), np.int32)
+    for b in range(B):
+        for h in range(QH):
+            idx[b, h] = np.sort(torch.randperm(N, generator=g)[:keep].numpy())
+    cnt = np.full((B, QH), keep, np.int32)
+    out = ops.sparse_attn_decode(q.to(DEV), k.to(DEV), v.to(DEV), torch.from_numpy(idx).to(DEV), torch.from_numpy(cnt).to(DEV))
+    k_rep, v_rep = k.repeat_interleave(G, dim=2), v.repeat_interleave(G, dim=2)      # [B,N,QH,128], head j <- kv head j // G
+    ref = O.sparse_attention(q, k_rep, v_rep, idx, cnt, O.BLOCKED)
+    assert (out.float().cpu() - ref).abs().max().item() <= 2e-2
+
+
 def test_merge_lse_equals_unsplit(ops):
     """Attention over 4 sequence shards merged by log-sum-exp equals attention over the whole list."""
     B, N, KH, QH, R = 2, 8000, 4, 20, 4

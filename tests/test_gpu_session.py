@@ -72,3 +72,55 @@ def test_layer_step_equals_the_single_ops():
     assert torch.equal(out, s.out[0])
     assert np.array_equal(cnt.cpu().numpy(), s.cnt.cpu().numpy())
     ops.check_status()
+
+
+def test_one_graph_serves_every_token():
+    """The position lives in device memory: ONE captured step (sl_decode_step_dev) replayed for
+    consecutive tokens must produce what the per-position launches produce -- outputs, appended codes
+    and K/V rows, attended counts -- bit for bit."""
+    from spotlight_b200 import ops
+    a, ga, n = _session(seed=9, extra=12)
+    b, gb, _ = _session(seed=9, extra=12)
+    b.set_position_table(n, 12, 500000.0)
+    b.pos_dev.fill_(n)
+    graph = b.capture_dev()
+    b.pos_dev.fill_(n)
+    for step in range(6):
+        pos = n + step
+        _token(a, ga)
+        _token(b, gb)
+        a.set_position(pos, 500000.0)
+        a.step(pos)
+        graph.replay()
+        torch.cuda.synchronize()
+        assert int(b.pos_dev.item()) == pos + 1
+        assert torch.equal(a.out, b.out), f"token {step}"
+        assert torch.equal(a.cnt, b.cnt)
+        for layer in range(a.cfg.layers):
+            assert torch.equal(a.codes[layer][:, : pos + 1], b.codes[layer][:, : pos + 1])
+            assert torch.equal(a.k_cache[layer][:, pos], b.k_cache[layer][:, pos])
+            assert torch.equal(a.v_cache[layer][:, pos], b.v_cache[layer][:, pos])
+    ops.check_status()
+
+
+def test_fused_and_separate_caches_agree():
+    from spotlight_b200 import ops
+    import dataclasses
+    a, ga, n = _session(seed=11)
+    b, gb, _ = _session(seed=11)
+    assert a.kv_cache is not None                       # the default: one fused cache per layer
+    from spotlight_b200.session import DecodeSession
+    c = DecodeSession(dataclasses.replace(b.cfg, fused_kv=False), b.hash_q, b.hash_k, DEV)
+    for layer in range(b.cfg.layers):
+        c.load_context(layer, b.k_cache[layer][:, :n].contiguous(), b.v_cache[layer][:, :n].contiguous())
+    for step in range(2):
+        pos = n + step
+        _token(a, ga)
+        c.q_in.copy_(a.q_in); c.k_in.copy_(a.k_in); c.v_in.copy_(a.v_in)
+        a.set_position(pos, 500000.0)
+        c.set_position(pos, 500000.0)
+        a.step(pos)
+        c.step_native(pos)
+        torch.cuda.synchronize()
+        assert torch.equal(a.out, c.out)
+    ops.check_status()
