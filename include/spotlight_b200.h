@@ -11,7 +11,9 @@
  *  - Layouts follow the reference's caches (spotlight/modifiers/gpu_cache.py:28-36): token-major
  *    with heads interleaved. Keys/values: [B, N, KH, 128]; codes: [B, N, KH, 4] uint32
  *    (one 128-bit code = 16 contiguous bytes). A batch row may be a slice of a longer
- *    pre-allocated cache, hence the explicit batch strides.
+ *    pre-allocated cache, hence the explicit batch strides; a batch stride of 0 on a READ-ONLY
+ *    input (codes of sl_hamming_scores / sl_scan_topk, caches of sl_sparse_attn_decode_ex) makes
+ *    every batch row read the same data (the reference's spotlight/modifiers/fake_cache.py).
  *  - gqa_layout says which query heads share kv head h (G = QH / KH):
  *      SL_GQA_INTERLEAVED: q heads { g*KH + h }   (the reference kernels,
  *                          spotlight/kernel/attn_k4_q28.cu:75, attn_dx_u32.py:110-113)

@@ -148,6 +148,47 @@ def select(scores: np.ndarray, k: int, sink: int = 4, recent: int = 64):
     return idx, cnt
 
 
+def exact_logits(q_rot: torch.Tensor, k_rot: torch.Tensor, per_query_head: bool) -> np.ndarray:
+    """The oracle-selection baseline's scores (spotlight/modifiers/upperbound_generation.py:12-15:
+    ``query @ key.transpose(-1,-2)`` on rotated q and k, keys repeated to the query heads): fp64 logits
+    [B,QH,N] for q_rot [B,QH,D], k_rot [B,N,KH,D]; with per_query_head False the logits of the query
+    heads of a group are added up, [B,KH,N] (the per-kv-head counterpart used by this library)."""
+    B, QH, D = q_rot.shape
+    KH = k_rot.shape[2]
+    G = QH // KH
+    qg = q_rot.to(torch.float64).view(B, KH, G, D)
+    lg = torch.einsum("bhgd,bnhd->bhgn", qg, k_rot.to(torch.float64))
+    lg = lg.reshape(B, QH, -1) if per_query_head else lg.sum(dim=2)
+    return lg.numpy()
+
+
+def select_by_logits(logits: np.ndarray, k: int, sink: int = 4, recent: int = 64):
+    """Exact top-k of real-valued scores [B,H,N] (ties, should there be any, to the lowest index) plus the
+    sink / recent ranges -> (idx int32 [B,H,cap] padded with -1, cnt int32 [B,H]); the selection of
+    spotlight/modifiers/upperbound_generation.py:140-150 with the window of
+    spotlight_evaluation.py:341-346."""
+    B, H, N = logits.shape
+    cap = min(N, k + sink + recent)
+    idx = np.full((B, H, cap), -1, dtype=np.int32)
+    cnt = np.zeros((B, H), dtype=np.int32)
+    s_end, r_start = forced_ranges(N, sink, recent)
+    forced = np.concatenate([np.arange(0, s_end), np.arange(r_start, N)]).astype(np.int32)
+    for b in range(B):
+        for h in range(H):
+            top = np.sort(np.argsort(-logits[b, h], kind="stable")[: min(k, N)])
+            s = np.union1d(top, forced).astype(np.int32)
+            idx[b, h, : len(s)] = s
+            cnt[b, h] = len(s)
+    return idx, cnt
+
+
+def iou(a: np.ndarray, b: np.ndarray) -> float:
+    """Intersection over union of two index sets (the per-head figure of the reference's bench_mark
+    mode, spotlight/modifiers/spotlight_evaluation.py:303-316)."""
+    a, b = set(np.asarray(a).tolist()), set(np.asarray(b).tolist())
+    return len(a & b) / max(1, len(a | b))
+
+
 def histogram(scores: np.ndarray, nbins: int) -> np.ndarray:
     """Per-(b,h) histogram of match counts, int64 [B,KH,nbins]."""
     B, N, KH = scores.shape

@@ -152,7 +152,7 @@ extern "C" int sl_hamming_scores(const uint32_t* d_q, const uint32_t* d_k, int64
     SL_REQUIRE(W == 1 || W == 2 || W == 4 || W == 8, SL_ESHAPE, "sl_hamming_scores: W=%d not in {1,2,4,8}", W);
     SL_REQUIRE(gqa_layout == SL_GQA_INTERLEAVED || gqa_layout == SL_GQA_BLOCKED, SL_EINVAL,
                "sl_hamming_scores: unknown gqa_layout %d", gqa_layout);
-    SL_REQUIRE(k_batch_stride >= N * KH * W, SL_ESHAPE, "sl_hamming_scores: batch stride shorter than a batch row");
+    SL_REQUIRE(k_batch_stride == 0 || k_batch_stride >= N * KH * W, SL_ESHAPE, "sl_hamming_scores: batch stride shorter than a batch row");
     SL_REQUIRE((int64_t)QH * W * 4 <= 48 * 1024, SL_ESHAPE, "sl_hamming_scores: QH*W too large");
     SL_REQUIRE(B <= 65535, SL_ESHAPE, "sl_hamming_scores: B > 65535");
     if (W == 4) SL_REQUIRE(sl::aligned16(d_k) && (k_batch_stride % 4 == 0), SL_EALIGN, "sl_hamming_scores: codes not 16-byte aligned");

@@ -745,7 +745,7 @@ int sl::scan_topk_impl(const uint32_t* d_q_codes, const uint32_t* d_k_codes, int
     SL_REQUIRE(k >= 0 && sink >= 0 && recent >= 0, SL_EINVAL, "sl_scan_topk: negative k/sink/recent");
     SL_REQUIRE(sl::aligned16(d_q_codes) && sl::aligned16(d_k_codes) && k_batch_stride % 4 == 0, SL_EALIGN,
                "sl_scan_topk: codes must be 16-byte aligned");
-    SL_REQUIRE(k_batch_stride >= N * KH * 4, SL_ESHAPE, "sl_scan_topk: batch stride shorter than a batch row");
+    SL_REQUIRE(k_batch_stride == 0 || k_batch_stride >= N * KH * 4, SL_ESHAPE, "sl_scan_topk: batch stride shorter than a batch row");
     const int64_t need = std::min<int64_t>(N, (int64_t)k + sink + recent);
     SL_REQUIRE(idx_capacity >= need, SL_ESHAPE, "sl_scan_topk: idx_capacity %d < min(N, k+sink+recent) = %lld",
                idx_capacity, (long long)need);

@@ -51,13 +51,16 @@ class KVHash(_LayerBuffers):
         return self._append(layer_idx, key_cache=key)[0]
 
 
-def topk_and_gather(attn, keys, vals, budget):
+def topk_and_gather(attn, keys, vals, budget, max_score=None):
     """int16 scores [B,N,KH] + caches [B,>=N,KH,128] -> two [B,budget,KH,128] tensors
-    (gpu_cache.py:48-54)."""
+    (gpu_cache.py:48-54). `max_score` = 128 * (query heads per kv head) bounds the scores; given, the
+    call enqueues its kernels and returns without a host read. Left out (the reference's signature has
+    no such argument), it costs one device-to-host read of the largest score."""
     n = attn.shape[1]
     budget = min(int(budget), n)
-    top = int(attn.max().item()) if n else 0
-    idx, _ = ops.topk_from_scores(attn, budget, top, sink=0, recent=0)
+    if max_score is None:
+        max_score = int(attn.max().item()) if n else 0
+    idx, _ = ops.topk_from_scores(attn, budget, int(max_score), sink=0, recent=0)
     return ops.gather_rows(keys[:, :n], idx, budget), ops.gather_rows(vals[:, :n], idx, budget)
 
 
@@ -69,5 +72,7 @@ class KVCache(_LayerBuffers):
         k, v = self._append(layer_idx, key_cache=key, val_cache=val)
         return k, v
 
+    max_score = None     # set to 128 * (query heads per kv head) to keep gather() free of host reads
+
     def gather(self, layer_idx, attn, budget):
-        return topk_and_gather(attn, self.key_cache[layer_idx], self.val_cache[layer_idx], budget)
+        return topk_and_gather(attn, self.key_cache[layer_idx], self.val_cache[layer_idx], budget, self.max_score)

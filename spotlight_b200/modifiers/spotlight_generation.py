@@ -13,12 +13,19 @@ Per decode token the hook runs three launches of the CUDA library:
 The q/k/v/o projections stay torch ``nn.Linear`` calls: they are not part of the retrieval path.
 
 Semantics fixed where the reference is silent (all explicit, none hidden):
-  * keys are hashed per KV head and scores are summed over the query heads of a group, as in
-    the reference's kernels (spotlight/kernel/attn_k4_q28.cu:72-92); with QH == KH this is the
-    modifier's per-head computation (spotlight_generation.py:13-23) exactly;
+  * ``draft_kwargs['gqa_mode']`` chooses between the reference's two GQA semantics:
+      "kv_head" (default)  keys are hashed per KV head (with the hash parameters of the group's first
+                   query head, or of ``hash_fn_k`` when the layer has one), scores are summed over the
+                   query heads of a group and one top-k is taken per KV head, as in the reference's
+                   kernels (spotlight/kernel/attn_k4_q28.cu:72-92, spotlight/modifiers/gpu_cache.py:48-54);
+      "query_head" every query head hashes the (shared) keys with its OWN parameters and takes its own
+                   top-k, as in the reference's modifier (spotlight_generation.py:128-165); the code
+                   cache holds one code per query head (G times the bytes to scan), K/V stay per KV head.
+    With QH == KH the two are the same computation;
   * query head j belongs to kv head j // G (HF ``repeat_kv``, spotlight_generation.py:128-129);
   * the sink (4) and recent (64) windows of spotlight/modifiers/spotlight_evaluation.py:341-346
-    are applied at decode; ``draft_kwargs['sink'] / ['recent']`` override them;
+    are applied at decode; ``draft_kwargs['sink'] / ['recent']`` override them (0 / 0 is the reference's
+    generation modifier, which has no window);
   * keys are cached AFTER RoPE (their position never changes), q is rotated at its position;
     the reference re-rotates the whole cache every step (modify_llama.py:98-108) with the same
     result; positions beyond the reference's 8192-row table (spotlight_generation.py:139) work;
@@ -88,25 +95,36 @@ class LinearHashingFunction(torch.nn.Module):
 # ------------------------------------------------------------------------------- per-layer state
 class LayerState:
     """What the hook keeps per layer between steps (the reference keeps two concatenated
-    tensors, spotlight_generation.py:131-136)."""
+    tensors, spotlight_generation.py:131-136): one fused K|V cache [B, cap, KH, 2, 128] (a key's K and
+    V rows adjacent), keys stored AFTER RoPE, and the code cache [B, cap, LH, 4] with LH = KH
+    ("kv_head" mode) or QH ("query_head" mode)."""
 
-    def __init__(self, batch, kv_heads, capacity, dtype, device):
-        self.k = torch.empty((batch, capacity, kv_heads, 128), dtype=dtype, device=device)
-        self.v = torch.empty((batch, capacity, kv_heads, 128), dtype=dtype, device=device)
-        self.codes = torch.empty((batch, capacity, kv_heads, 4), dtype=torch.uint32, device=device)
+    def __init__(self, batch, kv_heads, capacity, dtype, device, list_heads=None):
+        self.kv = torch.empty((batch, capacity, kv_heads, 2, 128), dtype=dtype, device=device)
+        self.codes = torch.empty((batch, capacity, list_heads or kv_heads, 4), dtype=torch.uint32, device=device)
         self.length = 0
         self.last_idx = None
         self.last_cnt = None
 
     @property
+    def k(self):
+        return self.kv[:, :, :, 0]
+
+    @property
+    def v(self):
+        return self.kv[:, :, :, 1]
+
+    @property
     def capacity(self):
-        return self.k.shape[1]
+        return self.kv.shape[1]
 
     def reserve(self, n):
+        """Grow (doubling) when a caller outruns the capacity it announced with
+        ``draft_kwargs['max_seq_len']``; a correctly sized state never takes this path."""
         if n <= self.capacity:
             return
         cap = max(n, 2 * self.capacity)
-        for name in ("k", "v", "codes"):
+        for name in ("kv", "codes"):
             old = getattr(self, name)
             new = torch.empty((old.shape[0], cap, *old.shape[2:]), dtype=old.dtype, device=old.device)
             new[:, : self.length] = old[:, : self.length]
@@ -127,12 +145,35 @@ def _rope_rows(positions: torch.Tensor, theta: float, dtype: torch.dtype):
     return emb.cos().to(dtype), emb.sin().to(dtype)
 
 
+_ROPE_TABLES = {}
+
+
+def _rope_table(n: int, theta: float, dtype: torch.dtype, device):
+    """cos / sin rows of positions [0, n) on `device`, computed once and grown by doubling: the decode
+    hook reads row `pos` as a view, so a token costs no host-to-device copy and no table kernels."""
+    key = (torch.device(device), dtype, float(theta))
+    cur = _ROPE_TABLES.get(key)
+    if cur is None or cur[0].shape[0] < n:
+        rows = max(n, 4096, 0 if cur is None else 2 * cur[0].shape[0])
+        cur = _rope_rows(torch.arange(rows, device=device), theta, dtype)
+        _ROPE_TABLES[key] = cur
+    return cur
+
+
 def _rotate(x, cos, sin):
     half = x.shape[-1] // 2
     return x * cos + torch.cat([-x[..., half:], x[..., :half]], dim=-1) * sin
 
 
 # ------------------------------------------------------------------------------- the hook
+def _select(self, q_rot, q_codes, st, n, lh):
+    """Index source of the pruned layers: Hamming scan + exact top-k + window over the code cache.
+    Returns (idx int32 [B,LH,cap] ascending, cnt int32 [B,LH])."""
+    kw = self.draft_kwargs
+    keep = budget(n, kw["mask_out"], kw.get("min_remain", 20))
+    return ops.scan_topk(q_codes, st.codes[:, :n], keep, int(kw.get("sink", 4)), int(kw.get("recent", 64)), GQA_BLOCKED)
+
+
 def self_attn_forward(self, hidden_states: torch.Tensor, kv_cache: Optional[LayerState] = None):
     cfg = self.config
     num_heads, num_kv_heads = cfg.num_attention_heads, cfg.num_key_value_heads
@@ -140,7 +181,11 @@ def self_attn_forward(self, hidden_states: torch.Tensor, kv_cache: Optional[Laye
     assert head_dim == 128, "the retrieval kernels are built for head_dim 128"
     B, T, _ = hidden_states.shape
     kw = self.draft_kwargs
-    is_prefill = T > 1 and kv_cache is None
+    G = num_heads // num_kv_heads
+    per_q = kw.get("gqa_mode", "kv_head") == "query_head" and G > 1
+    pruned = bool(kw.get("enable", True)) and not self.is_fix_layer
+    hashed = pruned and getattr(self, "index_source", "hash") == "hash"
+    lh = num_heads if (per_q and hashed) else num_kv_heads     # heads of the code cache: per kv head or per query head
 
     q = self.q_proj(hidden_states).view(B, T, num_heads, head_dim)
     k = self.k_proj(hidden_states).view(B, T, num_kv_heads, head_dim)
@@ -149,21 +194,24 @@ def self_attn_forward(self, hidden_states: torch.Tensor, kv_cache: Optional[Laye
 
     if kv_cache is None:
         cap = int(kw.get("max_seq_len", 0)) or (T + 4096)
-        kv_cache = LayerState(B, num_kv_heads, max(cap, T), q.dtype, q.device)
+        kv_cache = LayerState(B, num_kv_heads, max(cap, T), q.dtype, q.device, lh)
     st = kv_cache
 
     if T > 1:
         # prefill (or a multi-token append): dense causal attention, as the reference does
         # (spotlight_generation.py:145-147, 217-224); then build the code cache of the new keys.
         st.reserve(st.length + T)
-        pos = torch.arange(st.length, st.length + T, device=q.device)
-        cos, sin = _rope_rows(pos, theta, q.dtype)
-        qr = _rotate(q, cos[None, :, None, :], sin[None, :, None, :])
-        kr = _rotate(k, cos[None, :, None, :], sin[None, :, None, :])
         lo, hi = st.length, st.length + T
-        st.k[:, lo:hi] = kr
+        cos, sin = _rope_table(hi, theta, q.dtype, q.device)
+        cos, sin = cos[lo:hi], sin[lo:hi]
+        qr = _rotate(q, cos[None, :, None, :], sin[None, :, None, :])
+        st.k[:, lo:hi] = _rotate(k, cos[None, :, None, :], sin[None, :, None, :])
         st.v[:, lo:hi] = v
-        ops.hash_encode(st.k[:, lo:hi], self._hash_k_params(), out=st.codes[:, lo:hi])
+        if hashed:
+            if per_q:   # every query head's own code of the shared key (repeat_kv, then hash_fn, spotlight_generation.py:128,17)
+                ops.hash_encode(st.k[:, lo:hi].repeat_interleave(G, dim=2), self._hash_q_params(), out=st.codes[:, lo:hi])
+            else:
+                ops.hash_encode(st.k[:, lo:hi], self._hash_k_params(), out=st.codes[:, lo:hi])
         st.length = hi
         kk = st.k[:, :hi].permute(0, 2, 1, 3)
         vv = st.v[:, :hi].permute(0, 2, 1, 3)
@@ -176,21 +224,49 @@ def self_attn_forward(self, hidden_states: torch.Tensor, kv_cache: Optional[Laye
     # ---- one decode token
     st.reserve(st.length + 1)
     pos = st.length
-    cos, sin = _rope_rows(torch.tensor([pos], device=q.device), theta, q.dtype)
-    q_rot, q_codes = ops.decode_prepare(
-        q[:, 0], k[:, 0], v[:, 0], self._hash_q_params(), self._hash_k_params(), pos,
-        code_cache=st.codes, k_cache=st.k, v_cache=st.v, cos=cos[0].contiguous(), sin=sin[0].contiguous())
+    cos, sin = _rope_table(pos + 1, theta, q.dtype, q.device)
+    cos, sin = cos[pos], sin[pos]
+    if hashed and per_q:
+        # codes of the new key under every query head's parameters; its K/V rows are appended per KV head
+        q_rot, q_codes = ops.decode_prepare(q[:, 0], k[:, 0].repeat_interleave(G, dim=1), None, self._hash_q_params(),
+                                            self._hash_q_params(), pos, code_cache=st.codes, cos=cos, sin=sin)
+        st.k[:, pos] = _rotate(k[:, 0], cos, sin)
+        st.v[:, pos] = v[:, 0]
+    else:
+        q_rot, q_codes = ops.decode_prepare(
+            q[:, 0], k[:, 0], v[:, 0], self._hash_q_params() if hashed else _IDENTITY_HASH.get(num_heads, q),
+            self._hash_k_params() if hashed else _IDENTITY_HASH.get(num_kv_heads, q), pos,
+            code_cache=st.codes, k_cache=st.k, v_cache=st.v, cos=cos, sin=sin)
     st.length = n = pos + 1
-    if kw.get("enable", True) and not self.is_fix_layer:
-        keep = budget(n, kw["mask_out"], kw.get("min_remain", 20))
-        idx, cnt = ops.scan_topk(q_codes, st.codes[:, :n], keep, int(kw.get("sink", 4)), int(kw.get("recent", 64)),
-                                 GQA_BLOCKED)
+    if hashed:
+        idx, cnt = _select(self, q_rot, q_codes, st, n, lh)
+    elif pruned:
+        idx, cnt = self.select_indices(q_rot, st, n)          # another index source (e.g. the exact top-k)
     else:
         idx = torch.arange(n, dtype=torch.int32, device=q.device).expand(B, num_kv_heads, n).contiguous()
         cnt = torch.full((B, num_kv_heads), n, dtype=torch.int32, device=q.device)
     st.last_idx, st.last_cnt = idx, cnt
     o = ops.sparse_attn_decode(q_rot, st.k[:, :n], st.v[:, :n], idx, cnt, GQA_BLOCKED)
     return self.o_proj(o.view(B, 1, num_heads * head_dim)), st
+
+
+class _IdentityHash:
+    """Layers that do not hash (dense layers, other index sources) still go through decode_prepare for
+    RoPE and the cache appends; it needs SOME hash parameters, so they get a 128x128 linear one per
+    (heads, dtype, device), built once. The codes it produces are never read."""
+
+    def __init__(self):
+        self._cache = {}
+
+    def get(self, heads, like):
+        key = (heads, like.dtype, like.device)
+        if key not in self._cache:
+            w = torch.zeros((heads, 128, 128), dtype=like.dtype, device=like.device)
+            self._cache[key] = ops.HashParams([w], [None], False)
+        return self._cache[key]
+
+
+_IDENTITY_HASH = _IdentityHash()
 
 
 def _hash_q_params(self):
@@ -254,6 +330,7 @@ class Decoder(torch.nn.Module):
         super().__init__()
         self.decoder = decoder
         self.draft_kwargs = draft_kwargs
+        self.hash_kind = hash_kind
         fix_layers = draft_kwargs.get("fix_layers", [])
         num_mlp_layers = draft_kwargs.get("num_mlp_layers", 2)
         mlp_dims = draft_kwargs.get("mlp_dims", "[128,128,128]")
@@ -274,10 +351,15 @@ class Decoder(torch.nn.Module):
             attn.forward = types.MethodType(self_attn_forward, attn)
             attn._hash_q_params = types.MethodType(_hash_q_params, attn)
             attn._hash_k_params = types.MethodType(_hash_k_params, attn)
+            attn._hq = attn._hk = None
             if hash_kind == "linear":
-                attn.hash_fn = LinearHashingFunction(info, heads)
-            else:
+                # as the reference, which gives only the pruned layers a hash (linearhashing_generation.py:330-331)
+                if not attn.is_fix_layer:
+                    attn.hash_fn = LinearHashingFunction(info, heads)
+            elif hash_kind == "mlp":
                 attn.hash_fn = MLPHashingFunction(info, heads, num_mlp_layers, mlp_dims, mlp_residue)
+            else:
+                attn.index_source = hash_kind            # no hash at all: the layer brings its own select_indices
 
     @property
     def layers(self):
@@ -291,10 +373,21 @@ class Decoder(torch.nn.Module):
         for layer in self.layers:
             layer.self_attn._hq = layer.self_attn._hk = None
 
+    def layer_ft_params(self, layer):
+        """spotlight_generation.py:357-360."""
+        attn = self.layers[layer].self_attn
+        if attn.is_fix_layer or not hasattr(attn, "hash_fn"):
+            return []
+        return list(attn.hash_fn.parameters())
+
     def ft_params(self, layer=None):
+        """The reference's order: layer by layer, per layer ``proj, bias`` of every MLP layer
+        (spotlight_generation.py:363-369); every layer for the MLP hash, the pruned layers only for the
+        linear hash (linearhashing_generation.py:375-382)."""
         params = []
         for l in self.layers:
-            params += l.self_attn.hash_fn.parameters()
+            if hasattr(l.self_attn, "hash_fn"):
+                params += l.self_attn.hash_fn.parameters()
         return list(params)
 
     def forward(self, input_ids, labels=None, kv_cache=None):
@@ -338,26 +431,39 @@ class Spotlight(torch.nn.Module):
 
     @torch.no_grad()
     def generate(self, input_ids, max_new_tokens=128, eos_token_id=(2,)):
-        """Greedy decoding; the new tokens stay on the device until the end (the reference
-        synchronises with ``.item()`` per token, spotlight_generation.py:485-487), so an EOS is
-        honoured by truncation afterwards."""
+        """Greedy decoding (spotlight_generation.py:470-495). The new tokens stay on the device until the
+        end -- the reference synchronises with ``.item()`` per token (:485-487) -- so an EOS is honoured
+        by truncation afterwards; the caches are sized once for prompt + new tokens; the forward pass
+        after the last token, whose logits nobody reads, is not run. One host read of the kernels'
+        status words at the end turns a device-side wait that ran out into an exception."""
         if input_ids.ndim == 3:
             input_ids = input_ids.flatten(0, 1)
         device = next(iter(self.model.parameters())).device
         input_ids = input_ids.to(device)
-        out = self.model(input_ids=input_ids)
-        kv_cache = out.past_key_values
-        tok = out.logits[:, -1:].argmax(dim=-1)
-        new = []
-        for _ in range(max_new_tokens):
-            new.append(tok)
-            out = self.model(input_ids=tok, kv_cache=kv_cache)
+        kw = self.model.draft_kwargs
+        hint, had = kw.get("max_seq_len"), "max_seq_len" in kw
+        if not hint:
+            kw["max_seq_len"] = input_ids.shape[1] + max_new_tokens + 1
+        try:
+            out = self.model(input_ids=input_ids)
             kv_cache = out.past_key_values
-            tok = out.logits.argmax(dim=-1).view(-1, 1)
-        new = torch.cat(new, dim=-1)
+            tok = out.logits[:, -1:].argmax(dim=-1)
+            new = [tok]
+            for _ in range(max_new_tokens - 1):
+                out = self.model(input_ids=tok, kv_cache=kv_cache)
+                kv_cache = out.past_key_values
+                tok = out.logits.argmax(dim=-1).view(-1, 1)
+                new.append(tok)
+        finally:
+            if had:
+                kw["max_seq_len"] = hint
+            else:
+                kw.pop("max_seq_len", None)
+        new = torch.cat(new[:max_new_tokens], dim=-1) if max_new_tokens > 0 else input_ids[:, :0]
         if new.shape[0] == 1 and eos_token_id:
             hit = torch.isin(new[0], torch.tensor(list(eos_token_id), device=device)).nonzero()
             if hit.numel():
                 new = new[:, : int(hit[0])]
+        ops.check_status(device)
         self.model.reset()
         return torch.cat([input_ids, new.to(input_ids.dtype)], dim=-1)

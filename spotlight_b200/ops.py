@@ -466,12 +466,18 @@ def merge_lse(o_parts: torch.Tensor, lse_parts: torch.Tensor, dtype: torch.dtype
     return out
 
 
-def gather_rows(cache: torch.Tensor, idx: torch.Tensor, budget: int) -> torch.Tensor:
+def gather_rows(cache: torch.Tensor, idx: torch.Tensor, budget: int, device=None) -> torch.Tensor:
     """cache [B,N,KH,128], idx int32 [B,KH,cap] -> [B,budget,KH,128] with
-    out[b,j,h] = cache[b, idx[b,h,j], h]."""
+    out[b,j,h] = cache[b, idx[b,h,j], h]. The cache may be PINNED host memory (the kernel then pulls
+    the selected rows across PCIe); the result is on the device of idx."""
     B, N, KH, D = cache.shape
     assert D == 128
-    dev = _cuda(cache, idx)
+    if cache.is_cuda:
+        dev = _cuda(cache, idx)
+    else:
+        if not cache.is_pinned():
+            raise RuntimeError("a host-resident cache must be pinned memory so that the GPU can address it")
+        dev = _cuda(idx)
     cb = _rows_view(cache, 128)
     out = torch.empty((B, budget, KH, D), dtype=cache.dtype, device=dev)
     check(lib.sl_gather_rows(cache.data_ptr(), cb, cache.element_size(), idx.data_ptr(), idx.shape[2], B, KH, budget,

@@ -21,3 +21,24 @@ def pytest_collection_modifyitems(config, items):
     for item in items:
         if "gpu" in item.keywords:
             item.add_marker(skip)
+
+
+# Parity figures measured by the GPU tests against the reference's fixtures (code bits that differ,
+# scores that differ, overlap of the attended sets): collected here and printed after the run, so that
+# the numbers behind the asserted bounds are in the log.
+PARITY_REPORT = []
+
+
+@pytest.fixture
+def parity_report():
+    def add(name, **figures):
+        PARITY_REPORT.append((name, figures))
+    return add
+
+
+def pytest_terminal_summary(terminalreporter):
+    if not PARITY_REPORT:
+        return
+    terminalreporter.section("parity against the reference's fixtures (measured)")
+    for name, figures in PARITY_REPORT:
+        terminalreporter.write_line(name + ": " + ", ".join(f"{k}={v}" for k, v in figures.items()))

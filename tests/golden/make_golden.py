@@ -2,7 +2,7 @@
 
 Run in a container that has the reference checkout (the fixtures, not the checkout, are what the tests read):
 
-    python tests/golden/make_golden.py /path/to/reference
+    python tests/golden/make_golden.py /path/to/reference [case ...]
 
 The reference is imported unmodified; three import shims are needed with the installed
 library versions: stub modules ``peft`` and ``profiler`` (imported but unused by
@@ -53,14 +53,23 @@ def digest(t: torch.Tensor) -> str:
     return hashlib.sha256(t.detach().contiguous().view(torch.uint8).numpy().tobytes()).hexdigest()
 
 
-def main(root):
+def main(root, only=()):
     sg, lg, mll = import_reference(root)
     from spotlight_b200.workloads import budget, rope_tables
 
     from cases import CASES, build_case
     for name in CASES:
+        if only and name not in only:
+            continue
         c = build_case(name)
-        q, k, v, dtype, H, N = c["q"], c["k"], c["v"], c["dtype"], c["heads"], c["n"]
+        q, dtype, H, N = c["q"], c["dtype"], c["heads"], c["n"]
+        G = H // c["kv_heads"]
+        if G > 1:      # keys / values per kv head, repeated to the query heads by the reference's own import
+            from transformers.models.llama.modeling_llama import repeat_kv
+            k, v = repeat_kv(c["k_kv"], G), repeat_kv(c["v_kv"], G)
+            assert torch.equal(k, c["k"]) and torch.equal(v, c["v"])
+        else:
+            k, v = c["k"], c["v"]
         mask_out, residue, theta, kind = c["mask_out"], c["residue"], c["theta"], c["params"]["kind"]
         seed = CASES[name][0]
         info = {"device": "cpu", "dtype": dtype}
@@ -112,6 +121,6 @@ def main(root):
 
 
 if __name__ == "__main__":
-    if len(sys.argv) != 2:
-        sys.exit("usage: make_golden.py <reference checkout>")
-    main(sys.argv[1])
+    if len(sys.argv) < 2:
+        sys.exit("usage: make_golden.py <reference checkout> [case ...]")
+    main(sys.argv[1], tuple(sys.argv[2:]))
