@@ -36,11 +36,18 @@ from spotlight_b200.workloads import CONFIGS, HEAD_DIM, budget, make_hash_params
 
 METRIC = "decode_attn_us_per_layer_128k_llama3_8b_shape"
 UNIT = "us/layer"
-# DRAM bytes per launch (dram bytes read + written) from the ncu captures summarised under profiles/
-# (scan_fused_headline.md, sparse_attn_headline.md, decode_prepare_headline.md; same per-launch size as
-# the benchmark's launches, captured at 90 % pruning). decode_prepare's figure includes the 16.8 MB of
-# the code cache it prefetches into L2 for the scan that follows.
-NCU_TRAFFIC = {"scan_topk": 16.85e6, "sparse_attn": 54.76e6, "decode_prepare": 22.08e6}
+def measured_traffic(cfg, kernel):
+    """DRAM bytes per launch (read + written) of `kernel` as one ncu capture measured them, from the small
+    tracked table beside the capture summaries; None when no capture covers this workload."""
+    path = os.path.join(ROOT, "profiles", "dram_traffic.json")
+    try:
+        with open(path) as f:
+            table = json.load(f)
+    except (OSError, ValueError):
+        return None
+    key = f"{cfg.name}:B{cfg.batch}:N{cfg.context}:{cfg.q_heads}/{cfg.kv_heads}:mask_out={cfg.mask_out}"
+    entry = table.get(key, {}).get(kernel)
+    return None if entry is None else float(entry["dram_bytes_per_launch"])
 
 
 def peaks():
@@ -160,13 +167,16 @@ def run_reference(args, cfg):
     sample = (f"one layer-step of the reference modifier path (RoPE all keys, hash all keys, sign matmul, topk, "
               f"mask, dense SDPA) at N={cfg.context}, fp32, {heads} of {cfg.q_heads} q heads per step, "
               f"scaled x{cfg.q_heads / heads:g}")
+    # One timed step = one call of the restated operator sequence on `heads` query heads (the sample);
+    # `value` scales it to all query heads of one layer; a whole token (all layers) is extrapolated apart.
     line = {
         "impl": "reference", "metric": METRIC, "value": us, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
-        "warmup": args.warmup, "ms_per_step": us * cfg.layers / 1e3, "higher_is_better": False, "scaling": "weak",
+        "warmup": args.warmup, "ms_per_step": sec * 1e3, "higher_is_better": False, "scaling": "weak",
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": workload_config(cfg),
         "cpu_baseline": {"value": us, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample},
         "e2e": {"value": us, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "extrapolated_ms_per_token_all_layers": us * cfg.layers / 1e3,
         "gpu_launches": 0,
     }
     print(json.dumps(line), flush=True)
@@ -319,28 +329,44 @@ def run_ours(args, cfg):
         wall_e2e = (time.perf_counter() - t0) * 1e3 / args.steps
     ops.check_status(device)
     clk = clocks.summary()
+    hash_weight_bytes = sum(w.numel() * w.element_size() for w in s.hash_q[0].weights + s.hash_k[0].weights)
+    host_bytes = s.host_bytes_per_step
+    lru_slots = s.cfg.lru_slots
 
     if dist is not None:
         t = torch.tensor([ms_step, ms_e2e, wall_e2e], device=device, dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms_step, ms_e2e, wall_e2e = t.tolist()
+    extras = {}
+    if dist is not None and cfg.name == "headline" and not args.no_extras:
+        checksum = float(out_host.float().abs().sum())
+        g_all = g = None
+        del s
+        torch.cuda.empty_cache()
+        try:
+            extras = multi_rank_extras(args, device, dist, world, rank)
+        except Exception as e:
+            extras = {"multi_rank_extras_error": str(e)[:300]}
+        s = None
     if rank != 0:
         if dist is not None:
-            dist.destroy_process_group()
+            torch.cuda.synchronize(device)
+            dist.barrier()
+            os._exit(0)
         return
 
     us_layer = ms_step * 1e3 / L
     peak, peak_kind = peaks()
     by_scan = cfg.batch * n * cfg.kv_heads * 16 + cfg.batch * cfg.q_heads * 16
     by_attn = mean_nsel * HEAD_DIM * 2 * 2 + cfg.batch * cfg.q_heads * HEAD_DIM * 2
-    wbytes = sum(w.numel() * w.element_size() for w in s.hash_q[0].weights + s.hash_k[0].weights)
+    wbytes = hash_weight_bytes
     kern = {
         "scan_topk": {"bytes": by_scan, "us": stage_ms["scan"] * 1e3},
         "sparse_attn": {"bytes": by_attn, "us": stage_ms["attn"] * 1e3},
         "decode_prepare": {"bytes": wbytes, "us": stage_ms["prepare"] * 1e3},
     }
     if args.lru:     # stage 3: bytes of the slot tables it walks (rows only move on misses; none in a replayed step)
-        kern["lru_update"] = {"bytes": cfg.batch * cfg.kv_heads * s.cfg.lru_slots * 8, "us": stage_ms["lru"] * 1e3}
+        kern["lru_update"] = {"bytes": cfg.batch * cfg.kv_heads * lru_slots * 8, "us": stage_ms["lru"] * 1e3}
     for k_, d in kern.items():
         d["gbs"] = d["bytes"] / (d["us"] * 1e-6) / 1e9
         d["frac"] = d["gbs"] / peak
@@ -352,13 +378,13 @@ def run_ours(args, cfg):
         "data": "synthetic", "config": workload_config(cfg),
         "tokens_per_s": world * cfg.batch / (ms_step * 1e-3),
         "e2e": {"value": max(ms_e2e, wall_e2e) * 1e3 / L, "unit": UNIT,
-                "h2d_bytes_per_step": s.host_bytes_per_step[0], "d2h_bytes_per_step": s.host_bytes_per_step[1],
+                "h2d_bytes_per_step": host_bytes[0], "d2h_bytes_per_step": host_bytes[1],
                 "device_ms_per_step": ms_e2e, "wall_ms_per_step": wall_e2e},
         "gpu_launches": (5 if args.lru else 4) * L * args.steps,
         "lru_stage": bool(args.lru),
         "cuda_graph": use_graph,
         "roofline": {"bound": "hbm", "kernel": dom, "achieved": kern[dom]["gbs"], "peak": peak, "unit": "GB/s",
-                     "frac": kern[dom]["frac"], "traffic": NCU_TRAFFIC[dom], "peak_kind": peak_kind,
+                     "frac": kern[dom]["frac"], "traffic": measured_traffic(cfg, dom), "peak_kind": peak_kind,
                      "algorithmic_bytes_per_launch": kern[dom]["bytes"], "us_per_launch": kern[dom]["us"],
                      "frac_of_nominal_8TBs": kern[dom]["gbs"] / 8000.0},
         "kernels": kern,
@@ -366,8 +392,14 @@ def run_ours(args, cfg):
                  "attended_keys_per_head": mean_nsel / (cfg.batch * cfg.kv_heads), "budget_k": budget(n, cfg.mask_out, cfg.min_remain)},
         "code_build_ms_per_layer": code_build_ms,
         "clocks": clk,
-        "checksum": float(out_host.float().abs().sum()),
+        "checksum": checksum if extras else float(out_host.float().abs().sum()),
     }
+    line.update(extras)
+    if world == 1 and not args.no_reference_kernels and cfg.name == "headline":
+        g_all = g = None
+        del s
+        torch.cuda.empty_cache()
+        line["reference_gpu_kernels"] = reference_gpu_kernels(device)
     if world == 1 and not args.no_cpu_baseline:
         us, heads, threads, sec = time_cpu(cfg, n, steps=2, warmup=1, budget_s=25.0)
         line["cpu_baseline"] = {
@@ -375,8 +407,11 @@ def run_ours(args, cfg):
             "sample": f"one layer-step of the reference modifier path at N={n}, fp32, {heads} of {cfg.q_heads} q heads, "
                       f"scaled x{cfg.q_heads / heads:g}; median of 2 after 1 warm-up ({sec:.2f} s each)"}
     print(json.dumps(line), flush=True)
-    if dist is not None:
-        dist.destroy_process_group()
+    if dist is not None:      # captured graphs may hold communicator work: leave without the group's teardown
+        sys.stdout.flush()
+        torch.cuda.synchronize(device)
+        dist.barrier()
+        os._exit(0)
 
 
 def run_decode_loop(args, cfg):
@@ -433,51 +468,43 @@ def run_decode_loop(args, cfg):
     print(json.dumps(line), flush=True)
 
 
-def run_sharded(args, cfg):
-    """Sequence-sharded layer-step (config 4: 1M-token context): every rank owns n/world keys of
-    `layers` rotating layers, a step is one layer-step through sharded_decode_attention (local scan +
-    histogram, all-gather, emission, local attention, all-gather of (o, lse), merge). Launched under
-    torchrun; with one rank it times the unsharded kernels on the same global shape."""
-    rank = int(os.environ.get("RANK", "0"))
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    local = int(os.environ.get("LOCAL_RANK", "0"))
-    if not torch.cuda.is_available():
-        raise SystemExit("bench.py needs a CUDA device: the retrieval path has no CPU fallback")
-    torch.cuda.set_device(local)
-    device = torch.device("cuda", local)
-    import torch.distributed as dist
-    if world > 1:
-        dist.init_process_group("nccl", device_id=device)
-    from spotlight_b200 import ops
-    from spotlight_b200.sharded import shard_bounds, sharded_decode_attention
+def sharded_setup(cfg, device, world, rank, L):
+    """Per-rank inputs of the sequence-sharded layer-step: this rank's contiguous share of the keys of L
+    rotating layers (working set >> L2) and the query, which is the same on every rank."""
+    from spotlight_b200.sharded import shard_bounds
     from spotlight_b200.workloads import torch_dtype
     dt = torch_dtype(cfg.dtype)
     n, B, QH, KH = cfg.context, cfg.batch, cfg.q_heads, cfg.kv_heads
-    L = max(2, min(args.layers or 4, 8))                       # rotating layers: working set >> L2
     lo, hi = shard_bounds(n, world, rank)
     nl = hi - lo
-    kb = budget(n, cfg.mask_out, cfg.min_remain)
     g = torch.Generator(device=device).manual_seed(cfg.seed + rank)
     codes, ks, vs = [], [], []
     for _ in range(L):
         codes.append(torch.randint(0, 2 ** 31, (B, nl, KH, 4), generator=g, device=device, dtype=torch.int64).to(torch.uint32))
         ks.append(torch.randn((B, nl, KH, HEAD_DIM), generator=g, device=device).to(dt))
         vs.append(torch.randn((B, nl, KH, HEAD_DIM), generator=g, device=device).to(dt))
-    gq = torch.Generator().manual_seed(cfg.seed)                 # the query is the same on every rank
+    gq = torch.Generator().manual_seed(cfg.seed)
     q_rot = torch.randn((B, QH, HEAD_DIM), generator=gq).to(dt).to(device)
     q_codes = torch.randint(0, 2 ** 31, (B, QH, 4), generator=gq, dtype=torch.int64).to(torch.uint32).to(device)
+    return dict(codes=codes, ks=ks, vs=vs, q_rot=q_rot, q_codes=q_codes, lo=lo, nl=nl, L=L)
 
-    exchange = None
-    if world > 1 and args.peer:
-        from spotlight_b200.sharded import make_peer_exchange
-        exchange = make_peer_exchange(B, KH, QH, device, fused_scan=not args.no_fused_scan)
+
+def sharded_time(args, cfg, data, device, dist, world, exchange, steps, warmup):
+    """us per layer of the sharded layer-step (one CUDA graph over the L rotating layers), max over ranks.
+    `exchange`: None = NCCL all-gathers, else the peer-memory exchange objects."""
+    from spotlight_b200 import ops
+    from spotlight_b200.sharded import sharded_decode_attention
+    n = cfg.context
+    kb = budget(n, cfg.mask_out, cfg.min_remain)
+    L = data["L"]
 
     def layer_step(layer):
         if world > 1:
-            return sharded_decode_attention(q_rot, q_codes, codes[layer], ks[layer], vs[layer], lo, n, kb,
-                                            cfg.sink, cfg.recent, ops.GQA_BLOCKED, exchange=exchange)
-        idx, cnt = ops.scan_topk(q_codes, codes[layer], kb, cfg.sink, cfg.recent, ops.GQA_BLOCKED)
-        return ops.sparse_attn_decode(q_rot, ks[layer], vs[layer], idx, cnt, ops.GQA_BLOCKED)
+            return sharded_decode_attention(data["q_rot"], data["q_codes"], data["codes"][layer], data["ks"][layer],
+                                            data["vs"][layer], data["lo"], n, kb, cfg.sink, cfg.recent, ops.GQA_BLOCKED,
+                                            exchange=exchange)
+        idx, cnt = ops.scan_topk(data["q_codes"], data["codes"][layer], kb, cfg.sink, cfg.recent, ops.GQA_BLOCKED)
+        return ops.sparse_attn_decode(data["q_rot"], data["ks"][layer], data["vs"][layer], idx, cnt, ops.GQA_BLOCKED)
 
     def step():
         out = None
@@ -494,7 +521,7 @@ def run_sharded(args, cfg):
         try:
             graph = torch.cuda.CUDAGraph()
             with torch.cuda.graph(graph):
-                out = step()
+                step()
         except RuntimeError as e:
             print(f"# graph capture failed ({e}); timing eager launches", file=sys.stderr)
             graph, use_graph = None, False
@@ -507,47 +534,190 @@ def run_sharded(args, cfg):
             else:
                 step()
 
-    with ClockSampler(local) as clocks:
-        ms_step = time_graph(Runner(), args.steps, args.warmup, device, dist if world > 1 else None)
+    ms_step = time_graph(Runner(), steps, warmup, device, dist if world > 1 else None)
     ops.check_status(device)
+    status_ok = True
     if exchange:
         for e in exchange:
-            e.check_status()
-    clk = clocks.summary()
+            try:
+                e.check_status()
+            except RuntimeError:
+                status_ok = False
     if world > 1:
-        t = torch.tensor([ms_step], device=device, dtype=torch.float64)
+        t = torch.tensor([ms_step, 0.0 if status_ok else 1.0], device=device, dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms_step = float(t.item())
+        ms_step, bad = t.tolist()
+        status_ok = bad == 0.0
+    del graph
+    torch.cuda.synchronize(device)
+    return ms_step * 1e3 / L, use_graph, status_ok
+
+
+def run_sharded(args, cfg):
+    """Sequence-sharded layer-step (config 4: 1M-token context): every rank owns n/world keys of
+    `layers` rotating layers, a step is one layer-step through sharded_decode_attention (local scan +
+    histogram, all-gather, emission, local attention, all-gather of (o, lse), merge). Launched under
+    torchrun; with one rank it times the unsharded kernels on the same global shape."""
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the retrieval path has no CPU fallback")
+    torch.cuda.set_device(local)
+    device = torch.device("cuda", local)
+    import torch.distributed as dist
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+    n, B, QH, KH = cfg.context, cfg.batch, cfg.q_heads, cfg.kv_heads
+    L = max(2, min(args.layers or 4, 8))                       # rotating layers: working set >> L2
+    data = sharded_setup(cfg, device, world, rank, L)
+    kb = budget(n, cfg.mask_out, cfg.min_remain)
+    exchange = None
+    if world > 1 and args.peer:
+        from spotlight_b200.sharded import make_peer_exchange
+        exchange = make_peer_exchange(B, KH, QH, device, fused_scan=not args.no_fused_scan)
+    with ClockSampler(local) as clocks:
+        us_layer, use_graph, status_ok = sharded_time(args, cfg, data, device, dist, world, exchange, args.steps, args.warmup)
+    clk = clocks.summary()
     if rank == 0:
-        us_layer = ms_step * 1e3 / L
         peak, peak_kind = peaks()
         by = B * n * KH * 16 + kb * B * KH * HEAD_DIM * 2 * 2            # codes + attended K/V rows, whole job
         line = {
             "metric": "decode_attn_us_per_layer_seq_sharded", "value": us_layer, "unit": UNIT, "n_gpus": world,
-            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": False,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": us_layer * L / 1e3, "higher_is_better": False,
             "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "config": {"workload": f"{cfg.name}: sequence-sharded decode attention, batch {B}, {QH}/{KH} heads, context {n} "
                                    f"over {world} rank(s), mask_out {cfg.mask_out}, sink {cfg.sink}, recent {cfg.recent}",
-                       "context": n, "keys_per_rank": nl, "rotating_layers": L,
+                       "context": n, "keys_per_rank": data["nl"], "rotating_layers": L,
                        "exchange": ("peer memory, fused scan" if exchange and len(exchange) > 2 else "peer memory") if exchange
                        else ("nccl" if world > 1 else "none"),
                        "l2": "inputs larger than L2 (layers rotate)"},
             "tokens_per_s": B / (us_layer * 1e-6 * 48) if cfg.name == "cfg4" else None,
-            "cuda_graph": use_graph,
+            "cuda_graph": use_graph, "status_words_ok": status_ok,
             "path": {"algorithmic_bytes_per_layer": by, "gbs": by / (us_layer * 1e-6) / 1e9,
                      "frac_of_aggregate_peak": by / (us_layer * 1e-6) / 1e9 / (peak * world), "peak_kind": peak_kind},
             "clocks": clk,
         }
         print(json.dumps(line), flush=True)
-    # A captured graph holds NCCL work: release it before the process group goes away, and leave
-    # without the group's teardown (a hang there would only cost time, the numbers are out).
-    graph = None
+    # A captured graph holds NCCL work: leave without the group's teardown (a hang there would only cost
+    # time, the numbers are out).
     torch.cuda.synchronize(device)
     if world > 1:
         dist.barrier()
         torch.cuda.synchronize(device)
         sys.stdout.flush()
         os._exit(0)
+
+
+def multi_rank_extras(args, device, dist, world, rank):
+    """What the ranks of one node measure beyond the replicated headline step (rank 0 prints them inside the
+    one JSON line): config 4's sequence-sharded layer-step in both forms of the exchange (strong scaling of a
+    1M-token context: the path's only step that communicates), and config 3's batch of 8 split over the ranks
+    (strong scaling without communication)."""
+    import dataclasses
+    from spotlight_b200.sharded import make_peer_exchange
+    peak, _ = peaks()
+    out = {}
+    # ---- config 4, sequence shards
+    cfg4 = CONFIGS["cfg4"]
+    L = 4
+    data = sharded_setup(cfg4, device, world, rank, L)
+    kb = budget(cfg4.context, cfg4.mask_out, cfg4.min_remain)
+    by = cfg4.batch * cfg4.context * cfg4.kv_heads * 16 + kb * cfg4.batch * cfg4.kv_heads * HEAD_DIM * 2 * 2
+    seq = {"workload": f"cfg4: batch 1, {cfg4.q_heads}/{cfg4.kv_heads} heads, context {cfg4.context} over {world} ranks, "
+                       f"mask_out {cfg4.mask_out}", "ranks": world, "keys_per_rank": data["nl"], "rotating_layers": L,
+           "algorithmic_bytes_per_layer": by}
+    us, graph, ok = sharded_time(args, cfg4, data, device, dist, world, None, 20, 5)
+    seq["nccl"] = {"us_per_layer": us, "frac_of_aggregate_peak": by / (us * 1e-6) / 1e9 / (peak * world), "cuda_graph": graph}
+    try:
+        ex = make_peer_exchange(cfg4.batch, cfg4.kv_heads, cfg4.q_heads, device, fused_scan=True)
+        us, graph, ok = sharded_time(args, cfg4, data, device, dist, world, ex, 20, 5)
+        seq["peer_memory_fused_scan"] = {"us_per_layer": us, "frac_of_aggregate_peak": by / (us * 1e-6) / 1e9 / (peak * world),
+                                         "cuda_graph": graph, "status_words_ok": ok}
+    except Exception as e:        # peer mappings need the GPUs of one node with peer access
+        seq["peer_memory_fused_scan"] = {"unavailable": str(e)[:200]}
+    out["seq_sharded"] = seq
+    del data
+    torch.cuda.empty_cache()
+    # ---- config 3, batch split (strong scaling, no exchange)
+    cfg3 = CONFIGS["cfg3"]
+    if cfg3.batch % world == 0:
+        c3 = dataclasses.replace(cfg3, batch=cfg3.batch // world, layers=4)
+        s3, _ = build_session(c3, device)
+        g3 = s3.capture(c3.context - 1)
+        ms = time_graph(g3, 20, 5, device, dist)
+        t = torch.tensor([ms], device=device, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        out["cfg3_batch_split"] = {"workload": f"cfg3: batch {cfg3.batch} split over {world} ranks ({c3.batch} rows each), "
+                                               f"{cfg3.q_heads}/{cfg3.kv_heads} heads, context {cfg3.context}, mask_out {cfg3.mask_out}",
+                                   "us_per_layer": float(t.item()) * 1e3 / c3.layers, "scaling": "strong", "collectives": 0}
+        del s3, g3
+        torch.cuda.empty_cache()
+    return out
+
+
+def reference_gpu_kernels(device):
+    """The reference's own CUDA scorer beside this library's kernels, on the one shape it supports
+    ((KH, QH) = (4, 28), spotlight/kernel/__init__.py:14-16): B 8 x 128K keys, three rotating code buffers.
+    attn_k4_q28 is the reference's attn_k4_q28.cu compiled UNCHANGED for sm_100a into the checker's directory
+    (oracle/build_ref.py); its top-k + gather is the operator sequence of spotlight/modifiers/gpu_cache.py:48-54
+    (attn.topk(sorted=False), two torch.gather) run eagerly. The reference's Triton scorer is a source file of the
+    reference and is not available where this runs."""
+    import importlib.util
+    path = os.path.join(ROOT, "oracle", "_ref", "attn_k4_q28.so")
+    if not os.path.exists(path):
+        return {"unavailable": "oracle/_ref/attn_k4_q28.so not built (oracle/build_ref.py needs a checkout of the reference)"}
+    try:
+        spec = importlib.util.spec_from_file_location("attn_k4_q28", path)
+        ref = importlib.util.module_from_spec(spec)
+        spec.loader.exec_module(ref)
+    except Exception as e:
+        return {"unavailable": f"could not load the reference kernel: {str(e)[:160]}"}
+    import spotlight_b200.kernel as K
+    from spotlight_b200 import ops
+    g = torch.Generator(device=device).manual_seed(3)
+    B, N, KH, QH, keep = 8, 131072, 4, 28, 2622
+    q = torch.randint(0, 2 ** 31, (B, 1, QH, 4), generator=g, device=device).to(torch.int32).view(torch.uint32)
+    ks = [torch.randint(0, 2 ** 31, (B, N, KH, 4), generator=g, device=device).to(torch.int32).view(torch.uint32) for _ in range(3)]
+    kc = torch.randn((B, N, KH, HEAD_DIM), generator=g, device=device).to(torch.bfloat16)
+    vc = torch.randn((B, N, KH, HEAD_DIM), generator=g, device=device).to(torch.bfloat16)
+
+    def timed(fn, iters=30):
+        for i in range(5):
+            fn(ks[i % 3])
+        torch.cuda.synchronize(device)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for i in range(iters):
+            fn(ks[i % 3])
+        e1.record()
+        torch.cuda.synchronize(device)
+        return e0.elapsed_time(e1) / iters * 1e3
+
+    def ref_topk_and_gather(k):
+        attn = ref.attn_k4_q28(q, k)
+        ind = attn.topk(k=keep, dim=1, sorted=False).indices.unsqueeze(-1).expand(-1, -1, -1, HEAD_DIM)
+        return torch.gather(kc, 1, ind), torch.gather(vc, 1, ind)
+
+    qr = torch.randn((B, QH, HEAD_DIM), generator=g, device=device).to(torch.bfloat16)
+
+    def ours_scan_and_attention(k):
+        idx, cnt = ops.scan_topk(q, k, keep, 4, 64, 0)
+        return ops.sparse_attn_decode(qr, kc, vc, idx, cnt, 0)
+
+    res = {
+        "shape": f"B{B} x {N} keys x ({KH},{QH}) heads, {B * N * KH * 16 / 1e6:.1f} MB of codes, top {keep}",
+        "reference_attn_k4_q28_us": timed(lambda k: ref.attn_k4_q28(q, k)),
+        "reference_attn_k4_q28_plus_torch_topk_us": timed(lambda k: ref.attn_k4_q28(q, k).topk(k=keep, dim=1, sorted=False)),
+        "reference_scores_topk_and_gather_us": timed(ref_topk_and_gather),
+        "ours_scores_only_us": timed(lambda k: K.attn_cuda_func(q, k)),
+        "ours_fused_scan_topk_window_us": timed(lambda k: ops.scan_topk(q, k, keep, 4, 64, 0)),
+        "ours_scan_topk_plus_sparse_attention_us": timed(ours_scan_and_attention),
+        "triton_scorer": "not run: spotlight/kernel/attn_dx_u32.py is a source file of the reference, absent here",
+    }
+    del ks, kc, vc
+    torch.cuda.empty_cache()
+    return res
 
 
 def main():
@@ -565,6 +735,8 @@ def main():
     ap.add_argument("--separate-kv", action="store_true", help="two K/V caches per layer instead of one fused cache")
     ap.add_argument("--attn-warps", type=int, default=0, choices=[0, 4, 8], help="warps per CTA of the attention kernel (0: by shape)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-reference-kernels", action="store_true", help="skip timing the reference's CUDA scorer beside ours (1 GPU)")
+    ap.add_argument("--no-extras", action="store_true", help="with several ranks: skip the sharded / batch-split measurements")
     ap.add_argument("--decode-steps", type=int, default=0,
                     help="run this many consecutive decode tokens at advancing positions (config 1: 256) instead of "
                          "replaying one position")

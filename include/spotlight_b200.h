@@ -58,8 +58,11 @@ int sl_set_device(int device);
  *                       sl_scan_topk of the same step streams next (caches of at most 24 MB); 0: off
  *   SL_OPT_SCAN_KERNEL  which kernel sl_scan_topk uses where several apply (results are identical):
  *                       1 (default) the one-barrier kernel, 2 the flagged-word kernel, 0 the general kernel
- *   SL_OPT_ATTN_WARPS   warps per CTA of the bf16 attention kernel: 0 (default) by shape, 4 or 8 */
-typedef enum { SL_OPT_PDL = 0, SL_OPT_L2_PREFETCH = 1, SL_OPT_SCAN_KERNEL = 2, SL_OPT_ATTN_WARPS = 3 } sl_option;
+ *   SL_OPT_ATTN_WARPS   warps per CTA of the bf16 attention kernel: 0 (default) by shape, 4 or 8
+ *   SL_OPT_PEER_SPIN_LIMIT  polls (100 ns apart) after which the peer-memory exchanges stop waiting for another
+ *                       rank's message and set their status word to 3; default 400000, about a second */
+typedef enum { SL_OPT_PDL = 0, SL_OPT_L2_PREFETCH = 1, SL_OPT_SCAN_KERNEL = 2, SL_OPT_ATTN_WARPS = 3,
+               SL_OPT_PEER_SPIN_LIMIT = 4 } sl_option;
 int sl_configure(int option, int value);
 
 /* Sign-bit packing: bit j of output byte i  <=>  x[8*i + j] > 0 (LSB first). Read as uint32

@@ -71,7 +71,7 @@ extern "C" int sl_workspace_init(void* d_workspace, size_t bytes, void* stream) 
 }
 
 namespace slscan { void set_scan_kernel(int v); }
-namespace sl { void set_attn_warps(int v); }
+namespace sl { void set_attn_warps(int v); void set_peer_spin_limit(unsigned v); }
 
 extern "C" int sl_configure(int option, int value) {
     switch (option) {
@@ -84,6 +84,10 @@ extern "C" int sl_configure(int option, int value) {
         case SL_OPT_ATTN_WARPS:
             SL_REQUIRE(value == 0 || value == 4 || value == 8, SL_EINVAL, "sl_configure: SL_OPT_ATTN_WARPS takes 0, 4 or 8");
             sl::set_attn_warps(value);
+            return SL_OK;
+        case SL_OPT_PEER_SPIN_LIMIT:
+            SL_REQUIRE(value >= 1, SL_EINVAL, "sl_configure: SL_OPT_PEER_SPIN_LIMIT takes a positive number of polls");
+            sl::set_peer_spin_limit((unsigned)value);
             return SL_OK;
         default: return sl::fail(SL_EINVAL, "sl_configure: unknown option %d", option);
     }

@@ -18,6 +18,7 @@ namespace {
 
 constexpr int MAX_RANKS = 8;
 constexpr int PT = 512;
+unsigned g_peer_spin_limit = 400000u;   // polls of 100 ns: about a second (sl_configure shortens it for tests)
 
 struct PeerArgs {
     unsigned char* base[MAX_RANKS];   // exchange buffer of every rank (own one included)
@@ -26,6 +27,7 @@ struct PeerArgs {
     unsigned n16;                     // message size in 16-byte units
     unsigned long long slot_stride, flags_off;
     int* status;
+    unsigned spin_limit;              // polls of a peer's flag before the wait gives up
 };
 
 __global__ void __launch_bounds__(PT) peer_allgather_kernel(const PeerArgs a) {
@@ -57,7 +59,7 @@ __global__ void __launch_bounds__(PT) peer_allgather_kernel(const PeerArgs a) {
         for (;;) {
             asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(lf) : "memory");
             if ((int)(v - e) >= 0) break;
-            if (++it > 400000u) {    // about a second: give up, tell the host, let the stream go on
+            if (++it > a.spin_limit) {    // about a second by default: give up, tell the host, let the stream go on
                 if (a.status) atomicExch(a.status, 3);
                 break;
             }
@@ -110,7 +112,7 @@ __global__ void __launch_bounds__(PT) peer_merge_lse_kernel(const PeerArgs a, co
         for (;;) {
             asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(lf) : "memory");
             if ((int)(v - e) >= 0) break;
-            if (++it > 400000u) {
+            if (++it > a.spin_limit) {
                 if (a.status) atomicExch(a.status, 3);
                 break;
             }
@@ -148,10 +150,13 @@ int fill_args(PeerArgs& a, void* const* peer_bufs, int rank, int R, size_t slot_
     a.slot_stride = slot_stride;
     a.flags_off = (unsigned long long)R * slot_stride;
     a.status = d_status;
+    a.spin_limit = g_peer_spin_limit;
     return SL_OK;
 }
 
 }  // namespace
+
+namespace sl { void set_peer_spin_limit(unsigned v) { g_peer_spin_limit = v; } }
 
 extern "C" int sl_peer_merge_lse(const void* d_o, const float* d_lse, int dtype, int64_t rows, void* const* peer_bufs,
                                  int rank, int R, size_t slot_stride, void* d_out, int32_t* d_status, void* stream) {
@@ -238,6 +243,7 @@ extern "C" int sl_peer_allgather(const void* d_src, size_t bytes, void* const* p
     a.slot_stride = slot_stride;
     a.flags_off = (unsigned long long)R * slot_stride;
     a.status = d_status;
+    a.spin_limit = g_peer_spin_limit;
     SL_CUDA_OK(sl::launch_kernel(peer_allgather_kernel, dim3(1), dim3(PT), 0, static_cast<cudaStream_t>(stream), false, a));
     return SL_OK;
 }

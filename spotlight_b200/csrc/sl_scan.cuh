@@ -9,7 +9,7 @@ constexpr int NT = 512;            // threads per CTA
 constexpr int NW = NT / 32;
 constexpr int U = 8;               // 16-byte loads in flight per thread
 constexpr int NCOPY = 4;           // copies of the global histograms in the workspace
-constexpr int SHARD_EPOCH_WORD = 2040;   // the flag area of an exchange buffer is 8 KB: [R][B] flags, epoch here
+constexpr int SHARD_EPOCH_WORD = 2040;   // the flag area of an exchange buffer is 8 KB: [R][B] flags, the epoch of batch row b at this word - b
 
 struct FusedArgs {
     const uint4* q;            // [B,QH] codes

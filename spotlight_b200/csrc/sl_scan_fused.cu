@@ -147,9 +147,9 @@ __global__ void __launch_bounds__(NT, 1) scan_fused_kernel(const FusedArgs a) {
     SL_STAMP(2)
     const int W = KH * nbins + KH * NC;                          // words of one batch row's message
     if (SHARD) {
-        // own buffer: [R slots][flags [R][B]] ... [epoch at word SHARD_EPOCH_WORD of the flag area]
+        // own buffer: [R slots][flags [R][B]] ... [epoch of row b at word SHARD_EPOCH_WORD - b of the flag area]
         unsigned* own_words = reinterpret_cast<unsigned*>(a.peer[a.rank] + a.pflags_off);
-        const unsigned target = __ldcg(own_words + SHARD_EPOCH_WORD) + 1u;        // this launch's epoch
+        const unsigned target = __ldcg(own_words + SHARD_EPOCH_WORD - b) + 1u;    // this launch's epoch of the row
         if (c == 0) {
             // One CTA per batch row carries the row's message (a few thousand words) to every rank and
             // then publishes the epoch in the row's flag on every rank. A system-scope fence costs
@@ -451,15 +451,15 @@ __global__ void __launch_bounds__(NT, 1) scan_fused_kernel(const FusedArgs a) {
 #pragma unroll 1
         for (int i = c * NT + tid; i < NCOPY * ctot; i += cpb * NT) chist_b[(i / ctot) * cslice + i % ctot] = 0;
         __syncthreads();
-        if (SHARD && blockIdx.x == 0 && tid == 0) {      // every CTA read the epoch before it went on to emit
-            unsigned* epoch_w = reinterpret_cast<unsigned*>(a.peer[a.rank] + a.pflags_off) + SHARD_EPOCH_WORD;
-            *epoch_w = __ldcg(epoch_w) + 1u;
-        }
         if (tid == 0) {
             unsigned* sync = a.sync + 2 * b;
             __threadfence();
             const unsigned old = atomicAdd(&sync[1], 1u);
             if (old == (unsigned)cpb - 1u) {
+                if (SHARD) {     // the row's last CTA: every CTA of the row has read the row's epoch word by now
+                    unsigned* epoch_w = reinterpret_cast<unsigned*>(a.peer[a.rank] + a.pflags_off) + SHARD_EPOCH_WORD - b;
+                    *epoch_w = __ldcg(epoch_w) + 1u;
+                }
                 sync[0] = 0;
                 sync[1] = 0;
                 __threadfence();

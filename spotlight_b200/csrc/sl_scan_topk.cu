@@ -883,7 +883,8 @@ extern "C" int sl_scan_topk_sharded(const uint32_t* d_q_codes, const uint32_t* d
     SL_REQUIRE(gqa_layout == SL_GQA_INTERLEAVED || gqa_layout == SL_GQA_BLOCKED, SL_EINVAL,
                "sl_scan_topk_sharded: unknown gqa_layout %d", gqa_layout);
     SL_REQUIRE(R >= 1 && R <= 8 && rank >= 0 && rank < R, SL_EINVAL, "sl_scan_topk_sharded: bad rank %d of %d", rank, R);
-    SL_REQUIRE(R * B <= slscan::SHARD_EPOCH_WORD, SL_ESHAPE, "sl_scan_topk_sharded: R*B exceeds the flag area");
+    SL_REQUIRE(R * B + B <= slscan::SHARD_EPOCH_WORD + 1, SL_ESHAPE, "sl_scan_topk_sharded: (R+1)*B exceeds the flag area");
+    SL_REQUIRE(N_local > 0, SL_ESHAPE, "sl_scan_topk_sharded: an empty shard must use sl_scan_hist + sl_select_emit (every rank has to launch the exchange)");
     SL_REQUIRE(tok_offset >= 0 && tok_offset + N_local <= N_global, SL_ESHAPE, "sl_scan_topk_sharded: shard outside the context");
     SL_REQUIRE(k >= 0 && sink >= 0 && recent >= 0, SL_EINVAL, "sl_scan_topk_sharded: negative k/sink/recent");
     SL_REQUIRE(sl::aligned16(d_q_codes) && sl::aligned16(d_k_codes) && k_batch_stride % 4 == 0, SL_EALIGN,

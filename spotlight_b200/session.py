@@ -224,6 +224,7 @@ class DecodeSession:
             self.step_dev(max_context)
             if host_io:
                 self._host["out"].copy_(self.out, non_blocking=True)
+                self._host["status"].copy_(self._scan_status(), non_blocking=True)
 
         saved = self.pos_dev.clone()
         s = torch.cuda.Stream(device=self.device)
@@ -268,6 +269,14 @@ class DecodeSession:
         self.step(pos, stage)
         if host_io:
             self._host["out"].copy_(self.out, non_blocking=True)
+            self._host["status"].copy_(self._scan_status(), non_blocking=True)   # rides along with the outputs
+
+    def _scan_status(self) -> torch.Tensor:
+        """The status word of the scan workspace this session's steps use (set by a bounded wait that ran out)."""
+        from . import _lib
+        c = self.cfg
+        need = _lib.lib.sl_scan_topk_workspace_bytes(c.batch, c.capacity, c.kv_heads, c.q_heads)
+        return ops.workspaces.get("scan", self.device, need, (c.batch, c.kv_heads, c.q_heads))[1]
 
     # ------------------------------------------------------------------ host buffers
     def _ensure_host(self):
@@ -277,6 +286,7 @@ class DecodeSession:
                 "k": torch.zeros(self.k_in.shape, dtype=self.cfg.dtype).pin_memory(),
                 "v": torch.zeros(self.v_in.shape, dtype=self.cfg.dtype).pin_memory(),
                 "out": torch.zeros(self.out.shape, dtype=self.cfg.dtype).pin_memory(),
+                "status": torch.zeros((1,), dtype=torch.int32).pin_memory(),
             }
         return self._host
 
@@ -292,9 +302,11 @@ class DecodeSession:
         else:
             self._run(pos, None, True)
         torch.cuda.current_stream(self.device).synchronize()
+        if int(h["status"][0]) != 0:      # a device-side wait ran out: the step's results are not to be trusted
+            ops.check_status(self.device)
         return h["out"]
 
     @property
     def host_bytes_per_step(self):
         e = self.q_in.element_size()
-        return (self.q_in.numel() + self.k_in.numel() + self.v_in.numel()) * e, self.out.numel() * e
+        return (self.q_in.numel() + self.k_in.numel() + self.v_in.numel()) * e, self.out.numel() * e + 4   # + the status word

@@ -577,6 +577,42 @@ def test_peer_allgather_single_rank(ops):
         check(lib.sl_peer_free(buf))
 
 
+def test_peer_wait_runs_out_and_the_context_stays_usable(ops):
+    """A rank that never shows up: two exchange buffers on ONE GPU, the second never written by anybody.
+    The kernel's bounded wait on that rank's flag must run out (the limit is shortened for the test),
+    return normally with the status word set to 3, and the next exchange on fresh buffers must work."""
+    import ctypes as C
+    from spotlight_b200 import _lib
+    from spotlight_b200._lib import check, lib
+    nbytes = 1024
+    bufs = []
+    for _ in range(3):
+        p = C.c_void_p()
+        check(lib.sl_peer_alloc(lib.sl_peer_buffer_bytes(2, nbytes), C.byref(p)))
+        bufs.append(p)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    stream = torch.cuda.current_stream().cuda_stream
+    msg = torch.arange(nbytes // 4, dtype=torch.int32, device=DEV)
+    check(lib.sl_configure(_lib.SL_OPT_PEER_SPIN_LIMIT, 20000))               # ~2 ms instead of a second
+    try:
+        pair = (C.c_void_p * 2)(bufs[0].value, bufs[1].value)
+        check(lib.sl_peer_allgather(msg.data_ptr(), nbytes, pair, 0, 2, nbytes, status.data_ptr(), stream))
+        torch.cuda.synchronize()                                               # the kernel came back by itself
+        assert int(status.item()) == 3
+        with pytest.raises(RuntimeError):
+            _lib.check(_lib.SL_ETIMEOUT if int(status.item()) == 3 else 0)
+        status.zero_()
+        one = (C.c_void_p * 1)(bufs[2].value)
+        check(lib.sl_peer_allgather(msg.data_ptr(), nbytes, one, 0, 1, nbytes, status.data_ptr(), stream))
+        torch.cuda.synchronize()
+        assert int(status.item()) == 0
+        assert int((msg * 2).sum().item()) == int(msg.sum().item()) * 2        # the context still computes
+    finally:
+        check(lib.sl_configure(_lib.SL_OPT_PEER_SPIN_LIMIT, 400000))
+        for p in bufs:
+            lib.sl_peer_free(p)
+
+
 @pytest.mark.parametrize("B,N,KH,QH,k", [(1, 131072, 8, 32, 13108), (2, 60000, 4, 28, 1200), (1, 40000, 8, 40, 800)])
 def test_scan_topk_sharded_single_rank(ops, B, N, KH, QH, k):
     """The one-launch sharded scan with a world of one rank (histograms go through the rank's own
