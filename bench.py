@@ -240,6 +240,57 @@ def build_session(cfg, device, lru=False, extra_capacity=0, fused_kv=True):
     return s, t_codes / cfg.layers
 
 
+def time_four_stage(args, cfg, s, device, dist, tokens, drift=0.25):
+    """The four-stage layer-step (hash -> scan + top-k -> LRU update -> attention over the resident buffers) as ONE
+    graph replayed for consecutive tokens: the position, and with it the clock of the LRU tables, lives in device
+    memory and advances with every replay; the query drifts from token to token (a fixed query plus fresh noise), so
+    the selections overlap partially and the update sees hits AND misses. Returns us per layer (max over ranks) and
+    what the tables saw at the last token."""
+    was = s.use_lru
+    s.use_lru = True
+    n, L = cfg.context, cfg.layers
+    s.set_position_table(n - 1, s.cfg.capacity - (n - 1), cfg.rope_theta)
+    s.pos_dev.fill_(n - 1)
+    graph = s.capture_dev()
+    for t in s.lru:
+        t.tok2slot.fill_(-1); t.slot2tok.fill_(-1); t.last_used.fill_(-1)
+    s.pos_dev.fill_(n - 1)
+    g = torch.Generator(device=device).manual_seed(cfg.seed + 11)
+    base = s.q_in.clone().float()
+    qsets = [(base + drift * torch.randn(base.shape, generator=g, device=device)).to(s.cfg.dtype) for _ in range(8)]
+
+    def token(i):
+        s.q_in.copy_(qsets[i % len(qsets)], non_blocking=True)
+        graph.replay()
+
+    for i in range(args.warmup):
+        token(i)
+    torch.cuda.synchronize(device)
+    if dist is not None:
+        dist.barrier()
+        torch.cuda.synchronize(device)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(args.steps):
+        token(args.warmup + i)
+    e1.record()
+    torch.cuda.synchronize(device)
+    ms = e0.elapsed_time(e1) / args.steps
+    if dist is not None:
+        t = torch.tensor([ms], device=device, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    stats = torch.stack([t.stats.sum((0, 1)) for t in s.lru]).double().mean(0).tolist()     # last token, mean over layers
+    bad = sum(int(t.status.item()) != 0 for t in s.lru)
+    s.use_lru = was
+    hits, misses = stats
+    return {"value_with_lru": ms * 1e3 / L, "unit": UNIT, "tokens_timed": args.steps, "query_drift": drift,
+            "hit_rate_last_token": hits / max(1.0, hits + misses), "missed_rows_per_layer": misses,
+            "miss_bytes_per_layer": misses * HEAD_DIM * 2 * 2, "lru_slots_per_head": s.cfg.lru_slots,
+            "status_words_ok": bad == 0,
+            "note": "one CUDA graph for every token (device-side position and LRU clock); the query drifts, so the tables see hits and misses"}
+
+
 def time_graph(g, steps, warmup, device, dist=None):
     for _ in range(warmup):
         g.replay()
@@ -276,7 +327,11 @@ def run_ours(args, cfg):
     if args.attn_warps:
         from spotlight_b200 import _lib
         _lib.check(_lib.lib.sl_configure(_lib.SL_OPT_ATTN_WARPS, args.attn_warps))
-    s, code_build_ms = build_session(cfg, device, lru=args.lru, fused_kv=not args.separate_kv)
+    with_lru = not args.no_lru and cfg.name in ("headline", "cfg1", "cfg2")
+    lru_tokens = args.warmup + args.steps + 8
+    s, code_build_ms = build_session(cfg, device, lru=with_lru, fused_kv=not args.separate_kv,
+                                     extra_capacity=lru_tokens + 8 if with_lru else 0)
+    s.use_lru = bool(args.lru) and with_lru
     n, L = cfg.context, cfg.layers
     pos = n - 1
 
@@ -306,7 +361,7 @@ def run_ours(args, cfg):
     with ClockSampler(local) as clocks:
         ms_step = time_graph(g_all if use_graph else Eager(), args.steps, args.warmup, device, dist)
         stage_ms = {}
-        for stage in ("prepare", "scan", "attn") + (("lru",) if args.lru else ()):
+        for stage in ("prepare", "scan", "attn") + (("lru",) if s.use_lru else ()):
             g = s.capture(pos, stage) if use_graph else Eager(stage)
             stage_ms[stage] = time_graph(g, max(3, args.steps // 2), 3, device) / L
         # end to end: pinned host inputs in, outputs back, one host sync per token
@@ -327,6 +382,10 @@ def run_ours(args, cfg):
         torch.cuda.synchronize(device)
         ms_e2e = e0.elapsed_time(e1) / args.steps
         wall_e2e = (time.perf_counter() - t0) * 1e3 / args.steps
+        lru_info = None
+        if with_lru:
+            # two regimes: a slowly and a quickly drifting query (noise of 0.05 / 0.25 of a unit-variance query per token)
+            lru_info = [time_four_stage(args, cfg, s, device, dist, lru_tokens, drift) for drift in (0.05, 0.25)]
     ops.check_status(device)
     clk = clocks.summary()
     hash_weight_bytes = sum(w.numel() * w.element_size() for w in s.hash_q[0].weights + s.hash_k[0].weights)
@@ -365,7 +424,7 @@ def run_ours(args, cfg):
         "sparse_attn": {"bytes": by_attn, "us": stage_ms["attn"] * 1e3},
         "decode_prepare": {"bytes": wbytes, "us": stage_ms["prepare"] * 1e3},
     }
-    if args.lru:     # stage 3: bytes of the slot tables it walks (rows only move on misses; none in a replayed step)
+    if "lru" in stage_ms:     # stage 3 replayed at one position: every attended key is resident, only the tables are walked
         kern["lru_update"] = {"bytes": cfg.batch * cfg.kv_heads * lru_slots * 8, "us": stage_ms["lru"] * 1e3}
     for k_, d in kern.items():
         d["gbs"] = d["bytes"] / (d["us"] * 1e-6) / 1e9
@@ -380,8 +439,8 @@ def run_ours(args, cfg):
         "e2e": {"value": max(ms_e2e, wall_e2e) * 1e3 / L, "unit": UNIT,
                 "h2d_bytes_per_step": host_bytes[0], "d2h_bytes_per_step": host_bytes[1],
                 "device_ms_per_step": ms_e2e, "wall_ms_per_step": wall_e2e},
-        "gpu_launches": (5 if args.lru else 4) * L * args.steps,
-        "lru_stage": bool(args.lru),
+        "gpu_launches": (6 if args.lru and with_lru else 4) * L * args.steps,
+        "lru_stage": bool(args.lru and with_lru),
         "cuda_graph": use_graph,
         "roofline": {"bound": "hbm", "kernel": dom, "achieved": kern[dom]["gbs"], "peak": peak, "unit": "GB/s",
                      "frac": kern[dom]["frac"], "traffic": measured_traffic(cfg, dom), "peak_kind": peak_kind,
@@ -394,6 +453,8 @@ def run_ours(args, cfg):
         "clocks": clk,
         "checksum": checksum if extras else float(out_host.float().abs().sum()),
     }
+    if lru_info is not None:
+        line["four_stage"] = lru_info
     line.update(extras)
     if world == 1 and not args.no_reference_kernels and cfg.name == "headline":
         g_all = g = None
@@ -743,7 +804,8 @@ def main():
     ap.add_argument("--python-loop", action="store_true",
                     help="with --decode-steps: keep the layer loop in Python (three calls per layer) instead of sl_decode_step")
     ap.add_argument("--lru", action="store_true",
-                    help="include stage 3: update an LRU-resident K/V buffer every layer-step and attend over it")
+                    help="make the four-stage step (with the LRU update) the timed `value` instead of reporting it beside the three-stage one")
+    ap.add_argument("--no-lru", action="store_true", help="skip the four-stage measurement (stage 3: LRU-resident K/V buffer)")
     ap.add_argument("--peer", action="store_true",
                     help="with --sharded: exchange over peer memory (sl_peer_allgather) instead of NCCL all-gathers")
     ap.add_argument("--no-fused-scan", action="store_true",

@@ -290,6 +290,21 @@ int sl_lru_update(const int32_t* d_idx, int idx_capacity, const int32_t* d_cnt, 
                   int32_t* d_tok2slot, int64_t n_max, int32_t* d_slot2tok, int32_t* d_last_used,
                   int step, int32_t* d_slots_out, int32_t* d_stats, int32_t* d_status, void* stream);
 
+/* sl_lru_update with the cache geometries spelled out (backing store and resident buffers may be fused
+ * K|V caches or host memory with any strides), an optional step in DEVICE memory (*d_step, e.g. the decode
+ * position, so that a replayed CUDA graph advances the table's clock) and an optional workspace of
+ * sl_lru_workspace_bytes(B, KH, idx_capacity) bytes, zero-filled once and left zeroed by every call: with it
+ * the probe of the index list is spread over several CTAs per (b, kv head) -- the step in which (nearly)
+ * every attended key is already resident then costs a few microseconds instead of one CTA's walk over the
+ * whole list -- and only the last of them to finish handles the misses. Results are those of sl_lru_update. */
+size_t sl_lru_workspace_bytes(int B, int KH, int idx_capacity);
+int sl_lru_update_ex(const int32_t* d_idx, int idx_capacity, const int32_t* d_cnt, int B, int KH,
+                     const void* k_backing, const void* v_backing, const sl_kv_layout* backing, int elem_bytes,
+                     void* d_k_resident, void* d_v_resident, const sl_kv_layout* resident, int C,
+                     int32_t* d_tok2slot, int64_t n_max, int32_t* d_slot2tok, int32_t* d_last_used, int step,
+                     const int64_t* d_step, int32_t* d_slots_out, int32_t* d_stats, int32_t* d_status,
+                     void* d_workspace, size_t workspace_bytes, void* stream);
+
 /* Row gather for API parity with KVCache.gather (spotlight/modifiers/gpu_cache.py:100-106):
  * out[b,j,h,:] = cache[b, idx[b,h,j], h, :] for j < budget. */
 int sl_gather_rows(const void* d_cache, int64_t batch_stride, int elem_bytes,
@@ -302,9 +317,16 @@ int sl_gather_rows(const void* d_cache, int64_t batch_stride, int elem_bytes,
  * (spotlight/modifiers/spotlight_generation.py:162-164) -> sl_sparse_attn_decode.
  * Replaces the per-layer Python of the attention hook for callers that own the layer loop
  * (spotlight/modifiers/spotlight_generation.py:109-226 runs once per layer and token).
+ * With `lru` set the layer-step has four launches: ... -> sl_scan_topk -> sl_lru_update_ex (the attended keys
+ * are made resident) -> sl_sparse_attn_decode over the resident buffers.
  * Pointer tables are HOST arrays of `layers` device pointers; d_k / d_v tables (or entries) may be
  * NULL when the token's key/value are already in the caches. The scratch buffers are shared by all
  * layers (the launches are in stream order); workspaces as for the single entry points. */
+struct sl_lru_layer {
+    void* d_k_resident; void* d_v_resident;
+    int32_t* d_tok2slot; int32_t* d_slot2tok; int32_t* d_last_used;
+    int32_t* d_stats;                                /* [B,KH,2] hits and misses of the last step, or NULL */
+};
 typedef struct {
     int B, QH, KH, layers, dtype, gqa_layout;
     int sink, recent, min_remain;
@@ -326,6 +348,13 @@ typedef struct {
     void* d_scan_workspace; size_t scan_workspace_bytes;
     void* d_attn_workspace; size_t attn_workspace_bytes;
     int32_t* d_status;
+    /* stage (3), optional (lru == NULL: attention reads the caches directly): per layer the resident buffers
+     * and slot tables of sl_lru_update_ex; the step of the tables is the token's position */
+    const struct sl_lru_layer* lru;                  /* [layers] */
+    int lru_slots; int64_t lru_n_max;
+    int64_t lru_batch_stride, lru_token_stride, lru_head_stride;   /* geometry of the resident buffers, elements */
+    int32_t* d_slots;                                /* scratch [B,KH,idx_capacity] */
+    void* d_lru_workspace; size_t lru_workspace_bytes;
 } sl_decode_step_args;
 int sl_decode_step(const sl_decode_step_args* args, int64_t pos, void* stream);
 

@@ -27,6 +27,12 @@ _HP = C.POINTER(HashParamsStruct)
 _PP = C.POINTER(C.c_void_p)
 
 
+class LruLayer(C.Structure):
+    """sl_lru_layer of include/spotlight_b200.h."""
+    _fields_ = [("d_k_resident", _P), ("d_v_resident", _P), ("d_tok2slot", _P), ("d_slot2tok", _P),
+                ("d_last_used", _P), ("d_stats", _P)]
+
+
 class DecodeStepArgs(C.Structure):
     """sl_decode_step_args of include/spotlight_b200.h."""
     _fields_ = [("B", _I), ("QH", _I), ("KH", _I), ("layers", _I), ("dtype", _I), ("gqa_layout", _I),
@@ -37,7 +43,10 @@ class DecodeStepArgs(C.Structure):
                 ("d_cos", _P), ("d_sin", _P), ("d_q_rot", _P), ("d_q_codes", _P),
                 ("d_idx", _P), ("idx_capacity", _I), ("d_cnt", _P),
                 ("d_scan_workspace", _P), ("scan_workspace_bytes", _Z),
-                ("d_attn_workspace", _P), ("attn_workspace_bytes", _Z), ("d_status", _P)]
+                ("d_attn_workspace", _P), ("attn_workspace_bytes", _Z), ("d_status", _P),
+                ("lru", C.POINTER(LruLayer)), ("lru_slots", _I), ("lru_n_max", _L),
+                ("lru_batch_stride", _L), ("lru_token_stride", _L), ("lru_head_stride", _L),
+                ("d_slots", _P), ("d_lru_workspace", _P), ("lru_workspace_bytes", _Z)]
 
 class KvLayout(C.Structure):
     """sl_kv_layout of include/spotlight_b200.h (strides in elements)."""
@@ -79,6 +88,8 @@ SIGNATURES = {
     "sl_sparse_attn_decode_static": (_I, [_P, _P, _P, _I, _L, _P, _I, _P, _I, _I, _I, _I, _P, _P, _P]),
     "sl_merge_lse": (_I, [_P, _P, _I, _L, _I, _P, _P]),
     "sl_lru_update": (_I, [_P, _I, _P, _I, _I, _P, _P, _L, _I, _P, _P, _I, _P, _L, _P, _P, _I, _P, _P, _P, _P]),
+    "sl_lru_workspace_bytes": (_Z, [_I, _I, _I]),
+    "sl_lru_update_ex": (_I, [_P, _I, _P, _I, _I, _P, _P, _KV, _I, _P, _P, _KV, _I, _P, _L, _P, _P, _I, _P, _P, _P, _P, _P, _Z, _P]),
     "sl_gather_rows": (_I, [_P, _L, _I, _P, _I, _I, _I, _I, _P, _P]),
     "sl_decode_step": (_I, [C.POINTER(DecodeStepArgs), _L, _P]),
     "sl_decode_step_dev": (_I, [C.POINTER(DecodeStepArgs), C.POINTER(DecodeDev), _P]),

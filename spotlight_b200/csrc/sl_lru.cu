@@ -11,8 +11,11 @@
 //   output  the slot of every attended key, in the order of the index list, so attention over
 //           the resident buffer performs the same arithmetic as attention over the full cache.
 // The reference has no such stage; the policy is specified here and restated in the CPU checker.
-// One CTA of 1024 threads per (b, kv head); victim selection is a histogram select over ages
-// (no sort); the ordered assignments use bitmaps and block scans.
+// The common step -- (nearly) every attended key is already resident -- is spread over several CTAs per
+// (b, kv head): each probes a slice of the index list (list -> token-to-slot map, two dependent loads per
+// entry, many in flight), stamps the hits, writes their slots and records the misses in a bitmap; the
+// last CTA of the pair to finish (a ticket, nobody waits) handles the misses alone: victim selection is a
+// histogram select over ages (no sort), the ordered assignments use bitmaps and block scans.
 #include "sl_common.cuh"
 
 namespace {
@@ -25,10 +28,19 @@ constexpr int NBIN = AGE_MAX + 2;
 struct LruArgs {
     const int* idx; int cap; const int* cnt;
     int B, KH, C, step, row_bytes;
-    const unsigned char* k_back; const unsigned char* v_back; long long back_bstride;   // bytes
+    const long long* d_step;               // optional: the step (clock of the table) in device memory
+    const unsigned char* k_back; const unsigned char* v_back;
+    long long back_bstride, back_tok, back_head;     // bytes: batch row, key, kv head of the backing store
     unsigned char* k_res; unsigned char* v_res;
+    long long res_bstride, res_tok, res_head;        // bytes: batch row, slot, kv head of the resident buffers
     int* tok2slot; long long n_max; int* slot2tok; int* last_used;
     int* slots_out; int* stats; int* status;
+    // several CTAs per (b, kv head): slices of the list, the miss bitmap and the counters in global memory
+    int parts;                             // CTAs per (b, kv head); 1 = everything in one CTA
+    unsigned* g_miss;                      // [B*KH][nw] bitmap of the list entries that missed
+    unsigned* g_count;                     // [B*KH][2] hits of the step, finished CTAs (both left at zero)
+    int2* g_pairs;                         // [B*KH][cap] {key, slot} of the misses, copied by lru_copy_kernel
+    int* g_m;                              // [B*KH] number of misses of the step
 };
 
 // exclusive prefix of one value per thread over the block (thread order) and the block total
@@ -75,7 +87,7 @@ __global__ void __launch_bounds__(LT) lru_update_kernel(const LruArgs a) {
     __shared__ int wsum[LW];
     __shared__ int s_hits, s_tau, s_r;
 
-    const int h = blockIdx.x, b = blockIdx.y, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int h = blockIdx.x, b = blockIdx.y, part = blockIdx.z, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const long long bh = (long long)b * a.KH + h;
     const int n = min(a.cnt[bh], a.cap);
     const int* list = a.idx + bh * a.cap;
@@ -83,26 +95,33 @@ __global__ void __launch_bounds__(LT) lru_update_kernel(const LruArgs a) {
     int* t2s = a.tok2slot + bh * a.n_max;
     int* s2t = a.slot2tok + bh * a.C;
     int* lu = a.last_used + bh * a.C;
-    const int t = a.step;
+    const int t = a.d_step ? (int)__ldg(a.d_step) : a.step;
     const unsigned lt = (1u << lane) - 1u;
+    unsigned* gm = a.parts > 1 ? a.g_miss + bh * nw : nullptr;    // one CTA keeps its bitmap in shared memory
 
     if (tid == 0) s_hits = 0;
     for (int i = tid; i < NBIN; i += LT) hist[i] = 0;
     __syncthreads();
     if (n > a.C) {                          // the table cannot hold this step's attended set
-        if (tid == 0 && a.status) atomicExch(a.status, 3);
+        if (tid == 0 && part == 0) {
+            if (a.status) atomicExch(a.status, 3);
+            if (a.g_m) a.g_m[bh] = 0;
+        }
         return;
     }
 
     // ---- hits: stamp their slots; misses go into a bitmap (eight entries per thread and round, so
-    // that the two dependent loads of an entry cost one trip to memory per round, not per entry)
+    // that the two dependent loads of an entry cost one trip to memory per round, not per entry).
+    // This CTA's slice of the list: whole bitmap words [w0, w1).
+    const int wpp = (nw + a.parts - 1) / a.parts;
+    const int w0 = min(nw, part * wpp), w1 = min(nw, w0 + wpp);
     int myhits = 0;
-    for (int j0 = warp * 32; j0 < nw * 32; j0 += LT * 8) {
+    for (int j0 = w0 * 32 + warp * 32; j0 < w1 * 32; j0 += LT * 8) {
         int tok[8], sl_[8];
 #pragma unroll
         for (int u = 0; u < 8; ++u) {
             const int j = j0 + u * LT + lane;
-            tok[u] = j < n ? __ldg(list + j) : -1;
+            tok[u] = (j < n && j < w1 * 32) ? __ldg(list + j) : -1;
         }
 #pragma unroll
         for (int u = 0; u < 8; ++u) sl_[u] = tok[u] >= 0 ? t2s[tok[u]] : -1;
@@ -114,15 +133,41 @@ __global__ void __launch_bounds__(LT) lru_update_kernel(const LruArgs a) {
                 out[j] = sl_[u];
             }
             const unsigned mb = __ballot_sync(0xffffffffu, tok[u] >= 0 && sl_[u] < 0);
-            if (lane == 0 && (j0 + u * LT) < nw * 32) m_miss[(j0 + u * LT) >> 5] = mb;
+            if (lane == 0 && (j0 + u * LT) < w1 * 32) {
+                if (gm) gm[(j0 + u * LT) >> 5] = mb;
+                else m_miss[(j0 + u * LT) >> 5] = mb;
+            }
         }
     }
     myhits = __reduce_add_sync(0xffffffffu, myhits);
     if (lane == 0 && myhits) atomicAdd(&s_hits, myhits);
     __syncthreads();
+    if (a.parts > 1) {
+        // ticket: the CTA that finds the other slices done goes on (with everybody's hits and misses)
+        __shared__ int s_last;
+        if (tid == 0) {
+            unsigned* cnt2 = a.g_count + bh * 2;
+            if (s_hits) atomicAdd(cnt2, (unsigned)s_hits);
+            __threadfence();                                // this slice's stamps, slots and bitmap words first
+            const unsigned old = atomicAdd(cnt2 + 1, 1u);
+            s_last = old == (unsigned)a.parts - 1u;
+            if (s_last) {
+                __threadfence();
+                s_hits = (int)atomicExch(cnt2, 0u);         // both counters are left at zero for the next step
+                cnt2[1] = 0u;
+            }
+        }
+        __syncthreads();
+        if (!s_last) return;
+        for (int w = tid; w < nw; w += LT) m_miss[w] = __ldcg(gm + w);
+        __syncthreads();
+    }
     const int m = n - s_hits;              // misses = victims needed
     if (m == 0) {                           // everything was resident: nothing to evict or copy
-        if (tid == 0 && a.stats) { a.stats[bh * 2] = s_hits; a.stats[bh * 2 + 1] = 0; }
+        if (tid == 0) {
+            if (a.stats) { a.stats[bh * 2] = s_hits; a.stats[bh * 2 + 1] = 0; }
+            if (a.g_m) a.g_m[bh] = 0;
+        }
         return;
     }
 
@@ -130,7 +175,7 @@ __global__ void __launch_bounds__(LT) lru_update_kernel(const LruArgs a) {
     for (int s0 = tid; s0 < a.C; s0 += LT * 8) {
         int l[8];
 #pragma unroll
-        for (int u = 0; u < 8; ++u) l[u] = s0 + u * LT < a.C ? lu[s0 + u * LT] : t;
+        for (int u = 0; u < 8; ++u) l[u] = s0 + u * LT < a.C ? __ldcg(lu + s0 + u * LT) : t;   // other slices stamped hits
 #pragma unroll
         for (int u = 0; u < 8; ++u) {
             if (s0 + u * LT < a.C) {
@@ -243,31 +288,104 @@ __global__ void __launch_bounds__(LT) lru_update_kernel(const LruArgs a) {
     }
     __syncthreads();
 
-    // ---- copy the missing rows from the backing store into their slots (16-byte lanes)
-    const int lanes = a.row_bytes >> 4;                 // 16 (2-byte types) or 32 (4-byte types)
-    const int groups = LT / lanes, grp = tid / lanes, c = tid % lanes;
-    const long long row_stride = (long long)a.KH * a.row_bytes;
-    const unsigned char* kb = a.k_back + b * a.back_bstride + (long long)h * a.row_bytes + c * 16;
-    const unsigned char* vb = a.v_back + b * a.back_bstride + (long long)h * a.row_bytes + c * 16;
-    unsigned char* kr = a.k_res + ((long long)b * a.C * a.KH + h) * a.row_bytes + c * 16;
-    unsigned char* vr = a.v_res + ((long long)b * a.C * a.KH + h) * a.row_bytes + c * 16;
-    for (int i = grp; i < m; i += groups) {
-        const long long src = (long long)misstok[i] * row_stride, dst = (long long)victims[i] * row_stride;
-        const uint4 kv = *reinterpret_cast<const uint4*>(kb + src);
-        const uint4 vv = *reinterpret_cast<const uint4*>(vb + src);
-        *reinterpret_cast<uint4*>(kr + dst) = kv;
-        *reinterpret_cast<uint4*>(vr + dst) = vv;
+    if (a.g_pairs) {
+        // the rows are copied by the launch that follows (many CTAs): leave it the {key, slot} pairs
+        int2* pairs = a.g_pairs + bh * a.cap;
+        for (int i = tid; i < m; i += LT) pairs[i] = make_int2(misstok[i], victims[i]);
+        if (tid == 0) a.g_m[bh] = m;
+    } else {
+        // ---- copy the missing rows from the backing store into their slots (16-byte lanes, four rows in flight per group)
+        const int lanes = a.row_bytes >> 4;                 // 16 (2-byte types) or 32 (4-byte types)
+        const int groups = LT / lanes, grp = tid / lanes, c = tid % lanes;
+        const unsigned char* kb = a.k_back + b * a.back_bstride + (long long)h * a.back_head + c * 16;
+        const unsigned char* vb = a.v_back + b * a.back_bstride + (long long)h * a.back_head + c * 16;
+        unsigned char* kr = a.k_res + b * a.res_bstride + (long long)h * a.res_head + c * 16;
+        unsigned char* vr = a.v_res + b * a.res_bstride + (long long)h * a.res_head + c * 16;
+        for (int i0 = grp; i0 < m; i0 += 4 * groups) {
+            uint4 kv[4], vv[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const int i = i0 + u * groups;
+                if (i < m) {
+                    const long long src = (long long)misstok[i] * a.back_tok;
+                    kv[u] = *reinterpret_cast<const uint4*>(kb + src);
+                    vv[u] = *reinterpret_cast<const uint4*>(vb + src);
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const int i = i0 + u * groups;
+                if (i < m) {
+                    const long long dst = (long long)victims[i] * a.res_tok;
+                    *reinterpret_cast<uint4*>(kr + dst) = kv[u];
+                    *reinterpret_cast<uint4*>(vr + dst) = vv[u];
+                }
+            }
+        }
     }
     if (tid == 0 && a.stats) { a.stats[bh * 2] = s_hits; a.stats[bh * 2 + 1] = m; }
 }
 
+// The rows of the step's misses, copied from the backing store into their slots by CP CTAs per (b, kv head):
+// the {key, slot} pairs and their number come from lru_update_kernel; 16-byte lanes, four rows in flight per group.
+constexpr int CT = 256;
+__global__ void __launch_bounds__(CT) lru_copy_kernel(const LruArgs a) {
+    sl::pdl_trigger();
+    sl::pdl_wait();
+    const int h = blockIdx.y, b = blockIdx.z, tid = threadIdx.x;
+    const long long bh = (long long)b * a.KH + h;
+    const int m = a.g_m[bh];
+    if (m <= 0) return;
+    const int2* pairs = a.g_pairs + bh * a.cap;
+    const int lanes = a.row_bytes >> 4, groups = CT / lanes, grp = tid / lanes, c = tid % lanes;
+    const unsigned char* kb = a.k_back + b * a.back_bstride + (long long)h * a.back_head + c * 16;
+    const unsigned char* vb = a.v_back + b * a.back_bstride + (long long)h * a.back_head + c * 16;
+    unsigned char* kr = a.k_res + b * a.res_bstride + (long long)h * a.res_head + c * 16;
+    unsigned char* vr = a.v_res + b * a.res_bstride + (long long)h * a.res_head + c * 16;
+    const int stride = gridDim.x * groups;
+    for (int i0 = blockIdx.x * groups + grp; i0 < m; i0 += 4 * stride) {
+        int2 p[4];
+        uint4 kv[4], vv[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const int i = i0 + u * stride;
+            p[u] = i < m ? __ldcg(pairs + i) : make_int2(0, 0);
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            if (i0 + u * stride < m) {
+                const long long src = (long long)p[u].x * a.back_tok;
+                kv[u] = *reinterpret_cast<const uint4*>(kb + src);
+                vv[u] = *reinterpret_cast<const uint4*>(vb + src);
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            if (i0 + u * stride < m) {
+                const long long dst = (long long)p[u].y * a.res_tok;
+                *reinterpret_cast<uint4*>(kr + dst) = kv[u];
+                *reinterpret_cast<uint4*>(vr + dst) = vv[u];
+            }
+        }
+    }
+}
+
 }  // namespace
 
-extern "C" int sl_lru_update(const int32_t* d_idx, int idx_capacity, const int32_t* d_cnt, int B, int KH,
-                             const void* k_backing, const void* v_backing, int64_t backing_batch_stride, int elem_bytes,
-                             void* d_k_resident, void* d_v_resident, int C, int32_t* d_tok2slot, int64_t n_max,
-                             int32_t* d_slot2tok, int32_t* d_last_used, int step, int32_t* d_slots_out,
-                             int32_t* d_stats, int32_t* d_status, void* stream) {
+namespace {
+
+int lru_parts(int B, int KH, int idx_capacity) {
+    // enough CTAs to put every SM to work on the probe, at least 1024 list entries (one round of a CTA) each
+    const int by_work = std::max(1, idx_capacity / 1024);
+    const int by_sms = std::max(1, sl::sm_count() / std::max(1, B * KH));
+    return std::max(1, std::min(std::min(by_work, by_sms), 64));
+}
+
+int lru_launch(const int32_t* d_idx, int idx_capacity, const int32_t* d_cnt, int B, int KH, const void* k_backing,
+               const void* v_backing, const sl_kv_layout& back, int elem_bytes, void* d_k_resident, void* d_v_resident,
+               const sl_kv_layout& res, int C, int32_t* d_tok2slot, int64_t n_max, int32_t* d_slot2tok,
+               int32_t* d_last_used, int step, const int64_t* d_step, int32_t* d_slots_out, int32_t* d_stats,
+               int32_t* d_status, void* d_workspace, size_t workspace_bytes, void* stream) {
     SL_REQUIRE(d_idx && d_cnt && k_backing && v_backing && d_k_resident && d_v_resident && d_tok2slot && d_slot2tok &&
                    d_last_used && d_slots_out,
                SL_EINVAL, "sl_lru_update: null pointer");
@@ -275,23 +393,79 @@ extern "C" int sl_lru_update(const int32_t* d_idx, int idx_capacity, const int32
                "sl_lru_update: bad shape");
     SL_REQUIRE(elem_bytes == 2 || elem_bytes == 4, SL_EINVAL, "sl_lru_update: elem_bytes must be 2 or 4");
     SL_REQUIRE(sl::aligned16(k_backing) && sl::aligned16(v_backing) && sl::aligned16(d_k_resident) &&
-                   sl::aligned16(d_v_resident) && (backing_batch_stride * elem_bytes) % 16 == 0,
+                   sl::aligned16(d_v_resident),
                SL_EALIGN, "sl_lru_update: K/V buffers must be 16-byte aligned");
+    for (const sl_kv_layout* l : {&back, &res})
+        SL_REQUIRE((l->batch_stride * elem_bytes) % 16 == 0 && (l->token_stride * elem_bytes) % 16 == 0 &&
+                       (l->head_stride * elem_bytes) % 16 == 0 && l->token_stride >= 128 && l->head_stride >= 128,
+                   SL_EALIGN, "sl_lru_update: cache strides must be multiples of 16 bytes and hold a 128-value row");
     const size_t cw = ((size_t)C + 31) / 32, nw = ((size_t)idx_capacity + 31) / 32;
     const size_t smem = (size_t)idx_capacity * 2 * sizeof(int) + cw * 16 + nw * 8 + (size_t)C * 2 + 16;
     SL_REQUIRE(smem <= 220 * 1024, SL_ESHAPE, "sl_lru_update: idx_capacity %d / %d slots too large for shared memory",
                idx_capacity, C);
-    LruArgs a;
+    LruArgs a = {};
     a.idx = d_idx; a.cap = idx_capacity; a.cnt = d_cnt;
     a.B = B; a.KH = KH; a.C = C; a.step = step; a.row_bytes = 128 * elem_bytes;
+    a.d_step = reinterpret_cast<const long long*>(d_step);
     a.k_back = static_cast<const unsigned char*>(k_backing); a.v_back = static_cast<const unsigned char*>(v_backing);
-    a.back_bstride = backing_batch_stride * elem_bytes;
+    a.back_bstride = back.batch_stride * elem_bytes; a.back_tok = back.token_stride * elem_bytes; a.back_head = back.head_stride * elem_bytes;
     a.k_res = static_cast<unsigned char*>(d_k_resident); a.v_res = static_cast<unsigned char*>(d_v_resident);
+    a.res_bstride = res.batch_stride * elem_bytes; a.res_tok = res.token_stride * elem_bytes; a.res_head = res.head_stride * elem_bytes;
     a.tok2slot = d_tok2slot; a.n_max = n_max; a.slot2tok = d_slot2tok; a.last_used = d_last_used;
     a.slots_out = d_slots_out; a.stats = d_stats; a.status = d_status;
+    a.parts = 1;
+    if (d_workspace) {
+        SL_REQUIRE(workspace_bytes >= sl_lru_workspace_bytes(B, KH, idx_capacity), SL_EWORKSPACE,
+                   "sl_lru_update_ex: workspace %zu < required %zu", workspace_bytes, sl_lru_workspace_bytes(B, KH, idx_capacity));
+        SL_REQUIRE(sl::aligned16(d_workspace), SL_EALIGN, "sl_lru_update_ex: workspace not 16-byte aligned");
+        a.parts = lru_parts(B, KH, idx_capacity);
+        a.g_count = static_cast<unsigned*>(d_workspace);
+        a.g_m = reinterpret_cast<int*>(a.g_count + (((size_t)B * KH * 2 + 63) / 64) * 64);
+        a.g_miss = reinterpret_cast<unsigned*>(a.g_m + (((size_t)B * KH + 63) / 64) * 64);
+        a.g_pairs = reinterpret_cast<int2*>(a.g_miss + (((size_t)B * KH * nw + 3) / 4) * 4);
+    }
     SL_CUDA_OK(sl::ensure_dyn_smem(reinterpret_cast<const void*>(lru_update_kernel), smem));
-    dim3 grid((unsigned)KH, (unsigned)B);
+    dim3 grid((unsigned)KH, (unsigned)B, (unsigned)a.parts);
     lru_update_kernel<<<grid, LT, smem, static_cast<cudaStream_t>(stream)>>>(a);
     SL_CUDA_OK(cudaGetLastError());
+    if (a.g_pairs) {
+        const int cp = std::max(1, std::min(32, sl::sm_count() / std::max(1, B * KH)));
+        SL_CUDA_OK(sl::launch_kernel(lru_copy_kernel, dim3((unsigned)cp, (unsigned)KH, (unsigned)B), dim3(CT), 0,
+                                     static_cast<cudaStream_t>(stream), false, a));
+    }
     return SL_OK;
+}
+
+}  // namespace
+
+extern "C" size_t sl_lru_workspace_bytes(int B, int KH, int idx_capacity) {
+    if (B <= 0 || KH <= 0 || idx_capacity <= 0) return 0;
+    const size_t nw = ((size_t)idx_capacity + 31) / 32;
+    // counters, misses per pair, miss bitmaps, {key, slot} pairs of the misses
+    return ((((size_t)B * KH * 2 + 63) / 64) * 64 + (((size_t)B * KH + 63) / 64) * 64 + (((size_t)B * KH * nw + 3) / 4) * 4) * 4 +
+           (size_t)B * KH * idx_capacity * 8;
+}
+
+extern "C" int sl_lru_update(const int32_t* d_idx, int idx_capacity, const int32_t* d_cnt, int B, int KH,
+                             const void* k_backing, const void* v_backing, int64_t backing_batch_stride, int elem_bytes,
+                             void* d_k_resident, void* d_v_resident, int C, int32_t* d_tok2slot, int64_t n_max,
+                             int32_t* d_slot2tok, int32_t* d_last_used, int step, int32_t* d_slots_out,
+                             int32_t* d_stats, int32_t* d_status, void* stream) {
+    const sl_kv_layout back = {backing_batch_stride, (int64_t)KH * 128, 128, 1};
+    const sl_kv_layout res = {(int64_t)C * KH * 128, (int64_t)KH * 128, 128, 1};
+    return lru_launch(d_idx, idx_capacity, d_cnt, B, KH, k_backing, v_backing, back, elem_bytes, d_k_resident, d_v_resident,
+                      res, C, d_tok2slot, n_max, d_slot2tok, d_last_used, step, nullptr, d_slots_out, d_stats, d_status,
+                      nullptr, 0, stream);
+}
+
+extern "C" int sl_lru_update_ex(const int32_t* d_idx, int idx_capacity, const int32_t* d_cnt, int B, int KH,
+                                const void* k_backing, const void* v_backing, const sl_kv_layout* backing, int elem_bytes,
+                                void* d_k_resident, void* d_v_resident, const sl_kv_layout* resident, int C,
+                                int32_t* d_tok2slot, int64_t n_max, int32_t* d_slot2tok, int32_t* d_last_used, int step,
+                                const int64_t* d_step, int32_t* d_slots_out, int32_t* d_stats, int32_t* d_status,
+                                void* d_workspace, size_t workspace_bytes, void* stream) {
+    SL_REQUIRE(backing && resident, SL_EINVAL, "sl_lru_update_ex: null cache layout");
+    return lru_launch(d_idx, idx_capacity, d_cnt, B, KH, k_backing, v_backing, *backing, elem_bytes, d_k_resident,
+                      d_v_resident, *resident, C, d_tok2slot, n_max, d_slot2tok, d_last_used, step, d_step, d_slots_out,
+                      d_stats, d_status, d_workspace, workspace_bytes, stream);
 }

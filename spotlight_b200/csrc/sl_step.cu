@@ -17,6 +17,9 @@ int run_layers(const sl_decode_step_args* a, int64_t pos, const sl_decode_dev* d
     SL_REQUIRE(a->layers > 0 && a->d_q && a->d_out && a->hash_q && a->d_code_cache && a->d_k_cache && a->d_v_cache,
                SL_EINVAL, "sl_decode_step: null pointer table");
     SL_REQUIRE(pos >= 0, SL_ESHAPE, "sl_decode_step: negative position");
+    SL_REQUIRE(a->lru == nullptr || (a->d_slots && a->lru_slots > 0 && a->lru_n_max > 0 && a->lru_token_stride >= 128 &&
+                                     a->lru_head_stride >= 128),
+               SL_EINVAL, "sl_decode_step: incomplete description of the LRU-resident buffers");
     SL_REQUIRE((a->kv_token_stride == 0) == (a->kv_head_stride == 0), SL_EINVAL,
                "sl_decode_step: kv_token_stride and kv_head_stride must be given together");
     const sl_kv_layout kv = {a->kv_batch_stride, a->kv_token_stride ? a->kv_token_stride : (int64_t)a->KH * 128,
@@ -49,9 +52,23 @@ int run_layers(const sl_decode_step_args* a, int64_t pos, const sl_decode_dev* d
                                 a->scan_workspace_bytes, a->d_status, dev ? dp.d_pos : nullptr, a->mask_out, a->min_remain,
                                 stream);
         if (rc) return rc;
-        rc = sl_sparse_attn_decode_ex(a->d_q_rot, a->d_k_cache[l], a->d_v_cache[l], a->dtype, &kv, a->d_idx,
-                                      a->idx_capacity, a->d_cnt, a->B, a->KH, a->QH, a->gqa_layout, a->d_out[l], nullptr,
-                                      a->d_attn_workspace, a->attn_workspace_bytes, stream);
+        if (a->lru) {
+            const sl_lru_layer& t = a->lru[l];
+            const sl_kv_layout res = {a->lru_batch_stride, a->lru_token_stride, a->lru_head_stride, 1};
+            rc = sl_lru_update_ex(a->d_idx, a->idx_capacity, a->d_cnt, a->B, a->KH, a->d_k_cache[l], a->d_v_cache[l], &kv,
+                                  a->dtype == SL_F32 ? 4 : 2, t.d_k_resident, t.d_v_resident, &res, a->lru_slots, t.d_tok2slot,
+                                  a->lru_n_max, t.d_slot2tok, t.d_last_used, (int)pos,
+                                  dev ? reinterpret_cast<const int64_t*>(dp.d_pos) : nullptr, a->d_slots, t.d_stats,
+                                  a->d_status, a->d_lru_workspace, a->lru_workspace_bytes, stream);
+            if (rc) return rc;
+            rc = sl_sparse_attn_decode_ex(a->d_q_rot, t.d_k_resident, t.d_v_resident, a->dtype, &res, a->d_slots,
+                                          a->idx_capacity, a->d_cnt, a->B, a->KH, a->QH, a->gqa_layout, a->d_out[l], nullptr,
+                                          a->d_attn_workspace, a->attn_workspace_bytes, stream);
+        } else {
+            rc = sl_sparse_attn_decode_ex(a->d_q_rot, a->d_k_cache[l], a->d_v_cache[l], a->dtype, &kv, a->d_idx,
+                                          a->idx_capacity, a->d_cnt, a->B, a->KH, a->QH, a->gqa_layout, a->d_out[l], nullptr,
+                                          a->d_attn_workspace, a->attn_workspace_bytes, stream);
+        }
         if (rc) return rc;
     }
     if (dev && dev->advance)

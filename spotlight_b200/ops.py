@@ -414,42 +414,61 @@ def sparse_attn_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Te
 
 
 class LruTable:
-    """Resident K/V buffers [B,C,KH,128] and the slot tables of one layer (see sl_lru_update)."""
+    """Resident K/V buffers and the slot tables of one layer (see sl_lru_update). The buffers are
+    [B,C,KH,128] each, or -- fused=True -- the halves of one [B,C,KH,2,128] buffer, in which a slot's K and
+    V rows are adjacent like the rows of a fused cache."""
 
-    def __init__(self, batch: int, kv_heads: int, n_max: int, slots: int, dtype: torch.dtype, device):
+    def __init__(self, batch: int, kv_heads: int, n_max: int, slots: int, dtype: torch.dtype, device, fused: bool = False):
         self.B, self.KH, self.n_max, self.C = batch, kv_heads, n_max, slots
-        self.k = torch.zeros((batch, slots, kv_heads, 128), dtype=dtype, device=device)
-        self.v = torch.zeros((batch, slots, kv_heads, 128), dtype=dtype, device=device)
+        if fused:
+            self.kv = torch.zeros((batch, slots, kv_heads, 2, 128), dtype=dtype, device=device)
+            self.k, self.v = self.kv[:, :, :, 0], self.kv[:, :, :, 1]
+        else:
+            self.k = torch.zeros((batch, slots, kv_heads, 128), dtype=dtype, device=device)
+            self.v = torch.zeros((batch, slots, kv_heads, 128), dtype=dtype, device=device)
         self.tok2slot = torch.full((batch, kv_heads, n_max), -1, dtype=torch.int32, device=device)
         self.slot2tok = torch.full((batch, kv_heads, slots), -1, dtype=torch.int32, device=device)
         self.last_used = torch.full((batch, kv_heads, slots), -1, dtype=torch.int32, device=device)
         self.stats = torch.zeros((batch, kv_heads, 2), dtype=torch.int32, device=device)
         self.status = torch.zeros(1, dtype=torch.int32, device=device)
+        self.ws = None              # workspace of the multi-CTA probe, sized at the first update
         self.step = 0
 
 
 def lru_update(table: LruTable, idx: torch.Tensor, cnt: torch.Tensor, k_backing: torch.Tensor,
-               v_backing: torch.Tensor, slots_out: Optional[torch.Tensor] = None, backing_ptrs=None) -> torch.Tensor:
+               v_backing: torch.Tensor, slots_out: Optional[torch.Tensor] = None, backing_ptrs=None,
+               step_dev: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Make this step's attended keys resident; returns their slots int32 [B,KH,cap] in list order.
-    k_backing / v_backing: [B,N,KH,128] device tensors (views of a larger cache are fine), or pass
-    backing_ptrs=(k_ptr, v_ptr, batch_stride_elems) for mapped pinned host memory."""
+    k_backing / v_backing: [B,N,KH,128] device tensors (views of a larger or fused cache are fine), or pass
+    backing_ptrs=(k_ptr, v_ptr, batch_stride_elems) for mapped pinned host memory in the two-cache layout.
+    step_dev: int64 device tensor holding the step (the table's clock), e.g. the decode position, so that
+    a replayed CUDA graph advances it; else the table's host-side counter is used and incremented."""
     B, KH, cap = idx.shape
     dev = _cuda(idx, cnt, table.k)
     assert idx.is_contiguous() and cnt.is_contiguous() and (B, KH) == (table.B, table.KH)
     if slots_out is None:
         slots_out = torch.empty_like(idx)
     if backing_ptrs is None:
-        kb = _rows_view(k_backing, 128)
-        assert _rows_view(v_backing, 128) == kb and k_backing.dtype == table.k.dtype
+        back = _kv_layout(k_backing)
+        b2 = _kv_layout(v_backing)
+        assert (b2.batch_stride, b2.token_stride, b2.head_stride) == (back.batch_stride, back.token_stride, back.head_stride)
+        assert k_backing.dtype == table.k.dtype
         kp, vp = k_backing.data_ptr(), v_backing.data_ptr()
     else:
         kp, vp, kb = backing_ptrs
-    check(lib.sl_lru_update(idx.data_ptr(), cap, cnt.data_ptr(), B, KH, kp, vp, kb, table.k.element_size(),
-                            table.k.data_ptr(), table.v.data_ptr(), table.C, table.tok2slot.data_ptr(), table.n_max,
-                            table.slot2tok.data_ptr(), table.last_used.data_ptr(), table.step, slots_out.data_ptr(),
-                            table.stats.data_ptr(), table.status.data_ptr(), _stream()))
-    table.step += 1
-    _count()
+        back = _lib.KvLayout(kb, KH * 128, 128, 1)
+    res = _kv_layout(table.k)
+    need = lib.sl_lru_workspace_bytes(B, KH, cap)
+    if table.ws is None or table.ws.numel() < need:
+        table.ws = torch.zeros(need, dtype=torch.uint8, device=dev)
+    check(lib.sl_lru_update_ex(idx.data_ptr(), cap, cnt.data_ptr(), B, KH, kp, vp, C.byref(back), table.k.element_size(),
+                               table.k.data_ptr(), table.v.data_ptr(), C.byref(res), table.C, table.tok2slot.data_ptr(),
+                               table.n_max, table.slot2tok.data_ptr(), table.last_used.data_ptr(), table.step,
+                               _ptr(step_dev), slots_out.data_ptr(), table.stats.data_ptr(), table.status.data_ptr(),
+                               table.ws.data_ptr(), table.ws.numel(), _stream()))
+    if step_dev is None:
+        table.step += 1
+    _count(2)        # the update and the row copy
     return slots_out
 
 

@@ -48,7 +48,7 @@ class DecodeSession:
         B, QH, KH, L, C = cfg.batch, cfg.q_heads, cfg.kv_heads, cfg.layers, cfg.capacity
         dev, dt = self.device, cfg.dtype
         self.hash_q, self.hash_k = hash_q, hash_k
-        if cfg.fused_kv and cfg.lru_slots == 0:
+        if cfg.fused_kv:
             # a gathered key is then ONE 512-byte piece of memory: k_cache / v_cache are strided views
             self.kv_cache = [torch.empty((B, C, KH, 2, 128), dtype=dt, device=dev) for _ in range(L)]
             self.k_cache = [kv[:, :, :, 0] for kv in self.kv_cache]
@@ -75,8 +75,9 @@ class DecodeSession:
         # attention reads that buffer through the slots the update returns
         self.lru = None
         if cfg.lru_slots > 0:
-            self.lru = [ops.LruTable(B, KH, C, cfg.lru_slots, dt, dev) for _ in range(L)]
+            self.lru = [ops.LruTable(B, KH, C, cfg.lru_slots, dt, dev, fused=cfg.fused_kv) for _ in range(L)]
             self.slots = torch.empty_like(self.idx)
+        self.use_lru = self.lru is not None      # stage 3 can be switched off to time the three-stage step on the same caches
         self._graphs = {}
         self._host = None
         # device-side position: one captured step serves every token (see step_dev)
@@ -128,11 +129,11 @@ class DecodeSession:
                 raise NotImplementedError("dense layers are served by the attention hook, not the session")
             ops.scan_topk(self.q_codes, self.codes[layer][:, :n], budget(n, c.mask_out, c.min_remain), c.sink,
                           c.recent, c.layout, idx=self.idx, cnt=self.cnt)
-        if self.lru is not None and stage in (None, "lru"):
+        if self.lru is not None and self.use_lru and stage in (None, "lru"):
             ops.lru_update(self.lru[layer], self.idx, self.cnt, self.k_cache[layer][:, :n], self.v_cache[layer][:, :n],
                            slots_out=self.slots)
         if stage in (None, "attn"):
-            if self.lru is not None:
+            if self.lru is not None and self.use_lru:
                 ops.sparse_attn_decode(self.q_rot, self.lru[layer].k, self.lru[layer].v, self.slots, self.cnt, c.layout,
                                        out=self.out[layer])
             else:
@@ -147,8 +148,10 @@ class DecodeSession:
         import ctypes as C
         from . import _lib
         c = self.cfg
-        assert self.lru is None and not c.fix_layers
+        assert not c.fix_layers
         if getattr(self, "_native", None) is None:
+            self._native = {}
+        if self.use_lru not in self._native:
             L = c.layers
             arr = lambda ts: (C.c_void_p * L)(*[t.data_ptr() for t in ts])
             a = _lib.DecodeStepArgs()
@@ -177,8 +180,22 @@ class DecodeSession:
             a.d_scan_workspace, a.scan_workspace_bytes = sw.data_ptr(), sw.numel()
             a.d_attn_workspace, a.attn_workspace_bytes = aw.data_ptr(), aw.numel()
             a.d_status = status.data_ptr()
-            self._native = (a, keep, sw, aw, status)
-        return self._native[0]
+            if self.lru is not None and self.use_lru:   # stage 3: the attended keys are made resident, attention reads the resident buffers
+                keep["lru"] = (_lib.LruLayer * L)()
+                for l, t in enumerate(self.lru):
+                    keep["lru"][l].d_k_resident, keep["lru"][l].d_v_resident = t.k.data_ptr(), t.v.data_ptr()
+                    keep["lru"][l].d_tok2slot, keep["lru"][l].d_slot2tok = t.tok2slot.data_ptr(), t.slot2tok.data_ptr()
+                    keep["lru"][l].d_last_used, keep["lru"][l].d_stats = t.last_used.data_ptr(), t.stats.data_ptr()
+                a.lru = keep["lru"]
+                a.lru_slots, a.lru_n_max = c.lru_slots, c.capacity
+                res = ops._kv_layout(self.lru[0].k)
+                a.lru_batch_stride, a.lru_token_stride, a.lru_head_stride = res.batch_stride, res.token_stride, res.head_stride
+                a.d_slots = self.slots.data_ptr()
+                need = _lib.lib.sl_lru_workspace_bytes(c.batch, c.kv_heads, self.idx.shape[2])
+                keep["lru_ws"] = torch.zeros(need, dtype=torch.uint8, device=self.device)
+                a.d_lru_workspace, a.lru_workspace_bytes = keep["lru_ws"].data_ptr(), need
+            self._native[self.use_lru] = (a, keep, sw, aw, status)
+        return self._native[self.use_lru][0]
 
     def step_native(self, pos: int):
         """`step(pos)` with the layer loop in the library (sl_decode_step): one call per token instead
@@ -187,7 +204,7 @@ class DecodeSession:
         from . import _lib
         _lib.check(_lib.lib.sl_decode_step(C.byref(self._native_args()), pos,
                                            torch.cuda.current_stream(self.device).cuda_stream))
-        ops.launch_count += 3 * self.cfg.layers
+        ops.launch_count += (6 if self.use_lru else 4) * self.cfg.layers
 
     def step_dev(self, max_context: Optional[int] = None, advance: bool = True):
         """One token at the position held in `self.pos_dev` (device memory): the launches depend on no
@@ -204,13 +221,13 @@ class DecodeSession:
         d.advance = int(advance)
         _lib.check(_lib.lib.sl_decode_step_dev(C.byref(self._native_args()), C.byref(d),
                                                torch.cuda.current_stream(self.device).cuda_stream))
-        ops.launch_count += 3 * self.cfg.layers + int(advance)
+        ops.launch_count += (6 if self.use_lru else 4) * self.cfg.layers + int(advance)
 
     def capture_dev(self, host_io: bool = False, max_context: Optional[int] = None) -> torch.cuda.CUDAGraph:
         """One CUDA graph for every token: step_dev (which advances the device-side position at its end),
         optionally with the pinned-host copies of the token's inputs and outputs around it. The warm-up
         run outside the capture executes one token: set `pos_dev` afterwards."""
-        key = ("dev", host_io, max_context)
+        key = ("dev", host_io, max_context, self.use_lru)
         if key in self._graphs:
             return self._graphs[key]
         if host_io:
@@ -244,7 +261,7 @@ class DecodeSession:
     def capture(self, pos: int, stage: Optional[str] = None, host_io: bool = False) -> torch.cuda.CUDAGraph:
         """Capture `step(pos)` (optionally one stage only, optionally with the pinned-host copies)
         into a CUDA graph; replays reuse the same position and buffers."""
-        key = (pos, stage, host_io)
+        key = (pos, stage, host_io, self.use_lru)
         if key in self._graphs:
             return self._graphs[key]
         if host_io:

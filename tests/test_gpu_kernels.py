@@ -462,17 +462,24 @@ def test_errors_are_exceptions_not_crashes(ops):
 
 # ------------------------------------------------------------------------------------------ LRU
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
-@pytest.mark.parametrize("B,KH,N,C,keep", [(2, 4, 3000, 400, 300), (1, 8, 5000, 1500, 1400), (3, 2, 200, 64, 64)])
+@pytest.mark.parametrize("B,KH,N,C,keep", [(2, 4, 3000, 400, 300), (1, 8, 5000, 1500, 1400), (3, 2, 200, 64, 64),
+                                           (1, 4, 60000, 9000, 4200), (2, 2, 40000, 14000, 6500)])
 def test_lru_resident_buffer_is_results_invisible(ops, dtype, B, KH, N, C, keep):
     """A dozen decode steps with drifting attended sets: slot tables bit-exact against the CPU
     model of the policy, resident rows equal to the backing rows, and attention over the resident
-    buffer bit-identical to attention over the full cache."""
+    buffer bit-identical to attention over the full cache. The long lists are probed by several CTAs
+    per (row, kv head); the last of them handles the misses. Fused K|V buffers on both sides in the
+    bf16 runs of the long lists."""
     QH = KH * 2
     g = torch.Generator().manual_seed(B * 100 + C)
     k = torch.randn((B, N, KH, 128), generator=g).to(dtype)
     v = torch.randn((B, N, KH, 128), generator=g).to(dtype)
     kd, vd = k.to(DEV), v.to(DEV)
-    table = ops.LruTable(B, KH, N, C, dtype, DEV)
+    fused = keep > 4000 and dtype == torch.bfloat16
+    if fused:
+        kvd = torch.stack([kd, vd], dim=3)                           # [B,N,KH,2,128]
+        kd, vd = kvd[:, :, :, 0], kvd[:, :, :, 1]
+    table = ops.LruTable(B, KH, N, C, dtype, DEV, fused=fused)
     models = [[O.LruModel(N, C) for _ in range(KH)] for _ in range(B)]
     pool = [[torch.randperm(N, generator=g)[: 2 * keep] for _ in range(KH)] for _ in range(B)]   # working set
     for step in range(12):

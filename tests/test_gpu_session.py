@@ -124,3 +124,45 @@ def test_fused_and_separate_caches_agree():
         torch.cuda.synchronize()
         assert torch.equal(a.out, c.out)
     ops.check_status()
+
+
+def test_four_stage_step_with_a_device_side_clock():
+    """hash -> scan + top-k -> LRU update -> attention over the resident buffers, as ONE replayed graph with
+    the position (and with it the LRU clock) in device memory: outputs must equal the three-stage step's bit
+    for bit (the stage is results-invisible), and the tables must register hits once the selections overlap."""
+    import dataclasses
+    from spotlight_b200 import ops
+    from spotlight_b200.session import DecodeSession
+    from spotlight_b200.workloads import budget
+    a, ga, n = _session(seed=13, extra=12)
+    b0, gb, _ = _session(seed=13, extra=12)
+    slots = 2 * (budget(n + 12, a.cfg.mask_out, a.cfg.min_remain) + 68)
+    b = DecodeSession(dataclasses.replace(b0.cfg, lru_slots=slots), b0.hash_q, b0.hash_k, DEV)
+    for layer in range(b.cfg.layers):
+        b.load_context(layer, b0.k_cache[layer][:, :n].contiguous(), b0.v_cache[layer][:, :n].contiguous())
+    b.set_position_table(n, 12, 500000.0)
+    b.pos_dev.fill_(n)
+    graph = b.capture_dev()
+    for t in b.lru:                                    # the warm-up token of the capture touched the tables: start clean
+        t.tok2slot.fill_(-1); t.slot2tok.fill_(-1); t.last_used.fill_(-1)
+    b.pos_dev.fill_(n)
+    base_q = torch.randn(a.q_in.shape, generator=ga).to(a.q_in.dtype)
+    hits = []
+    for step in range(5):
+        pos = n + step
+        q = (base_q + 0.2 * torch.randn(a.q_in.shape, generator=ga).to(a.q_in.dtype))       # drifting query: overlapping selections
+        kk = torch.randn(a.k_in.shape, generator=ga).to(a.k_in.dtype)
+        vv = torch.randn(a.v_in.shape, generator=ga).to(a.v_in.dtype)
+        for s_ in (a, b):
+            s_.q_in.copy_(q); s_.k_in.copy_(kk); s_.v_in.copy_(vv)
+        a.set_position(pos, 500000.0)
+        a.step(pos)
+        graph.replay()
+        torch.cuda.synchronize()
+        assert torch.equal(a.out, b.out), f"token {step}"
+        st = b.lru[-1].stats.sum((0, 1)).cpu().numpy()
+        assert st[0] + st[1] == int(b.cnt.sum())
+        hits.append(int(st[0]))
+        assert int(b.lru[-1].status.item()) == 0
+    assert hits[0] == 0 and min(hits[1:]) > 0
+    ops.check_status()
