@@ -405,7 +405,9 @@ int sl_peer_allgather(const void* d_src, size_t bytes, void* const* peer_bufs, i
 /* The exchange of attention partials and their merge in one launch: this rank's partial output
  * d_o [rows,128] (`dtype`) and d_lse [rows] go to every rank as [rows][129] floats, and d_out
  * [rows,128] receives the log-sum-exp merge of all R partials (the arithmetic of sl_merge_lse).
- * slot_stride >= rows*129*4; the same calling rules as sl_peer_allgather. */
+ * slot_stride >= rows*129*4; the same calling rules as sl_peer_allgather. Several CTAs send and merge a few
+ * rows each and count their arrivals in the buffers' flag area, which they lay out in their own way: a buffer
+ * given to this entry point is used for nothing else. */
 int sl_peer_merge_lse(const void* d_o, const float* d_lse, int dtype, int64_t rows, void* const* peer_bufs,
                       int rank, int R, size_t slot_stride, void* d_out, int32_t* d_status, void* stream);
 

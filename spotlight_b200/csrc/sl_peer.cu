@@ -70,48 +70,47 @@ __global__ void __launch_bounds__(PT) peer_allgather_kernel(const PeerArgs a) {
 }
 
 // The second exchange of a sharded step in one launch: pack this rank's partial (o rounded to the
-// run dtype as sl_sparse_attn_decode leaves it, lse in fp32) as rows*129 floats, all-gather it
-// as above ([rows][128] floats, then lse [rows]), and merge the R partials by log-sum-exp into
-// out [rows][128].
+// run dtype as sl_sparse_attn_decode leaves it, lse in fp32) as rows*129 floats, send it to every rank
+// ([rows][128] floats, then lse [rows]), and merge the R partials by log-sum-exp into out [rows][128].
+// Several CTAs, MERGE_ROWS rows each: a CTA stores its rows into slot `rank` of every rank's buffer, fences at
+// system scope and adds its share to an arrival counter in every buffer; when its own buffer's counter shows
+// that every CTA of every rank has arrived (bounded wait), it merges its rows from the R slots. The flag area
+// of such a buffer holds, after the R flag words of sl_peer_allgather (unused here): [R] launches completed,
+// [R+1] arrival counter, [R+2] CTAs of the running launch that have finished.
+constexpr int MERGE_ROWS = 4;      // rows per CTA: 128 threads per row
 template <typename T>
 __global__ void __launch_bounds__(PT) peer_merge_lse_kernel(const PeerArgs a, const T* __restrict__ o,
                                                             const float* __restrict__ lse, int rows, T* __restrict__ out) {
-    __shared__ unsigned s_epoch;
     sl::pdl_trigger();
     sl::pdl_wait();
-    const int tid = threadIdx.x;
-    // message: o as [rows][128] floats (16-byte stores), then lse [rows]
-    for (int i = tid; i < rows * 32; i += PT) {
-        const T* src = o + i * 4;
-        const float4 v = make_float4(sl::VT<T>::to_f(src[0]), sl::VT<T>::to_f(src[1]), sl::VT<T>::to_f(src[2]), sl::VT<T>::to_f(src[3]));
+    const int tid = threadIdx.x, ncta = gridDim.x;
+    const int row = blockIdx.x * MERGE_ROWS + (tid >> 7), col = tid & 127;
+    const bool live = row < rows;
+    unsigned* own_words = reinterpret_cast<unsigned*>(a.base[a.rank] + a.flags_off) + a.R;
+    const unsigned ep = __ldcg(own_words);                        // launches completed on this buffer
+    if (live) {
+        const float v = sl::VT<T>::to_f(o[row * 128 + col]);
         for (int r = 0; r < a.R; ++r)
-            reinterpret_cast<float4*>(a.base[r] + (unsigned long long)a.rank * a.slot_stride)[i] = v;
-    }
-    for (int i = tid; i < rows; i += PT) {
-        const float v = lse[i];
-        for (int r = 0; r < a.R; ++r)
-            reinterpret_cast<float*>(a.base[r] + (unsigned long long)a.rank * a.slot_stride)[rows * 128 + i] = v;
-    }
-    __syncthreads();
-    if (tid == 0) {
-        unsigned* epoch = reinterpret_cast<unsigned*>(a.base[a.rank] + a.flags_off) + a.R;
-        const unsigned e = *epoch + 1u;
-        *epoch = e;
-        s_epoch = e;
-        __threadfence_system();
-        for (int r = 0; r < a.R; ++r) {
-            unsigned* pf = reinterpret_cast<unsigned*>(a.base[r] + a.flags_off) + a.rank;
-            asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(pf), "r"(e) : "memory");
+            reinterpret_cast<float*>(a.base[r] + (unsigned long long)a.rank * a.slot_stride)[row * 128 + col] = v;
+        if (col == 0) {
+            const float l = lse[row];
+            for (int r = 0; r < a.R; ++r)
+                reinterpret_cast<float*>(a.base[r] + (unsigned long long)a.rank * a.slot_stride)[rows * 128 + row] = l;
         }
     }
     __syncthreads();
-    if (tid < a.R) {
-        const unsigned e = s_epoch;
-        const unsigned* lf = reinterpret_cast<const unsigned*>(a.base[a.rank] + a.flags_off) + tid;
+    if (tid == 0) {
+        const unsigned share = (unsigned)(((unsigned long long)(blockIdx.x + 1) << 16) / ncta - ((unsigned long long)blockIdx.x << 16) / ncta);
+        __threadfence_system();          // the CTA's stores (ordered before this by the barrier) before its arrival
+        for (int r = 0; r < a.R; ++r) {
+            unsigned* pf = reinterpret_cast<unsigned*>(a.base[r] + a.flags_off) + a.R + 1;
+            asm volatile("red.relaxed.sys.global.add.u32 [%0], %1;" ::"l"(pf), "r"(share) : "memory");
+        }
+        const unsigned target = (ep + 1u) * (unsigned)a.R * 65536u;
         unsigned v = 0, it = 0;
         for (;;) {
-            asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(lf) : "memory");
-            if ((int)(v - e) >= 0) break;
+            asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(own_words + 1) : "memory");
+            if ((int)(v - target) >= 0) break;
             if (++it > a.spin_limit) {
                 if (a.status) atomicExch(a.status, 3);
                 break;
@@ -120,21 +119,41 @@ __global__ void __launch_bounds__(PT) peer_merge_lse_kernel(const PeerArgs a, co
         }
     }
     __syncthreads();
-    const float* own = reinterpret_cast<const float*>(a.base[a.rank]);
-    const long long sstr = (long long)(a.slot_stride >> 2);
-    for (int e = tid; e < rows * 128; e += PT) {
-        const int row = e >> 7;
+    if (live) {
+        const float* own = reinterpret_cast<const float*>(a.base[a.rank]);
+        const long long sstr = (long long)(a.slot_stride >> 2);
+        float lv[MAX_RANKS], ov[MAX_RANKS];
+#pragma unroll
+        for (int r = 0; r < MAX_RANKS; ++r) {                    // every load in flight at once
+            lv[r] = r < a.R ? __ldcg(own + r * sstr + rows * 128 + row) : -INFINITY;
+            ov[r] = r < a.R ? __ldcg(own + r * sstr + row * 128 + col) : 0.0f;
+        }
         float M = -INFINITY;
-        for (int r = 0; r < a.R; ++r) M = fmaxf(M, __ldcg(own + r * sstr + rows * 128 + row));
+#pragma unroll
+        for (int r = 0; r < MAX_RANKS; ++r) M = fmaxf(M, lv[r]);
         float L = 0.0f, O = 0.0f;
         if (M != -INFINITY) {
-            for (int r = 0; r < a.R; ++r) {
-                const float w = expf(__ldcg(own + r * sstr + rows * 128 + row) - M);
-                L += w;
-                O += w * __ldcg(own + r * sstr + e);
+#pragma unroll
+            for (int r = 0; r < MAX_RANKS; ++r) {
+                if (r < a.R) {
+                    const float w = expf(lv[r] - M);
+                    L += w;
+                    O += w * ov[r];
+                }
             }
         }
-        out[e] = sl::VT<T>::from_f(L > 0.0f ? O / L : 0.0f);
+        out[row * 128 + col] = sl::VT<T>::from_f(L > 0.0f ? O / L : 0.0f);
+    }
+    // the last CTA to finish closes the launch: every CTA has read the launch count by now
+    __syncthreads();
+    if (tid == 0) {
+        __threadfence();
+        const unsigned old = atomicAdd(own_words + 2, 1u);
+        if (old == (unsigned)ncta - 1u) {
+            own_words[2] = 0u;
+            own_words[0] = ep + 1u;
+            __threadfence();
+        }
     }
 }
 
@@ -167,17 +186,18 @@ extern "C" int sl_peer_merge_lse(const void* d_o, const float* d_lse, int dtype,
     PeerArgs a = {};
     if (int rc = fill_args(a, peer_bufs, rank, R, slot_stride, d_status, "sl_peer_merge_lse")) return rc;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const dim3 grid((unsigned)((rows + MERGE_ROWS - 1) / MERGE_ROWS));
     switch (dtype) {
         case SL_BF16:
-            SL_CUDA_OK(sl::launch_kernel(peer_merge_lse_kernel<__nv_bfloat16>, dim3(1), dim3(PT), 0, s, false, a,
+            SL_CUDA_OK(sl::launch_kernel(peer_merge_lse_kernel<__nv_bfloat16>, grid, dim3(PT), 0, s, false, a,
                                          static_cast<const __nv_bfloat16*>(d_o), d_lse, (int)rows, static_cast<__nv_bfloat16*>(d_out)));
             break;
         case SL_F16:
-            SL_CUDA_OK(sl::launch_kernel(peer_merge_lse_kernel<__half>, dim3(1), dim3(PT), 0, s, false, a,
+            SL_CUDA_OK(sl::launch_kernel(peer_merge_lse_kernel<__half>, grid, dim3(PT), 0, s, false, a,
                                          static_cast<const __half*>(d_o), d_lse, (int)rows, static_cast<__half*>(d_out)));
             break;
         case SL_F32:
-            SL_CUDA_OK(sl::launch_kernel(peer_merge_lse_kernel<float>, dim3(1), dim3(PT), 0, s, false, a,
+            SL_CUDA_OK(sl::launch_kernel(peer_merge_lse_kernel<float>, grid, dim3(PT), 0, s, false, a,
                                          static_cast<const float*>(d_o), d_lse, (int)rows, static_cast<float*>(d_out)));
             break;
         default: return sl::fail(SL_EINVAL, "sl_peer_merge_lse: unsupported dtype %d", dtype);

@@ -73,6 +73,12 @@ struct LeanArgs {
     const long long* d_pos;    // position of the decode token: the context is *d_pos + 1 keys
     int sink, recent, min_remain;
     double mask_out;
+    // sequence shards (R > 0): N, s_end, r_start and the indices written are local to this rank's keys; the rank's
+    // counts travel to every rank's exchange buffer and the threshold comes from all R of them
+    unsigned char* peer[8];    // exchange buffer of every rank: [R slots][arrival counter per row ... epoch per row]
+    int R, rank;
+    unsigned long long slot_stride, pflags_off;
+    int kk;                    // min(k, global number of keys)
     unsigned long long* dbg;   // optional [grid][16] phase stamps (profiling builds only)
 };
 
@@ -80,6 +86,7 @@ bool lean_covers(int KH, int G, int ctas_per_b, int chunk, int nwin);
 int lean_nc(int nbins);
 size_t lean_plan_smem(LeanArgs& f, int KH, int nbins, int S, int chunk);   // fills the offsets, returns the total
 int launch_lean(const LeanArgs& a, size_t smem, cudaStream_t s);
+size_t lean_shard_message_bytes(int B, int KH, int nbins);   // one rank's message to every rank, padded to 16 bytes
 
 bool fused_covers(int KH, int G);
 size_t fused_fixed_smem(int KH, int nbins, int S);

@@ -45,7 +45,14 @@ __device__ __forceinline__ unsigned ldcg_u16(const void* p) {
     return r;
 }
 
-template <int PT>
+// SHARD: this rank holds a contiguous part of a longer context (N, s_end, r_start and the indices written are
+// local). After the local barrier the CTAs of a batch row add up the chunks' records, a few (head, coarse bin) pairs
+// each, and store the rank's counts per score and per coarse bin straight into slot `rank` of EVERY rank's exchange
+// buffer (peer stores over NVLink from all SMs at once); each CTA then fences at system scope and adds its share to
+// an arrival counter in every buffer, and waits (bounded) until its own buffer's counter shows that all CTAs of all
+// ranks have arrived. The threshold is then searched over the R slots, the ties that belong to lower ranks (lower
+// key indices) come off this rank's tie quota, and the local prefix comes from the local records as before.
+template <int PT, bool SHARD>
 __global__ void __launch_bounds__(NT, 1) scan_lean_kernel(const LeanArgs a) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     const int KH = a.KH, nbins = a.nbins, nb1 = (nbins + 4) & ~3, cpb = a.ctas_per_b, S = a.S;   // rows of nb1 words: 16-byte aligned, R[nbins..] = 0
@@ -208,11 +215,67 @@ __global__ void __launch_bounds__(NT, 1) scan_lean_kernel(const LeanArgs a) {
     SL_STAMP(3)
     sl::grid_barrier(a.sync + 2 * b, (unsigned)cpb, a.status);
     SL_STAMP(4)
+    const int npairs = KH * NC;                                   // (head, coarse bin) pairs of a batch row
+    if (SHARD) {
+        unsigned* own_words = reinterpret_cast<unsigned*>(a.peer[a.rank] + a.pflags_off);
+        const unsigned ep = __ldcg(own_words + SHARD_EPOCH_WORD - b);        // launches completed on this buffer for the row
+        const size_t fine_off = (size_t)a.B * npairs;                          // slot: coarse [B][KH][NC], fine [B][KH][NC][8]
+#pragma unroll 1
+        for (int p = c + warp * cpb; p < npairs; p += NW * cpb) {
+            const size_t e0 = ((size_t)b * npairs + p) * cpb;
+            unsigned pk[4] = {0u, 0u, 0u, 0u};
+#pragma unroll
+            for (int j = 0; j < LEAN_CPL_MAX; ++j) {
+                const int cc = lane + 32 * j;
+                if (cc < cpb) {
+                    const uint4 x = __ldcg(a.pub + e0 + cc);
+                    pk[0] += x.x; pk[1] += x.y; pk[2] += x.z; pk[3] += x.w;
+                }
+            }
+            unsigned val = 0, coarse = 0;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const unsigned v = (unsigned)__reduce_add_sync(0xffffffffu, (int)((i & 1) ? (pk[i >> 1] >> 16) : (pk[i >> 1] & 0xffffu)));
+                coarse += v;
+                val = lane == i ? v : val;
+            }
+            if (lane == 8) val = coarse;
+            if (lane < 9) {
+                const size_t w = lane < 8 ? fine_off + ((size_t)b * npairs + p) * 8 + lane : (size_t)b * npairs + p;
+                for (int r = 0; r < a.R; ++r)
+                    reinterpret_cast<unsigned*>(a.peer[r] + (unsigned long long)a.rank * a.slot_stride)[w] = val;
+            }
+        }
+        __syncthreads();
+        if (tid == 0) {
+            // every CTA's share of a fixed per-rank total, so that ranks with differently cut rows still agree on the target
+            const unsigned share = (unsigned)(((unsigned long long)(c + 1) << 16) / cpb - ((unsigned long long)c << 16) / cpb);
+            __threadfence_system();              // the CTA's peer stores (ordered before this by the barrier) first
+            for (int r = 0; r < a.R; ++r) {
+                unsigned* pf = reinterpret_cast<unsigned*>(a.peer[r] + a.pflags_off) + b;
+                asm volatile("red.relaxed.sys.global.add.u32 [%0], %1;" ::"l"(pf), "r"(share) : "memory");
+            }
+            const unsigned target = (ep + 1u) * (unsigned)a.R * 65536u;
+            unsigned v = 0, it = 0;
+            for (;;) {
+                asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(own_words + b) : "memory");
+                if ((int)(v - target) >= 0) break;
+                if (++it > 400000u) {            // about a second: give up, tell the host, finish with what is there
+                    if (a.status) atomicExch(a.status, 3);
+                    break;
+                }
+                __nanosleep(64);
+            }
+        }
+        __syncthreads();
+    }
 
     // ------------------------------------------------------------------ T: threshold, quota, counts before this chunk
     {
-        const int kk = min(k_budget, N);
+        const int kk = SHARD ? a.kk : min(k_budget, N);
         const int CPL = (NC + 31) >> 5;                      // coarse bins per lane, consecutive
+        const unsigned* own_slots = SHARD ? reinterpret_cast<const unsigned*>(a.peer[a.rank]) : nullptr;
+        const size_t sstr = SHARD ? (size_t)(a.slot_stride >> 2) : 0;
 #pragma unroll 1
         for (int h = warp; h < KH; h += NW) {
             unsigned wv[LEAN_MAX_WIN / 32];                      // scores of the row's always-kept keys
@@ -224,10 +287,17 @@ __global__ void __launch_bounds__(NT, 1) scan_lean_kernel(const LeanArgs a) {
                 unsigned cv[LEAN_CPL_MAX];
                 unsigned csum = 0;
                 {
-                    const unsigned* src = chist_b + h * NC + lane * CPL;
+                    const unsigned* src = SHARD ? own_slots + (size_t)(b * KH + h) * NC + lane * CPL : chist_b + h * NC + lane * CPL;
 #pragma unroll
                     for (int i = 0; i < LEAN_CPL_MAX; ++i) {
-                        cv[i] = (i < CPL && lane * CPL + i < NC) ? __ldcg(src + i) : 0u;
+                        cv[i] = 0u;
+                        if (i < CPL && lane * CPL + i < NC) {
+                            if (SHARD) {
+                                for (int r = 0; r < a.R; ++r) cv[i] += __ldcg(src + r * sstr + i);     // the ranks' coarse bins
+                            } else {
+                                cv[i] = __ldcg(src + i);
+                            }
+                        }
                         csum += cv[i];
                     }
                 }
@@ -239,16 +309,23 @@ __global__ void __launch_bounds__(NT, 1) scan_lean_kernel(const LeanArgs a) {
                 const unsigned suf = suffix_sum(csum, lane);
                 const unsigned ball = __ballot_sync(0xffffffffu, suf >= (unsigned)kk);   // not empty: the row holds N >= kk keys
                 const int Ll = 31 - __clz(ball | 1u);
-                int Lc_l = 0;
+                int Lc_l = 0, A_l = 0;
                 {
                     unsigned above = suf - csum;
 #pragma unroll
                     for (int i = LEAN_CPL_MAX - 1; i >= 0; --i) {
-                        if (above < (unsigned)kk && above + cv[i] >= (unsigned)kk) Lc_l = lane * CPL + i;
+                        if (above < (unsigned)kk && above + cv[i] >= (unsigned)kk) { Lc_l = lane * CPL + i; A_l = (int)above; }
                         above += cv[i];
                     }
                 }
                 const int Lc = __shfl_sync(0xffffffffu, Lc_l, Ll), Lb = Lc << LEAN_CWS;
+                // all ranks' counts at the 8 scores of that bin: lane l holds rank l / 8 (and 4 + l / 8), score l % 8
+                unsigned g0 = 0, g1 = 0;
+                if (SHARD) {
+                    const unsigned* fsrc = own_slots + (size_t)a.B * npairs + ((size_t)(b * KH + h) * NC + Lc) * 8 + (lane & 7);
+                    if ((lane >> 3) < a.R) g0 = __ldcg(fsrc + (lane >> 3) * sstr);
+                    if (4 + (lane >> 3) < a.R) g1 = __ldcg(fsrc + (4 + (lane >> 3)) * sstr);
+                }
                 SL_STAMP(8)
                 // every chunk's record of coarse bin Lc and its count above the bin, chunk = lane + 32 j.
                 // Sums of one lane stay below 2^16 per 16-bit field (chunk * LEAN_CPL_MAX < 65536): pairs are added packed.
@@ -280,17 +357,34 @@ __global__ void __launch_bounds__(NT, 1) scan_lean_kernel(const LeanArgs a) {
                     tot[2 * i] = tot[2 * i + 1] + __reduce_add_sync(0xffffffffu, (int)(pk[i] & 0xffffu));
                 }
                 SL_STAMP(10)
-                int ls = 0;                                   // tot[0] >= kk > tot[8] by the choice of Lc
+                int ls = 0, r = 0;                            // (all ranks') tot[0] >= kk > tot[8] by the choice of Lc
+                if (SHARD) {
+                    unsigned t = g0 + g1;
+                    t += __shfl_xor_sync(0xffffffffu, t, 8);
+                    t += __shfl_xor_sync(0xffffffffu, t, 16);         // lane l: all ranks' keys with score Lb + l % 8
+                    int run = __shfl_sync(0xffffffffu, A_l, Ll), gt_all = 0;    // keys of all ranks above the bin
 #pragma unroll
-                for (int i = 1; i < 8; ++i) ls += tot[i] >= kk ? 1 : 0;
+                    for (int i = 7; i >= 0; --i) {
+                        const int above_i = run;
+                        run += (int)__shfl_sync(0xffffffffu, t, i);
+                        if (i >= 1 && run >= kk) ++ls;
+                        if (run >= kk && above_i < kk) gt_all = above_i;       // i is the threshold's place in the bin
+                    }
+                    // threshold ties on lower ranks come first in key order
+                    const int lower = ((lane & 7) == ls) ? (int)(((lane >> 3) < a.rank ? g0 : 0u) + ((4 + (lane >> 3)) < a.rank ? g1 : 0u)) : 0;
+                    r = max(kk - gt_all - __reduce_add_sync(0xffffffffu, lower), 0);
+                } else {
+#pragma unroll
+                    for (int i = 1; i < 8; ++i) ls += tot[i] >= kk ? 1 : 0;
+                }
                 tau = Lb + ls;
-                int ge_tot = 0, gt_tot = 0;
+                int ge_tot = 0, gt_tot = 0;                   // this rank's keys at or above / above the threshold
 #pragma unroll
                 for (int i = 0; i < 8; ++i) {
                     ge_tot = i == ls ? tot[i] : ge_tot;
                     gt_tot = i == ls ? tot[i + 1] : gt_tot;
                 }
-                const int r = kk - gt_tot;
+                if (!SHARD) r = kk - gt_tot;
                 // keys above / at the threshold in the chunks before this one, from the lane's packed sums
                 {
                     int gt = (int)qa, eq = 0;
@@ -447,6 +541,10 @@ __global__ void __launch_bounds__(NT, 1) scan_lean_kernel(const LeanArgs a) {
         if (old == (unsigned)cpb - 1u) {
             sync[0] = 0;
             sync[1] = 0;
+            if (SHARD) {     // the row's last CTA: every CTA of the row has read the buffer's epoch word by now
+                unsigned* epoch_w = reinterpret_cast<unsigned*>(a.peer[a.rank] + a.pflags_off) + SHARD_EPOCH_WORD - b;
+                *epoch_w = __ldcg(epoch_w) + 1u;
+            }
             a.epoch[b] = __ldcg(a.epoch + b) + 1u;           // the next launch takes the other coarse buffer
             __threadfence();
         }
@@ -455,12 +553,13 @@ __global__ void __launch_bounds__(NT, 1) scan_lean_kernel(const LeanArgs a) {
 
 typedef void (*lean_kernel_t)(const LeanArgs);
 
+template <bool SHARD>
 lean_kernel_t pick(int P) {
     switch (P) {
-        case 1: return scan_lean_kernel<1>;
-        case 2: return scan_lean_kernel<2>;
-        case 3: return scan_lean_kernel<3>;
-        default: return scan_lean_kernel<4>;
+        case 1: return scan_lean_kernel<1, SHARD>;
+        case 2: return scan_lean_kernel<2, SHARD>;
+        case 3: return scan_lean_kernel<3, SHARD>;
+        default: return scan_lean_kernel<4, SHARD>;
     }
 }
 
@@ -490,10 +589,14 @@ size_t lean_plan_smem(LeanArgs& f, int KH, int nbins, int S, int chunk) {
     return off;
 }
 
+size_t lean_shard_message_bytes(int B, int KH, int nbins) {
+    return ((size_t)B * KH * lean_nc(nbins) * 9 * 4 + 15) / 16 * 16;      // coarse [B][KH][NC] + fine [B][KH][NC][8], 32 bits each
+}
+
 int launch_lean(const LeanArgs& a_in, size_t smem, cudaStream_t s) {
     LeanArgs a = a_in;
     a.dbg = SL_STAMP_BUF;
-    lean_kernel_t kern = pick(sliced_planes(a.G));
+    lean_kernel_t kern = a.R > 0 ? pick<true>(sliced_planes(a.G)) : pick<false>(sliced_planes(a.G));
     SL_CUDA_OK(sl::ensure_dyn_smem(reinterpret_cast<const void*>(kern), smem));
     SL_CUDA_OK(sl::launch_kernel(kern, dim3((unsigned)(a.B * a.ctas_per_b)), dim3(NT), smem, s, true, a));
     return SL_OK;

@@ -869,7 +869,8 @@ extern "C" int sl_scan_hist(const uint32_t* d_q_codes, const uint32_t* d_k_codes
 extern "C" size_t sl_scan_topk_sharded_slot_bytes(int B, int KH, int QH) {
     if (B <= 0 || KH <= 0 || QH <= 0 || QH % KH) return 0;
     const int nbins = 128 * (QH / KH) + 1;
-    return slscan::shard_message_bytes(B, KH, nbins, coarse_shift(nbins));
+    // whichever of the two kernels serves the shape: the larger of their messages
+    return std::max(slscan::shard_message_bytes(B, KH, nbins, coarse_shift(nbins)), slscan::lean_shard_message_bytes(B, KH, nbins));
 }
 
 extern "C" int sl_scan_topk_sharded(const uint32_t* d_q_codes, const uint32_t* d_k_codes, int64_t k_batch_stride, int B,
@@ -908,6 +909,40 @@ extern "C" int sl_scan_topk_sharded(const uint32_t* d_q_codes, const uint32_t* d
     const int64_t need = std::min<int64_t>(N_local, (int64_t)k + s_end + (N_local - r_start));
     SL_REQUIRE(idx_capacity >= need, SL_ESHAPE, "sl_scan_topk_sharded: idx_capacity %d < %lld", idx_capacity, (long long)need);
     unsigned char* ws = static_cast<unsigned char*>(d_workspace);
+    for (int r = 0; r < R; ++r)
+        SL_REQUIRE(peer_bufs[r] != nullptr && sl::aligned16(peer_bufs[r]), SL_EINVAL, "sl_scan_topk_sharded: bad buffer of rank %d", r);
+    if (g_lean == 1 && B * p.ctas_per_b <= sl::sm_count() && 2 * B <= slscan::SHARD_EPOCH_WORD &&
+        slscan::lean_covers(KH, G, p.ctas_per_b, p.chunk, sink + recent) &&
+        slot_stride >= slscan::lean_shard_message_bytes(B, KH, p.nbins)) {
+        // the one-barrier kernel: records of every chunk, the rank's counts sent by all CTAs at once
+        slscan::LeanArgs f = {};
+        f.q = reinterpret_cast<const uint4*>(d_q_codes);
+        f.k = reinterpret_cast<const uint4*>(d_k_codes);
+        f.k_bstride = k_batch_stride / 4;
+        f.B = B; f.KH = KH; f.G = G; f.layout = gqa_layout; f.N = (int)N_local;
+        f.k_budget = k;
+        f.kk = (int)std::min<int64_t>(k, N_global);
+        f.s_end = (int)s_end; f.r_start = (int)r_start;
+        f.idx = d_idx; f.cap = idx_capacity; f.cnt = d_cnt;
+        f.sync = reinterpret_cast<unsigned*>(ws + w.sync_off);
+        f.epoch = reinterpret_cast<unsigned*>(ws + w.epoch_off);
+        f.chist = reinterpret_cast<unsigned*>(ws + w.chist2_off);
+        f.pub = reinterpret_cast<uint4*>(ws + w.pub_off);
+        f.puba = reinterpret_cast<unsigned short*>(ws + w.puba_off);
+        f.wsc = reinterpret_cast<unsigned short*>(ws + w.wsc_off);
+        f.status = d_status;
+        f.ctas_per_b = p.ctas_per_b; f.chunk = p.chunk; f.nbins = p.nbins; f.S = p.S;
+        f.NC = slscan::lean_nc(p.nbins);
+        f.nc_magic = (unsigned)(((1ull << 32) + f.NC - 1) / f.NC);
+        const int roww = (p.chunk >> 1) + ((4 - (p.chunk >> 1)) & 31);
+        f.rowh = 2 * roww;
+        for (int r = 0; r < R; ++r) f.peer[r] = static_cast<unsigned char*>(peer_bufs[r]);
+        f.R = R; f.rank = rank;
+        f.slot_stride = slot_stride;
+        f.pflags_off = (unsigned long long)R * slot_stride;
+        const size_t smem = slscan::lean_plan_smem(f, KH, p.nbins, p.S, p.chunk);
+        if (smem <= (size_t)SMEM_BUDGET + 24 * 1024) return slscan::launch_lean(f, smem, static_cast<cudaStream_t>(stream));
+    }
     slscan::FusedArgs f = {};
     f.q = reinterpret_cast<const uint4*>(d_q_codes);
     f.k = reinterpret_cast<const uint4*>(d_k_codes);

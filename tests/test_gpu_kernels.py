@@ -620,11 +620,14 @@ def test_peer_wait_runs_out_and_the_context_stays_usable(ops):
             lib.sl_peer_free(p)
 
 
-@pytest.mark.parametrize("B,N,KH,QH,k", [(1, 131072, 8, 32, 13108), (2, 60000, 4, 28, 1200), (1, 40000, 8, 40, 800)])
-def test_scan_topk_sharded_single_rank(ops, B, N, KH, QH, k):
-    """The one-launch sharded scan with a world of one rank (histograms go through the rank's own
-    exchange buffer) must reproduce sl_scan_topk; run three times: epochs advance, buffers are reused."""
+@pytest.mark.parametrize("kernel", [1, 2], ids=["one-barrier", "flagged-words"])
+@pytest.mark.parametrize("B,N,KH,QH,k", [(1, 131072, 8, 32, 13108), (2, 60000, 4, 28, 1200), (1, 40000, 8, 40, 800), (3, 9000, 2, 2, 50)])
+def test_scan_topk_sharded_single_rank(ops, B, N, KH, QH, k, kernel):
+    """The one-launch sharded scan with a world of one rank (the rank's counts go through its own exchange
+    buffer) must reproduce sl_scan_topk, with either of the two kernels that serve it; run three times: epochs
+    advance, buffers are reused. (A buffer stays with one kernel: the two lay its flag area out differently.)"""
     import ctypes as C
+    from spotlight_b200 import _lib
     from spotlight_b200._lib import check, lib
 
     class Peer:
@@ -640,6 +643,7 @@ def test_scan_topk_sharded_single_rank(ops, B, N, KH, QH, k):
         q = rand_codes(g, (B, QH, 4), True).to(DEV)
         cache = rand_codes(g, (B, N, KH, 4), True).to(DEV)
         ref_idx, ref_cnt = ops.scan_topk(q, cache, k, 4, 64, O.BLOCKED)
+        check(lib.sl_configure(_lib.SL_OPT_SCAN_KERNEL, kernel))
         for _ in range(3):
             idx, cnt = ops.scan_topk_sharded(q, cache, peer, 0, N, k, 4, 64, O.BLOCKED)
             torch.testing.assert_close(cnt, ref_cnt, rtol=0, atol=0)
@@ -649,5 +653,6 @@ def test_scan_topk_sharded_single_rank(ops, B, N, KH, QH, k):
                     torch.testing.assert_close(idx[b, h, :c], ref_idx[b, h, :c], rtol=0, atol=0)
         ops.check_status()
     finally:
+        check(lib.sl_configure(_lib.SL_OPT_SCAN_KERNEL, 1))
         torch.cuda.synchronize()
         check(lib.sl_peer_free(own))
