@@ -1,5 +1,5 @@
-// Shared between the two scan + top-k translation units (sl_scan_topk.cu: every mode and shape;
-// sl_scan_fused.cu: the lean kernel of the decode step).
+// Shared between the scan + top-k translation units (sl_scan_topk.cu: every mode and shape;
+// sl_scan_lean.cu: the one-barrier kernel of the decode step; sl_scan_fused.cu: its predecessor).
 #pragma once
 #include "sl_common.cuh"
 

@@ -103,6 +103,12 @@ class _Workspaces:
 workspaces = _Workspaces()
 
 
+def configure(option: int, value: int) -> None:
+    """Process-wide switch of the library (`_lib.SL_OPT_*`): measurement and test aid; every default is
+    the fast path."""
+    _lib.check(_lib.lib.sl_configure(int(option), int(value)))
+
+
 def check_status(device=None) -> None:
     """Host-side read of every status word (synchronises). Raises if a bounded device-side wait
     ran out; the affected workspace is dropped so the next call starts from a clean one."""
