@@ -60,10 +60,17 @@ int sl_set_device(int device);
  *                       1 (default) the one-barrier kernel, 2 the flagged-word kernel, 0 the general kernel
  *   SL_OPT_ATTN_WARPS   warps per CTA of the bf16 attention kernel: 0 (default) by shape, 4 or 8
  *   SL_OPT_PEER_SPIN_LIMIT  polls (100 ns apart) after which the peer-memory exchanges stop waiting for another
- *                       rank's message and set their status word to 3; default 400000, about a second */
+ *                       rank's message and set their status word to 3; default 400000, about a second
+ *   SL_OPT_HASH_KERNEL  which kernel sl_hash_encode uses for bf16 rows of a 128 -> 256 -> 128 hash: 0 (default)
+ *                       by size, 1 the warp-level tensor-core kernel, 2 the tcgen05 / TMEM kernel for every size */
 typedef enum { SL_OPT_PDL = 0, SL_OPT_L2_PREFETCH = 1, SL_OPT_SCAN_KERNEL = 2, SL_OPT_ATTN_WARPS = 3,
-               SL_OPT_PEER_SPIN_LIMIT = 4 } sl_option;
+               SL_OPT_PEER_SPIN_LIMIT = 4, SL_OPT_HASH_KERNEL = 5 } sl_option;
 int sl_configure(int option, int value);
+
+/* Status of the prefill hash kernels since the last call: 0, or 3 after a bounded device-side wait (an mbarrier
+ * of the tcgen05 kernel) ran out. Reading clears it. Synchronise the streams that ran sl_hash_encode first.
+ * No reference counterpart. */
+int sl_hash_status(void);
 
 /* Sign-bit packing: bit j of output byte i  <=>  x[8*i + j] > 0 (LSB first). Read as uint32
  * words on a little-endian machine this is the 32-bit packing of the reference.

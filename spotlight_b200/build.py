@@ -13,7 +13,7 @@ PKG = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(PKG, "csrc")
 LIB_DIR = os.path.join(PKG, "lib")
 LIB = os.path.join(LIB_DIR, "libspotlight_b200.so")
-SOURCES = ["sl_api.cu", "sl_pack.cu", "sl_scan_topk.cu", "sl_scan_fused.cu", "sl_scan_lean.cu", "sl_hash.cu", "sl_hash_mma.cu", "sl_attn.cu", "sl_attn_mma.cu", "sl_lru.cu", "sl_peer.cu", "sl_step.cu"]
+SOURCES = ["sl_api.cu", "sl_pack.cu", "sl_scan_topk.cu", "sl_scan_fused.cu", "sl_scan_lean.cu", "sl_hash.cu", "sl_hash_mma.cu", "sl_hash_tc.cu", "sl_attn.cu", "sl_attn_mma.cu", "sl_lru.cu", "sl_peer.cu", "sl_step.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-lineinfo", "-std=c++17",
               "-Xcompiler", "-fPIC"]
 

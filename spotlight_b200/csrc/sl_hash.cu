@@ -14,6 +14,8 @@
 namespace sl {
 int launch_hash_encode_mma(const void* x, long long xs_b, long long xs_tok, long long xs_h, int B, long long T, int H, const sl_hash_params* hp,
                            uint32_t* codes, long long cs_b, cudaStream_t s);
+int launch_hash_encode_tc(const void* x, long long xs_b, long long xs_tok, long long xs_h, int B, long long T, int H, const sl_hash_params* hp,
+                          uint32_t* codes, long long cs_b, cudaStream_t s);
 }
 
 namespace {
@@ -498,7 +500,10 @@ extern "C" int sl_hash_encode_ex(const void* d_x, int64_t x_batch_stride, int64_
     if (T == 0) return SL_OK;
     if (dtype == SL_BF16 && (long long)B * T >= 64 && sl::aligned16(d_x) && x_batch_stride % 8 == 0 &&
         x_token_stride % 8 == 0 && x_head_stride % 8 == 0) {
-        // many rows: the tensor-core kernel (weights resident in shared memory); 1 = shape not covered
+        // many rows: the tensor-core kernels (weights resident in shared memory); 1 = shape not covered
+        const int rt = sl::launch_hash_encode_tc(d_x, x_batch_stride, x_token_stride, x_head_stride, B, T, H, hash, d_codes,
+                                                 code_batch_stride, static_cast<cudaStream_t>(stream));
+        if (rt <= 0) return rt;
         const int rc = sl::launch_hash_encode_mma(d_x, x_batch_stride, x_token_stride, x_head_stride, B, T, H, hash, d_codes,
                                                   code_batch_stride, static_cast<cudaStream_t>(stream));
         if (rc <= 0) return rc;

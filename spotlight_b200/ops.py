@@ -119,6 +119,9 @@ def check_status(device=None) -> None:
         if int(status.item()) != 0:
             bad.append((key, int(status.item())))
             del workspaces._bufs[key]
+    hs = int(_lib.lib.sl_hash_status())
+    if hs != 0:
+        bad.append((("hash_encode",), hs))
     if bad:
         raise RuntimeError(f"spotlight_b200 [{_lib.SL_ETIMEOUT}]: device-side status set: {bad}")
 
