@@ -2,25 +2,26 @@
 // sign and pack of many rows of one head per CTA. This is the one dense contraction of the retrieval path
 // (reference math: spotlight/modifiers/spotlight_generation.py:229-255).
 //
-// One persistent CTA per SM works on 128-row tiles of one head. The head's weights stay in shared memory
+// One persistent CTA per SM works on 128-row tiles of one head, one tile after the other. The head's weights stay in shared memory
 // for the whole launch, transposed to K-major rows in the 128-byte-swizzled layout tcgen05.mma reads; the
 // accumulators live in tensor memory (TMEM); input tiles arrive by TMA (cp.async.bulk.tensor, no multicast,
 // this GPU's own memory) straight into the same swizzled layout.
 //
-// Two pipelines share the SM, each with 256 TMEM columns, one stage of input rows, four epilogue warps
-// (a thread owns one row = one TMEM lane) and one issuing thread:
-//   TMA   X tile [128 x 128]                                   -> x_full
+// TMEM columns: D1 [0,256) fp32, H [256,384) packed bf16 pairs, D2 [384,512) fp32. Sixteen epilogue warps (a thread
+// owns one row = one TMEM lane and a quarter of the columns) and one issuing thread:
+//   TMA   X tile [128 x 128] into one of two stages            -> x_full[stage]
 //   MMA1  D1[128 x 256] = X W1            (8 x  M128 N256 K16)  -> d1_full   (the input stage is free again)
 //   EPI1  D1 -> registers, torch's rounding points (matmul -> bf16, + bias -> bf16, SiLU -> bf16), packed
-//         pairs of bf16 written back to TMEM over the columns already read: the A operand of layer 2
-//                                                               -> h_full
+//         pairs of bf16 written to H: the A operand of layer 2  -> h_full    (D1 is free: MMA1 of the next tile
+//         is issued behind MMA2 of this one and runs under EPI2)
 //   MMA2  D2[128 x 128] = H W2            (16 x M128 N128 K16, A from TMEM) -> d2_full
-//   EPI2  D2 -> registers, rounding points, sign bit of every value: the thread holds its row's 128 bits
-//         and stores them as one 16-byte code                   -> d_free
-// While one pipeline's warps are in an epilogue the tensor core runs the other's contraction. The epilogue
-// (one exp and one division per hidden value on the special-function units) takes longer than the
-// contraction, so the kernel is bound by it. Every wait on an mbarrier is bounded; a wait that runs out
-// raises the library's hash status word, the CTA drains what it has in flight, frees its TMEM and returns.
+//   EPI2  D2 -> registers, rounding points, sign bit of every value: a thread holds one 32-bit word of its
+//         row's code and stores it                              -> d2_free
+// The epilogue (one exp and one division per hidden value, at full fp32 accuracy so that the codes equal the
+// other kernels' bit for bit) takes several times longer than the contraction, so the kernel is bound by
+// instruction issue of the epilogue warps, not by the tensor core. Every wait on an mbarrier is bounded; a
+// wait that runs out raises the library's hash status word, the CTA lets its copies in flight land, frees its
+// TMEM and returns.
 // Same arithmetic as the warp-level kernel in sl_hash_mma.cu up to the order of the fp32 additions.
 #include <cuda.h>
 
@@ -28,13 +29,13 @@
 
 namespace {
 
-constexpr int TC_EPI_WARPS = 8;                 // 2 pipelines x 4 warps
-constexpr int TC_THREADS = (TC_EPI_WARPS + 2) * 32;
+constexpr int TC_EPI_WARPS = 16;                // 4 lane quadrants x 4 column groups
+constexpr int TC_THREADS = (TC_EPI_WARPS + 1) * 32;
 constexpr int TC_TILE = 128;
 constexpr unsigned W1_BYTES = 128 * 256 * 2, W2_BYTES = 256 * 128 * 2, X_BYTES = TC_TILE * 128 * 2;
 constexpr unsigned OFF_W1 = 0, OFF_W2 = W1_BYTES, OFF_X = W1_BYTES + W2_BYTES, OFF_B1 = OFF_X + 2 * X_BYTES,
-                   OFF_B2 = OFF_B1 + 512, OFF_BAR = OFF_B2 + 256, OFF_MISC = OFF_BAR + 2 * 5 * 8, TC_SMEM = OFF_MISC + 16 + 1024;
-constexpr unsigned WAIT_FAST = 1u << 14, WAIT_LIMIT = 1u << 22;   // polls (non-blocking test_wait) without / with a 256 ns pause: about a second in all
+                   OFF_B2 = OFF_B1 + 512, OFF_LUT = OFF_B2 + 256, OFF_BAR = OFF_LUT + 16384, OFF_MISC = OFF_BAR + 8 * 8, TC_SMEM = OFF_MISC + 16 + 1024;
+constexpr unsigned WAIT_NS = 20000u, WAIT_TRIES = 50000u, WAIT_LIMIT = 1u << 22;
 
 struct HashTcArgs {
     long long T; int H; int B;
@@ -44,9 +45,32 @@ struct HashTcArgs {
     int* status;                                  // mapped host word: 3 = a wait ran out
 };
 
-__device__ __forceinline__ float bfr(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
-__device__ __forceinline__ unsigned pack2(float lo, float hi) {
-    return (unsigned)__bfloat16_as_ushort(__float2bfloat16_rn(lo)) | ((unsigned)__bfloat16_as_ushort(__float2bfloat16_rn(hi)) << 16);
+__device__ __forceinline__ unsigned pack2(float lo, float hi) {      // two fp32 -> two bf16, round to nearest even, one instruction
+    unsigned r;
+    asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+    return r;
+}
+
+// sum of two pairs of bf16, each rounded to nearest even once: equal to the fp32 sum rounded to bf16
+__device__ __forceinline__ unsigned add_bf16x2(unsigned x, unsigned y) {
+    unsigned r;
+    asm("add.rn.bf16x2 %0, %1, %2;" : "=r"(r) : "r"(x), "r"(y));
+    return r;
+}
+
+// SiLU of a bf16 at torch's rounding point: fp32 x / (1 + exp(-x)) with the accurate exp and the IEEE division, rounded once.
+__device__ __forceinline__ unsigned short silu_bf16(unsigned short u) {
+    const float y = __uint_as_float((unsigned)u << 16);
+    return __bfloat16_as_ushort(__float2bfloat16_rn(y / (1.0f + expf(-y))));
+}
+// The activation has one bf16 argument, so it is a function of 16 bits. Its values for 2^-28 <= |x| < 16 (both signs:
+// 8192 arguments, where all of a layer's values lie but exact zeros and outliers) are tabulated in shared memory at the
+// start of the kernel with the formula above; the other arguments go through the formula itself. Either way the
+// result is the formula's, bit for bit.
+constexpr unsigned LUT_LO = 99u << 7;       // 2^-28
+
+__device__ __noinline__ unsigned silu_pair(unsigned y) {
+    return (unsigned)silu_bf16((unsigned short)(y & 0xffffu)) | ((unsigned)silu_bf16((unsigned short)(y >> 16)) << 16);
 }
 
 // ---- mbarrier, TMA, tcgen05 in PTX
@@ -65,14 +89,21 @@ __device__ __forceinline__ bool mbar_test(unsigned bar, unsigned parity) {
                  : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
     return ok != 0;
 }
-// Bounded wait: false when the limit ran out or another thread of the CTA has already given up.
+// Suspends the thread until the phase completes or about `ns` nanoseconds have passed (no spinning on shared memory,
+// which the tensor core is reading its operands from).
+__device__ __forceinline__ bool mbar_try(unsigned bar, unsigned parity, unsigned ns) {
+    unsigned ok;
+    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                 : "=r"(ok) : "r"(bar), "r"(parity), "r"(ns) : "memory");
+    return ok != 0;
+}
+// Bounded wait: false when the limit ran out (WAIT_TRIES suspensions of at most WAIT_NS each and a pause between them:
+// about a second) or another thread of the CTA has already given up.
 __device__ __forceinline__ bool mbar_wait(unsigned bar, unsigned parity, volatile int* abort_flag) {
-    for (unsigned i = 0; i < WAIT_LIMIT; ++i) {
-        if (mbar_test(bar, parity)) return true;
-        if (i >= WAIT_FAST) {
-            if (*abort_flag) return false;
-            __nanosleep(256);
-        }
+    for (unsigned i = 0; i < WAIT_TRIES; ++i) {
+        if (mbar_try(bar, parity, WAIT_NS)) return true;
+        if (*abort_flag) return false;
+        __nanosleep(64);
     }
     return false;
 }
@@ -125,6 +156,17 @@ __device__ __forceinline__ unsigned kmajor_off(int row, int k, int rows) {
     return (unsigned)((k >> 6) * rows * 128 + row * 128 + ((((k & 63) >> 3) ^ (row & 7)) << 4) + (k & 7) * 2);
 }
 
+// Phase stamps exist only in profiling builds (-DSL_TC_TIMING): CTA (0,0) stores the SM cycle counter at its phase boundaries.
+#ifdef SL_TC_TIMING
+__device__ unsigned long long g_tc_dbg[2][64][4];
+__device__ unsigned long long g_tc_dbgw[16][4];
+#define TC_STAMPW(k) if (blockIdx.x == 0 && blockIdx.y == 0 && it == 3 && lane == 0) g_tc_dbgw[warp][k] = (unsigned long long)clock64();
+#define TC_STAMP(who, i, k) if (blockIdx.x == 0 && blockIdx.y == 0 && (i) < 64) g_tc_dbg[who][i][k] = (unsigned long long)clock64();
+#else
+#define TC_STAMP(who, i, k)
+#define TC_STAMPW(k)
+#endif
+
 __global__ void __launch_bounds__(TC_THREADS, 1) hash_encode_tc_kernel(const __grid_constant__ CUtensorMap xmap, const HashTcArgs a) {
     extern __shared__ unsigned char smem_raw[];
     const unsigned raw = (unsigned)__cvta_generic_to_shared(smem_raw);
@@ -134,14 +176,14 @@ __global__ void __launch_bounds__(TC_THREADS, 1) hash_encode_tc_kernel(const __g
     const int h = blockIdx.y;
     volatile int* abort_flag = reinterpret_cast<volatile int*>(g + OFF_MISC + 4);
     unsigned* tmem_slot = reinterpret_cast<unsigned*>(g + OFF_MISC);
-    auto bar = [&](int p, int i) { return base + OFF_BAR + (unsigned)(p * 5 + i) * 8u; };   // 0 x_full 1 d1_full 2 h_full 3 d2_full 4 d_free
+    auto bar = [&](int i) { return base + OFF_BAR + (unsigned)i * 8u; };
+    constexpr int X_FULL = 0 /* and 1 */, D1_FULL = 2, H_FULL = 3, D2_FULL = 4, D2_FREE = 5;
 
     // ---- set-up: barriers, TMEM, this head's weights (transposed to K-major) and biases
     if (tid == 0) {
         *abort_flag = 0;
-        for (int p = 0; p < 2; ++p) {
-            mbar_init(bar(p, 0), 1); mbar_init(bar(p, 1), 1); mbar_init(bar(p, 2), 128); mbar_init(bar(p, 3), 1); mbar_init(bar(p, 4), 128);
-        }
+        mbar_init(bar(X_FULL), 1); mbar_init(bar(X_FULL + 1), 1); mbar_init(bar(D1_FULL), 1);
+        mbar_init(bar(H_FULL), TC_EPI_WARPS * 32); mbar_init(bar(D2_FULL), 1); mbar_init(bar(D2_FREE), TC_EPI_WARPS * 32);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == TC_EPI_WARPS) {
@@ -149,24 +191,32 @@ __global__ void __launch_bounds__(TC_THREADS, 1) hash_encode_tc_kernel(const __g
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
     {
-        const unsigned* w1 = reinterpret_cast<const unsigned*>(a.w1 + (long long)h * 128 * 256);   // [k][n], pairs of n
-        for (int i = tid; i < 128 * 128; i += TC_THREADS) {
-            const int k = i >> 7, n = (i & 127) * 2;
-            const unsigned v = w1[i];
-            *reinterpret_cast<unsigned short*>(g + OFF_W1 + kmajor_off(n, k, 256)) = (unsigned short)(v & 0xffffu);
-            *reinterpret_cast<unsigned short*>(g + OFF_W1 + kmajor_off(n + 1, k, 256)) = (unsigned short)(v >> 16);
+        // a warp takes 32 consecutive k of 8 columns: each lane reads 16 bytes of its row and writes 8 halfwords; the
+        // 32 lanes of a store fall into distinct banks (k runs along the swizzled 128-byte row)
+        const int NWARP = TC_THREADS / 32;
+        const uint4* w1 = reinterpret_cast<const uint4*>(a.w1 + (long long)h * 128 * 256);        // [k][n], 32 groups of 8 n per row
+        for (int task = warp; task < 4 * 32; task += NWARP) {
+            const int k = (task >> 5) * 32 + lane, n0 = (task & 31) * 8;
+            const uint4 v = w1[k * 32 + (task & 31)];
+            const unsigned short* e = reinterpret_cast<const unsigned short*>(&v);
+#pragma unroll
+            for (int c = 0; c < 8; ++c) *reinterpret_cast<unsigned short*>(g + OFF_W1 + kmajor_off(n0 + c, k, 256)) = e[c];
         }
-        const unsigned* w2 = reinterpret_cast<const unsigned*>(a.w2 + (long long)h * 256 * 128);
-        for (int i = tid; i < 256 * 64; i += TC_THREADS) {
-            const int k = i >> 6, n = (i & 63) * 2;
-            const unsigned v = w2[i];
-            *reinterpret_cast<unsigned short*>(g + OFF_W2 + kmajor_off(n, k, 128)) = (unsigned short)(v & 0xffffu);
-            *reinterpret_cast<unsigned short*>(g + OFF_W2 + kmajor_off(n + 1, k, 128)) = (unsigned short)(v >> 16);
+        const uint4* w2 = reinterpret_cast<const uint4*>(a.w2 + (long long)h * 256 * 128);        // [k][n], 16 groups of 8 n per row
+        for (int task = warp; task < 8 * 16; task += NWARP) {
+            const int k = (task >> 4) * 32 + lane, n0 = (task & 15) * 8;
+            const uint4 v = w2[k * 16 + (task & 15)];
+            const unsigned short* e = reinterpret_cast<const unsigned short*>(&v);
+#pragma unroll
+            for (int c = 0; c < 8; ++c) *reinterpret_cast<unsigned short*>(g + OFF_W2 + kmajor_off(n0 + c, k, 128)) = e[c];
         }
         __nv_bfloat16* sb1 = reinterpret_cast<__nv_bfloat16*>(g + OFF_B1);
         __nv_bfloat16* sb2 = reinterpret_cast<__nv_bfloat16*>(g + OFF_B2);
         for (int i = tid; i < 256; i += TC_THREADS) sb1[i] = a.b1 ? a.b1[(long long)h * 256 + i] : __float2bfloat16_rn(0.0f);
         for (int i = tid; i < 128; i += TC_THREADS) sb2[i] = a.b2 ? a.b2[(long long)h * 128 + i] : __float2bfloat16_rn(0.0f);
+        unsigned short* lut = reinterpret_cast<unsigned short*>(g + OFF_LUT);
+        for (unsigned i = tid; i < 8192u; i += TC_THREADS)
+            lut[i] = silu_bf16((unsigned short)(((i & 0xfffu) + LUT_LO) | ((i & 0x1000u) << 3)));
     }
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");     // the weights were written by ordinary stores, the tensor core reads them
     tc_fence_before();
@@ -174,108 +224,135 @@ __global__ void __launch_bounds__(TC_THREADS, 1) hash_encode_tc_kernel(const __g
     tc_fence_after();
     const unsigned tmem = *tmem_slot;
 
-    const int p = warp < TC_EPI_WARPS ? warp >> 2 : warp - TC_EPI_WARPS;          // pipeline of this warp
-    const long long first = (long long)blockIdx.x + (long long)p * gridDim.x, step = 2ll * gridDim.x;
+    const long long first = blockIdx.x, step = gridDim.x;
     bool failed = false;
 
     if (warp < TC_EPI_WARPS) {
-        // ================= epilogue warps: thread = row = TMEM lane =================
-        const int q = warp & 3, row = q * 32 + lane;
-        const unsigned t_d1 = tmem + ((unsigned)(q * 32) << 16) + (unsigned)p * 256u;   // D1 columns [0,256), H over [0,128), D2 [128,256)
-        const __nv_bfloat16* sb1 = reinterpret_cast<const __nv_bfloat16*>(g + OFF_B1);
-        const __nv_bfloat16* sb2 = reinterpret_cast<const __nv_bfloat16*>(g + OFF_B2);
-        const bool has_b1 = a.b1 != nullptr, has_b2 = a.b2 != nullptr;
+        // ================= epilogue warps: thread = row = TMEM lane, warp group cg = a quarter of the columns =================
+        const int q = warp & 3, cg = warp >> 2, row = q * 32 + lane;
+        const unsigned t_row = tmem + ((unsigned)(q * 32) << 16);
+        const unsigned t_d1 = t_row + 64u * cg, t_h = t_row + 256u + 32u * cg, t_d2 = t_row + 384u + 32u * cg;
+        const unsigned* sb1 = reinterpret_cast<const unsigned*>(g + OFF_B1) + 32 * cg;     // pairs of bf16
+        const unsigned* sb2 = reinterpret_cast<const unsigned*>(g + OFF_B2) + 16 * cg;
+        const unsigned char* lutb = g + OFF_LUT;
         unsigned it = 0;
         for (long long tile = first; tile < a.n_tiles; tile += step, ++it) {
             const unsigned par = it & 1u;
-            if (!__all_sync(0xffffffffu, mbar_wait(bar(p, 1), par, abort_flag))) { failed = true; break; }   // warp-uniform: the TMEM accesses below are warp-wide
+            if (!__all_sync(0xffffffffu, mbar_wait(bar(D1_FULL), par, abort_flag))) { failed = true; break; }   // warp-uniform: the TMEM accesses below are warp-wide
             tc_fence_after();
+            if (tid == 0) { TC_STAMP(0, it, 0) }
+            TC_STAMPW(0)
+            unsigned v[1][32];
 #pragma unroll 1
-            for (int j = 0; j < 8; ++j) {
-                unsigned v[32], pk[16];
-                tmem_ld32(t_d1 + 32u * j, v);
+            for (int jj = 0; jj < 2; ++jj) {
+                constexpr int j = 0;
+                unsigned pk[16], oob = 0u;
+                tmem_ld32(t_d1 + 32u * jj, v[0]);
                 tmem_wait_ld();
 #pragma unroll
-                for (int e = 0; e < 32; e += 2) {
-                    float y0 = bfr(__uint_as_float(v[e])), y1 = bfr(__uint_as_float(v[e + 1]));
-                    if (has_b1) {
-                        y0 = bfr(y0 + __bfloat162float(sb1[32 * j + e]));
-                        y1 = bfr(y1 + __bfloat162float(sb1[32 * j + e + 1]));
-                    }
-                    y0 = y0 / (1.0f + expf(-y0));
-                    y1 = y1 / (1.0f + expf(-y1));
-                    pk[e >> 1] = pack2(y0, y1);
+                for (int e = 0; e < 16; ++e) {
+                    unsigned y = pack2(__uint_as_float(v[j][2 * e]), __uint_as_float(v[j][2 * e + 1]));   // matmul -> bf16
+                    y = add_bf16x2(y, sb1[16 * jj + e]);                                                   // + bias -> bf16 (a null bias is a row of zeros)
+                    v[j][e] = y;
+                    // both halves at once: a half outside the table's range leaves bits in 0x7000 (a borrow from the low half can
+                    // only come from such a half), and then the pair goes through the formula below
+                    const unsigned d = y - (LUT_LO | (LUT_LO << 16)), dh = d >> 16;
+                    oob |= d;
+                    const unsigned i0 = ((d << 1) & 0x1ffeu) | ((d >> 2) & 0x2000u), i1 = ((dh << 1) & 0x1ffeu) | ((dh >> 2) & 0x2000u);
+                    pk[e] = (unsigned)*reinterpret_cast<const unsigned short*>(lutb + i0) |
+                            ((unsigned)*reinterpret_cast<const unsigned short*>(lutb + i1) << 16);         // SiLU -> bf16
                 }
-                tmem_st16(t_d1 + 16u * j, pk);
+                if (oob & 0x70007000u) {
+#pragma unroll
+                    for (int e = 0; e < 16; ++e)                                  // only the pairs that need it (an exact zero, mostly: a sum that
+                        if ((v[j][e] - (LUT_LO | (LUT_LO << 16))) & 0x70007000u)  // cancelled its bias); a call each, so the arrays stay in registers
+                            pk[e] = silu_pair(v[j][e]);
+                }
+                tmem_st16(t_h + 16u * jj, pk);
             }
             tmem_wait_st();
             tc_fence_before();
-            mbar_arrive(bar(p, 2));
+            mbar_arrive(bar(H_FULL));
+            if (tid == 0) { TC_STAMP(0, it, 1) }
+            TC_STAMPW(1)
 
-            if (!__all_sync(0xffffffffu, mbar_wait(bar(p, 3), par, abort_flag))) { failed = true; break; }
+            if (!__all_sync(0xffffffffu, mbar_wait(bar(D2_FULL), par, abort_flag))) { failed = true; break; }
             tc_fence_after();
-            unsigned word[4];
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                unsigned v[32];
-                tmem_ld32(t_d1 + 128u + 32u * j, v);
-                tmem_wait_ld();
-                unsigned bits = 0u;
-#pragma unroll
-                for (int e = 0; e < 32; ++e) {
-                    float y = bfr(__uint_as_float(v[e]));
-                    if (has_b2) y = bfr(y + __bfloat162float(sb2[32 * j + e]));
-                    bits |= (y > 0.0f ? 1u : 0u) << e;
-                }
-                word[j] = bits;
-            }
+            if (tid == 0) { TC_STAMP(0, it, 2) }
+            TC_STAMPW(2)
+            tmem_ld32(t_d2, v[0]);
+            tmem_wait_ld();
             tc_fence_before();
-            mbar_arrive(bar(p, 4));
+            mbar_arrive(bar(D2_FREE));
+            unsigned bits = 0u;
+#pragma unroll
+            for (int e = 0; e < 16; ++e) {
+                unsigned y = pack2(__uint_as_float(v[0][2 * e]), __uint_as_float(v[0][2 * e + 1]));
+                y = add_bf16x2(y, sb2[e]);
+                const float y0 = __uint_as_float(y << 16), y1 = __uint_as_float(y & 0xffff0000u);
+                bits |= ((y0 > 0.0f ? 1u : 0u) | (y1 > 0.0f ? 2u : 0u)) << (2 * e);
+            }
             const long long b = tile / a.tiles_per_b, t = (tile - b * a.tiles_per_b) * TC_TILE + row;
-            if (t < a.T)
-                *reinterpret_cast<uint4*>(a.codes + b * a.cs_b + (t * a.H + h) * 4) = make_uint4(word[0], word[1], word[2], word[3]);
+            if (t < a.T) a.codes[b * a.cs_b + (t * a.H + h) * 4 + cg] = bits;
+            if (tid == 0) { TC_STAMP(0, it, 3) }
+            TC_STAMPW(3)
         }
     } else if (lane == 0) {
-        // ================= issuing thread of pipeline p: TMA loads and tensor-core instructions =================
-        const unsigned x_s = base + OFF_X + (unsigned)p * X_BYTES;
-        const unsigned t_d1 = tmem + (unsigned)p * 256u;
+        // ================= issuing thread: TMA loads and tensor-core instructions =================
+        const unsigned x_s = base + OFF_X;
         constexpr unsigned I1 = instr_desc(256), I2 = instr_desc(128);
-        bool load_pending = false;
-        auto load = [&](long long tile) {
+        bool pending[2] = {false, false};                     // a copy into this stage is in flight
+        auto load = [&](long long tile, int st) {
             const long long b = tile / a.tiles_per_b;
             const int t0 = (int)((tile - b * a.tiles_per_b) * TC_TILE);
-            mbar_expect_tx(bar(p, 0), X_BYTES);
-            tma_load_4d(x_s, &xmap, bar(p, 0), 0, t0, h, (int)b);                 // k 0..63 of the 128 rows
-            tma_load_4d(x_s + X_BYTES / 2, &xmap, bar(p, 0), 64, t0, h, (int)b);  // k 64..127
-            load_pending = true;
+            const unsigned dst = x_s + (unsigned)st * X_BYTES;
+            mbar_expect_tx(bar(X_FULL + st), X_BYTES);
+            tma_load_4d(dst, &xmap, bar(X_FULL + st), 0, t0, h, (int)b);                 // k 0..63 of the 128 rows
+            tma_load_4d(dst + X_BYTES / 2, &xmap, bar(X_FULL + st), 64, t0, h, (int)b);  // k 64..127
+            pending[st] = true;
         };
-        if (first < a.n_tiles) load(first);
-        unsigned it = 0;
-        for (long long tile = first; tile < a.n_tiles; tile += step, ++it) {
-            const unsigned par = it & 1u;
-            if (!mbar_wait(bar(p, 0), par, abort_flag)) { failed = true; break; }
-            load_pending = false;
-            if (it > 0 && !mbar_wait(bar(p, 4), par ^ 1u, abort_flag)) { failed = true; break; }   // D2 of the previous tile has been read
+        auto mma1 = [&](unsigned n) -> bool {                 // layer 1 of this CTA's n-th tile, once its rows have landed
+            const int st = (int)(n & 1u);
+            if (!mbar_wait(bar(X_FULL + st), (n >> 1) & 1u, abort_flag)) return false;
+            pending[st] = false;
             tc_fence_after();
 #pragma unroll
             for (int ks = 0; ks < 8; ++ks) {
-                const unsigned ao = (unsigned)(ks >> 2) * (X_BYTES / 2) + (unsigned)(ks & 3) * 32u;
+                const unsigned ao = (unsigned)st * X_BYTES + (unsigned)(ks >> 2) * (X_BYTES / 2) + (unsigned)(ks & 3) * 32u;
                 const unsigned bo = (unsigned)(ks >> 2) * (256u * 128u) + (unsigned)(ks & 3) * 32u;
-                mma_ss(t_d1, smem_desc(x_s + ao), smem_desc(base + OFF_W1 + bo), I1, ks > 0 ? 1u : 0u);
+                mma_ss(tmem, smem_desc(x_s + ao), smem_desc(base + OFF_W1 + bo), I1, ks > 0 ? 1u : 0u);
             }
-            tc_commit(bar(p, 1));
-            if (!mbar_wait(bar(p, 1), par, abort_flag)) { failed = true; break; }                  // the input stage is free
-            if (tile + step < a.n_tiles) load(tile + step);
-            if (!mbar_wait(bar(p, 2), par, abort_flag)) { failed = true; break; }                  // H is in TMEM
+            tc_commit(bar(D1_FULL));
+            return true;
+        };
+        if (first < a.n_tiles) load(first, 0);
+        if (first + step < a.n_tiles) load(first + step, 1);
+        if (first < a.n_tiles && !mma1(0)) failed = true;
+        unsigned it = 0;
+        for (long long tile = first; tile < a.n_tiles && !failed; tile += step, ++it) {
+            const unsigned par = it & 1u;
+            TC_STAMP(1, it, 0)
+            if (!mbar_wait(bar(H_FULL), par, abort_flag)) { failed = true; break; }        // H written, D1 read: layer 1 of this tile is over
+            TC_STAMP(1, it, 1)
+            if (tile + 2 * step < a.n_tiles) load(tile + 2 * step, (int)par);               // ... so its input stage is free
+            if (it > 0 && !mbar_wait(bar(D2_FREE), par ^ 1u, abort_flag)) { failed = true; break; }   // D2 of the previous tile has been read
             tc_fence_after();
 #pragma unroll
             for (int ks = 0; ks < 16; ++ks) {
                 const unsigned bo = (unsigned)(ks >> 2) * (128u * 128u) + (unsigned)(ks & 3) * 32u;
-                mma_ts(t_d1 + 128u, t_d1 + 8u * ks, smem_desc(base + OFF_W2 + bo), I2, ks > 0 ? 1u : 0u);
+                mma_ts(tmem + 384u, tmem + 256u + 8u * ks, smem_desc(base + OFF_W2 + bo), I2, ks > 0 ? 1u : 0u);
             }
-            tc_commit(bar(p, 3));
+            tc_commit(bar(D2_FULL));
+            TC_STAMP(1, it, 2)
+            if (tile + step < a.n_tiles && !mma1(it + 1)) { failed = true; break; }         // runs under the second epilogue of this tile
         }
-        if (failed && load_pending) mbar_wait(bar(p, 0), it & 1u, abort_flag);    // a copy of ours is still in flight: let it land (bounded)
+        TC_STAMP(1, 63, 3)
+        if (failed) {                                         // copies of ours still in flight: let them land (bounded)
+            for (int st = 0; st < 2; ++st)
+                if (pending[st]) {
+                    for (unsigned i = 0; i < WAIT_LIMIT && !(mbar_test(bar(X_FULL + st), 0u) || mbar_test(bar(X_FULL + st), 1u)); ++i) __nanosleep(256);
+                }
+        }
     }
     if (failed) {
         *abort_flag = 1;
@@ -307,6 +384,13 @@ int* g_status_host = nullptr;     // one mapped host word for the process: any d
 int g_hash_kernel = 0;            // 0 by shape, 1 warp-level kernel only, 2 this kernel whenever it covers the shape
 
 }  // namespace
+
+#ifdef SL_TC_TIMING
+extern "C" int sl_profile_tc_timing(unsigned long long* host_out) {
+    if (cudaMemcpyFromSymbol(host_out + 2 * 64 * 4, g_tc_dbgw, sizeof(g_tc_dbgw)) != cudaSuccess) return 1;
+    return cudaMemcpyFromSymbol(host_out, g_tc_dbg, sizeof(g_tc_dbg)) == cudaSuccess ? 0 : 1;
+}
+#endif
 
 namespace sl {
 
