@@ -12,8 +12,9 @@
 //   TMA   X tile [128 x 128] into one of two stages            -> x_full[stage]
 //   MMA1  D1[128 x 256] = X W1            (8 x  M128 N256 K16)  -> d1_full   (the input stage is free again)
 //   EPI1  D1 -> registers, torch's rounding points (matmul -> bf16, + bias -> bf16, SiLU -> bf16), packed
-//         pairs of bf16 written to H: the A operand of layer 2  -> h_full    (D1 is free: MMA1 of the next tile
-//         is issued behind MMA2 of this one and runs under EPI2)
+//         pairs of bf16 written to H: the A operand of layer 2  -> h_full, h_full2 (a warp's columns in two halves:
+//         MMA2 starts on the first; after the second D1 is free, and MMA1 of the next tile, issued behind MMA2 of
+//         this one, runs under EPI2)
 //   MMA2  D2[128 x 128] = H W2            (16 x M128 N128 K16, A from TMEM) -> d2_full
 //   EPI2  D2 -> registers, rounding points, sign bit of every value: a thread holds one 32-bit word of its
 //         row's code and stores it                              -> d2_free
@@ -177,13 +178,13 @@ __global__ void __launch_bounds__(TC_THREADS, 1) hash_encode_tc_kernel(const __g
     volatile int* abort_flag = reinterpret_cast<volatile int*>(g + OFF_MISC + 4);
     unsigned* tmem_slot = reinterpret_cast<unsigned*>(g + OFF_MISC);
     auto bar = [&](int i) { return base + OFF_BAR + (unsigned)i * 8u; };
-    constexpr int X_FULL = 0 /* and 1 */, D1_FULL = 2, H_FULL = 3, D2_FULL = 4, D2_FREE = 5;
+    constexpr int X_FULL = 0 /* and 1 */, D1_FULL = 2, H_FULL = 3 /* first half of every warp's columns */, D2_FULL = 4, D2_FREE = 5, H_FULL2 = 6;
 
     // ---- set-up: barriers, TMEM, this head's weights (transposed to K-major) and biases
     if (tid == 0) {
         *abort_flag = 0;
         mbar_init(bar(X_FULL), 1); mbar_init(bar(X_FULL + 1), 1); mbar_init(bar(D1_FULL), 1);
-        mbar_init(bar(H_FULL), TC_EPI_WARPS * 32); mbar_init(bar(D2_FULL), 1); mbar_init(bar(D2_FREE), TC_EPI_WARPS * 32);
+        mbar_init(bar(H_FULL), TC_EPI_WARPS * 32); mbar_init(bar(H_FULL2), TC_EPI_WARPS * 32); mbar_init(bar(D2_FULL), 1); mbar_init(bar(D2_FREE), TC_EPI_WARPS * 32);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == TC_EPI_WARPS) {
@@ -269,10 +270,10 @@ __global__ void __launch_bounds__(TC_THREADS, 1) hash_encode_tc_kernel(const __g
                             pk[e] = silu_pair(v[j][e]);
                 }
                 tmem_st16(t_h + 16u * jj, pk);
+                tmem_wait_st();
+                tc_fence_before();
+                mbar_arrive(bar(jj == 0 ? H_FULL : H_FULL2));     // layer 2 starts on the half that is there
             }
-            tmem_wait_st();
-            tc_fence_before();
-            mbar_arrive(bar(H_FULL));
             if (tid == 0) { TC_STAMP(0, it, 1) }
             TC_STAMPW(1)
 
@@ -332,16 +333,25 @@ __global__ void __launch_bounds__(TC_THREADS, 1) hash_encode_tc_kernel(const __g
         for (long long tile = first; tile < a.n_tiles && !failed; tile += step, ++it) {
             const unsigned par = it & 1u;
             TC_STAMP(1, it, 0)
-            if (!mbar_wait(bar(H_FULL), par, abort_flag)) { failed = true; break; }        // H written, D1 read: layer 1 of this tile is over
+            if (!mbar_wait(bar(H_FULL), par, abort_flag)) { failed = true; break; }        // the first half of every warp's H columns is written
             TC_STAMP(1, it, 1)
-            if (tile + 2 * step < a.n_tiles) load(tile + 2 * step, (int)par);               // ... so its input stage is free
+            if (tile + 2 * step < a.n_tiles) load(tile + 2 * step, (int)par);               // layer 1 of this tile is long over: its input stage is free
             if (it > 0 && !mbar_wait(bar(D2_FREE), par ^ 1u, abort_flag)) { failed = true; break; }   // D2 of the previous tile has been read
             tc_fence_after();
 #pragma unroll
-            for (int ks = 0; ks < 16; ++ks) {
-                const unsigned bo = (unsigned)(ks >> 2) * (128u * 128u) + (unsigned)(ks & 3) * 32u;
-                mma_ts(tmem + 384u, tmem + 256u + 8u * ks, smem_desc(base + OFF_W2 + bo), I2, ks > 0 ? 1u : 0u);
+            for (int half = 0; half < 2; ++half) {
+                if (half == 1) {
+                    if (!mbar_wait(bar(H_FULL2), par, abort_flag)) { failed = true; break; }   // the rest of H is written and all of D1 read
+                    tc_fence_after();
+                }
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    const int ks = 4 * (i >> 1) + 2 * half + (i & 1);       // warp group cg wrote K [64 cg + 32 half, + 32)
+                    const unsigned bo = (unsigned)(ks >> 2) * (128u * 128u) + (unsigned)(ks & 3) * 32u;
+                    mma_ts(tmem + 384u, tmem + 256u + 8u * ks, smem_desc(base + OFF_W2 + bo), I2, (half | i) ? 1u : 0u);
+                }
             }
+            if (failed) break;
             tc_commit(bar(D2_FULL));
             TC_STAMP(1, it, 2)
             if (tile + step < a.n_tiles && !mma1(it + 1)) { failed = true; break; }         // runs under the second epilogue of this tile
