@@ -194,6 +194,9 @@ def workload_config(cfg):
 # ------------------------------------------------------------------------------------------
 # GPU arm
 # ------------------------------------------------------------------------------------------
+PREFILL_CODE_BUILD = None
+
+
 def build_session(cfg, device, lru=False, extra_capacity=0, fused_kv=True):
     from spotlight_b200 import ops
     from spotlight_b200.session import DecodeSession, SessionConfig
@@ -215,6 +218,7 @@ def build_session(cfg, device, lru=False, extra_capacity=0, fused_kv=True):
     ch = torch.randperm(HEAD_DIM, generator=gen)[:4].to(device)
     chunk = 16384
     t_codes = 0.0
+    t_layers = []
     for layer in range(cfg.layers):
         for lo in range(0, n, chunk):
             hi = min(n, lo + chunk)
@@ -233,10 +237,22 @@ def build_session(cfg, device, lru=False, extra_capacity=0, fused_kv=True):
         e1.record()
         torch.cuda.synchronize(device)
         t_codes += e0.elapsed_time(e1)
+        t_layers.append(e0.elapsed_time(e1))
     s.q_in.copy_(torch.randn(s.q_in.shape, generator=dgen, device=device).to(dt))
     s.k_in.copy_(torch.randn(s.k_in.shape, generator=dgen, device=device).to(dt))
     s.v_in.copy_(torch.randn(s.v_in.shape, generator=dgen, device=device).to(dt))
     s.set_position(n - 1, cfg.rope_theta)
+    # the prefill contraction: all keys of a layer through the key-side hash (the first layer also pays one-time set-up)
+    warm = t_layers[1:] if len(t_layers) > 1 else t_layers
+    dims = cfg.mlp_dims if cfg.hash == "mlp" else (HEAD_DIM, HEAD_DIM)
+    rows = cfg.batch * n * cfg.kv_heads
+    flop = rows * sum(2.0 * a * b for a, b in zip(dims[:-1], dims[1:]))
+    ms = sum(warm) / len(warm)
+    global PREFILL_CODE_BUILD
+    PREFILL_CODE_BUILD = {"ms_per_layer": ms, "rows_per_layer": rows, "tflops": flop / ms / 1e9,
+                          "gbs": rows * (HEAD_DIM * s.k_cache[0].element_size() + 16) / ms / 1e6,
+                          "kernel": "tcgen05 (TMEM accumulators, TMA input tiles)" if (cfg.hash == "mlp" and tuple(dims) == (128, 256, 128)
+                                     and dt == torch.bfloat16 and not cfg.mlp_residue) else "warp-level mma / scalar"}
     return s, t_codes / cfg.layers
 
 
@@ -450,6 +466,7 @@ def run_ours(args, cfg):
         "path": {"algorithmic_bytes_per_layer": by_scan + by_attn, "gbs": path_gbs, "frac": path_gbs / peak,
                  "attended_keys_per_head": mean_nsel / (cfg.batch * cfg.kv_heads), "budget_k": budget(n, cfg.mask_out, cfg.min_remain)},
         "code_build_ms_per_layer": code_build_ms,
+        "prefill_code_build": PREFILL_CODE_BUILD,
         "clocks": clk,
         "checksum": checksum if extras else float(out_host.float().abs().sum()),
     }
@@ -457,10 +474,18 @@ def run_ours(args, cfg):
         line["four_stage"] = lru_info
     line.update(extras)
     if world == 1 and not args.no_reference_kernels and cfg.name == "headline":
+        try:
+            line["row_gather"] = row_gather(cfg, s, device)
+        except Exception as e:                       # a measurement beside the headline, never a reason to lose the line
+            line["row_gather"] = {"error": str(e)[:200]}
         g_all = g = None
         del s
         torch.cuda.empty_cache()
         line["reference_gpu_kernels"] = reference_gpu_kernels(device)
+        try:
+            line["host_backing_store"] = host_backing_store(cfg, device)
+        except Exception as e:
+            line["host_backing_store"] = {"error": str(e)[:200]}
     if world == 1 and not args.no_cpu_baseline:
         us, heads, threads, sec = time_cpu(cfg, n, steps=2, warmup=1, budget_s=25.0)
         line["cpu_baseline"] = {
@@ -715,6 +740,77 @@ def multi_rank_extras(args, device, dist, world, rank):
         del s3, g3
         torch.cuda.empty_cache()
     return out
+
+
+def row_gather(cfg, s, device, steps=10):
+    """The reference's gather step on the attended keys' index lists: sl_gather_rows (KVCache.gather of
+    spotlight/modifiers/gpu_cache.py:51-54) copies the selected 256-byte rows of ONE dense [B, N, KH, 128] cache into a
+    packed buffer; three caches of the layer's size rotate, so the rows come from HBM. The sparse attention kernel
+    reads the same rows of K and of V without writing them anywhere: twice the gathered bytes in about the same time."""
+    from spotlight_b200 import ops
+    n = cfg.context
+    caches = [torch.randn((cfg.batch, n, cfg.kv_heads, HEAD_DIM), device=device).to(s.cfg.dtype) for _ in range(3)]
+    nsel = int(s.cnt.min().item())
+    rows = cfg.batch * cfg.kv_heads * nsel
+    for c in caches:
+        ops.gather_rows(c, s.idx, nsel)
+    torch.cuda.synchronize(device)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(steps * 3):
+        ops.gather_rows(caches[i % 3], s.idx, nsel)
+    e1.record()
+    torch.cuda.synchronize(device)
+    us = e0.elapsed_time(e1) * 1e3 / (steps * 3)
+    row_bytes = HEAD_DIM * caches[0].element_size()
+    return {"kernel": "sl_gather_rows", "rows_per_launch": rows, "us_per_launch": us,
+            "read_gbs": rows * row_bytes / us / 1e3, "read_plus_write_gbs": 2 * rows * row_bytes / us / 1e3}
+
+
+def host_backing_store(cfg, device, steps=8, churn=0.1):
+    """Stage 3 with the backing K/V store in pinned HOST memory (the offloaded variant of the reference,
+    spotlight/modifiers/cpu_cache.py:60-130): one layer of the workload's shape; every step a tenth of each head's
+    attended keys is replaced by new ones, which sl_lru_update pulls across PCIe into the resident buffer. Reports
+    the time of the update and the rate of the missed rows (K and V, 512 bytes per miss)."""
+    from spotlight_b200 import ops
+    from spotlight_b200.workloads import torch_dtype
+    dt = torch_dtype(cfg.dtype)
+    B, KH, n = cfg.batch, cfg.kv_heads, cfg.context
+    nsel = budget(n, cfg.mask_out, cfg.min_remain) + cfg.sink + cfg.recent
+    k_host = torch.empty((B, n, KH, HEAD_DIM), dtype=dt).pin_memory()
+    v_host = torch.empty((B, n, KH, HEAD_DIM), dtype=dt).pin_memory()
+    k_host.normal_(); v_host.normal_()
+    table = ops.LruTable(B, KH, n, 2 * nsel, dt, device)
+    g = torch.Generator(device=device).manual_seed(cfg.seed + 11)
+    cur = torch.stack([torch.randperm(n, generator=g, device=device)[:nsel] for _ in range(B * KH)]).view(B, KH, nsel)
+    cnt = torch.full((B, KH), nsel, dtype=torch.int32, device=device)
+    ptrs = (k_host.data_ptr(), v_host.data_ptr(), k_host.stride(0))
+    times, missed = [], []
+    for step in range(steps + 2):
+        idx = torch.sort(cur, dim=-1).values.to(torch.int32).contiguous()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        ops.lru_update(table, idx, cnt, None, None, backing_ptrs=ptrs)
+        e1.record()
+        torch.cuda.synchronize(device)
+        if step >= 2:                                    # step 0 fills the table, step 1 warms up
+            times.append(e0.elapsed_time(e1) * 1e3)
+            missed.append(table.stats[..., 1].sum().item())      # the table's counters are per update: [hits, misses]
+        nswap = max(1, int(churn * nsel))
+        flat = cur.view(B * KH, nsel)
+        for r in range(B * KH):                          # replace nswap entries of every list by tokens that are not in it
+            absent = torch.ones(n, dtype=torch.bool, device=device)
+            absent[flat[r]] = False
+            pool = absent.nonzero().flatten()
+            fresh = pool[torch.randperm(pool.numel(), generator=g, device=device)[:nswap]]
+            where = torch.randperm(nsel, generator=g, device=device)[:nswap]
+            flat[r, where] = fresh
+    ok = int(table.status.item()) == 0
+    us = sum(times) / len(times)
+    rows = sum(missed) / len(missed)
+    return {"workload": f"one layer, B{B} x {n} keys x {KH} kv heads, {nsel} attended keys per head, {churn:.0%} replaced per step",
+            "us_per_update": us, "missed_rows_per_update": rows, "pcie_gbs": rows * 2 * HEAD_DIM * k_host.element_size() / us / 1e3,
+            "status_words_ok": ok}
 
 
 def reference_gpu_kernels(device):
