@@ -343,6 +343,9 @@ def run_ours(args, cfg):
     if args.attn_warps:
         from spotlight_b200 import _lib
         _lib.check(_lib.lib.sl_configure(_lib.SL_OPT_ATTN_WARPS, args.attn_warps))
+    if args.no_attn_cluster:
+        from spotlight_b200 import _lib
+        ops.configure(_lib.SL_OPT_ATTN_CLUSTER, 0)
     with_lru = not args.no_lru and cfg.name in ("headline", "cfg1", "cfg2")
     lru_tokens = args.warmup + args.steps + 8
     s, code_build_ms = build_session(cfg, device, lru=with_lru, fused_kv=not args.separate_kv,
@@ -891,6 +894,7 @@ def main():
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--separate-kv", action="store_true", help="two K/V caches per layer instead of one fused cache")
     ap.add_argument("--attn-warps", type=int, default=0, choices=[0, 4, 8], help="warps per CTA of the attention kernel (0: by shape)")
+    ap.add_argument("--no-attn-cluster", action="store_true", help="combine the attention splits with the merge kernel even where a thread-block cluster fits")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-reference-kernels", action="store_true", help="skip timing the reference's CUDA scorer beside ours (1 GPU)")
     ap.add_argument("--no-extras", action="store_true", help="with several ranks: skip the sharded / batch-split measurements")

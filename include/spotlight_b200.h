@@ -62,10 +62,19 @@ int sl_set_device(int device);
  *   SL_OPT_PEER_SPIN_LIMIT  polls (100 ns apart) after which the peer-memory exchanges stop waiting for another
  *                       rank's message and set their status word to 3; default 400000, about a second
  *   SL_OPT_HASH_KERNEL  which kernel sl_hash_encode uses for bf16 rows of a 128 -> 256 -> 128 hash: 0 (default)
- *                       by size, 1 the warp-level tensor-core kernel, 2 the tcgen05 / TMEM kernel for every size */
+ *                       by size, 1 the warp-level tensor-core kernel, 2 the tcgen05 / TMEM kernel for every size
+ *   SL_OPT_ATTN_CLUSTER 1 (default): the CTAs that share a (batch row, kv head) pair of the bf16 attention kernel form a
+ *                       thread-block cluster and combine their partials through distributed shared memory where
+ *                       all clusters of the launch fit on the device at once; 0: partials in the workspace and a merge kernel */
 typedef enum { SL_OPT_PDL = 0, SL_OPT_L2_PREFETCH = 1, SL_OPT_SCAN_KERNEL = 2, SL_OPT_ATTN_WARPS = 3,
-               SL_OPT_PEER_SPIN_LIMIT = 4, SL_OPT_HASH_KERNEL = 5 } sl_option;
+               SL_OPT_PEER_SPIN_LIMIT = 4, SL_OPT_HASH_KERNEL = 5, SL_OPT_ATTN_CLUSTER = 6 } sl_option;
 int sl_configure(int option, int value);
+
+/* How many thread-block clusters of `cluster_size` CTAs (2..16) of the bf16 attention kernel with `warps_per_cta`
+ * (4 or 8) warps the current device holds at once; 0 when it holds none. The attention kernel combines the splits
+ * of a (batch row, kv head) pair inside such a cluster when all clusters of a launch fit at once (SL_OPT_ATTN_CLUSTER).
+ * No reference counterpart. */
+int sl_attn_cluster_capacity(int warps_per_cta, int cluster_size);
 
 /* Status of the prefill hash kernels since the last call: 0, or 3 after a bounded device-side wait (an mbarrier
  * of the tcgen05 kernel) ran out. Reading clears it. Synchronise the streams that ran sl_hash_encode first.

@@ -14,7 +14,7 @@ LIB_PATH = os.path.join(_HERE, "lib", "libspotlight_b200.so")
 SL_OK, SL_EINVAL, SL_ESHAPE, SL_EALIGN, SL_EWORKSPACE, SL_ECUDA, SL_ETIMEOUT = 0, -1, -2, -3, -4, -5, -6
 SL_BF16, SL_F32, SL_F16, SL_BOOL = 0, 1, 2, 3
 GQA_INTERLEAVED, GQA_BLOCKED = 0, 1
-SL_OPT_PDL, SL_OPT_L2_PREFETCH, SL_OPT_SCAN_KERNEL, SL_OPT_ATTN_WARPS, SL_OPT_PEER_SPIN_LIMIT, SL_OPT_HASH_KERNEL = 0, 1, 2, 3, 4, 5
+SL_OPT_PDL, SL_OPT_L2_PREFETCH, SL_OPT_SCAN_KERNEL, SL_OPT_ATTN_WARPS, SL_OPT_PEER_SPIN_LIMIT, SL_OPT_HASH_KERNEL, SL_OPT_ATTN_CLUSTER = 0, 1, 2, 3, 4, 5, 6
 
 
 class HashParamsStruct(C.Structure):
@@ -68,6 +68,7 @@ SIGNATURES = {
     "sl_set_device": (_I, [_I]),
     "sl_configure": (_I, [_I, _I]),
     "sl_hash_status": (_I, []),
+    "sl_attn_cluster_capacity": (_I, [_I, _I]),
     "sl_pack_signbits": (_I, [_P, _I, _L, _P, _P]),
     "sl_hamming_scores": (_I, [_P, _P, _L, _P, _I, _L, _I, _I, _I, _I, _P]),
     "sl_hamming_scores_u8": (_I, [_P, _P, _P, _L, _L, _I, _P]),

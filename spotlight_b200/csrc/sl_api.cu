@@ -71,7 +71,7 @@ extern "C" int sl_workspace_init(void* d_workspace, size_t bytes, void* stream) 
 }
 
 namespace slscan { void set_scan_kernel(int v); }
-namespace sl { void set_attn_warps(int v); void set_peer_spin_limit(unsigned v); void set_hash_kernel(int mode); int take_hash_status(); }
+namespace sl { void set_attn_warps(int v); void set_peer_spin_limit(unsigned v); void set_hash_kernel(int mode); int take_hash_status(); void set_attn_cluster(int v); int attn_cluster_capacity(int warps, int cs); }
 
 extern "C" int sl_configure(int option, int value) {
     switch (option) {
@@ -89,6 +89,7 @@ extern "C" int sl_configure(int option, int value) {
             SL_REQUIRE(value >= 1, SL_EINVAL, "sl_configure: SL_OPT_PEER_SPIN_LIMIT takes a positive number of polls");
             sl::set_peer_spin_limit((unsigned)value);
             return SL_OK;
+        case SL_OPT_ATTN_CLUSTER: sl::set_attn_cluster(value ? 1 : 0); return SL_OK;
         case SL_OPT_HASH_KERNEL:
             SL_REQUIRE(value >= 0 && value <= 2, SL_EINVAL, "sl_configure: SL_OPT_HASH_KERNEL takes 0, 1 or 2");
             sl::set_hash_kernel(value);
@@ -98,3 +99,8 @@ extern "C" int sl_configure(int option, int value) {
 }
 
 extern "C" int sl_hash_status(void) { return sl::take_hash_status(); }
+
+extern "C" int sl_attn_cluster_capacity(int warps_per_cta, int cluster_size) {
+    SL_REQUIRE(warps_per_cta == 4 || warps_per_cta == 8, SL_EINVAL, "sl_attn_cluster_capacity: warps_per_cta is 4 or 8");
+    return sl::attn_cluster_capacity(warps_per_cta, cluster_size);
+}

@@ -22,8 +22,12 @@
 // [B, N, KH, 128] or one cache [B, N, KH, 2, 128] in which a key's K and V rows are adjacent, so
 // that one gathered key is ONE 512-byte piece of DRAM instead of two 256-byte ones (measured on
 // B200: no difference in time, 17.25 against 17.31 us at the headline shape).
+#include <cooperative_groups.h>
+
 #include "sl_attn.cuh"
 #include "sl_mma.cuh"
+
+namespace cg = cooperative_groups;
 
 namespace {
 
@@ -41,7 +45,9 @@ __device__ __forceinline__ unsigned swz(int r, int c) { return (unsigned)(r * 25
 // HI: the group has more than 8 query heads (rows 8..15 of the tile are used).
 // MW warps per CTA: 8 (one CTA per SM) when there are at most as many (batch row, kv head) pairs as
 // SMs -- fewer, fatter CTAs mean fewer partials to combine -- else 4 (two CTAs per SM).
-template <bool HI, int MW>
+// CL: the CTAs of a (batch row, kv head) are one thread-block cluster and combine their partials through
+// distributed shared memory (no partials in global memory, no merge kernel).
+template <bool HI, int MW, bool CL>
 __global__ void __launch_bounds__(MW * 32, 8 / MW) sparse_attn_mma_kernel(const AttnArgs a, const int G) {
     constexpr int MT = MW * 32;
     extern __shared__ __align__(128) unsigned char ring[];          // [MW][ST][K 4 KB | V 4 KB]; reused by the epilogue
@@ -237,6 +243,7 @@ __global__ void __launch_bounds__(MW * 32, 8 / MW) sparse_attn_mma_kernel(const 
 
     const long long bh = (long long)b * KH + h;
     float* part = a.part + (bh * a.splits + sp) * G * 130;
+    float* cpart = reinterpret_cast<float*>(ring + 65536);          // this CTA's partial [G][130], behind sm_acc (cluster mode)
     for (int e = tid; e < G * 128; e += MT) {
         const int g = e >> 7, col = e & 127;
         float M = -INFINITY;
@@ -257,9 +264,46 @@ __global__ void __launch_bounds__(MW * 32, 8 / MW) sparse_attn_mma_kernel(const 
             reinterpret_cast<__nv_bfloat16*>(a.out)[oo] = __float2bfloat16_rn(L > 0.0f ? O / L : 0.0f);
             if (a.lse && col == 0) a.lse[(long long)b * KH * G + qh] = L > 0.0f ? (M + log2f(L)) * LN2 : -INFINITY;
         } else {
-            part[g * 130 + col] = O;
-            if (col == 0) { part[g * 130 + 128] = M; part[g * 130 + 129] = L; }
+            float* dst = CL ? cpart : part;
+            dst[g * 130 + col] = O;
+            if (col == 0) { dst[g * 130 + 128] = M; dst[g * 130 + 129] = L; }
         }
+    }
+    if (CL) {
+        // ---- every CTA of the cluster combines a slice of the (query head, column) pairs from all partials
+        cg::cluster_group cluster = cg::this_cluster();
+        cluster.sync();
+        const int CS = a.splits;                                   // cluster size = splits <= 16, rank = sp
+        const int total = G * 128, per = (total + CS - 1) / CS;
+        const int lo = sp * per, hi = min(total, lo + per);
+        for (int e = lo + tid; e < hi; e += MT) {
+            const int g = e >> 7, col = e & 127;
+            float ms[16], ls[16], os[16];
+            float M = -INFINITY;
+#pragma unroll
+            for (int c = 0; c < 16; ++c) {
+                ms[c] = -INFINITY; ls[c] = 0.0f; os[c] = 0.0f;
+                if (c < CS) {
+                    const float* r = cluster.map_shared_rank(cpart, c) + g * 130;
+                    ms[c] = r[128]; ls[c] = r[129]; os[c] = r[col];
+                }
+                M = fmaxf(M, ms[c]);
+            }
+            float L = 0.0f, O = 0.0f;
+            if (M != -INFINITY) {
+#pragma unroll
+                for (int c = 0; c < 16; ++c) {
+                    const float w = exp2f(ms[c] - M);              // 0 for the ranks that do not exist
+                    L += ls[c] * w;
+                    O += os[c] * w;
+                }
+            }
+            const int qh = a.layout == SL_GQA_INTERLEAVED ? g * KH + h : h * G + g;
+            const long long oo = ((long long)b * KH * G + qh) * 128 + col;
+            reinterpret_cast<__nv_bfloat16*>(a.out)[oo] = __float2bfloat16_rn(L > 0.0f ? O / L : 0.0f);
+            if (a.lse && col == 0) a.lse[(long long)b * KH * G + qh] = L > 0.0f ? (M + log2f(L)) * LN2 : -INFINITY;
+        }
+        cluster.sync();                                            // nobody leaves while its partial is still being read
     }
 }
 
@@ -268,8 +312,63 @@ __global__ void __launch_bounds__(MW * 32, 8 / MW) sparse_attn_mma_kernel(const 
 namespace sl {
 
 static int g_attn_warps = 0;        // 0: by shape; 4 / 8: forced (sl_configure, for measurements)
+static int g_attn_cluster = 1;      // 1: combine the splits inside a thread-block cluster where one fits; 0: always the merge kernel
 void set_attn_warps(int v) { g_attn_warps = v; }
+void set_attn_cluster(int v) { g_attn_cluster = v; }
 static bool fat_ctas(int B, int KH) { return g_attn_warps ? g_attn_warps == 8 : B * KH <= sm_count(); }
+
+template <bool HI, int MW>
+static cudaError_t cluster_config(cudaLaunchConfig_t& cfg, cudaLaunchAttribute* attrs, int cs, int KH, int B, cudaStream_t s) {
+    const size_t ring_bytes = (size_t)MW * ST * STAGE_BYTES;
+    const void* fn = reinterpret_cast<const void*>(sparse_attn_mma_kernel<HI, MW, true>);
+    cudaError_t e = ensure_dyn_smem(fn, ring_bytes);
+    if (e != cudaSuccess) return e;
+    static bool allowed = false;                       // per instantiation: clusters of more than 8 CTAs are an opt-in
+    if (!allowed) {
+        e = cudaFuncSetAttribute(fn, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+        if (e != cudaSuccess) return e;
+        allowed = true;
+    }
+    cfg = {};
+    cfg.gridDim = dim3((unsigned)cs, (unsigned)KH, (unsigned)B); cfg.blockDim = dim3(MW * 32); cfg.dynamicSmemBytes = ring_bytes; cfg.stream = s;
+    unsigned n = 0;
+    attrs[n].id = cudaLaunchAttributeClusterDimension;
+    attrs[n].val.clusterDim.x = (unsigned)cs; attrs[n].val.clusterDim.y = 1; attrs[n].val.clusterDim.z = 1;
+    ++n;
+    if (pdl_enabled()) {
+        attrs[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attrs[n].val.programmaticStreamSerializationAllowed = 1;
+        ++n;
+    }
+    cfg.attrs = attrs; cfg.numAttrs = n;
+    return cudaSuccess;
+}
+
+// How many clusters of cs CTAs of MW warps the device holds at once (0: none, or the query failed); cached.
+template <int MW>
+static int max_clusters(int cs) {
+    static int cache[17] = {};                         // 0 = not asked yet, -1 = none
+    if (cs < 2 || cs > 16) return 0;
+    if (cache[cs] == 0) {
+        cudaLaunchConfig_t cfg;
+        cudaLaunchAttribute attrs[2];
+        int n = 0;
+        if (cluster_config<false, MW>(cfg, attrs, cs, 1, 1, nullptr) != cudaSuccess ||
+            cudaOccupancyMaxActiveClusters(&n, reinterpret_cast<const void*>(sparse_attn_mma_kernel<false, MW, true>), &cfg) != cudaSuccess) {
+            cudaGetLastError();
+            n = 0;
+        }
+        cache[cs] = n > 0 ? n : -1;
+    }
+    return cache[cs] > 0 ? cache[cs] : 0;
+}
+
+// The splits of a (row, head) pair form one cluster when all the clusters of the launch fit on the device at once.
+static bool use_cluster(int B, int KH, int splits) {
+    if (!g_attn_cluster || splits < 2 || splits > 16) return false;
+    const int have = fat_ctas(B, KH) ? max_clusters<8>(splits) : max_clusters<4>(splits);
+    return have >= B * KH;
+}
 
 int attn_mma_splits(int B, int KH, int cap) {
     // never more CTAs than fit at once (one of eight warps per SM, or two of four); every warp
@@ -279,18 +378,30 @@ int attn_mma_splits(int B, int KH, int cap) {
     const int mw = fat_ctas(B, KH) ? 8 : 4;
     int s = ((8 / mw) * sm_count()) / ctas;
     s = std::min(s, std::min(ATTN_MAX_SPLITS, std::max(1, tiles / mw)));
-    return std::max(s, 1);
+    s = std::max(s, 1);
+    // a few more keys per CTA are cheaper than partials in global memory and a merge kernel
+    if (s > 16 && s <= 24 && use_cluster(B, KH, 16)) s = 16;
+    return s;
 }
 
 template <bool HI, int MW>
 static int launch_one(const AttnArgs& a, int G, cudaStream_t s) {
     const size_t ring_bytes = (size_t)MW * ST * STAGE_BYTES;
+    if (use_cluster(a.B, a.KH, a.splits)) {
+        cudaLaunchConfig_t cfg;
+        cudaLaunchAttribute attrs[2];
+        SL_CUDA_OK((cluster_config<HI, MW>(cfg, attrs, a.splits, a.KH, a.B, s)));
+        SL_CUDA_OK(cudaLaunchKernelEx(&cfg, sparse_attn_mma_kernel<HI, MW, true>, a, G));
+        return SL_OK;
+    }
     dim3 grid((unsigned)a.splits, (unsigned)a.KH, (unsigned)a.B);
-    SL_CUDA_OK(ensure_dyn_smem(reinterpret_cast<const void*>(sparse_attn_mma_kernel<HI, MW>), ring_bytes));
-    SL_CUDA_OK(launch_kernel(sparse_attn_mma_kernel<HI, MW>, grid, dim3(MW * 32), ring_bytes, s, false, a, G));
+    SL_CUDA_OK(ensure_dyn_smem(reinterpret_cast<const void*>(sparse_attn_mma_kernel<HI, MW, false>), ring_bytes));
+    SL_CUDA_OK(launch_kernel(sparse_attn_mma_kernel<HI, MW, false>, grid, dim3(MW * 32), ring_bytes, s, false, a, G));
     if (a.splits > 1) return launch_attn_merge(a, G, SL_BF16, s);
     return SL_OK;
 }
+
+int attn_cluster_capacity(int warps, int cs) { return warps == 8 ? max_clusters<8>(cs) : max_clusters<4>(cs); }
 
 int launch_attn_mma(const AttnArgs& a, int G, cudaStream_t s) {
     if (fat_ctas(a.B, a.KH)) return G > 8 ? launch_one<true, 8>(a, G, s) : launch_one<false, 8>(a, G, s);

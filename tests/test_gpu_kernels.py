@@ -419,6 +419,32 @@ def test_sparse_attention(ops, B, N, KH, QH, keep, dtype, tol, layout):
     assert torch.equal(out, out2)                                             # deterministic, workspace self-cleans
 
 
+@pytest.mark.parametrize("B,N,KH,QH,keep", [(1, 131072, 8, 32, 13176), (1, 40000, 8, 32, 900), (8, 20000, 4, 28, 470), (2, 9000, 2, 24, 3000)])
+def test_sparse_attention_cluster_merge(ops, B, N, KH, QH, keep):
+    """The splits of a (row, head) pair combined inside a thread-block cluster (distributed shared memory) against
+    the same launch with partials in the workspace and the merge kernel, and both against the checker."""
+    from spotlight_b200 import _lib
+    q, k, v, g = _attn_inputs(B, N, KH, QH, torch.bfloat16, 5)
+    idx = torch.stack([torch.stack([torch.sort(torch.randperm(N, generator=g)[:keep]).values for _ in range(KH)])
+                       for _ in range(B)]).to(torch.int32)
+    cnt = torch.full((B, KH), keep, dtype=torch.int32)
+    qd, kd, vd, idd, cd = q.to(DEV), k.to(DEV), v.to(DEV), idx.to(DEV), cnt.to(DEV)
+    try:
+        ops.configure(_lib.SL_OPT_ATTN_CLUSTER, 1)
+        out_c, lse_c = ops.sparse_attn_decode(qd, kd, vd, idd, cd, return_lse=True)
+        ops.configure(_lib.SL_OPT_ATTN_CLUSTER, 0)
+        out_m, lse_m = ops.sparse_attn_decode(qd, kd, vd, idd, cd, return_lse=True)
+    finally:
+        ops.configure(_lib.SL_OPT_ATTN_CLUSTER, 1)
+    assert (out_c.float() - out_m.float()).abs().max().item() <= 2e-3
+    assert (lse_c - lse_m).abs().max().item() <= 1e-4
+    if N <= 40000:
+        ref, ref_lse = O.sparse_attention(q, k, v, idx.numpy(), cnt.numpy(), O.BLOCKED, return_lse=True)
+        assert (out_c.float().cpu() - ref).abs().max().item() <= 2e-2
+        assert (lse_c.cpu() - torch.as_tensor(ref_lse)).abs().max().item() <= 2e-2
+
+
+
 @pytest.mark.parametrize("B,N,KH,QH,keep", [(1, 30000, 8, 32, 3000), (2, 5000, 4, 28, 600), (9, 3000, 32, 32, 200)])
 def test_sparse_attention_cache_geometries(ops, B, N, KH, QH, keep):
     """The same attention over two caches [B,N,KH,128], over the halves of one fused cache
