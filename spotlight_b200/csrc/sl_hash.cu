@@ -102,30 +102,44 @@ __device__ __forceinline__ void stage_rows(const HashJob& J, int h, long long r0
         rinfo[tid] = ri;
     }
     __syncthreads();
-    // raw rows first, then the rotation (the rotated copy may overwrite the input in place)
-    for (int e = tid; e < R * 128; e += HT) {
-        const int r = e >> 7, j = e & 127;
-        float val = 0.0f;
-        if (rinfo[r].valid) {
-            val = sl::VT<T>::to_f((reinterpret_cast<const T*>(J.x) + rinfo[r].x)[j]);
-            if (J.v_dst) (reinterpret_cast<T*>(J.v_dst) + rinfo[r].vdst)[j] = (reinterpret_cast<const T*>(J.v_src) + rinfo[r].vsrc)[j];
+    // raw rows first, then the rotation (the rotated copy may overwrite the input in place); the cos / sin values
+    // of an element are fetched together with it, so that the rotation does not wait for another trip to memory
+    constexpr int EPT = (R * 128 + HT - 1) / HT;             // elements per thread
+    float cs[EPT], sn[EPT];
+#pragma unroll
+    for (int i = 0; i < EPT; ++i) {
+        const int e = tid + i * HT;
+        cs[i] = 1.0f; sn[i] = 0.0f;
+        if (e < R * 128) {
+            const int r = e >> 7, j = e & 127;
+            float val = 0.0f;
+            if (rinfo[r].valid) {
+                val = sl::VT<T>::to_f((reinterpret_cast<const T*>(J.x) + rinfo[r].x)[j]);
+                if (J.v_dst) (reinterpret_cast<T*>(J.v_dst) + rinfo[r].vdst)[j] = (reinterpret_cast<const T*>(J.v_src) + rinfo[r].vsrc)[j];
+            }
+            if (J.cosr) {
+                const long long trow = rinfo[r].trow;
+                cs[i] = sl::VT<T>::to_f(reinterpret_cast<const T*>(J.cosr)[trow + j]);
+                sn[i] = sl::VT<T>::to_f(reinterpret_cast<const T*>(J.sinr)[trow + j]);
+            }
+            xb[r * MAXD + j] = val;
         }
-        xb[r * MAXD + j] = val;
     }
     __syncthreads();
-    for (int e = tid; e < R * 128; e += HT) {
-        const int r = e >> 7, j = e & 127;
-        float val = xb[r * MAXD + j];
-        if (J.cosr) {
-            const float other = xb[r * MAXD + (j ^ 64)];
-            const float rot = j < 64 ? -other : other;
-            const long long trow = rinfo[r].trow;
-            const float c = sl::VT<T>::to_f(reinterpret_cast<const T*>(J.cosr)[trow + j]);
-            const float sn = sl::VT<T>::to_f(reinterpret_cast<const T*>(J.sinr)[trow + j]);
-            val = sl::VT<T>::round(__fadd_rn(sl::VT<T>::round(__fmul_rn(val, c)), sl::VT<T>::round(__fmul_rn(rot, sn))));
+#pragma unroll
+    for (int i = 0; i < EPT; ++i) {
+        const int e = tid + i * HT;
+        if (e < R * 128) {
+            const int r = e >> 7, j = e & 127;
+            float val = xb[r * MAXD + j];
+            if (J.cosr) {
+                const float other = xb[r * MAXD + (j ^ 64)];
+                const float rot = j < 64 ? -other : other;
+                val = sl::VT<T>::round(__fadd_rn(sl::VT<T>::round(__fmul_rn(val, cs[i])), sl::VT<T>::round(__fmul_rn(rot, sn[i]))));
+            }
+            if (J.x_rot && rinfo[r].valid) (reinterpret_cast<T*>(J.x_rot) + rinfo[r].xrot)[j] = sl::VT<T>::from_f(val);
+            xa[r * MAXD + j] = val;
         }
-        if (J.x_rot && rinfo[r].valid) (reinterpret_cast<T*>(J.x_rot) + rinfo[r].xrot)[j] = sl::VT<T>::from_f(val);
-        xa[r * MAXD + j] = val;
     }
     __syncthreads();
 }
@@ -133,8 +147,8 @@ __device__ __forceinline__ void stage_rows(const HashJob& J, int h, long long r0
 // Partial sums of the k-splits -> rounded layer output (bias, SiLU, residual at torch's rounding points).
 template <typename T, int R>
 __device__ __forceinline__ void finish_layer(const HashJob& J, int h, int layer, int dout, int KS, const float* red,
-                                             const float* xin, float* xout) {
-    const T* bias = J.hp.d_b[layer] ? reinterpret_cast<const T*>(J.hp.d_b[layer]) + (long long)h * dout : nullptr;
+                                             const float* xin, float* xout, const T* bias_staged = nullptr) {
+    const T* bias = J.hp.d_b[layer] ? (bias_staged ? bias_staged : reinterpret_cast<const T*>(J.hp.d_b[layer]) + (long long)h * dout) : nullptr;
     const bool act = layer < J.hp.n_layers - 1;
     for (int e = threadIdx.x; e < R * dout; e += HT) {
         const int r = e / dout, j = e - r * dout;
@@ -234,6 +248,17 @@ __global__ void __launch_bounds__(HT) hash_kernel_fixed(const HashArgs args) {
     sl::pdl_trigger();
     if (hy >= args.heads) { prefetch_codes(args); sl::pdl_wait(); return; }
     if ((long long)blockIdx.x >= J.row_tiles) { sl::pdl_wait(); return; }
+    // the biases travel with the first weight matrix (16-byte pieces; a bias that is not 16-byte aligned is read in place)
+    __shared__ __align__(16) unsigned char sbias[2][MAXD * sizeof(T)];
+    bool staged[2] = {false, false};
+#pragma unroll
+    for (int l = 0; l < NL; ++l) {
+        const int dout = l == NL - 1 ? 128 : DH;
+        const unsigned char* bsrc = reinterpret_cast<const unsigned char*>(J.hp.d_b[l]) + (size_t)h * dout * sizeof(T);
+        staged[l] = J.hp.d_b[l] != nullptr && (reinterpret_cast<uintptr_t>(bsrc) & 15u) == 0;
+        if (staged[l] && threadIdx.x * 16 < dout * (int)sizeof(T))
+            cp_async16((unsigned)__cvta_generic_to_shared(sbias[l]) + threadIdx.x * 16, bsrc + threadIdx.x * 16);
+    }
     L0::fetch(J.hp.d_w[0], h, w0);
     if (NL == 2) L1::fetch(J.hp.d_w[1], h, w1);
     sl::pdl_wait();                 // weights are nobody's output; everything below may be
@@ -241,12 +266,12 @@ __global__ void __launch_bounds__(HT) hash_kernel_fixed(const HashArgs args) {
     if (NL == 2) cp_async_wait<1>(); else cp_async_wait<0>();
     __syncthreads();
     L0::template mac<R>(w0, xa, red);
-    finish_layer<T, R>(J, h, 0, NL == 1 ? 128 : DH, L0::KS, red, xa, xb);
+    finish_layer<T, R>(J, h, 0, NL == 1 ? 128 : DH, L0::KS, red, xa, xb, staged[0] ? reinterpret_cast<const T*>(sbias[0]) : nullptr);
     if (NL == 2) {
         cp_async_wait<0>();
         __syncthreads();
         L1::template mac<R>(w1, xb, red);
-        finish_layer<T, R>(J, h, 1, 128, L1::KS, red, xb, xa);
+        finish_layer<T, R>(J, h, 1, 128, L1::KS, red, xb, xa, staged[1] ? reinterpret_cast<const T*>(sbias[1]) : nullptr);
     }
     sign_pack<R>(J, rinfo, NL == 2 ? xa : xb);
 }
