@@ -384,9 +384,10 @@ def run_ours(args, cfg):
             g = s.capture(pos, stage) if use_graph else Eager(stage)
             stage_ms[stage] = time_graph(g, max(3, args.steps // 2), 3, device) / L
         # end to end: pinned host inputs in, outputs back, one host sync per token
-        hq = torch.randn(s.q_in.shape).to(s.cfg.dtype)
-        hk = torch.randn(s.k_in.shape).to(s.cfg.dtype)
-        hv = torch.randn(s.v_in.shape).to(s.cfg.dtype)
+        hq, hk, hv = s.host_inputs()                 # the token's inputs are produced straight in pinned host memory
+        hq.copy_(torch.randn(s.q_in.shape).to(s.cfg.dtype))
+        hk.copy_(torch.randn(s.k_in.shape).to(s.cfg.dtype))
+        hv.copy_(torch.randn(s.v_in.shape).to(s.cfg.dtype))
         for _ in range(max(3, args.warmup)):
             s.step_host(hq, hk, hv, pos, graph=use_graph)
         if dist is not None:

@@ -65,9 +65,11 @@ int sl_set_device(int device);
  *                       by size, 1 the warp-level tensor-core kernel, 2 the tcgen05 / TMEM kernel for every size
  *   SL_OPT_ATTN_CLUSTER 1 (default): the CTAs that share a (batch row, kv head) pair of the bf16 attention kernel form a
  *                       thread-block cluster and combine their partials through distributed shared memory where
- *                       all clusters of the launch fit on the device at once; 0: partials in the workspace and a merge kernel */
+ *                       all clusters of the launch fit on the device at once; 0: partials in the workspace and a merge kernel
+ *   SL_OPT_LRU_FUSED_FILL  1 (default): sl_decode_step[_dev] with an LRU stage issue sl_lru_update_deferred +
+ *                       sl_sparse_attn_decode_fill (bf16); 0: sl_lru_update_ex (which copies the missed rows) + sl_sparse_attn_decode_ex */
 typedef enum { SL_OPT_PDL = 0, SL_OPT_L2_PREFETCH = 1, SL_OPT_SCAN_KERNEL = 2, SL_OPT_ATTN_WARPS = 3,
-               SL_OPT_PEER_SPIN_LIMIT = 4, SL_OPT_HASH_KERNEL = 5, SL_OPT_ATTN_CLUSTER = 6 } sl_option;
+               SL_OPT_PEER_SPIN_LIMIT = 4, SL_OPT_HASH_KERNEL = 5, SL_OPT_ATTN_CLUSTER = 6, SL_OPT_LRU_FUSED_FILL = 7 } sl_option;
 int sl_configure(int option, int value);
 
 /* How many thread-block clusters of `cluster_size` CTAs (2..16) of the bf16 attention kernel with `warps_per_cta`
@@ -320,6 +322,36 @@ int sl_lru_update_ex(const int32_t* d_idx, int idx_capacity, const int32_t* d_cn
                      int32_t* d_tok2slot, int64_t n_max, int32_t* d_slot2tok, int32_t* d_last_used, int step,
                      const int64_t* d_step, int32_t* d_slots_out, int32_t* d_stats, int32_t* d_status,
                      void* d_workspace, size_t workspace_bytes, void* stream);
+
+/* Stage (3) without its own copy of the missed rows: the slot tables are updated exactly as by sl_lru_update_ex, but
+ * the K/V rows of this step's misses are NOT copied; their entries of d_slots_out are -(slot + 1). The attention
+ * call that follows, sl_sparse_attn_decode_fill, fetches those rows from the backing store, attends to them and
+ * writes them into their slots of the resident buffers on the way, so a missed row crosses memory once instead of
+ * three times and the step has one launch less. The pair must be issued together: after sl_lru_update_deferred the
+ * resident buffers are complete only once sl_sparse_attn_decode_fill has run on the same lists. No reference counterpart. */
+int sl_lru_update_deferred(const int32_t* d_idx, int idx_capacity, const int32_t* d_cnt, int B, int KH, int elem_bytes,
+                           void* d_k_resident, void* d_v_resident, const sl_kv_layout* resident, int C,
+                           int32_t* d_tok2slot, int64_t n_max, int32_t* d_slot2tok, int32_t* d_last_used, int step,
+                           const int64_t* d_step, int32_t* d_slots_out, int32_t* d_stats, int32_t* d_status,
+                           void* d_workspace, size_t workspace_bytes, void* stream);
+
+/* Where sl_sparse_attn_decode_fill finds the rows that are not resident yet: the keys of the list entries (the index
+ * list the slots were made from, [B, KH, idx_capacity]) and the backing K/V store with its geometry (device memory or
+ * mapped pinned host memory). */
+typedef struct sl_attn_fill {
+    const int32_t* d_tokens;
+    const void* k_backing; const void* v_backing;
+    sl_kv_layout backing;
+} sl_attn_fill;
+
+/* sl_sparse_attn_decode_ex over the resident buffers of an LRU table, with the slot list of sl_lru_update_deferred:
+ * entries >= 0 are read from the resident buffers; an entry -(slot + 1) is read from the backing store at the key's
+ * index and written into that slot. bf16, at most 16 query heads per list head. The arithmetic, and so the output, is
+ * that of sl_sparse_attn_decode_ex over the full caches with the index list. */
+int sl_sparse_attn_decode_fill(const void* d_q, void* d_k_resident, void* d_v_resident, int dtype,
+                               const sl_kv_layout* resident, const int32_t* d_slots, int idx_capacity,
+                               const int32_t* d_cnt, int B, int KH, int QH, int gqa_layout, void* d_out, float* d_lse,
+                               void* d_workspace, size_t workspace_bytes, const sl_attn_fill* fill, void* stream);
 
 /* Row gather for API parity with KVCache.gather (spotlight/modifiers/gpu_cache.py:100-106):
  * out[b,j,h,:] = cache[b, idx[b,h,j], h, :] for j < budget. */

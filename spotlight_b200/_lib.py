@@ -14,7 +14,7 @@ LIB_PATH = os.path.join(_HERE, "lib", "libspotlight_b200.so")
 SL_OK, SL_EINVAL, SL_ESHAPE, SL_EALIGN, SL_EWORKSPACE, SL_ECUDA, SL_ETIMEOUT = 0, -1, -2, -3, -4, -5, -6
 SL_BF16, SL_F32, SL_F16, SL_BOOL = 0, 1, 2, 3
 GQA_INTERLEAVED, GQA_BLOCKED = 0, 1
-SL_OPT_PDL, SL_OPT_L2_PREFETCH, SL_OPT_SCAN_KERNEL, SL_OPT_ATTN_WARPS, SL_OPT_PEER_SPIN_LIMIT, SL_OPT_HASH_KERNEL, SL_OPT_ATTN_CLUSTER = 0, 1, 2, 3, 4, 5, 6
+SL_OPT_PDL, SL_OPT_L2_PREFETCH, SL_OPT_SCAN_KERNEL, SL_OPT_ATTN_WARPS, SL_OPT_PEER_SPIN_LIMIT, SL_OPT_HASH_KERNEL, SL_OPT_ATTN_CLUSTER, SL_OPT_LRU_FUSED_FILL = 0, 1, 2, 3, 4, 5, 6, 7
 
 
 class HashParamsStruct(C.Structure):
@@ -59,6 +59,11 @@ class DecodeDev(C.Structure):
                 ("table_pos0", _L), ("table_rows", _L), ("advance", _I)]
 
 
+class AttnFill(C.Structure):
+    """sl_attn_fill of include/spotlight_b200.h."""
+    _fields_ = [("d_tokens", _P), ("k_backing", _P), ("v_backing", _P), ("backing", KvLayout)]
+
+
 _KV = C.POINTER(KvLayout)
 
 # name -> (restype, argtypes); must list every symbol of include/spotlight_b200.h
@@ -87,6 +92,8 @@ SIGNATURES = {
     "sl_sparse_attn_workspace_bytes": (_Z, [_I, _I, _I]),
     "sl_sparse_attn_decode": (_I, [_P, _P, _P, _I, _L, _P, _I, _P, _I, _I, _I, _I, _P, _P, _P, _Z, _P]),
     "sl_sparse_attn_decode_ex": (_I, [_P, _P, _P, _I, _KV, _P, _I, _P, _I, _I, _I, _I, _P, _P, _P, _Z, _P]),
+    "sl_sparse_attn_decode_fill": (_I, [_P, _P, _P, _I, _KV, _P, _I, _P, _I, _I, _I, _I, _P, _P, _P, _Z, C.POINTER(AttnFill), _P]),
+    "sl_lru_update_deferred": (_I, [_P, _I, _P, _I, _I, _I, _P, _P, _KV, _I, _P, _L, _P, _P, _I, _P, _P, _P, _P, _P, _Z, _P]),
     "sl_sparse_attn_decode_static": (_I, [_P, _P, _P, _I, _L, _P, _I, _P, _I, _I, _I, _I, _P, _P, _P]),
     "sl_merge_lse": (_I, [_P, _P, _I, _L, _I, _P, _P]),
     "sl_lru_update": (_I, [_P, _I, _P, _I, _I, _P, _P, _L, _I, _P, _P, _I, _P, _L, _P, _P, _I, _P, _P, _P, _P]),

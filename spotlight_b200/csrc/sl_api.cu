@@ -19,10 +19,11 @@ int fail(int code, const char* fmt, ...) {
     return code;
 }
 
-static int g_pdl = 1, g_l2pf = 1;
+static int g_pdl = 1, g_l2pf = 1, g_lru_fill = 1;
 
 bool pdl_enabled() { return g_pdl != 0; }
 bool l2_prefetch_enabled() { return g_l2pf != 0; }
+bool lru_fused_fill() { return g_lru_fill != 0; }
 
 // cudaFuncSetAttribute costs a microsecond or two; a decode loop launches thousands of kernels per
 // second, so the largest dynamic shared-memory size set per (device, kernel) is remembered.
@@ -89,6 +90,7 @@ extern "C" int sl_configure(int option, int value) {
             SL_REQUIRE(value >= 1, SL_EINVAL, "sl_configure: SL_OPT_PEER_SPIN_LIMIT takes a positive number of polls");
             sl::set_peer_spin_limit((unsigned)value);
             return SL_OK;
+        case SL_OPT_LRU_FUSED_FILL: sl::g_lru_fill = value ? 1 : 0; return SL_OK;
         case SL_OPT_ATTN_CLUSTER: sl::set_attn_cluster(value ? 1 : 0); return SL_OK;
         case SL_OPT_HASH_KERNEL:
             SL_REQUIRE(value >= 0 && value <= 2, SL_EINVAL, "sl_configure: SL_OPT_HASH_KERNEL takes 0, 1 or 2");

@@ -302,10 +302,10 @@ extern "C" size_t sl_sparse_attn_workspace_bytes(int B, int KH, int QH) {
     return (size_t)B * QH * MAX_SPLITS * 130 * 4;
 }
 
-extern "C" int sl_sparse_attn_decode_ex(const void* d_q, const void* d_k, const void* d_v, int dtype, const sl_kv_layout* kv,
-                                        const int32_t* d_idx, int idx_capacity, const int32_t* d_cnt, int B, int KH, int QH,
-                                        int gqa_layout, void* d_out, float* d_lse, void* d_workspace, size_t workspace_bytes,
-                                        void* stream) {
+static int attn_decode(const void* d_q, const void* d_k, const void* d_v, int dtype, const sl_kv_layout* kv,
+                       const int32_t* d_idx, int idx_capacity, const int32_t* d_cnt, int B, int KH, int QH,
+                       int gqa_layout, void* d_out, float* d_lse, void* d_workspace, size_t workspace_bytes,
+                       const sl_attn_fill* fill, void* stream) {
     SL_REQUIRE(d_q && d_k && d_v && kv && d_idx && d_cnt && d_out && d_workspace, SL_EINVAL, "sl_sparse_attn_decode: null pointer");
     SL_REQUIRE(B > 0 && KH > 0 && QH > 0 && QH % KH == 0 && idx_capacity > 0, SL_ESHAPE, "sl_sparse_attn_decode: bad shape");
     SL_REQUIRE(B <= 65535 && KH <= 65535, SL_ESHAPE, "sl_sparse_attn_decode: B or KH > 65535");
@@ -323,7 +323,7 @@ extern "C" int sl_sparse_attn_decode_ex(const void* d_q, const void* d_k, const 
     SL_REQUIRE(workspace_bytes >= sl_sparse_attn_workspace_bytes(B, KH, QH), SL_EWORKSPACE,
                "sl_sparse_attn_decode: workspace %zu < required %zu", workspace_bytes, sl_sparse_attn_workspace_bytes(B, KH, QH));
     SL_REQUIRE(sl::aligned16(d_workspace), SL_EALIGN, "sl_sparse_attn_decode: workspace not 16-byte aligned");
-    AttnArgs a;
+    AttnArgs a = {};
     a.q = d_q; a.k = d_k; a.v = d_v; a.kv_b = kv->batch_stride;
     a.tok_stride = kv->token_stride; a.head_stride = kv->head_stride; a.kv_div = kv->list_heads_per_kv_head;
     a.idx = d_idx; a.cap = idx_capacity; a.cnt = d_cnt;
@@ -333,6 +333,19 @@ extern "C" int sl_sparse_attn_decode_ex(const void* d_q, const void* d_k, const 
     a.part = static_cast<float*>(d_workspace);
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     const int G = QH / KH;
+    if (fill) {
+        SL_REQUIRE(dtype == SL_BF16 && G <= 16, SL_ESHAPE, "sl_sparse_attn_decode_fill: bf16 and at most 16 query heads per list head");
+        SL_REQUIRE(fill->d_tokens && fill->k_backing && fill->v_backing, SL_EINVAL, "sl_sparse_attn_decode_fill: null pointer");
+        const sl_kv_layout& bk = fill->backing;
+        SL_REQUIRE(bk.batch_stride >= 0 && bk.token_stride >= 128 && bk.head_stride >= 128 &&
+                       bk.list_heads_per_kv_head == kv->list_heads_per_kv_head, SL_ESHAPE,
+                   "sl_sparse_attn_decode_fill: backing-store strides must leave room for a 128-value row and group the list heads as the resident buffers do");
+        SL_REQUIRE(sl::aligned16(fill->k_backing) && sl::aligned16(fill->v_backing) && (bk.batch_stride * 2) % 16 == 0 &&
+                       (bk.token_stride * 2) % 16 == 0 && (bk.head_stride * 2) % 16 == 0, SL_EALIGN,
+                   "sl_sparse_attn_decode_fill: the backing store and its strides must be 16-byte aligned");
+        a.tok = fill->d_tokens; a.k_back = fill->k_backing; a.v_back = fill->v_backing;
+        a.back_b = bk.batch_stride; a.back_tok = bk.token_stride; a.back_head = bk.head_stride;
+    }
     if (dtype == SL_BF16 && G <= 16) {
         a.splits = sl::attn_mma_splits(B, KH, idx_capacity);
         return sl::launch_attn_mma(a, G, s);
@@ -342,6 +355,23 @@ extern "C" int sl_sparse_attn_decode_ex(const void* d_q, const void* d_k, const 
         case SL_F16: return dispatch_g<__half>(a, G, s);
         default: return dispatch_g<float>(a, G, s);
     }
+}
+
+extern "C" int sl_sparse_attn_decode_ex(const void* d_q, const void* d_k, const void* d_v, int dtype, const sl_kv_layout* kv,
+                                        const int32_t* d_idx, int idx_capacity, const int32_t* d_cnt, int B, int KH, int QH,
+                                        int gqa_layout, void* d_out, float* d_lse, void* d_workspace, size_t workspace_bytes,
+                                        void* stream) {
+    return attn_decode(d_q, d_k, d_v, dtype, kv, d_idx, idx_capacity, d_cnt, B, KH, QH, gqa_layout, d_out, d_lse, d_workspace,
+                       workspace_bytes, nullptr, stream);
+}
+
+extern "C" int sl_sparse_attn_decode_fill(const void* d_q, void* d_k_resident, void* d_v_resident, int dtype,
+                                          const sl_kv_layout* resident, const int32_t* d_slots, int idx_capacity,
+                                          const int32_t* d_cnt, int B, int KH, int QH, int gqa_layout, void* d_out, float* d_lse,
+                                          void* d_workspace, size_t workspace_bytes, const sl_attn_fill* fill, void* stream) {
+    SL_REQUIRE(fill, SL_EINVAL, "sl_sparse_attn_decode_fill: null fill description");
+    return attn_decode(d_q, d_k_resident, d_v_resident, dtype, resident, d_slots, idx_capacity, d_cnt, B, KH, QH, gqa_layout,
+                       d_out, d_lse, d_workspace, workspace_bytes, fill, stream);
 }
 
 extern "C" int sl_sparse_attn_decode(const void* d_q, const void* d_k, const void* d_v, int dtype,

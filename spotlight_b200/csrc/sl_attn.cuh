@@ -16,6 +16,12 @@ struct AttnArgs {
     int B, KH, layout, splits;
     void* out; float* lse;
     float* part;                   // [B*KH][splits][G][130]: o[128], m, l
+    // fill mode (bf16 tensor-core kernel only): k / v are the resident buffers of an LRU table and idx holds SLOTS; a
+    // negative entry -(slot + 1) is a key whose rows are not resident yet: they are fetched from the backing store at
+    // the key's index (tok) and written into the slot on the way
+    const int* tok;                // [B*KH][cap] keys of the list entries, or null: no fill mode
+    const void* k_back; const void* v_back;
+    long long back_b, back_tok, back_head;   // elements
 };
 
 

@@ -47,7 +47,9 @@ __device__ __forceinline__ unsigned swz(int r, int c) { return (unsigned)(r * 25
 // SMs -- fewer, fatter CTAs mean fewer partials to combine -- else 4 (two CTAs per SM).
 // CL: the CTAs of a (batch row, kv head) are one thread-block cluster and combine their partials through
 // distributed shared memory (no partials in global memory, no merge kernel).
-template <bool HI, int MW, bool CL>
+// FILL: the caches are the resident buffers of an LRU table and the list holds slots; rows of entries -(slot + 1) come
+// from the backing store and are written into their slot from shared memory once they have landed.
+template <bool HI, int MW, bool CL, bool FILL>
 __global__ void __launch_bounds__(MW * 32, 8 / MW) sparse_attn_mma_kernel(const AttnArgs a, const int G) {
     constexpr int MT = MW * 32;
     extern __shared__ __align__(128) unsigned char ring[];          // [MW][ST][K 4 KB | V 4 KB]; reused by the epilogue
@@ -68,6 +70,10 @@ __global__ void __launch_bounds__(MW * 32, 8 / MW) sparse_attn_mma_kernel(const 
     const __nv_bfloat16* kb = reinterpret_cast<const __nv_bfloat16*>(a.k) + hoff + (lane & 15) * 8;
     const __nv_bfloat16* vb = reinterpret_cast<const __nv_bfloat16*>(a.v) + hoff + (lane & 15) * 8;
     const unsigned wring = (unsigned)__cvta_generic_to_shared(ring) + warp * (ST * STAGE_BYTES);
+    const int* toks = FILL ? a.tok + ((long long)b * KH + h) * a.cap : nullptr;
+    const long long bhoff = FILL ? (long long)b * a.back_b + (long long)(h / a.kv_div) * a.back_head : 0;
+    const __nv_bfloat16* kbb = FILL ? reinterpret_cast<const __nv_bfloat16*>(a.k_back) + bhoff + (lane & 15) * 8 : nullptr;
+    const __nv_bfloat16* vbb = FILL ? reinterpret_cast<const __nv_bfloat16*>(a.v_back) + bhoff + (lane & 15) * 8 : nullptr;
 
     // one tile = list entries [16 t, 16 t + 16); lane l < 16 fetches entry l (clamped to the last one)
     auto entry = [&](int t) -> int { return list[min(t * 16 + (lane & 15), n - 1)]; };
@@ -75,14 +81,42 @@ __global__ void __launch_bounds__(MW * 32, 8 / MW) sparse_attn_mma_kernel(const 
     auto issue = [&](int t, int tok, int stage) {
         const unsigned sbase = wring + stage * STAGE_BYTES;
         const int c = lane & 15;
+        int key = 0;
+        if (FILL) key = __any_sync(0xffffffffu, tok < 0) ? toks[min(t * 16 + (lane & 15), n - 1)] : 0;   // only tiles with a miss look the keys up
 #pragma unroll
         for (int it = 0; it < 8; ++it) {
             const int r = 2 * it + (lane >> 4);
-            const long long off = (long long)__shfl_sync(0xffffffffu, tok, r) * row_stride;
-            cp_async16(sbase + swz(r, c), kb + off);
-            cp_async16(sbase + 4096 + swz(r, c), vb + off);
+            const int e = __shfl_sync(0xffffffffu, tok, r);
+            const int kr = FILL ? __shfl_sync(0xffffffffu, key, r) : 0;      // both half-warps take part, whatever their rows are
+            if (FILL && e < 0) {
+                const long long off = (long long)kr * a.back_tok;
+                cp_async16(sbase + swz(r, c), kbb + off);
+                cp_async16(sbase + 4096 + swz(r, c), vbb + off);
+            } else {
+                const long long off = (long long)e * row_stride;
+                cp_async16(sbase + swz(r, c), kb + off);
+                cp_async16(sbase + 4096 + swz(r, c), vb + off);
+            }
         }
-        (void)t;
+    };
+    // fill mode: the rows of this tile that came from the backing store go into their slots of the resident buffers
+    auto write_through = [&](int t, int stage) {
+        const int e_own = entry(t);
+        if (!__any_sync(0xffffffffu, e_own < 0)) return;
+        const unsigned char* sb = ring + (size_t)warp * (ST * STAGE_BYTES) + stage * STAGE_BYTES;
+        const int c = lane & 15;
+        __nv_bfloat16* kw = const_cast<__nv_bfloat16*>(kb);
+        __nv_bfloat16* vw = const_cast<__nv_bfloat16*>(vb);
+#pragma unroll
+        for (int it = 0; it < 8; ++it) {
+            const int r = 2 * it + (lane >> 4);
+            const int e = __shfl_sync(0xffffffffu, e_own, r);
+            if (e < 0) {
+                const long long off = (long long)(-e - 1) * row_stride;
+                *reinterpret_cast<uint4*>(kw + off) = *reinterpret_cast<const uint4*>(sb + swz(r, c));
+                *reinterpret_cast<uint4*>(vw + off) = *reinterpret_cast<const uint4*>(sb + 4096 + swz(r, c));
+            }
+        }
     };
 
     // ---- prologue: fill ST-1 stages
@@ -133,6 +167,7 @@ __global__ void __launch_bounds__(MW * 32, 8 / MW) sparse_attn_mma_kernel(const 
         }
         cp_async_wait<ST - 1>();
         __syncwarp();
+        if (FILL) write_through(tile, stage);
         const unsigned kbase = wring + stage * STAGE_BYTES, vbase = kbase + 4096;
         const int valid = n - tile * 16;                    // list entries of this tile that exist
 
@@ -317,10 +352,10 @@ void set_attn_warps(int v) { g_attn_warps = v; }
 void set_attn_cluster(int v) { g_attn_cluster = v; }
 static bool fat_ctas(int B, int KH) { return g_attn_warps ? g_attn_warps == 8 : B * KH <= sm_count(); }
 
-template <bool HI, int MW>
+template <bool HI, int MW, bool FILL>
 static cudaError_t cluster_config(cudaLaunchConfig_t& cfg, cudaLaunchAttribute* attrs, int cs, int KH, int B, cudaStream_t s) {
     const size_t ring_bytes = (size_t)MW * ST * STAGE_BYTES;
-    const void* fn = reinterpret_cast<const void*>(sparse_attn_mma_kernel<HI, MW, true>);
+    const void* fn = reinterpret_cast<const void*>(sparse_attn_mma_kernel<HI, MW, true, FILL>);
     cudaError_t e = ensure_dyn_smem(fn, ring_bytes);
     if (e != cudaSuccess) return e;
     static bool allowed = false;                       // per instantiation: clusters of more than 8 CTAs are an opt-in
@@ -353,8 +388,8 @@ static int max_clusters(int cs) {
         cudaLaunchConfig_t cfg;
         cudaLaunchAttribute attrs[2];
         int n = 0;
-        if (cluster_config<false, MW>(cfg, attrs, cs, 1, 1, nullptr) != cudaSuccess ||
-            cudaOccupancyMaxActiveClusters(&n, reinterpret_cast<const void*>(sparse_attn_mma_kernel<false, MW, true>), &cfg) != cudaSuccess) {
+        if (cluster_config<false, MW, false>(cfg, attrs, cs, 1, 1, nullptr) != cudaSuccess ||
+            cudaOccupancyMaxActiveClusters(&n, reinterpret_cast<const void*>(sparse_attn_mma_kernel<false, MW, true, false>), &cfg) != cudaSuccess) {
             cudaGetLastError();
             n = 0;
         }
@@ -384,28 +419,33 @@ int attn_mma_splits(int B, int KH, int cap) {
     return s;
 }
 
-template <bool HI, int MW>
+template <bool HI, int MW, bool FILL>
 static int launch_one(const AttnArgs& a, int G, cudaStream_t s) {
     const size_t ring_bytes = (size_t)MW * ST * STAGE_BYTES;
     if (use_cluster(a.B, a.KH, a.splits)) {
         cudaLaunchConfig_t cfg;
         cudaLaunchAttribute attrs[2];
-        SL_CUDA_OK((cluster_config<HI, MW>(cfg, attrs, a.splits, a.KH, a.B, s)));
-        SL_CUDA_OK(cudaLaunchKernelEx(&cfg, sparse_attn_mma_kernel<HI, MW, true>, a, G));
+        SL_CUDA_OK((cluster_config<HI, MW, FILL>(cfg, attrs, a.splits, a.KH, a.B, s)));
+        SL_CUDA_OK(cudaLaunchKernelEx(&cfg, sparse_attn_mma_kernel<HI, MW, true, FILL>, a, G));
         return SL_OK;
     }
     dim3 grid((unsigned)a.splits, (unsigned)a.KH, (unsigned)a.B);
-    SL_CUDA_OK(ensure_dyn_smem(reinterpret_cast<const void*>(sparse_attn_mma_kernel<HI, MW, false>), ring_bytes));
-    SL_CUDA_OK(launch_kernel(sparse_attn_mma_kernel<HI, MW, false>, grid, dim3(MW * 32), ring_bytes, s, false, a, G));
+    SL_CUDA_OK(ensure_dyn_smem(reinterpret_cast<const void*>(sparse_attn_mma_kernel<HI, MW, false, FILL>), ring_bytes));
+    SL_CUDA_OK(launch_kernel(sparse_attn_mma_kernel<HI, MW, false, FILL>, grid, dim3(MW * 32), ring_bytes, s, false, a, G));
     if (a.splits > 1) return launch_attn_merge(a, G, SL_BF16, s);
     return SL_OK;
+}
+
+template <bool FILL>
+static int launch_by_shape(const AttnArgs& a, int G, cudaStream_t s) {
+    if (fat_ctas(a.B, a.KH)) return G > 8 ? launch_one<true, 8, FILL>(a, G, s) : launch_one<false, 8, FILL>(a, G, s);
+    return G > 8 ? launch_one<true, 4, FILL>(a, G, s) : launch_one<false, 4, FILL>(a, G, s);
 }
 
 int attn_cluster_capacity(int warps, int cs) { return warps == 8 ? max_clusters<8>(cs) : max_clusters<4>(cs); }
 
 int launch_attn_mma(const AttnArgs& a, int G, cudaStream_t s) {
-    if (fat_ctas(a.B, a.KH)) return G > 8 ? launch_one<true, 8>(a, G, s) : launch_one<false, 8>(a, G, s);
-    return G > 8 ? launch_one<true, 4>(a, G, s) : launch_one<false, 4>(a, G, s);
+    return a.tok ? launch_by_shape<true>(a, G, s) : launch_by_shape<false>(a, G, s);
 }
 
 }  // namespace sl

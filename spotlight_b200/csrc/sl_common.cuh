@@ -20,6 +20,7 @@ int sm_count();          // SMs of the current device (cached per device)
 cudaError_t ensure_dyn_smem(const void* func, size_t bytes);   // opt-in to `bytes` of dynamic shared memory, once
 bool pdl_enabled();      // programmatic dependent launch on (default) / off (sl_configure)
 bool l2_prefetch_enabled();   // the decode-step hash warms L2 with the code cache (sl_configure)
+bool lru_fused_fill();        // the decode step lets the attention launch fetch and fill the LRU misses (sl_configure)
 
 #define SL_CUDA_OK(expr)                                                                    \
     do {                                                                                    \

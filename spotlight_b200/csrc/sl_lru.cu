@@ -41,6 +41,7 @@ struct LruArgs {
     unsigned* g_count;                     // [B*KH][2] hits of the step, finished CTAs (both left at zero)
     int2* g_pairs;                         // [B*KH][cap] {key, slot} of the misses, copied by lru_copy_kernel
     int* g_m;                              // [B*KH] number of misses of the step
+    int deferred;                          // the rows of the misses are not copied here: their slots go out as -(slot + 1)
 };
 
 // exclusive prefix of one value per thread over the block (thread order) and the block total
@@ -89,6 +90,8 @@ __global__ void __launch_bounds__(LT) lru_update_kernel(const LruArgs a) {
 
     const int h = blockIdx.x, b = blockIdx.y, part = blockIdx.z, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const long long bh = (long long)b * a.KH + h;
+    sl::pdl_trigger();
+    sl::pdl_wait();                        // the index list and the counts come from the scan before this launch
     const int n = min(a.cnt[bh], a.cap);
     const int* list = a.idx + bh * a.cap;
     int* out = a.slots_out + bh * a.cap;
@@ -282,13 +285,16 @@ __global__ void __launch_bounds__(LT) lru_update_kernel(const LruArgs a) {
             t2s[tok] = v;
             s2t[v] = tok;
             lu[v] = t;
-            out[j] = v;
+            out[j] = a.deferred ? -(v + 1) : v;
             misstok[rank] = tok;
         }
     }
     __syncthreads();
 
-    if (a.g_pairs) {
+    if (a.deferred) {
+        // the attention launch that follows fetches these rows from the backing store and fills the slots on the way
+        if (tid == 0 && a.g_m) a.g_m[bh] = m;
+    } else if (a.g_pairs) {
         // the rows are copied by the launch that follows (many CTAs): leave it the {key, slot} pairs
         int2* pairs = a.g_pairs + bh * a.cap;
         for (int i = tid; i < m; i += LT) pairs[i] = make_int2(misstok[i], victims[i]);
@@ -385,14 +391,14 @@ int lru_launch(const int32_t* d_idx, int idx_capacity, const int32_t* d_cnt, int
                const void* v_backing, const sl_kv_layout& back, int elem_bytes, void* d_k_resident, void* d_v_resident,
                const sl_kv_layout& res, int C, int32_t* d_tok2slot, int64_t n_max, int32_t* d_slot2tok,
                int32_t* d_last_used, int step, const int64_t* d_step, int32_t* d_slots_out, int32_t* d_stats,
-               int32_t* d_status, void* d_workspace, size_t workspace_bytes, void* stream) {
-    SL_REQUIRE(d_idx && d_cnt && k_backing && v_backing && d_k_resident && d_v_resident && d_tok2slot && d_slot2tok &&
+               int32_t* d_status, void* d_workspace, size_t workspace_bytes, void* stream, bool deferred = false) {
+    SL_REQUIRE(d_idx && d_cnt && (deferred || (k_backing && v_backing)) && d_k_resident && d_v_resident && d_tok2slot && d_slot2tok &&
                    d_last_used && d_slots_out,
                SL_EINVAL, "sl_lru_update: null pointer");
     SL_REQUIRE(B > 0 && B <= 65535 && KH > 0 && C > 0 && idx_capacity > 0 && n_max > 0 && step >= 0, SL_ESHAPE,
                "sl_lru_update: bad shape");
     SL_REQUIRE(elem_bytes == 2 || elem_bytes == 4, SL_EINVAL, "sl_lru_update: elem_bytes must be 2 or 4");
-    SL_REQUIRE(sl::aligned16(k_backing) && sl::aligned16(v_backing) && sl::aligned16(d_k_resident) &&
+    SL_REQUIRE((deferred || (sl::aligned16(k_backing) && sl::aligned16(v_backing))) && sl::aligned16(d_k_resident) &&
                    sl::aligned16(d_v_resident),
                SL_EALIGN, "sl_lru_update: K/V buffers must be 16-byte aligned");
     for (const sl_kv_layout* l : {&back, &res})
@@ -414,6 +420,7 @@ int lru_launch(const int32_t* d_idx, int idx_capacity, const int32_t* d_cnt, int
     a.tok2slot = d_tok2slot; a.n_max = n_max; a.slot2tok = d_slot2tok; a.last_used = d_last_used;
     a.slots_out = d_slots_out; a.stats = d_stats; a.status = d_status;
     a.parts = 1;
+    a.deferred = deferred ? 1 : 0;
     if (d_workspace) {
         SL_REQUIRE(workspace_bytes >= sl_lru_workspace_bytes(B, KH, idx_capacity), SL_EWORKSPACE,
                    "sl_lru_update_ex: workspace %zu < required %zu", workspace_bytes, sl_lru_workspace_bytes(B, KH, idx_capacity));
@@ -426,9 +433,8 @@ int lru_launch(const int32_t* d_idx, int idx_capacity, const int32_t* d_cnt, int
     }
     SL_CUDA_OK(sl::ensure_dyn_smem(reinterpret_cast<const void*>(lru_update_kernel), smem));
     dim3 grid((unsigned)KH, (unsigned)B, (unsigned)a.parts);
-    lru_update_kernel<<<grid, LT, smem, static_cast<cudaStream_t>(stream)>>>(a);
-    SL_CUDA_OK(cudaGetLastError());
-    if (a.g_pairs) {
+    SL_CUDA_OK(sl::launch_kernel(lru_update_kernel, grid, dim3(LT), smem, static_cast<cudaStream_t>(stream), false, a));
+    if (a.g_pairs && !deferred) {
         const int cp = std::max(1, std::min(32, sl::sm_count() / std::max(1, B * KH)));
         SL_CUDA_OK(sl::launch_kernel(lru_copy_kernel, dim3((unsigned)cp, (unsigned)KH, (unsigned)B), dim3(CT), 0,
                                      static_cast<cudaStream_t>(stream), false, a));
@@ -468,4 +474,15 @@ extern "C" int sl_lru_update_ex(const int32_t* d_idx, int idx_capacity, const in
     return lru_launch(d_idx, idx_capacity, d_cnt, B, KH, k_backing, v_backing, *backing, elem_bytes, d_k_resident,
                       d_v_resident, *resident, C, d_tok2slot, n_max, d_slot2tok, d_last_used, step, d_step, d_slots_out,
                       d_stats, d_status, d_workspace, workspace_bytes, stream);
+}
+
+extern "C" int sl_lru_update_deferred(const int32_t* d_idx, int idx_capacity, const int32_t* d_cnt, int B, int KH, int elem_bytes,
+                                      void* d_k_resident, void* d_v_resident, const sl_kv_layout* resident, int C,
+                                      int32_t* d_tok2slot, int64_t n_max, int32_t* d_slot2tok, int32_t* d_last_used, int step,
+                                      const int64_t* d_step, int32_t* d_slots_out, int32_t* d_stats, int32_t* d_status,
+                                      void* d_workspace, size_t workspace_bytes, void* stream) {
+    SL_REQUIRE(resident, SL_EINVAL, "sl_lru_update_deferred: null cache layout");
+    return lru_launch(d_idx, idx_capacity, d_cnt, B, KH, nullptr, nullptr, *resident, elem_bytes, d_k_resident, d_v_resident,
+                      *resident, C, d_tok2slot, n_max, d_slot2tok, d_last_used, step, d_step, d_slots_out, d_stats, d_status,
+                      d_workspace, workspace_bytes, stream, true);
 }

@@ -55,15 +55,28 @@ int run_layers(const sl_decode_step_args* a, int64_t pos, const sl_decode_dev* d
         if (a->lru) {
             const sl_lru_layer& t = a->lru[l];
             const sl_kv_layout res = {a->lru_batch_stride, a->lru_token_stride, a->lru_head_stride, 1};
-            rc = sl_lru_update_ex(a->d_idx, a->idx_capacity, a->d_cnt, a->B, a->KH, a->d_k_cache[l], a->d_v_cache[l], &kv,
-                                  a->dtype == SL_F32 ? 4 : 2, t.d_k_resident, t.d_v_resident, &res, a->lru_slots, t.d_tok2slot,
-                                  a->lru_n_max, t.d_slot2tok, t.d_last_used, (int)pos,
-                                  dev ? reinterpret_cast<const int64_t*>(dp.d_pos) : nullptr, a->d_slots, t.d_stats,
-                                  a->d_status, a->d_lru_workspace, a->lru_workspace_bytes, stream);
-            if (rc) return rc;
-            rc = sl_sparse_attn_decode_ex(a->d_q_rot, t.d_k_resident, t.d_v_resident, a->dtype, &res, a->d_slots,
-                                          a->idx_capacity, a->d_cnt, a->B, a->KH, a->QH, a->gqa_layout, a->d_out[l], nullptr,
-                                          a->d_attn_workspace, a->attn_workspace_bytes, stream);
+            const int64_t* d_step = dev ? reinterpret_cast<const int64_t*>(dp.d_pos) : nullptr;
+            if (sl::lru_fused_fill() && a->dtype == SL_BF16 && a->QH / a->KH <= 16) {
+                // the attention launch fetches the rows of the misses itself and fills their slots on the way
+                rc = sl_lru_update_deferred(a->d_idx, a->idx_capacity, a->d_cnt, a->B, a->KH, 2, t.d_k_resident, t.d_v_resident,
+                                            &res, a->lru_slots, t.d_tok2slot, a->lru_n_max, t.d_slot2tok, t.d_last_used, (int)pos,
+                                            d_step, a->d_slots, t.d_stats, a->d_status, a->d_lru_workspace,
+                                            a->lru_workspace_bytes, stream);
+                if (rc) return rc;
+                const sl_attn_fill fill = {a->d_idx, a->d_k_cache[l], a->d_v_cache[l], kv};
+                rc = sl_sparse_attn_decode_fill(a->d_q_rot, t.d_k_resident, t.d_v_resident, a->dtype, &res, a->d_slots,
+                                                a->idx_capacity, a->d_cnt, a->B, a->KH, a->QH, a->gqa_layout, a->d_out[l], nullptr,
+                                                a->d_attn_workspace, a->attn_workspace_bytes, &fill, stream);
+            } else {
+                rc = sl_lru_update_ex(a->d_idx, a->idx_capacity, a->d_cnt, a->B, a->KH, a->d_k_cache[l], a->d_v_cache[l], &kv,
+                                      a->dtype == SL_F32 ? 4 : 2, t.d_k_resident, t.d_v_resident, &res, a->lru_slots, t.d_tok2slot,
+                                      a->lru_n_max, t.d_slot2tok, t.d_last_used, (int)pos, d_step, a->d_slots, t.d_stats,
+                                      a->d_status, a->d_lru_workspace, a->lru_workspace_bytes, stream);
+                if (rc) return rc;
+                rc = sl_sparse_attn_decode_ex(a->d_q_rot, t.d_k_resident, t.d_v_resident, a->dtype, &res, a->d_slots,
+                                              a->idx_capacity, a->d_cnt, a->B, a->KH, a->QH, a->gqa_layout, a->d_out[l], nullptr,
+                                              a->d_attn_workspace, a->attn_workspace_bytes, stream);
+            }
         } else {
             rc = sl_sparse_attn_decode_ex(a->d_q_rot, a->d_k_cache[l], a->d_v_cache[l], a->dtype, &kv, a->d_idx,
                                           a->idx_capacity, a->d_cnt, a->B, a->KH, a->QH, a->gqa_layout, a->d_out[l], nullptr,

@@ -422,6 +422,41 @@ def sparse_attn_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Te
     return (out, lse) if return_lse else out
 
 
+def sparse_attn_decode_fill(q: torch.Tensor, table: "LruTable", slots: torch.Tensor, idx: torch.Tensor, cnt: torch.Tensor,
+                            k_backing: Optional[torch.Tensor], v_backing: Optional[torch.Tensor], layout: int = GQA_BLOCKED,
+                            out: Optional[torch.Tensor] = None, return_lse: bool = False, backing_ptrs=None):
+    """Attention over the resident buffers of an LRU table with the slot list of lru_update(..., defer_copy=True):
+    the rows of the entries -(slot + 1) are fetched from the backing store (k_backing / v_backing [B,N,KH,128] views,
+    or backing_ptrs=(k_ptr, v_ptr, batch_stride_elems) for mapped pinned host memory) at the keys idx names, and
+    written into their slots on the way. bf16. Same arithmetic as sparse_attn_decode over the full caches."""
+    B, QH, D = q.shape
+    KH = table.KH
+    assert D == 128 and q.dtype == torch.bfloat16 and table.k.dtype == q.dtype
+    dev = _cuda(q, table.k, slots, idx, cnt)
+    q = q.contiguous()
+    assert slots.is_contiguous() and idx.is_contiguous() and cnt.is_contiguous() and slots.shape == idx.shape
+    res = _kv_layout(table.k)
+    if backing_ptrs is None:
+        back = _kv_layout(k_backing)
+        b2 = _kv_layout(v_backing)
+        assert (b2.batch_stride, b2.token_stride, b2.head_stride) == (back.batch_stride, back.token_stride, back.head_stride)
+        kp, vp = k_backing.data_ptr(), v_backing.data_ptr()
+    else:
+        kp, vp, kb = backing_ptrs
+        back = _lib.KvLayout(kb, KH * 128, 128, 1)
+    fill = _lib.AttnFill(idx.data_ptr(), kp, vp, back)
+    if out is None:
+        out = torch.empty_like(q)
+    lse = torch.empty((B, QH), dtype=torch.float32, device=dev) if return_lse else None
+    need = lib.sl_sparse_attn_workspace_bytes(B, KH, QH)
+    ws, _ = workspaces.get("attn", dev, need, (B, KH, QH))
+    check(lib.sl_sparse_attn_decode_fill(q.data_ptr(), table.k.data_ptr(), table.v.data_ptr(), _dt(q), C.byref(res),
+                                         slots.data_ptr(), slots.shape[2], cnt.data_ptr(), B, KH, QH, layout, out.data_ptr(),
+                                         _ptr(lse), ws.data_ptr(), ws.numel(), C.byref(fill), _stream()))
+    _count()
+    return (out, lse) if return_lse else out
+
+
 class LruTable:
     """Resident K/V buffers and the slot tables of one layer (see sl_lru_update). The buffers are
     [B,C,KH,128] each, or -- fused=True -- the halves of one [B,C,KH,2,128] buffer, in which a slot's K and
@@ -446,8 +481,10 @@ class LruTable:
 
 def lru_update(table: LruTable, idx: torch.Tensor, cnt: torch.Tensor, k_backing: torch.Tensor,
                v_backing: torch.Tensor, slots_out: Optional[torch.Tensor] = None, backing_ptrs=None,
-               step_dev: Optional[torch.Tensor] = None) -> torch.Tensor:
+               step_dev: Optional[torch.Tensor] = None, defer_copy: bool = False) -> torch.Tensor:
     """Make this step's attended keys resident; returns their slots int32 [B,KH,cap] in list order.
+    defer_copy: only the tables are updated; the slots of the misses come back as -(slot + 1) and the
+    sparse_attn_decode_fill call that must follow fetches those rows and fills the slots on the way.
     k_backing / v_backing: [B,N,KH,128] device tensors (views of a larger or fused cache are fine), or pass
     backing_ptrs=(k_ptr, v_ptr, batch_stride_elems) for mapped pinned host memory in the two-cache layout.
     step_dev: int64 device tensor holding the step (the table's clock), e.g. the decode position, so that
@@ -457,7 +494,9 @@ def lru_update(table: LruTable, idx: torch.Tensor, cnt: torch.Tensor, k_backing:
     assert idx.is_contiguous() and cnt.is_contiguous() and (B, KH) == (table.B, table.KH)
     if slots_out is None:
         slots_out = torch.empty_like(idx)
-    if backing_ptrs is None:
+    if defer_copy:
+        kp = vp = back = None
+    elif backing_ptrs is None:
         back = _kv_layout(k_backing)
         b2 = _kv_layout(v_backing)
         assert (b2.batch_stride, b2.token_stride, b2.head_stride) == (back.batch_stride, back.token_stride, back.head_stride)
@@ -470,6 +509,17 @@ def lru_update(table: LruTable, idx: torch.Tensor, cnt: torch.Tensor, k_backing:
     need = lib.sl_lru_workspace_bytes(B, KH, cap)
     if table.ws is None or table.ws.numel() < need:
         table.ws = torch.zeros(need, dtype=torch.uint8, device=dev)
+    if defer_copy:
+        check(lib.sl_lru_update_deferred(idx.data_ptr(), cap, cnt.data_ptr(), B, KH, table.k.element_size(),
+                                         table.k.data_ptr(), table.v.data_ptr(), C.byref(res), table.C,
+                                         table.tok2slot.data_ptr(), table.n_max, table.slot2tok.data_ptr(),
+                                         table.last_used.data_ptr(), table.step, _ptr(step_dev), slots_out.data_ptr(),
+                                         table.stats.data_ptr(), table.status.data_ptr(), table.ws.data_ptr(),
+                                         table.ws.numel(), _stream()))
+        if step_dev is None:
+            table.step += 1
+        _count()
+        return slots_out
     check(lib.sl_lru_update_ex(idx.data_ptr(), cap, cnt.data_ptr(), B, KH, kp, vp, C.byref(back), table.k.element_size(),
                                table.k.data_ptr(), table.v.data_ptr(), C.byref(res), table.C, table.tok2slot.data_ptr(),
                                table.n_max, table.slot2tok.data_ptr(), table.last_used.data_ptr(), table.step,

@@ -129,11 +129,16 @@ class DecodeSession:
                 raise NotImplementedError("dense layers are served by the attention hook, not the session")
             ops.scan_topk(self.q_codes, self.codes[layer][:, :n], budget(n, c.mask_out, c.min_remain), c.sink,
                           c.recent, c.layout, idx=self.idx, cnt=self.cnt)
+        # bf16: the attention launch fetches the rows of the LRU misses itself and fills their slots on the way
+        fill = c.dtype == torch.bfloat16 and c.q_heads // c.kv_heads <= 16
         if self.lru is not None and self.use_lru and stage in (None, "lru"):
             ops.lru_update(self.lru[layer], self.idx, self.cnt, self.k_cache[layer][:, :n], self.v_cache[layer][:, :n],
-                           slots_out=self.slots)
+                           slots_out=self.slots, defer_copy=fill)
         if stage in (None, "attn"):
-            if self.lru is not None and self.use_lru:
+            if self.lru is not None and self.use_lru and fill:
+                ops.sparse_attn_decode_fill(self.q_rot, self.lru[layer], self.slots, self.idx, self.cnt,
+                                            self.k_cache[layer][:, :n], self.v_cache[layer][:, :n], c.layout, out=self.out[layer])
+            elif self.lru is not None and self.use_lru:
                 ops.sparse_attn_decode(self.q_rot, self.lru[layer].k, self.lru[layer].v, self.slots, self.cnt, c.layout,
                                        out=self.out[layer])
             else:
@@ -311,9 +316,12 @@ class DecodeSession:
         """One token with HOST inputs q [L,B,QH,128], k/v [L,B,KH,128]: stage them in pinned memory,
         copy to the device, run every layer, copy the outputs [L,B,QH,128] back and wait for them."""
         h = self._ensure_host()
-        h["q"].copy_(q)
-        h["k"].copy_(k)
-        h["v"].copy_(v)
+        if q is not h["q"]:               # callers that fill host_inputs() in place skip the staging copy
+            h["q"].copy_(q)
+        if k is not h["k"]:
+            h["k"].copy_(k)
+        if v is not h["v"]:
+            h["v"].copy_(v)
         if graph:
             self.capture(pos, None, True).replay()
         else:
@@ -322,6 +330,12 @@ class DecodeSession:
         if int(h["status"][0]) != 0:      # a device-side wait ran out: the step's results are not to be trusted
             ops.check_status(self.device)
         return h["out"]
+
+    def host_inputs(self):
+        """The pinned host buffers q [L,B,QH,128], k, v [L,B,KH,128] that step_host copies to the device: a caller
+        that writes a token's inputs straight into them and passes them to step_host saves the staging copy."""
+        h = self._ensure_host()
+        return h["q"], h["k"], h["v"]
 
     @property
     def host_bytes_per_step(self):

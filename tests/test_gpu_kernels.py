@@ -610,6 +610,55 @@ def test_lru_refuses_a_table_smaller_than_the_attended_set(ops):
     assert int((table.slot2tok >= 0).sum()) == 0                      # nothing was touched
 
 
+@pytest.mark.parametrize("fused,host", [(False, False), (True, False), (False, True)])
+def test_lru_deferred_fill(ops, fused, host):
+    """lru_update(defer_copy=True) + sparse_attn_decode_fill against the table that copies the missed rows itself: the
+    same slots, the same resident rows after every step, and attention bit-identical to attention over the full caches."""
+    B, KH, QH, N, C, keep = 2, 4, 16, 6000, 900, 700
+    g = torch.Generator().manual_seed(21)
+    if fused:
+        kv = torch.randn((B, N, KH, 2, 128), generator=g).to(torch.bfloat16).to(DEV)
+        kd, vd = kv[:, :, :, 0], kv[:, :, :, 1]
+    else:
+        kd = torch.randn((B, N, KH, 128), generator=g).to(torch.bfloat16).to(DEV)
+        vd = torch.randn((B, N, KH, 128), generator=g).to(torch.bfloat16).to(DEV)
+    ptrs = None
+    if host:
+        k_host, v_host = kd.cpu().pin_memory(), vd.cpu().pin_memory()
+        ptrs = (k_host.data_ptr(), v_host.data_ptr(), k_host.stride(0))
+    ta = ops.LruTable(B, KH, N, C, torch.bfloat16, DEV, fused=fused)
+    tb = ops.LruTable(B, KH, N, C, torch.bfloat16, DEV, fused=fused)
+    cur = torch.stack([torch.randperm(N, generator=g)[:keep] for _ in range(B * KH)]).view(B, KH, keep)
+    misses = 0
+    for step in range(6):
+        idx = torch.sort(cur, dim=-1).values.to(torch.int32).to(DEV)
+        cnt = torch.full((B, KH), keep - (step % 3), dtype=torch.int32, device=DEV)      # ragged: the last entries are unused
+        q = torch.randn((B, QH, 128), generator=g).to(torch.bfloat16).to(DEV)
+        slots_a = ops.lru_update(ta, idx, cnt, kd, vd)
+        slots_b = ops.lru_update(tb, idx, cnt, None, None, defer_copy=True)
+        out_b = ops.sparse_attn_decode_fill(q, tb, slots_b, idx, cnt, kd, vd, backing_ptrs=ptrs)
+        n = int(cnt[0, 0])
+        sa, sb = slots_a[..., :n], slots_b[..., :n]
+        assert torch.equal(torch.where(sb < 0, -sb - 1, sb), sa)
+        misses += int((sb < 0).sum())
+        assert torch.equal(out_b, ops.sparse_attn_decode(q, kd, vd, idx, cnt))
+        assert torch.equal(out_b, ops.sparse_attn_decode(q, ta.k, ta.v, slots_a, cnt))
+        used = ta.slot2tok >= 0                                                            # [B,KH,C]
+        assert torch.equal(ta.slot2tok, tb.slot2tok) and torch.equal(ta.tok2slot, tb.tok2slot)
+        ka, kb_ = ta.k.permute(0, 2, 1, 3)[used], tb.k.permute(0, 2, 1, 3)[used]
+        assert torch.equal(ka, kb_) and torch.equal(ta.v.permute(0, 2, 1, 3)[used], tb.v.permute(0, 2, 1, 3)[used])
+        assert int(ta.status.item()) == 0 and int(tb.status.item()) == 0
+        # drift: a fifth of every list is replaced by keys that are not in it
+        for r in range(B * KH):
+            flat = cur.view(B * KH, keep)
+            absent = torch.ones(N, dtype=torch.bool)
+            absent[flat[r]] = False
+            pool = absent.nonzero().flatten()
+            fresh = pool[torch.randperm(pool.numel(), generator=g)[:keep // 5]]
+            flat[r, torch.randperm(keep, generator=g)[:keep // 5]] = fresh
+    assert misses > B * KH * keep            # the first step and the drift both missed
+
+
 def test_lru_with_host_backing_store(ops):
     """The backing K/V store lives in pinned HOST memory (the offloaded variant of the reference,
     spotlight/modifiers/cpu_cache.py:60-130): the kernel reads the missed rows straight from
