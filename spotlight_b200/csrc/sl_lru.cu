@@ -175,12 +175,12 @@ __global__ void __launch_bounds__(LT) lru_update_kernel(const LruArgs a) {
     }
 
     // ---- ages of the slots not used in this step: kept in shared memory, histogrammed
-    for (int s0 = tid; s0 < a.C; s0 += LT * 8) {
-        int l[8];
+    for (int s0 = tid; s0 < a.C; s0 += LT * 16) {
+        int l[16];
 #pragma unroll
-        for (int u = 0; u < 8; ++u) l[u] = s0 + u * LT < a.C ? __ldcg(lu + s0 + u * LT) : t;   // other slices stamped hits
+        for (int u = 0; u < 16; ++u) l[u] = s0 + u * LT < a.C ? __ldcg(lu + s0 + u * LT) : t;   // other slices stamped hits
 #pragma unroll
-        for (int u = 0; u < 8; ++u) {
+        for (int u = 0; u < 16; ++u) {
             if (s0 + u * LT < a.C) {
                 const int age = l[u] < 0 ? AGE_MAX + 1 : min(t - l[u], AGE_MAX);
                 age16[s0 + u * LT] = (unsigned short)age;
@@ -221,6 +221,7 @@ __global__ void __launch_bounds__(LT) lru_update_kernel(const LruArgs a) {
     const int tau = s_tau, r = s_r;
 
     // ---- victim bitmaps: every slot older than tau, and the slots of age tau (the first r are taken)
+#pragma unroll 4
     for (int w = warp; w < cw; w += LW) {
         const int s = w * 32 + lane;
         const int age = s < a.C ? (int)age16[s] : 0;
@@ -250,6 +251,7 @@ __global__ void __launch_bounds__(LT) lru_update_kernel(const LruArgs a) {
     }
     __syncthreads();
     // victims in slot order: a taken slot's position is (older slots before it) + (taken ties before it)
+#pragma unroll 4
     for (int w = warp; w < cw; w += LW) {
         const unsigned g = m_gt[w], e = m_eq[w];
         const int gb = p_gt[w] + __popc(g & lt), eb = p_eq[w] + __popc(e & lt);
@@ -274,19 +276,33 @@ __global__ void __launch_bounds__(LT) lru_update_kernel(const LruArgs a) {
     __syncthreads();
 
     // ---- misses in list order take the victims in that order
-    for (int w = warp; w < nw; w += LW) {
-        const unsigned mm = m_miss[w];
-        if ((mm >> lane) & 1u) {
-            const int j = w * 32 + lane;
-            const int rank = p_miss[w] + __popc(mm & lt);
-            const int v = victims[rank], tok = list[j];
-            const int old = s2t[v];
-            if (old >= 0) t2s[old] = -1;
-            t2s[tok] = v;
-            s2t[v] = tok;
-            lu[v] = t;
-            out[j] = a.deferred ? -(v + 1) : v;
-            misstok[rank] = tok;
+    // (four list words per round: the loads of a round -- the key, the victim's old key -- are in flight together; the
+    // stores cannot collide: victims are distinct slots, their old keys are resident and the misses are not)
+    for (int w0 = warp; w0 < nw; w0 += 4 * LW) {
+        int jv[4], vv[4], tokv[4], oldv[4], rankv[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const int w = w0 + u * LW;
+            const unsigned mm = w < nw ? m_miss[w] : 0u;
+            jv[u] = -1;
+            if ((mm >> lane) & 1u) {
+                jv[u] = w * 32 + lane;
+                rankv[u] = p_miss[w] + __popc(mm & lt);
+                vv[u] = victims[rankv[u]];
+                tokv[u] = __ldg(list + jv[u]);
+                oldv[u] = s2t[vv[u]];
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            if (jv[u] >= 0) {
+                if (oldv[u] >= 0) t2s[oldv[u]] = -1;
+                t2s[tokv[u]] = vv[u];
+                s2t[vv[u]] = tokv[u];
+                lu[vv[u]] = t;
+                out[jv[u]] = a.deferred ? -(vv[u] + 1) : vv[u];
+                misstok[rankv[u]] = tokv[u];
+            }
         }
     }
     __syncthreads();
