@@ -459,7 +459,9 @@ def run_ours(args, cfg):
         "e2e": {"value": max(ms_e2e, wall_e2e) * 1e3 / L, "unit": UNIT,
                 "h2d_bytes_per_step": host_bytes[0], "d2h_bytes_per_step": host_bytes[1],
                 "device_ms_per_step": ms_e2e, "wall_ms_per_step": wall_e2e},
-        "gpu_launches": (6 if args.lru and with_lru else 4) * L * args.steps,
+        # per layer: decode_prepare, scan, attention, its merge kernel (+ the LRU table update when stage 3 runs; the
+        # attention launch then fetches and fills the missed rows itself)
+        "gpu_launches": (5 if args.lru and with_lru else 4) * L * args.steps,
         "lru_stage": bool(args.lru and with_lru),
         "cuda_graph": use_graph,
         "roofline": {"bound": "hbm", "kernel": dom, "achieved": kern[dom]["gbs"], "peak": peak, "unit": "GB/s",

@@ -365,8 +365,10 @@ int sl_gather_rows(const void* d_cache, int64_t batch_stride, int elem_bytes,
  * (spotlight/modifiers/spotlight_generation.py:162-164) -> sl_sparse_attn_decode.
  * Replaces the per-layer Python of the attention hook for callers that own the layer loop
  * (spotlight/modifiers/spotlight_generation.py:109-226 runs once per layer and token).
- * With `lru` set the layer-step has four launches: ... -> sl_scan_topk -> sl_lru_update_ex (the attended keys
- * are made resident) -> sl_sparse_attn_decode over the resident buffers.
+ * With `lru` set the layer-step has four launches: ... -> sl_scan_topk -> sl_lru_update_deferred (the slot tables
+ * are updated) -> sl_sparse_attn_decode_fill over the resident buffers, which fetches the rows of the step's misses
+ * from the caches and fills their slots (bf16; other dtypes: sl_lru_update_ex, which copies the rows, and
+ * sl_sparse_attn_decode_ex; SL_OPT_LRU_FUSED_FILL = 0 forces that form).
  * Pointer tables are HOST arrays of `layers` device pointers; d_k / d_v tables (or entries) may be
  * NULL when the token's key/value are already in the caches. The scratch buffers are shared by all
  * layers (the launches are in stream order); workspaces as for the single entry points. */
