@@ -1,4 +1,4 @@
-// Code-cache build at prefill on the 5th-generation tensor cores: hash MLP 128 -> 256 -> 128 (bf16),
+// Code-cache build at prefill on the 5th-generation tensor cores: hash MLP 128 -> 256 -> 128 and linear hash 128 -> 128 (bf16),
 // sign and pack of many rows of one head per CTA. This is the one dense contraction of the retrieval path
 // (reference math: spotlight/modifiers/spotlight_generation.py:229-255).
 //
@@ -375,6 +375,141 @@ __global__ void __launch_bounds__(TC_THREADS, 1) hash_encode_tc_kernel(const __g
     if (warp == TC_EPI_WARPS) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, 512;" ::"r"(tmem) : "memory");
 }
 
+// ---- the linear hash 128 -> 128 (one contraction per tile): bound by the stream of the input rows, so the kernel
+// keeps four input stages in flight and two accumulators in TMEM; two teams of four epilogue warps take alternate
+// tiles (a thread reads its row's 128 columns, adds the bias, takes the sign bits and stores the row's 16-byte code).
+constexpr int L1_NS = 4;                        // input stages
+constexpr int L1_THREADS = (8 + 1) * 32;
+constexpr unsigned L1_W = 128 * 128 * 2, L1_OFF_X = L1_W, L1_OFF_B = L1_OFF_X + L1_NS * X_BYTES, L1_OFF_BAR = L1_OFF_B + 256,
+                   L1_OFF_MISC = L1_OFF_BAR + 8 * 8, L1_SMEM = L1_OFF_MISC + 16 + 1024;
+
+__global__ void __launch_bounds__(L1_THREADS, 1) hash_encode_tc_linear_kernel(const __grid_constant__ CUtensorMap xmap, const HashTcArgs a) {
+    extern __shared__ unsigned char smem_raw[];
+    const unsigned raw = (unsigned)__cvta_generic_to_shared(smem_raw);
+    const unsigned base = (raw + 1023u) & ~1023u;
+    unsigned char* g = smem_raw + (base - raw);
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int h = blockIdx.y;
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(g + L1_OFF_MISC + 4);
+    unsigned* tmem_slot = reinterpret_cast<unsigned*>(g + L1_OFF_MISC);
+    auto bar = [&](int i) { return base + L1_OFF_BAR + (unsigned)i * 8u; };
+    constexpr int X_FULL = 0 /* .. 3 */, D_FULL = 4 /* , 5 */, D_FREE = 6 /* , 7 */;
+
+    if (tid == 0) {
+        *abort_flag = 0;
+        for (int i = 0; i < L1_NS; ++i) mbar_init(bar(X_FULL + i), 1);
+        for (int i = 0; i < 2; ++i) { mbar_init(bar(D_FULL + i), 1); mbar_init(bar(D_FREE + i), 128); }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 8) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], 256;" ::"r"(base + L1_OFF_MISC) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    {
+        const uint4* w1 = reinterpret_cast<const uint4*>(a.w1 + (long long)h * 128 * 128);        // [k][n], 16 groups of 8 n per row
+        for (int task = warp; task < 4 * 16; task += L1_THREADS / 32) {
+            const int k = (task >> 4) * 32 + lane, n0 = (task & 15) * 8;
+            const uint4 v = w1[k * 16 + (task & 15)];
+            const unsigned short* e = reinterpret_cast<const unsigned short*>(&v);
+#pragma unroll
+            for (int c = 0; c < 8; ++c) *reinterpret_cast<unsigned short*>(g + kmajor_off(n0 + c, k, 128)) = e[c];
+        }
+        __nv_bfloat16* sb = reinterpret_cast<__nv_bfloat16*>(g + L1_OFF_B);
+        for (int i = tid; i < 128; i += L1_THREADS) sb[i] = a.b1 ? a.b1[(long long)h * 128 + i] : __float2bfloat16_rn(0.0f);
+    }
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const unsigned tmem = *tmem_slot;
+    const long long first = blockIdx.x, step = gridDim.x;
+    bool failed = false;
+
+    if (warp < 8) {
+        // ================= epilogue team `team` takes the CTA's tiles team, team + 2, ... =================
+        const int team = warp >> 2, q = warp & 3, row = q * 32 + lane;
+        const unsigned t_d = tmem + ((unsigned)(q * 32) << 16) + 128u * team;
+        const unsigned* sb = reinterpret_cast<const unsigned*>(g + L1_OFF_B);
+        unsigned it = team;
+        for (long long tile = first + team * step; tile < a.n_tiles; tile += 2 * step, it += 2) {
+            if (!__all_sync(0xffffffffu, mbar_wait(bar(D_FULL + team), (it >> 1) & 1u, abort_flag))) { failed = true; break; }
+            tc_fence_after();
+            unsigned v[4][32];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) tmem_ld32(t_d + 32u * j, v[j]);
+            tmem_wait_ld();
+            tc_fence_before();
+            mbar_arrive(bar(D_FREE + team));
+            unsigned word[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                unsigned bits = 0u;
+#pragma unroll
+                for (int e = 0; e < 16; ++e) {
+                    unsigned y = pack2(__uint_as_float(v[j][2 * e]), __uint_as_float(v[j][2 * e + 1]));   // matmul -> bf16
+                    y = add_bf16x2(y, sb[16 * j + e]);                                                     // + bias -> bf16
+                    const float y0 = __uint_as_float(y << 16), y1 = __uint_as_float(y & 0xffff0000u);
+                    bits |= ((y0 > 0.0f ? 1u : 0u) | (y1 > 0.0f ? 2u : 0u)) << (2 * e);
+                }
+                word[j] = bits;
+            }
+            const long long b = tile / a.tiles_per_b, t = (tile - b * a.tiles_per_b) * TC_TILE + row;
+            if (t < a.T) *reinterpret_cast<uint4*>(a.codes + b * a.cs_b + (t * a.H + h) * 4) = make_uint4(word[0], word[1], word[2], word[3]);
+        }
+    } else if (lane == 0) {
+        // ================= issuing thread =================
+        const unsigned x_s = base + L1_OFF_X;
+        constexpr unsigned I1 = instr_desc(128);
+        bool pending[L1_NS] = {false, false, false, false};
+        auto load = [&](long long tile, int st) {
+            const long long b = tile / a.tiles_per_b;
+            const int t0 = (int)((tile - b * a.tiles_per_b) * TC_TILE);
+            const unsigned dst = x_s + (unsigned)st * X_BYTES;
+            mbar_expect_tx(bar(X_FULL + st), X_BYTES);
+            tma_load_4d(dst, &xmap, bar(X_FULL + st), 0, t0, h, (int)b);
+            tma_load_4d(dst + X_BYTES / 2, &xmap, bar(X_FULL + st), 64, t0, h, (int)b);
+            pending[st] = true;
+        };
+        for (int i = 0; i < L1_NS; ++i)
+            if (first + i * step < a.n_tiles) load(first + i * step, i);
+        unsigned it = 0;
+        for (long long tile = first; tile < a.n_tiles; tile += step, ++it) {
+            const int st = (int)(it % L1_NS), buf = (int)(it & 1u);
+            if (!mbar_wait(bar(X_FULL + st), (it / L1_NS) & 1u, abort_flag)) { failed = true; break; }
+            pending[st] = false;
+            if (it >= 2 && !mbar_wait(bar(D_FREE + buf), ((it >> 1) - 1u) & 1u, abort_flag)) { failed = true; break; }   // the accumulator has been read
+            tc_fence_after();
+#pragma unroll
+            for (int ks = 0; ks < 8; ++ks) {
+                const unsigned ao = (unsigned)st * X_BYTES + (unsigned)(ks >> 2) * (X_BYTES / 2) + (unsigned)(ks & 3) * 32u;
+                const unsigned bo = (unsigned)(ks >> 2) * (128u * 128u) + (unsigned)(ks & 3) * 32u;
+                mma_ss(tmem + 128u * buf, smem_desc(x_s + ao), smem_desc(base + bo), I1, ks > 0 ? 1u : 0u);
+            }
+            tc_commit(bar(D_FULL + buf));
+            if (it >= 1) {       // the contraction of the tile before this one is over by now or soon: its input stage takes the next rows
+                if (!mbar_wait(bar(D_FULL + (buf ^ 1)), ((it - 1u) >> 1) & 1u, abort_flag)) { failed = true; break; }
+                const long long nxt = tile + (long long)(L1_NS - 1) * step;
+                if (nxt < a.n_tiles) load(nxt, (int)((it - 1u) % L1_NS));
+            }
+        }
+        if (failed) {
+            for (int st = 0; st < L1_NS; ++st)
+                if (pending[st]) {
+                    for (unsigned i = 0; i < WAIT_LIMIT && !(mbar_test(bar(X_FULL + st), 0u) || mbar_test(bar(X_FULL + st), 1u)); ++i) __nanosleep(256);
+                }
+        }
+    }
+    if (failed) {
+        *abort_flag = 1;
+        if (a.status) *reinterpret_cast<volatile int*>(a.status) = 3;
+    }
+    __syncwarp();
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    if (warp == 8) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, 256;" ::"r"(tmem) : "memory");
+}
+
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
                                   const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -419,7 +554,9 @@ int take_hash_status() {
 int launch_hash_encode_tc(const void* x, long long xs_b, long long xs_tok, long long xs_h, int B, long long T, int H, const sl_hash_params* hp,
                           uint32_t* codes, long long cs_b, cudaStream_t s) {
     if (g_hash_kernel == 1) return 1;
-    if (hp->n_layers != 2 || hp->dims[0] != 128 || hp->dims[1] != 256 || hp->dims[2] != 128 || hp->residue) return 1;
+    const bool mlp = hp->n_layers == 2 && hp->dims[0] == 128 && hp->dims[1] == 256 && hp->dims[2] == 128;
+    const bool linear = hp->n_layers == 1 && hp->dims[0] == 128 && hp->dims[1] == 128;
+    if ((!mlp && !linear) || hp->residue) return 1;
     if (H > 65535 || B > 65535 || T > 0x7fffff00ll) return 1;
     if (g_hash_kernel == 0 && (long long)B * T * H < 32768) return 1;           // too few tiles to pay for the set-up
     if (!sl::aligned16(x) || !sl::aligned16(codes) || cs_b % 4 != 0) return 1;
@@ -445,16 +582,21 @@ int launch_hash_encode_tc(const void* x, long long xs_b, long long xs_tok, long 
 
     HashTcArgs a = {};
     a.T = T; a.H = H; a.B = B;
-    a.w1 = static_cast<const __nv_bfloat16*>(hp->d_w[0]); a.w2 = static_cast<const __nv_bfloat16*>(hp->d_w[1]);
-    a.b1 = static_cast<const __nv_bfloat16*>(hp->d_b[0]); a.b2 = static_cast<const __nv_bfloat16*>(hp->d_b[1]);
+    a.w1 = static_cast<const __nv_bfloat16*>(hp->d_w[0]); a.b1 = static_cast<const __nv_bfloat16*>(hp->d_b[0]);
+    if (mlp) { a.w2 = static_cast<const __nv_bfloat16*>(hp->d_w[1]); a.b2 = static_cast<const __nv_bfloat16*>(hp->d_b[1]); }
     a.codes = codes; a.cs_b = cs_b;
     a.tiles_per_b = (T + TC_TILE - 1) / TC_TILE;
     a.n_tiles = a.tiles_per_b * B;
     a.status = d_status;
-    SL_CUDA_OK(cudaFuncSetAttribute(hash_encode_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TC_SMEM));
     const long long per_head = std::max<long long>(1, (long long)sl::sm_count() / H);
     const unsigned gx = (unsigned)std::min<long long>(a.n_tiles, per_head);
-    hash_encode_tc_kernel<<<dim3(gx, (unsigned)H), TC_THREADS, TC_SMEM, s>>>(map, a);
+    if (mlp) {
+        SL_CUDA_OK(cudaFuncSetAttribute(hash_encode_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TC_SMEM));
+        hash_encode_tc_kernel<<<dim3(gx, (unsigned)H), TC_THREADS, TC_SMEM, s>>>(map, a);
+    } else {
+        SL_CUDA_OK(cudaFuncSetAttribute(hash_encode_tc_linear_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)L1_SMEM));
+        hash_encode_tc_linear_kernel<<<dim3(gx, (unsigned)H), L1_THREADS, L1_SMEM, s>>>(map, a);
+    }
     SL_CUDA_OK(cudaGetLastError());
     return SL_OK;
 }

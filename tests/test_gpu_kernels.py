@@ -327,12 +327,13 @@ def test_hash_encode_rows(ops, kind, dtype, dims, residue):
     _assert_codes_match(np_u32(codes), pre.permute(0, 2, 1, 3))
 
 
-@pytest.mark.parametrize("B,T,H,fused", [(2, 203, 4, False), (1, 1000, 3, True), (3, 128, 2, False), (1, 5, 1, False)])
-def test_hash_encode_tcgen05_kernel(ops, B, T, H, fused):
-    """The tcgen05 / TMEM kernel (forced for every size) against the checker: ragged tiles, several batch rows,
-    rows taken from the K half of a fused K|V cache."""
+@pytest.mark.parametrize("kind,dims", [("mlp", (128, 256, 128)), ("linear", (128, 128))])
+@pytest.mark.parametrize("B,T,H,fused", [(2, 203, 4, False), (1, 1000, 3, True), (3, 128, 2, False), (1, 5, 1, False), (1, 1500, 2, False)])
+def test_hash_encode_tcgen05_kernel(ops, B, T, H, fused, kind, dims):
+    """The tcgen05 / TMEM kernels (forced for every size) against the checker: ragged tiles, several batch rows,
+    rows taken from the K half of a fused K|V cache; the MLP hash and the linear hash."""
     from spotlight_b200 import _lib
-    hp = _hash_case("mlp", torch.bfloat16, H, (128, 256, 128), False, 41, 0.05)
+    hp = _hash_case(kind, torch.bfloat16, H, dims, False, 41, 0.05)
     g = torch.Generator().manual_seed(5)
     x = torch.randn((B, T + 9, H, 128), generator=g).to(torch.bfloat16)
     if fused:
@@ -357,12 +358,13 @@ def test_hash_encode_tcgen05_kernel(ops, B, T, H, fused):
     assert flips <= 1e-4, f"{flips:.2e} of the bits differ between the two tensor-core kernels"
 
 
-def test_hash_encode_tcgen05_many_tiles(ops, parity_report):
-    """Many tiles per CTA (both pipelines, barrier phases wrapping): the two tensor-core kernels agree except where
+@pytest.mark.parametrize("kind,dims", [("mlp", (128, 256, 128)), ("linear", (128, 128))])
+def test_hash_encode_tcgen05_many_tiles(ops, parity_report, kind, dims):
+    """Many tiles per CTA (barrier phases wrapping many times): the two tensor-core kernels agree except where
     a pre-sign value is within rounding of zero, and the kernel is deterministic."""
     from spotlight_b200 import _lib
     B, T, H = 1, 70001, 8
-    hp = _hash_case("mlp", torch.bfloat16, H, (128, 256, 128), False, 43, 0.05)
+    hp = _hash_case(kind, torch.bfloat16, H, dims, False, 43, 0.05)
     g = torch.Generator(device=DEV).manual_seed(7)
     x = torch.randn((B, T, H, 128), generator=g, device=DEV).to(torch.bfloat16)
     params = ops.HashParams.from_dict(hp, DEV, False)
@@ -378,7 +380,7 @@ def test_hash_encode_tcgen05_many_tiles(ops, parity_report):
         ops.configure(_lib.SL_OPT_HASH_KERNEL, 0)
     assert torch.equal(a.view(torch.int32), b.view(torch.int32))
     flips = np.bitwise_count(np_u32(a) ^ np_u32(c)).sum() / (a.numel() * 32.0)
-    parity_report("tcgen05 hash kernel vs warp-level kernel (70 001 x 8 rows, bf16 MLP)", bit_flip_rate=f"{flips:.2e}")
+    parity_report(f"tcgen05 hash kernel vs warp-level kernel (70 001 x 8 rows, bf16, {kind})", bit_flip_rate=f"{flips:.2e}")
     assert flips <= 1e-4
 
 
