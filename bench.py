@@ -251,8 +251,8 @@ def build_session(cfg, device, lru=False, extra_capacity=0, fused_kv=True):
     global PREFILL_CODE_BUILD
     PREFILL_CODE_BUILD = {"ms_per_layer": ms, "rows_per_layer": rows, "tflops": flop / ms / 1e9,
                           "gbs": rows * (HEAD_DIM * s.k_cache[0].element_size() + 16) / ms / 1e6,
-                          "kernel": "tcgen05 (TMEM accumulators, TMA input tiles)" if (cfg.hash == "mlp" and tuple(dims) == (128, 256, 128)
-                                     and dt == torch.bfloat16 and not cfg.mlp_residue) else "warp-level mma / scalar"}
+                          "kernel": "tcgen05 (TMEM accumulators, TMA input tiles)" if (tuple(dims) in ((128, 256, 128), (128, 128)) and rows >= 32768
+                                     and dt == torch.bfloat16 and not (cfg.hash == "mlp" and cfg.mlp_residue)) else "warp-level mma / scalar"}
     return s, t_codes / cfg.layers
 
 
