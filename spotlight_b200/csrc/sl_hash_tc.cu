@@ -4,7 +4,7 @@
 //
 // One persistent CTA per SM works on 128-row tiles of one head, one tile after the other. The head's weights stay in shared memory
 // for the whole launch, transposed to K-major rows in the 128-byte-swizzled layout tcgen05.mma reads; the
-// accumulators live in tensor memory (TMEM); input tiles arrive by TMA (cp.async.bulk.tensor, no multicast,
+// accumulators live in tensor memory (TMEM); input tiles arrive by TMA (cp.async.bulk.tensor, one CTA per copy,
 // this GPU's own memory) straight into the same swizzled layout.
 //
 // TMEM columns: D1 [0,256) fp32, H [256,384) packed bf16 pairs, D2 [384,512) fp32. Sixteen epilogue warps (a thread
