@@ -60,11 +60,24 @@ __global__ void __launch_bounds__(MW * 32, 8 / MW) sparse_attn_mma_kernel(const 
     const int sp = blockIdx.x, h = blockIdx.y, b = blockIdx.z, KH = a.KH;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int grp = lane >> 2, tig = lane & 3;
+    const int* list = a.idx + ((long long)b * KH + h) * a.cap;
+    // The list length decides which tiles are this CTA's, and the list entries decide which rows to fetch: two dependent
+    // trips to memory before the first gather. The lists of a decode step are (nearly) as long as their capacity, so the
+    // first ST-1 tiles are read as if the length were the capacity, together with the length; they are used when the
+    // split turns out the same (entries past the end are re-read clamped), else read again.
+    int spec[ST - 1];
+    const int cap_tiles = (a.cap + 15) >> 4;
+    const int per_spec = (cap_tiles + a.splits - 1) / a.splits;
+    {
+        const int t_spec = min(cap_tiles, sp * per_spec) + warp;
+#pragma unroll
+        for (int s = 0; s < ST - 1; ++s) spec[s] = __ldg(list + min((t_spec + s * MW) * 16 + (lane & 15), a.cap - 1));
+    }
     const int n = a.cnt[b * KH + h];
     const int ntiles = (n + 15) >> 4;
     const int per = (ntiles + a.splits - 1) / a.splits;
     const int tile_lo = min(ntiles, sp * per), tile_hi = min(ntiles, tile_lo + per);
-    const int* list = a.idx + ((long long)b * KH + h) * a.cap;
+    const bool spec_ok = per == per_spec;               // then tile_lo is the speculated one as well
     const long long row_stride = a.tok_stride;
     const long long hoff = (long long)b * a.kv_b + (long long)(h / a.kv_div) * a.head_stride;
     const __nv_bfloat16* kb = reinterpret_cast<const __nv_bfloat16*>(a.k) + hoff + (lane & 15) * 8;
@@ -125,7 +138,7 @@ __global__ void __launch_bounds__(MW * 32, 8 / MW) sparse_attn_mma_kernel(const 
 #pragma unroll
     for (int s = 0; s < ST - 1; ++s) {
         const int t = tile + s * MW;
-        if (t < tile_hi) issue(t, entry(t), s);
+        if (t < tile_hi) issue(t, (spec_ok && t * 16 + 15 < n) ? spec[s] : entry(t), s);
         cp_async_commit();
     }
     if (tile + (ST - 1) * MW < tile_hi) tok_next = entry(tile + (ST - 1) * MW);
