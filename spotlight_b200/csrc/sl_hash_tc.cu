@@ -1,4 +1,5 @@
-// Code-cache build at prefill on the 5th-generation tensor cores: hash MLP 128 -> 256 -> 128 and linear hash 128 -> 128 (bf16),
+// Code-cache build at prefill on the 5th-generation tensor cores: hash MLP 128 -> {256, 128} -> 128 (the narrow one also
+// in the reference's residual form) and linear hash 128 -> 128 (bf16),
 // sign and pack of many rows of one head per CTA. This is the one dense contraction of the retrieval path
 // (reference math: spotlight/modifiers/spotlight_generation.py:229-255).
 //
@@ -168,7 +169,13 @@ __device__ unsigned long long g_tc_dbgw[16][4];
 #define TC_STAMPW(k)
 #endif
 
+// D1: width of the hidden layer (256, or 128: then a warp's columns are one piece and both halves of H arrive together).
+// RES (D1 == 128): the reference's residual form, layer output = f(x W + b) + input, rounded once more to bf16.
+template <int D1, bool RES>
 __global__ void __launch_bounds__(TC_THREADS, 1) hash_encode_tc_kernel(const __grid_constant__ CUtensorMap xmap, const HashTcArgs a) {
+    static_assert(D1 == 256 || (D1 == 128), "hidden width");
+    static_assert(!RES || D1 == 128, "a residual layer keeps its width");
+    constexpr int NCH = D1 / 128;                             // 32-column pieces of D1 per epilogue warp
     extern __shared__ unsigned char smem_raw[];
     const unsigned raw = (unsigned)__cvta_generic_to_shared(smem_raw);
     const unsigned base = (raw + 1023u) & ~1023u;             // operand slabs start on 1024-byte boundaries
@@ -195,16 +202,17 @@ __global__ void __launch_bounds__(TC_THREADS, 1) hash_encode_tc_kernel(const __g
         // a warp takes 32 consecutive k of 8 columns: each lane reads 16 bytes of its row and writes 8 halfwords; the
         // 32 lanes of a store fall into distinct banks (k runs along the swizzled 128-byte row)
         const int NWARP = TC_THREADS / 32;
-        const uint4* w1 = reinterpret_cast<const uint4*>(a.w1 + (long long)h * 128 * 256);        // [k][n], 32 groups of 8 n per row
-        for (int task = warp; task < 4 * 32; task += NWARP) {
-            const int k = (task >> 5) * 32 + lane, n0 = (task & 31) * 8;
-            const uint4 v = w1[k * 32 + (task & 31)];
+        constexpr int NG1 = D1 / 8;                                                               // groups of 8 n per row of W1
+        const uint4* w1 = reinterpret_cast<const uint4*>(a.w1 + (long long)h * 128 * D1);         // [k][n]
+        for (int task = warp; task < 4 * NG1; task += NWARP) {
+            const int k = (task / NG1) * 32 + lane, n0 = (task % NG1) * 8;
+            const uint4 v = w1[k * NG1 + (task % NG1)];
             const unsigned short* e = reinterpret_cast<const unsigned short*>(&v);
 #pragma unroll
-            for (int c = 0; c < 8; ++c) *reinterpret_cast<unsigned short*>(g + OFF_W1 + kmajor_off(n0 + c, k, 256)) = e[c];
+            for (int c = 0; c < 8; ++c) *reinterpret_cast<unsigned short*>(g + OFF_W1 + kmajor_off(n0 + c, k, D1)) = e[c];
         }
-        const uint4* w2 = reinterpret_cast<const uint4*>(a.w2 + (long long)h * 256 * 128);        // [k][n], 16 groups of 8 n per row
-        for (int task = warp; task < 8 * 16; task += NWARP) {
+        const uint4* w2 = reinterpret_cast<const uint4*>(a.w2 + (long long)h * D1 * 128);         // [k][n], 16 groups of 8 n per row
+        for (int task = warp; task < (D1 / 32) * 16; task += NWARP) {
             const int k = (task >> 4) * 32 + lane, n0 = (task & 15) * 8;
             const uint4 v = w2[k * 16 + (task & 15)];
             const unsigned short* e = reinterpret_cast<const unsigned short*>(&v);
@@ -213,7 +221,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) hash_encode_tc_kernel(const __g
         }
         __nv_bfloat16* sb1 = reinterpret_cast<__nv_bfloat16*>(g + OFF_B1);
         __nv_bfloat16* sb2 = reinterpret_cast<__nv_bfloat16*>(g + OFF_B2);
-        for (int i = tid; i < 256; i += TC_THREADS) sb1[i] = a.b1 ? a.b1[(long long)h * 256 + i] : __float2bfloat16_rn(0.0f);
+        for (int i = tid; i < D1; i += TC_THREADS) sb1[i] = a.b1 ? a.b1[(long long)h * D1 + i] : __float2bfloat16_rn(0.0f);
         for (int i = tid; i < 128; i += TC_THREADS) sb2[i] = a.b2 ? a.b2[(long long)h * 128 + i] : __float2bfloat16_rn(0.0f);
         unsigned short* lut = reinterpret_cast<unsigned short*>(g + OFF_LUT);
         for (unsigned i = tid; i < 8192u; i += TC_THREADS)
@@ -232,8 +240,9 @@ __global__ void __launch_bounds__(TC_THREADS, 1) hash_encode_tc_kernel(const __g
         // ================= epilogue warps: thread = row = TMEM lane, warp group cg = a quarter of the columns =================
         const int q = warp & 3, cg = warp >> 2, row = q * 32 + lane;
         const unsigned t_row = tmem + ((unsigned)(q * 32) << 16);
-        const unsigned t_d1 = t_row + 64u * cg, t_h = t_row + 256u + 32u * cg, t_d2 = t_row + 384u + 32u * cg;
-        const unsigned* sb1 = reinterpret_cast<const unsigned*>(g + OFF_B1) + 32 * cg;     // pairs of bf16
+        const unsigned t_d1 = t_row + (unsigned)(D1 / 4) * cg, t_h = t_row + 256u + (unsigned)(D1 / 8) * cg, t_d2 = t_row + 384u + 32u * cg;
+        const unsigned* sb1 = reinterpret_cast<const unsigned*>(g + OFF_B1) + (D1 / 8) * cg;     // pairs of bf16
+        unsigned hk[16];                                       // RES: this thread's 32 hidden values, the residual of layer 2
         const unsigned* sb2 = reinterpret_cast<const unsigned*>(g + OFF_B2) + 16 * cg;
         const unsigned char* lutb = g + OFF_LUT;
         unsigned it = 0;
@@ -245,7 +254,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) hash_encode_tc_kernel(const __g
             TC_STAMPW(0)
             unsigned v[1][32];
 #pragma unroll 1
-            for (int jj = 0; jj < 2; ++jj) {
+            for (int jj = 0; jj < NCH; ++jj) {
                 constexpr int j = 0;
                 unsigned pk[16], oob = 0u;
                 tmem_ld32(t_d1 + 32u * jj, v[0]);
@@ -269,10 +278,19 @@ __global__ void __launch_bounds__(TC_THREADS, 1) hash_encode_tc_kernel(const __g
                         if ((v[j][e] - (LUT_LO | (LUT_LO << 16))) & 0x70007000u)  // cancelled its bias); a call each, so the arrays stay in registers
                             pk[e] = silu_pair(v[j][e]);
                 }
+                if (RES) {                  // + input -> bf16: the thread's own row of the tile, still in its input stage
+                    const unsigned char* xrow = g + OFF_X + (it & 1u) * X_BYTES;
+#pragma unroll
+                    for (int e = 0; e < 16; ++e) {
+                        pk[e] = add_bf16x2(pk[e], *reinterpret_cast<const unsigned*>(xrow + kmajor_off(row, 32 * cg + 2 * e, TC_TILE)));
+                        hk[e] = pk[e];
+                    }
+                }
                 tmem_st16(t_h + 16u * jj, pk);
                 tmem_wait_st();
                 tc_fence_before();
-                mbar_arrive(bar(jj == 0 ? H_FULL : H_FULL2));     // layer 2 starts on the half that is there
+                if (NCH == 1 || jj == 0) mbar_arrive(bar(H_FULL));     // layer 2 starts on the half that is there
+                if (NCH == 1 || jj == 1) mbar_arrive(bar(H_FULL2));
             }
             if (tid == 0) { TC_STAMP(0, it, 1) }
             TC_STAMPW(1)
@@ -290,6 +308,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) hash_encode_tc_kernel(const __g
             for (int e = 0; e < 16; ++e) {
                 unsigned y = pack2(__uint_as_float(v[0][2 * e]), __uint_as_float(v[0][2 * e + 1]));
                 y = add_bf16x2(y, sb2[e]);
+                if (RES) y = add_bf16x2(y, hk[e]);              // + the layer's input (the hidden values of the same columns)
                 const float y0 = __uint_as_float(y << 16), y1 = __uint_as_float(y & 0xffff0000u);
                 bits |= ((y0 > 0.0f ? 1u : 0u) | (y1 > 0.0f ? 2u : 0u)) << (2 * e);
             }
@@ -301,7 +320,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) hash_encode_tc_kernel(const __g
     } else if (lane == 0) {
         // ================= issuing thread: TMA loads and tensor-core instructions =================
         const unsigned x_s = base + OFF_X;
-        constexpr unsigned I1 = instr_desc(256), I2 = instr_desc(128);
+        constexpr unsigned I1 = instr_desc(D1), I2 = instr_desc(128);
         bool pending[2] = {false, false};                     // a copy into this stage is in flight
         auto load = [&](long long tile, int st) {
             const long long b = tile / a.tiles_per_b;
@@ -320,7 +339,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) hash_encode_tc_kernel(const __g
 #pragma unroll
             for (int ks = 0; ks < 8; ++ks) {
                 const unsigned ao = (unsigned)st * X_BYTES + (unsigned)(ks >> 2) * (X_BYTES / 2) + (unsigned)(ks & 3) * 32u;
-                const unsigned bo = (unsigned)(ks >> 2) * (256u * 128u) + (unsigned)(ks & 3) * 32u;
+                const unsigned bo = (unsigned)(ks >> 2) * ((unsigned)D1 * 128u) + (unsigned)(ks & 3) * 32u;
                 mma_ss(tmem, smem_desc(x_s + ao), smem_desc(base + OFF_W1 + bo), I1, ks > 0 ? 1u : 0u);
             }
             tc_commit(bar(D1_FULL));
@@ -335,20 +354,24 @@ __global__ void __launch_bounds__(TC_THREADS, 1) hash_encode_tc_kernel(const __g
             TC_STAMP(1, it, 0)
             if (!mbar_wait(bar(H_FULL), par, abort_flag)) { failed = true; break; }        // the first half of every warp's H columns is written
             TC_STAMP(1, it, 1)
-            if (tile + 2 * step < a.n_tiles) load(tile + 2 * step, (int)par);               // layer 1 of this tile is long over: its input stage is free
             if (it > 0 && !mbar_wait(bar(D2_FREE), par ^ 1u, abort_flag)) { failed = true; break; }   // D2 of the previous tile has been read
             tc_fence_after();
 #pragma unroll
             for (int half = 0; half < 2; ++half) {
                 if (half == 1) {
-                    if (!mbar_wait(bar(H_FULL2), par, abort_flag)) { failed = true; break; }   // the rest of H is written and all of D1 read
+                    if (!mbar_wait(bar(H_FULL2), par, abort_flag)) { failed = true; break; }   // the rest of H is written, all of D1 read
                     tc_fence_after();
+                    // layer 1 of this tile is over and (RES) its input rows have been added: the input stage takes the next rows
+                    if (tile + 2 * step < a.n_tiles) load(tile + 2 * step, (int)par);
                 }
+                if (NCH == 2 || half == 0) {
 #pragma unroll
-                for (int i = 0; i < 8; ++i) {
-                    const int ks = 4 * (i >> 1) + 2 * half + (i & 1);       // warp group cg wrote K [64 cg + 32 half, + 32)
-                    const unsigned bo = (unsigned)(ks >> 2) * (128u * 128u) + (unsigned)(ks & 3) * 32u;
-                    mma_ts(tmem + 384u, tmem + 256u + 8u * ks, smem_desc(base + OFF_W2 + bo), I2, (half | i) ? 1u : 0u);
+                    for (int i = 0; i < 8; ++i) {
+                        // D1 = 256: warp group cg wrote K [64 cg + 32 half, + 32); D1 = 128: K [32 cg, + 32), all there at once
+                        const int ks = NCH == 2 ? 4 * (i >> 1) + 2 * half + (i & 1) : i;
+                        const unsigned bo = (unsigned)(ks >> 2) * (128u * 128u) + (unsigned)(ks & 3) * 32u;
+                        mma_ts(tmem + 384u, tmem + 256u + 8u * ks, smem_desc(base + OFF_W2 + bo), I2, (half | i) ? 1u : 0u);
+                    }
                 }
             }
             if (failed) break;
@@ -554,9 +577,9 @@ int take_hash_status() {
 int launch_hash_encode_tc(const void* x, long long xs_b, long long xs_tok, long long xs_h, int B, long long T, int H, const sl_hash_params* hp,
                           uint32_t* codes, long long cs_b, cudaStream_t s) {
     if (g_hash_kernel == 1) return 1;
-    const bool mlp = hp->n_layers == 2 && hp->dims[0] == 128 && hp->dims[1] == 256 && hp->dims[2] == 128;
+    const bool mlp = hp->n_layers == 2 && hp->dims[0] == 128 && (hp->dims[1] == 256 || hp->dims[1] == 128) && hp->dims[2] == 128;
     const bool linear = hp->n_layers == 1 && hp->dims[0] == 128 && hp->dims[1] == 128;
-    if ((!mlp && !linear) || hp->residue) return 1;
+    if ((!mlp && !linear) || (hp->residue && (linear || hp->dims[1] != 128))) return 1;
     if (H > 65535 || B > 65535 || T > 0x7fffff00ll) return 1;
     if (g_hash_kernel == 0 && (long long)B * T * H < 32768) return 1;           // too few tiles to pay for the set-up
     if (!sl::aligned16(x) || !sl::aligned16(codes) || cs_b % 4 != 0) return 1;
@@ -591,8 +614,11 @@ int launch_hash_encode_tc(const void* x, long long xs_b, long long xs_tok, long 
     const long long per_head = std::max<long long>(1, (long long)sl::sm_count() / H);
     const unsigned gx = (unsigned)std::min<long long>(a.n_tiles, per_head);
     if (mlp) {
-        SL_CUDA_OK(cudaFuncSetAttribute(hash_encode_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TC_SMEM));
-        hash_encode_tc_kernel<<<dim3(gx, (unsigned)H), TC_THREADS, TC_SMEM, s>>>(map, a);
+        void (*kern)(const CUtensorMap, const HashTcArgs) = hp->dims[1] == 256 ? hash_encode_tc_kernel<256, false>
+                                                          : hp->residue       ? hash_encode_tc_kernel<128, true>
+                                                                              : hash_encode_tc_kernel<128, false>;
+        SL_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TC_SMEM));
+        kern<<<dim3(gx, (unsigned)H), TC_THREADS, TC_SMEM, s>>>(map, a);
     } else {
         SL_CUDA_OK(cudaFuncSetAttribute(hash_encode_tc_linear_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)L1_SMEM));
         hash_encode_tc_linear_kernel<<<dim3(gx, (unsigned)H), L1_THREADS, L1_SMEM, s>>>(map, a);

@@ -327,13 +327,14 @@ def test_hash_encode_rows(ops, kind, dtype, dims, residue):
     _assert_codes_match(np_u32(codes), pre.permute(0, 2, 1, 3))
 
 
-@pytest.mark.parametrize("kind,dims", [("mlp", (128, 256, 128)), ("linear", (128, 128))])
+@pytest.mark.parametrize("kind,dims,residue", [("mlp", (128, 256, 128), False), ("mlp", (128, 128, 128), False),
+                                               ("mlp", (128, 128, 128), True), ("linear", (128, 128), False)])
 @pytest.mark.parametrize("B,T,H,fused", [(2, 203, 4, False), (1, 1000, 3, True), (3, 128, 2, False), (1, 5, 1, False), (1, 1500, 2, False)])
-def test_hash_encode_tcgen05_kernel(ops, B, T, H, fused, kind, dims):
+def test_hash_encode_tcgen05_kernel(ops, B, T, H, fused, kind, dims, residue):
     """The tcgen05 / TMEM kernels (forced for every size) against the checker: ragged tiles, several batch rows,
     rows taken from the K half of a fused K|V cache; the MLP hash and the linear hash."""
     from spotlight_b200 import _lib
-    hp = _hash_case(kind, torch.bfloat16, H, dims, False, 41, 0.05)
+    hp = _hash_case(kind, torch.bfloat16, H, dims, residue, 41, 0.05)
     g = torch.Generator().manual_seed(5)
     x = torch.randn((B, T + 9, H, 128), generator=g).to(torch.bfloat16)
     if fused:
@@ -342,7 +343,7 @@ def test_hash_encode_tcgen05_kernel(ops, B, T, H, fused, kind, dims):
         xd = cache[:, :T, :, 0]
     else:
         xd = x.to(DEV)[:, :T]
-    params = ops.HashParams.from_dict(hp, DEV, False)
+    params = ops.HashParams.from_dict(hp, DEV, residue)
     try:
         ops.configure(_lib.SL_OPT_HASH_KERNEL, 2)
         codes = ops.hash_encode(xd, params)
@@ -352,22 +353,22 @@ def test_hash_encode_tcgen05_kernel(ops, B, T, H, fused, kind, dims):
         codes_warp = ops.hash_encode(xd, params)
     finally:
         ops.configure(_lib.SL_OPT_HASH_KERNEL, 0)
-    _, pre = O.hash_codes(x[:, :T].permute(0, 2, 1, 3), hp, False)            # [B,H,T,128]
+    _, pre = O.hash_codes(x[:, :T].permute(0, 2, 1, 3), hp, residue)            # [B,H,T,128]
     _assert_codes_match(np_u32(codes), pre.permute(0, 2, 1, 3))
     flips = np.bitwise_count(np_u32(codes) ^ np_u32(codes_warp)).sum() / (codes.numel() * 32.0)
     assert flips <= 1e-4, f"{flips:.2e} of the bits differ between the two tensor-core kernels"
 
 
-@pytest.mark.parametrize("kind,dims", [("mlp", (128, 256, 128)), ("linear", (128, 128))])
-def test_hash_encode_tcgen05_many_tiles(ops, parity_report, kind, dims):
+@pytest.mark.parametrize("kind,dims,residue", [("mlp", (128, 256, 128), False), ("mlp", (128, 128, 128), True), ("linear", (128, 128), False)])
+def test_hash_encode_tcgen05_many_tiles(ops, parity_report, kind, dims, residue):
     """Many tiles per CTA (barrier phases wrapping many times): the two tensor-core kernels agree except where
     a pre-sign value is within rounding of zero, and the kernel is deterministic."""
     from spotlight_b200 import _lib
     B, T, H = 1, 70001, 8
-    hp = _hash_case(kind, torch.bfloat16, H, dims, False, 43, 0.05)
+    hp = _hash_case(kind, torch.bfloat16, H, dims, residue, 43, 0.05)
     g = torch.Generator(device=DEV).manual_seed(7)
     x = torch.randn((B, T, H, 128), generator=g, device=DEV).to(torch.bfloat16)
-    params = ops.HashParams.from_dict(hp, DEV, False)
+    params = ops.HashParams.from_dict(hp, DEV, residue)
     try:
         ops.configure(_lib.SL_OPT_HASH_KERNEL, 2)
         a = ops.hash_encode(x, params)
@@ -380,7 +381,7 @@ def test_hash_encode_tcgen05_many_tiles(ops, parity_report, kind, dims):
         ops.configure(_lib.SL_OPT_HASH_KERNEL, 0)
     assert torch.equal(a.view(torch.int32), b.view(torch.int32))
     flips = np.bitwise_count(np_u32(a) ^ np_u32(c)).sum() / (a.numel() * 32.0)
-    parity_report(f"tcgen05 hash kernel vs warp-level kernel (70 001 x 8 rows, bf16, {kind})", bit_flip_rate=f"{flips:.2e}")
+    parity_report(f"tcgen05 hash kernel vs warp-level kernel (70 001 x 8 rows, bf16, {kind} {dims}{' residual' if residue else ''})", bit_flip_rate=f"{flips:.2e}")
     assert flips <= 1e-4
 
 
