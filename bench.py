@@ -256,14 +256,14 @@ def build_session(cfg, device, lru=False, extra_capacity=0, fused_kv=True):
     return s, t_codes / cfg.layers
 
 
-def time_four_stage(args, cfg, s, device, dist, tokens, drift=0.25):
+def time_four_stage(args, cfg, s, device, dist, tokens, drift=0.25, with_lru=True):
     """The four-stage layer-step (hash -> scan + top-k -> LRU update -> attention over the resident buffers) as ONE
     graph replayed for consecutive tokens: the position, and with it the clock of the LRU tables, lives in device
     memory and advances with every replay; the query drifts from token to token (a fixed query plus fresh noise), so
     the selections overlap partially and the update sees hits AND misses. Returns us per layer (max over ranks) and
     what the tables saw at the last token."""
     was = s.use_lru
-    s.use_lru = True
+    s.use_lru = with_lru
     n, L = cfg.context, cfg.layers
     s.set_position_table(n - 1, s.cfg.capacity - (n - 1), cfg.rope_theta)
     s.pos_dev.fill_(n - 1)
@@ -300,6 +300,8 @@ def time_four_stage(args, cfg, s, device, dist, tokens, drift=0.25):
     bad = sum(int(t.status.item()) != 0 for t in s.lru)
     s.use_lru = was
     hits, misses = stats
+    if not with_lru:        # the same graph (device-side position, drifting query) without stage 3: what the stage adds is the difference
+        return {"value_without_lru_same_graph": ms * 1e3 / L, "unit": UNIT, "tokens_timed": args.steps, "query_drift": drift}
     return {"value_with_lru": ms * 1e3 / L, "unit": UNIT, "tokens_timed": args.steps, "query_drift": drift,
             "hit_rate_last_token": hits / max(1.0, hits + misses), "missed_rows_per_layer": misses,
             "miss_bytes_per_layer": misses * HEAD_DIM * 2 * 2, "lru_slots_per_head": s.cfg.lru_slots,
@@ -406,6 +408,7 @@ def run_ours(args, cfg):
         if with_lru:
             # two regimes: a slowly and a quickly drifting query (noise of 0.05 / 0.25 of a unit-variance query per token)
             lru_info = [time_four_stage(args, cfg, s, device, dist, lru_tokens, drift) for drift in (0.05, 0.25)]
+            lru_info.append(time_four_stage(args, cfg, s, device, dist, lru_tokens, 0.25, with_lru=False))
     ops.check_status(device)
     clk = clocks.summary()
     hash_weight_bytes = sum(w.numel() * w.element_size() for w in s.hash_q[0].weights + s.hash_k[0].weights)

@@ -91,11 +91,11 @@ __global__ void __launch_bounds__(MW * 32, 8 / MW) sparse_attn_mma_kernel(const 
     // one tile = list entries [16 t, 16 t + 16); lane l < 16 fetches entry l (clamped to the last one)
     auto entry = [&](int t) -> int { return list[min(t * 16 + (lane & 15), n - 1)]; };
     // a half-warp copies one 256-byte row per step: 8 steps for K, 8 for V
-    auto issue = [&](int t, int tok, int stage) {
+    // fill mode: the key of list entry 16 t + lane (read a tile ahead, like the entry itself)
+    auto key_of = [&](int t) -> int { return FILL ? toks[min(t * 16 + (lane & 15), n - 1)] : 0; };
+    auto issue = [&](int tok, int key, int stage) {
         const unsigned sbase = wring + stage * STAGE_BYTES;
         const int c = lane & 15;
-        int key = 0;
-        if (FILL) key = __any_sync(0xffffffffu, tok < 0) ? toks[min(t * 16 + (lane & 15), n - 1)] : 0;   // only tiles with a miss look the keys up
 #pragma unroll
         for (int it = 0; it < 8; ++it) {
             const int r = 2 * it + (lane >> 4);
@@ -113,8 +113,7 @@ __global__ void __launch_bounds__(MW * 32, 8 / MW) sparse_attn_mma_kernel(const 
         }
     };
     // fill mode: the rows of this tile that came from the backing store go into their slots of the resident buffers
-    auto write_through = [&](int t, int stage) {
-        const int e_own = entry(t);
+    auto write_through = [&](int e_own, int stage) {
         if (!__any_sync(0xffffffffu, e_own < 0)) return;
         const unsigned char* sb = ring + (size_t)warp * (ST * STAGE_BYTES) + stage * STAGE_BYTES;
         const int c = lane & 15;
@@ -134,14 +133,18 @@ __global__ void __launch_bounds__(MW * 32, 8 / MW) sparse_attn_mma_kernel(const 
 
     // ---- prologue: fill ST-1 stages
     int tile = tile_lo + warp;
-    int tok_next = 0;
+    int tok_next = 0, key_next = 0;
+    int inflight[ST - 1] = {};           // fill mode: the entries of the tiles on their way, oldest first
 #pragma unroll
     for (int s = 0; s < ST - 1; ++s) {
         const int t = tile + s * MW;
-        if (t < tile_hi) issue(t, (spec_ok && t * 16 + 15 < n) ? spec[s] : entry(t), s);
+        if (t < tile_hi) {
+            inflight[s] = (spec_ok && t * 16 + 15 < n) ? spec[s] : entry(t);
+            issue(inflight[s], key_of(t), s);
+        }
         cp_async_commit();
     }
-    if (tile + (ST - 1) * MW < tile_hi) tok_next = entry(tile + (ST - 1) * MW);
+    if (tile + (ST - 1) * MW < tile_hi) { tok_next = entry(tile + (ST - 1) * MW); key_next = key_of(tile + (ST - 1) * MW); }
 
     // ---- Q fragments (A operand), natural order
     unsigned qa[8][HI ? 4 : 2];
@@ -174,13 +177,19 @@ __global__ void __launch_bounds__(MW * 32, 8 / MW) sparse_attn_mma_kernel(const 
             const int t = tile + (ST - 1) * MW;
             int st2 = stage + (ST - 1);
             if (st2 >= ST) st2 -= ST;
-            if (t < tile_hi) issue(t, tok_next, st2);
+            if (t < tile_hi) issue(tok_next, key_next, st2);
             cp_async_commit();
-            if (t + MW < tile_hi) tok_next = entry(t + MW);
+            const int issued = tok_next;
+            if (t + MW < tile_hi) { tok_next = entry(t + MW); key_next = key_of(t + MW); }
+            cp_async_wait<ST - 1>();
+            __syncwarp();
+            if (FILL) {
+                write_through(inflight[0], stage);
+#pragma unroll
+                for (int i = 0; i + 1 < ST - 1; ++i) inflight[i] = inflight[i + 1];
+                inflight[ST - 2] = issued;
+            }
         }
-        cp_async_wait<ST - 1>();
-        __syncwarp();
-        if (FILL) write_through(tile, stage);
         const unsigned kbase = wring + stage * STAGE_BYTES, vbase = kbase + 4096;
         const int valid = n - tile * 16;                    // list entries of this tile that exist
 
