@@ -335,6 +335,27 @@ int sl_lru_update_deferred(const int32_t* d_idx, int idx_capacity, const int32_t
                            const int64_t* d_step, int32_t* d_slots_out, int32_t* d_stats, int32_t* d_status,
                            void* d_workspace, size_t workspace_bytes, void* stream);
 
+/* Stage (3) in two launches, so that the attention need not wait for the evictions:
+ *   sl_lru_probe   hits are stamped and their slots written to d_slots_out, misses get -1 there and are recorded in
+ *                  the workspace;
+ *   sl_lru_evict   the evictions of sl_lru_update_ex for those misses (same policy, same tables afterwards) and the copy
+ *                  of their rows into the slots. It does not touch the slot list, so it may run on another stream beside
+ *                  sl_sparse_attn_decode_fill with read_only = 1 on the probe's list (the slots it fills are not read by
+ *                  that call: they belong to no key of this step's hits). Both must be over before the next probe of the
+ *                  same table. The workspace (sl_lru_workspace_bytes) carries the misses from one launch to the other.
+ * A building block for callers that schedule their own streams; sl_decode_step uses the deferred form above (measured
+ * on B200 at the headline shape: running the evictions on a second stream beside the attention did not shorten the step,
+ * the evictions and the row copy together outlast everything that could hide them). No reference counterpart. */
+int sl_lru_probe(const int32_t* d_idx, int idx_capacity, const int32_t* d_cnt, int B, int KH, int elem_bytes,
+                 void* d_k_resident, void* d_v_resident, const sl_kv_layout* resident, int C, int32_t* d_tok2slot,
+                 int64_t n_max, int32_t* d_slot2tok, int32_t* d_last_used, int step, const int64_t* d_step,
+                 int32_t* d_slots_out, int32_t* d_status, void* d_workspace, size_t workspace_bytes, void* stream);
+int sl_lru_evict(const int32_t* d_idx, int idx_capacity, const int32_t* d_cnt, int B, int KH, const void* k_backing,
+                 const void* v_backing, const sl_kv_layout* backing, int elem_bytes, void* d_k_resident,
+                 void* d_v_resident, const sl_kv_layout* resident, int C, int32_t* d_tok2slot, int64_t n_max,
+                 int32_t* d_slot2tok, int32_t* d_last_used, int step, const int64_t* d_step, int32_t* d_slots,
+                 int32_t* d_stats, int32_t* d_status, void* d_workspace, size_t workspace_bytes, void* stream);
+
 /* Where sl_sparse_attn_decode_fill finds the rows that are not resident yet: the keys of the list entries (the index
  * list the slots were made from, [B, KH, idx_capacity]) and the backing K/V store with its geometry (device memory or
  * mapped pinned host memory). */
@@ -342,6 +363,8 @@ typedef struct sl_attn_fill {
     const int32_t* d_tokens;
     const void* k_backing; const void* v_backing;
     sl_kv_layout backing;
+    int read_only;      /* 1: the rows of negative entries are only read (any negative value marks a miss); the slots are
+                           filled by somebody else, e.g. sl_lru_evict running beside this call */
 } sl_attn_fill;
 
 /* sl_sparse_attn_decode_ex over the resident buffers of an LRU table, with the slot list of sl_lru_update_deferred:

@@ -61,7 +61,7 @@ class DecodeDev(C.Structure):
 
 class AttnFill(C.Structure):
     """sl_attn_fill of include/spotlight_b200.h."""
-    _fields_ = [("d_tokens", _P), ("k_backing", _P), ("v_backing", _P), ("backing", KvLayout)]
+    _fields_ = [("d_tokens", _P), ("k_backing", _P), ("v_backing", _P), ("backing", KvLayout), ("read_only", _I)]
 
 
 _KV = C.POINTER(KvLayout)
@@ -93,6 +93,8 @@ SIGNATURES = {
     "sl_sparse_attn_decode": (_I, [_P, _P, _P, _I, _L, _P, _I, _P, _I, _I, _I, _I, _P, _P, _P, _Z, _P]),
     "sl_sparse_attn_decode_ex": (_I, [_P, _P, _P, _I, _KV, _P, _I, _P, _I, _I, _I, _I, _P, _P, _P, _Z, _P]),
     "sl_sparse_attn_decode_fill": (_I, [_P, _P, _P, _I, _KV, _P, _I, _P, _I, _I, _I, _I, _P, _P, _P, _Z, C.POINTER(AttnFill), _P]),
+    "sl_lru_probe": (_I, [_P, _I, _P, _I, _I, _I, _P, _P, _KV, _I, _P, _L, _P, _P, _I, _P, _P, _P, _P, _Z, _P]),
+    "sl_lru_evict": (_I, [_P, _I, _P, _I, _I, _P, _P, _KV, _I, _P, _P, _KV, _I, _P, _L, _P, _P, _I, _P, _P, _P, _P, _P, _Z, _P]),
     "sl_lru_update_deferred": (_I, [_P, _I, _P, _I, _I, _I, _P, _P, _KV, _I, _P, _L, _P, _P, _I, _P, _P, _P, _P, _P, _Z, _P]),
     "sl_sparse_attn_decode_static": (_I, [_P, _P, _P, _I, _L, _P, _I, _P, _I, _I, _I, _I, _P, _P, _P]),
     "sl_merge_lse": (_I, [_P, _P, _I, _L, _I, _P, _P]),

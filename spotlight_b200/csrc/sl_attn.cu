@@ -345,9 +345,11 @@ static int attn_decode(const void* d_q, const void* d_k, const void* d_v, int dt
                    "sl_sparse_attn_decode_fill: the backing store and its strides must be 16-byte aligned");
         a.tok = fill->d_tokens; a.k_back = fill->k_backing; a.v_back = fill->v_backing;
         a.back_b = bk.batch_stride; a.back_tok = bk.token_stride; a.back_head = bk.head_stride;
+        a.fill_write = fill->read_only ? 0 : 1;
     }
     if (dtype == SL_BF16 && G <= 16) {
-        a.splits = sl::attn_mma_splits(B, KH, idx_capacity);
+        // read-only fill: the evictions of the same step run beside this launch, one CTA per (row, head): leave them their SMs
+        a.splits = sl::attn_mma_splits(B, KH, idx_capacity, (fill && fill->read_only) ? std::min(B * KH, 32) : 0);
         return sl::launch_attn_mma(a, G, s);
     }
     switch (dtype) {

@@ -22,6 +22,7 @@ struct AttnArgs {
     const int* tok;                // [B*KH][cap] keys of the list entries, or null: no fill mode
     const void* k_back; const void* v_back;
     long long back_b, back_tok, back_head;   // elements
+    int fill_write;                // 1: write the fetched rows into their slots; 0: only read them (somebody else fills the slots)
 };
 
 
@@ -30,6 +31,6 @@ int launch_attn_merge(const AttnArgs& a, int G, int dtype, cudaStream_t s);
 
 // bf16 tensor-core path (sl_attn_mma.cu); G = QH / KH <= 16.
 int launch_attn_mma(const AttnArgs& a, int G, cudaStream_t s);
-int attn_mma_splits(int B, int KH, int cap);
+int attn_mma_splits(int B, int KH, int cap, int reserve_sms = 0);
 
 }  // namespace sl

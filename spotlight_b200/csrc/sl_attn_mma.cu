@@ -184,7 +184,7 @@ __global__ void __launch_bounds__(MW * 32, 8 / MW) sparse_attn_mma_kernel(const 
             cp_async_wait<ST - 1>();
             __syncwarp();
             if (FILL) {
-                write_through(inflight[0], stage);
+                if (a.fill_write) write_through(inflight[0], stage);
 #pragma unroll
                 for (int i = 0; i + 1 < ST - 1; ++i) inflight[i] = inflight[i + 1];
                 inflight[ST - 2] = issued;
@@ -427,13 +427,13 @@ static bool use_cluster(int B, int KH, int splits) {
     return have >= B * KH;
 }
 
-int attn_mma_splits(int B, int KH, int cap) {
+int attn_mma_splits(int B, int KH, int cap, int reserve_sms) {
     // never more CTAs than fit at once (one of eight warps per SM, or two of four); every warp
     // should get at least one 16-row tile
     const int ctas = B * KH;
     const int tiles = (cap + 15) / 16;
     const int mw = fat_ctas(B, KH) ? 8 : 4;
-    int s = ((8 / mw) * sm_count()) / ctas;
+    int s = ((8 / mw) * std::max(1, sm_count() - reserve_sms)) / ctas;    // reserve_sms: left to a kernel that runs beside this one
     s = std::min(s, std::min(ATTN_MAX_SPLITS, std::max(1, tiles / mw)));
     s = std::max(s, 1);
     // a few more keys per CTA are cheaper than partials in global memory and a merge kernel

@@ -42,6 +42,11 @@ struct LruArgs {
     int2* g_pairs;                         // [B*KH][cap] {key, slot} of the misses, copied by lru_copy_kernel
     int* g_m;                              // [B*KH] number of misses of the step
     int deferred;                          // the rows of the misses are not copied here: their slots go out as -(slot + 1)
+    // 0: the whole update in one launch. The decode step splits it so that the attention need not wait for the evictions:
+    // 1: the probe only (hits stamped and their slots written, misses marked -1 and recorded in the bitmap, hits counted);
+    // 2: the evictions only, one CTA per (b, kv head), from the bitmap and the count of a phase-1 launch; the slot list is
+    //    not touched (the attention that runs beside it reads the misses from the backing store)
+    int phase;
 };
 
 // exclusive prefix of one value per thread over the block (thread order) and the block total
@@ -100,7 +105,7 @@ __global__ void __launch_bounds__(LT) lru_update_kernel(const LruArgs a) {
     int* lu = a.last_used + bh * a.C;
     const int t = a.d_step ? (int)__ldg(a.d_step) : a.step;
     const unsigned lt = (1u << lane) - 1u;
-    unsigned* gm = a.parts > 1 ? a.g_miss + bh * nw : nullptr;    // one CTA keeps its bitmap in shared memory
+    unsigned* gm = (a.parts > 1 || a.phase != 0) ? a.g_miss + bh * nw : nullptr;    // one CTA keeps its bitmap in shared memory
 
     if (tid == 0) s_hits = 0;
     for (int i = tid; i < NBIN; i += LT) hist[i] = 0;
@@ -119,7 +124,7 @@ __global__ void __launch_bounds__(LT) lru_update_kernel(const LruArgs a) {
     const int wpp = (nw + a.parts - 1) / a.parts;
     const int w0 = min(nw, part * wpp), w1 = min(nw, w0 + wpp);
     int myhits = 0;
-    for (int j0 = w0 * 32 + warp * 32; j0 < w1 * 32; j0 += LT * 8) {
+    for (int j0 = w0 * 32 + warp * 32; j0 < w1 * 32 && a.phase != 2; j0 += LT * 8) {
         int tok[8], sl_[8];
 #pragma unroll
         for (int u = 0; u < 8; ++u) {
@@ -145,7 +150,15 @@ __global__ void __launch_bounds__(LT) lru_update_kernel(const LruArgs a) {
     myhits = __reduce_add_sync(0xffffffffu, myhits);
     if (lane == 0 && myhits) atomicAdd(&s_hits, myhits);
     __syncthreads();
-    if (a.parts > 1) {
+    if (a.phase == 1) {                      // the probe alone: leave the hits of this slice to the eviction launch
+        if (tid == 0 && s_hits) atomicAdd(a.g_count + bh * 2, (unsigned)s_hits);
+        return;
+    }
+    if (a.phase == 2) {                      // the evictions alone: everybody's hits and misses come from the probe launch
+        if (tid == 0) s_hits = (int)atomicExch(a.g_count + bh * 2, 0u);
+        for (int w = tid; w < nw; w += LT) m_miss[w] = __ldcg(gm + w);
+        __syncthreads();
+    } else if (a.parts > 1) {
         // ticket: the CTA that finds the other slices done goes on (with everybody's hits and misses)
         __shared__ int s_last;
         if (tid == 0) {
@@ -300,7 +313,7 @@ __global__ void __launch_bounds__(LT) lru_update_kernel(const LruArgs a) {
                 t2s[tokv[u]] = vv[u];
                 s2t[vv[u]] = tokv[u];
                 lu[vv[u]] = t;
-                out[jv[u]] = a.deferred ? -(vv[u] + 1) : vv[u];
+                if (a.phase != 2) out[jv[u]] = a.deferred ? -(vv[u] + 1) : vv[u];
                 misstok[rankv[u]] = tokv[u];
             }
         }
@@ -407,14 +420,14 @@ int lru_launch(const int32_t* d_idx, int idx_capacity, const int32_t* d_cnt, int
                const void* v_backing, const sl_kv_layout& back, int elem_bytes, void* d_k_resident, void* d_v_resident,
                const sl_kv_layout& res, int C, int32_t* d_tok2slot, int64_t n_max, int32_t* d_slot2tok,
                int32_t* d_last_used, int step, const int64_t* d_step, int32_t* d_slots_out, int32_t* d_stats,
-               int32_t* d_status, void* d_workspace, size_t workspace_bytes, void* stream, bool deferred = false) {
-    SL_REQUIRE(d_idx && d_cnt && (deferred || (k_backing && v_backing)) && d_k_resident && d_v_resident && d_tok2slot && d_slot2tok &&
+               int32_t* d_status, void* d_workspace, size_t workspace_bytes, void* stream, bool deferred = false, int phase = 0) {
+    SL_REQUIRE(d_idx && d_cnt && (deferred || phase == 1 || (k_backing && v_backing)) && d_k_resident && d_v_resident && d_tok2slot && d_slot2tok &&
                    d_last_used && d_slots_out,
                SL_EINVAL, "sl_lru_update: null pointer");
     SL_REQUIRE(B > 0 && B <= 65535 && KH > 0 && C > 0 && idx_capacity > 0 && n_max > 0 && step >= 0, SL_ESHAPE,
                "sl_lru_update: bad shape");
     SL_REQUIRE(elem_bytes == 2 || elem_bytes == 4, SL_EINVAL, "sl_lru_update: elem_bytes must be 2 or 4");
-    SL_REQUIRE((deferred || (sl::aligned16(k_backing) && sl::aligned16(v_backing))) && sl::aligned16(d_k_resident) &&
+    SL_REQUIRE((deferred || phase == 1 || (sl::aligned16(k_backing) && sl::aligned16(v_backing))) && sl::aligned16(d_k_resident) &&
                    sl::aligned16(d_v_resident),
                SL_EALIGN, "sl_lru_update: K/V buffers must be 16-byte aligned");
     for (const sl_kv_layout* l : {&back, &res})
@@ -437,6 +450,8 @@ int lru_launch(const int32_t* d_idx, int idx_capacity, const int32_t* d_cnt, int
     a.slots_out = d_slots_out; a.stats = d_stats; a.status = d_status;
     a.parts = 1;
     a.deferred = deferred ? 1 : 0;
+    a.phase = phase;
+    SL_REQUIRE(phase == 0 || d_workspace, SL_EINVAL, "sl_lru_probe / sl_lru_evict: the workspace carries the misses from one launch to the other");
     if (d_workspace) {
         SL_REQUIRE(workspace_bytes >= sl_lru_workspace_bytes(B, KH, idx_capacity), SL_EWORKSPACE,
                    "sl_lru_update_ex: workspace %zu < required %zu", workspace_bytes, sl_lru_workspace_bytes(B, KH, idx_capacity));
@@ -448,9 +463,10 @@ int lru_launch(const int32_t* d_idx, int idx_capacity, const int32_t* d_cnt, int
         a.g_pairs = reinterpret_cast<int2*>(a.g_miss + (((size_t)B * KH * nw + 3) / 4) * 4);
     }
     SL_CUDA_OK(sl::ensure_dyn_smem(reinterpret_cast<const void*>(lru_update_kernel), smem));
+    if (phase == 2) a.parts = 1;
     dim3 grid((unsigned)KH, (unsigned)B, (unsigned)a.parts);
     SL_CUDA_OK(sl::launch_kernel(lru_update_kernel, grid, dim3(LT), smem, static_cast<cudaStream_t>(stream), false, a));
-    if (a.g_pairs && !deferred) {
+    if (a.g_pairs && !deferred && phase != 1) {
         const int cp = std::max(1, std::min(32, sl::sm_count() / std::max(1, B * KH)));
         SL_CUDA_OK(sl::launch_kernel(lru_copy_kernel, dim3((unsigned)cp, (unsigned)KH, (unsigned)B), dim3(CT), 0,
                                      static_cast<cudaStream_t>(stream), false, a));
@@ -501,4 +517,25 @@ extern "C" int sl_lru_update_deferred(const int32_t* d_idx, int idx_capacity, co
     return lru_launch(d_idx, idx_capacity, d_cnt, B, KH, nullptr, nullptr, *resident, elem_bytes, d_k_resident, d_v_resident,
                       *resident, C, d_tok2slot, n_max, d_slot2tok, d_last_used, step, d_step, d_slots_out, d_stats, d_status,
                       d_workspace, workspace_bytes, stream, true);
+}
+
+extern "C" int sl_lru_probe(const int32_t* d_idx, int idx_capacity, const int32_t* d_cnt, int B, int KH, int elem_bytes,
+                            void* d_k_resident, void* d_v_resident, const sl_kv_layout* resident, int C, int32_t* d_tok2slot,
+                            int64_t n_max, int32_t* d_slot2tok, int32_t* d_last_used, int step, const int64_t* d_step,
+                            int32_t* d_slots_out, int32_t* d_status, void* d_workspace, size_t workspace_bytes, void* stream) {
+    SL_REQUIRE(resident, SL_EINVAL, "sl_lru_probe: null cache layout");
+    return lru_launch(d_idx, idx_capacity, d_cnt, B, KH, nullptr, nullptr, *resident, elem_bytes, d_k_resident, d_v_resident,
+                      *resident, C, d_tok2slot, n_max, d_slot2tok, d_last_used, step, d_step, d_slots_out, nullptr, d_status,
+                      d_workspace, workspace_bytes, stream, false, 1);
+}
+
+extern "C" int sl_lru_evict(const int32_t* d_idx, int idx_capacity, const int32_t* d_cnt, int B, int KH, const void* k_backing,
+                            const void* v_backing, const sl_kv_layout* backing, int elem_bytes, void* d_k_resident,
+                            void* d_v_resident, const sl_kv_layout* resident, int C, int32_t* d_tok2slot, int64_t n_max,
+                            int32_t* d_slot2tok, int32_t* d_last_used, int step, const int64_t* d_step, int32_t* d_slots_scratch,
+                            int32_t* d_stats, int32_t* d_status, void* d_workspace, size_t workspace_bytes, void* stream) {
+    SL_REQUIRE(backing && resident, SL_EINVAL, "sl_lru_evict: null cache layout");
+    return lru_launch(d_idx, idx_capacity, d_cnt, B, KH, k_backing, v_backing, *backing, elem_bytes, d_k_resident, d_v_resident,
+                      *resident, C, d_tok2slot, n_max, d_slot2tok, d_last_used, step, d_step, d_slots_scratch, d_stats, d_status,
+                      d_workspace, workspace_bytes, stream, false, 2);
 }

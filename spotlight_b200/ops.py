@@ -424,11 +424,13 @@ def sparse_attn_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Te
 
 def sparse_attn_decode_fill(q: torch.Tensor, table: "LruTable", slots: torch.Tensor, idx: torch.Tensor, cnt: torch.Tensor,
                             k_backing: Optional[torch.Tensor], v_backing: Optional[torch.Tensor], layout: int = GQA_BLOCKED,
-                            out: Optional[torch.Tensor] = None, return_lse: bool = False, backing_ptrs=None):
+                            out: Optional[torch.Tensor] = None, return_lse: bool = False, backing_ptrs=None,
+                            read_only: bool = False):
     """Attention over the resident buffers of an LRU table with the slot list of lru_update(..., defer_copy=True):
     the rows of the entries -(slot + 1) are fetched from the backing store (k_backing / v_backing [B,N,KH,128] views,
     or backing_ptrs=(k_ptr, v_ptr, batch_stride_elems) for mapped pinned host memory) at the keys idx names, and
-    written into their slots on the way. bf16. Same arithmetic as sparse_attn_decode over the full caches."""
+    written into their slots on the way. bf16. Same arithmetic as sparse_attn_decode over the full caches.
+    read_only: the slot list comes from lru_probe (misses are -1); their rows are only read, lru_evict fills the slots."""
     B, QH, D = q.shape
     KH = table.KH
     assert D == 128 and q.dtype == torch.bfloat16 and table.k.dtype == q.dtype
@@ -444,7 +446,7 @@ def sparse_attn_decode_fill(q: torch.Tensor, table: "LruTable", slots: torch.Ten
     else:
         kp, vp, kb = backing_ptrs
         back = _lib.KvLayout(kb, KH * 128, 128, 1)
-    fill = _lib.AttnFill(idx.data_ptr(), kp, vp, back)
+    fill = _lib.AttnFill(idx.data_ptr(), kp, vp, back, 1 if read_only else 0)
     if out is None:
         out = torch.empty_like(q)
     lse = torch.empty((B, QH), dtype=torch.float32, device=dev) if return_lse else None
@@ -455,6 +457,49 @@ def sparse_attn_decode_fill(q: torch.Tensor, table: "LruTable", slots: torch.Ten
                                          _ptr(lse), ws.data_ptr(), ws.numel(), C.byref(fill), _stream()))
     _count()
     return (out, lse) if return_lse else out
+
+
+def _lru_ws(table: "LruTable", B, KH, cap, dev):
+    need = lib.sl_lru_workspace_bytes(B, KH, cap)
+    if table.ws is None or table.ws.numel() < need:
+        table.ws = torch.zeros(need, dtype=torch.uint8, device=dev)
+    return table.ws
+
+
+def lru_probe(table: "LruTable", idx: torch.Tensor, cnt: torch.Tensor, slots_out: Optional[torch.Tensor] = None,
+              step_dev: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """First half of stage 3: hits are stamped and their slots returned, misses come back as -1 and are left in the
+    table's workspace for lru_evict (which must follow before the table's next probe)."""
+    B, KH, cap = idx.shape
+    dev = _cuda(idx, cnt, table.k)
+    if slots_out is None:
+        slots_out = torch.empty_like(idx)
+    res = _kv_layout(table.k)
+    ws = _lru_ws(table, B, KH, cap, dev)
+    check(lib.sl_lru_probe(idx.data_ptr(), cap, cnt.data_ptr(), B, KH, table.k.element_size(), table.k.data_ptr(),
+                           table.v.data_ptr(), C.byref(res), table.C, table.tok2slot.data_ptr(), table.n_max,
+                           table.slot2tok.data_ptr(), table.last_used.data_ptr(), table.step, _ptr(step_dev),
+                           slots_out.data_ptr(), table.status.data_ptr(), ws.data_ptr(), ws.numel(), _stream()))
+    _count()
+    return slots_out
+
+
+def lru_evict(table: "LruTable", idx: torch.Tensor, cnt: torch.Tensor, k_backing: torch.Tensor, v_backing: torch.Tensor,
+              slots: torch.Tensor, step_dev: Optional[torch.Tensor] = None) -> None:
+    """Second half of stage 3: victims for the misses lru_probe recorded, table update, copy of the missed rows into
+    their slots. Does not touch `slots`; may run on another stream beside sparse_attn_decode_fill(read_only=True)."""
+    B, KH, cap = idx.shape
+    dev = _cuda(idx, cnt, table.k)
+    back, res = _kv_layout(k_backing), _kv_layout(table.k)
+    ws = _lru_ws(table, B, KH, cap, dev)
+    check(lib.sl_lru_evict(idx.data_ptr(), cap, cnt.data_ptr(), B, KH, k_backing.data_ptr(), v_backing.data_ptr(), C.byref(back),
+                           table.k.element_size(), table.k.data_ptr(), table.v.data_ptr(), C.byref(res), table.C,
+                           table.tok2slot.data_ptr(), table.n_max, table.slot2tok.data_ptr(), table.last_used.data_ptr(),
+                           table.step, _ptr(step_dev), slots.data_ptr(), table.stats.data_ptr(), table.status.data_ptr(),
+                           ws.data_ptr(), ws.numel(), _stream()))
+    if step_dev is None:
+        table.step += 1
+    _count(2)
 
 
 class LruTable:

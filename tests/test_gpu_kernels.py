@@ -632,6 +632,8 @@ def test_lru_deferred_fill(ops, fused, host):
         ptrs = (k_host.data_ptr(), v_host.data_ptr(), k_host.stride(0))
     ta = ops.LruTable(B, KH, N, C, torch.bfloat16, DEV, fused=fused)
     tb = ops.LruTable(B, KH, N, C, torch.bfloat16, DEV, fused=fused)
+    tc = ops.LruTable(B, KH, N, C, torch.bfloat16, DEV, fused=fused)      # probe / evict in two launches
+    side = torch.cuda.Stream(device=DEV)
     cur = torch.stack([torch.randperm(N, generator=g)[:keep] for _ in range(B * KH)]).view(B, KH, keep)
     misses = 0
     for step in range(6):
@@ -645,6 +647,19 @@ def test_lru_deferred_fill(ops, fused, host):
         sa, sb = slots_a[..., :n], slots_b[..., :n]
         assert torch.equal(torch.where(sb < 0, -sb - 1, sb), sa)
         misses += int((sb < 0).sum())
+        # the two-launch form: the evictions run on a second stream beside the attention that only reads the misses
+        slots_c = ops.lru_probe(tc, idx, cnt)
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            ops.lru_evict(tc, idx, cnt, kd, vd, slots_c)
+        out_c = ops.sparse_attn_decode_fill(q, tc, slots_c, idx, cnt, kd, vd, backing_ptrs=ptrs, read_only=True)
+        torch.cuda.current_stream().wait_stream(side)
+        assert torch.equal(out_c, out_b)
+        assert torch.equal(torch.where(slots_c[..., :n] < 0, sa, slots_c[..., :n]), sa) and torch.equal(slots_c[..., :n] < 0, sb < 0)
+        assert torch.equal(tc.slot2tok, ta.slot2tok) and torch.equal(tc.tok2slot, ta.tok2slot) and torch.equal(tc.last_used, ta.last_used)
+        assert torch.equal(tc.k.permute(0, 2, 1, 3)[ta.slot2tok >= 0], ta.k.permute(0, 2, 1, 3)[ta.slot2tok >= 0])
+        assert torch.equal(tc.v.permute(0, 2, 1, 3)[ta.slot2tok >= 0], ta.v.permute(0, 2, 1, 3)[ta.slot2tok >= 0])
+        assert torch.equal(tc.stats, ta.stats) and int(tc.status.item()) == 0
         assert torch.equal(out_b, ops.sparse_attn_decode(q, kd, vd, idx, cnt))
         assert torch.equal(out_b, ops.sparse_attn_decode(q, ta.k, ta.v, slots_a, cnt))
         used = ta.slot2tok >= 0                                                            # [B,KH,C]
