@@ -67,9 +67,11 @@ int sl_set_device(int device);
  *                       thread-block cluster and combine their partials through distributed shared memory where
  *                       all clusters of the launch fit on the device at once; 0: partials in the workspace and a merge kernel
  *   SL_OPT_LRU_FUSED_FILL  1 (default): sl_decode_step[_dev] with an LRU stage issue sl_lru_update_deferred +
- *                       sl_sparse_attn_decode_fill (bf16); 0: sl_lru_update_ex (which copies the missed rows) + sl_sparse_attn_decode_ex */
+ *                       sl_sparse_attn_decode_fill (bf16); 0: sl_lru_update_ex (which copies the missed rows) + sl_sparse_attn_decode_ex
+ *   SL_OPT_LRU_MULTI_CTA  1 (default): with a workspace every CTA of a (batch row, kv head) pair works through the whole table
+ *                       update (a cooperative launch, four barriers of the pair); 0: the last CTA of the pair handles the misses alone */
 typedef enum { SL_OPT_PDL = 0, SL_OPT_L2_PREFETCH = 1, SL_OPT_SCAN_KERNEL = 2, SL_OPT_ATTN_WARPS = 3,
-               SL_OPT_PEER_SPIN_LIMIT = 4, SL_OPT_HASH_KERNEL = 5, SL_OPT_ATTN_CLUSTER = 6, SL_OPT_LRU_FUSED_FILL = 7 } sl_option;
+               SL_OPT_PEER_SPIN_LIMIT = 4, SL_OPT_HASH_KERNEL = 5, SL_OPT_ATTN_CLUSTER = 6, SL_OPT_LRU_FUSED_FILL = 7, SL_OPT_LRU_MULTI_CTA = 8 } sl_option;
 int sl_configure(int option, int value);
 
 /* How many thread-block clusters of `cluster_size` CTAs (2..16) of the bf16 attention kernel with `warps_per_cta`

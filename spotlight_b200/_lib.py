@@ -14,7 +14,7 @@ LIB_PATH = os.path.join(_HERE, "lib", "libspotlight_b200.so")
 SL_OK, SL_EINVAL, SL_ESHAPE, SL_EALIGN, SL_EWORKSPACE, SL_ECUDA, SL_ETIMEOUT = 0, -1, -2, -3, -4, -5, -6
 SL_BF16, SL_F32, SL_F16, SL_BOOL = 0, 1, 2, 3
 GQA_INTERLEAVED, GQA_BLOCKED = 0, 1
-SL_OPT_PDL, SL_OPT_L2_PREFETCH, SL_OPT_SCAN_KERNEL, SL_OPT_ATTN_WARPS, SL_OPT_PEER_SPIN_LIMIT, SL_OPT_HASH_KERNEL, SL_OPT_ATTN_CLUSTER, SL_OPT_LRU_FUSED_FILL = 0, 1, 2, 3, 4, 5, 6, 7
+SL_OPT_PDL, SL_OPT_L2_PREFETCH, SL_OPT_SCAN_KERNEL, SL_OPT_ATTN_WARPS, SL_OPT_PEER_SPIN_LIMIT, SL_OPT_HASH_KERNEL, SL_OPT_ATTN_CLUSTER, SL_OPT_LRU_FUSED_FILL, SL_OPT_LRU_MULTI_CTA = 0, 1, 2, 3, 4, 5, 6, 7, 8
 
 
 class HashParamsStruct(C.Structure):

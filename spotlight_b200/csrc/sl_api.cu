@@ -72,7 +72,7 @@ extern "C" int sl_workspace_init(void* d_workspace, size_t bytes, void* stream) 
 }
 
 namespace slscan { void set_scan_kernel(int v); }
-namespace sl { void set_attn_warps(int v); void set_peer_spin_limit(unsigned v); void set_hash_kernel(int mode); int take_hash_status(); void set_attn_cluster(int v); int attn_cluster_capacity(int warps, int cs); }
+namespace sl { void set_attn_warps(int v); void set_peer_spin_limit(unsigned v); void set_hash_kernel(int mode); int take_hash_status(); void set_attn_cluster(int v); int attn_cluster_capacity(int warps, int cs); void set_lru_multi(int v); }
 
 extern "C" int sl_configure(int option, int value) {
     switch (option) {
@@ -90,6 +90,7 @@ extern "C" int sl_configure(int option, int value) {
             SL_REQUIRE(value >= 1, SL_EINVAL, "sl_configure: SL_OPT_PEER_SPIN_LIMIT takes a positive number of polls");
             sl::set_peer_spin_limit((unsigned)value);
             return SL_OK;
+        case SL_OPT_LRU_MULTI_CTA: sl::set_lru_multi(value); return SL_OK;
         case SL_OPT_LRU_FUSED_FILL: sl::g_lru_fill = value ? 1 : 0; return SL_OK;
         case SL_OPT_ATTN_CLUSTER: sl::set_attn_cluster(value ? 1 : 0); return SL_OK;
         case SL_OPT_HASH_KERNEL:

@@ -41,6 +41,12 @@ struct LruArgs {
     unsigned* g_count;                     // [B*KH][2] hits of the step, finished CTAs (both left at zero)
     int2* g_pairs;                         // [B*KH][cap] {key, slot} of the misses, copied by lru_copy_kernel
     int* g_m;                              // [B*KH] number of misses of the step
+    // the update spread over the CTAs of a (b, kv head) pair (lru_update_multi_kernel)
+    unsigned* g_hist;                      // [B*KH][NBIN] ages of the pair's slots, all parts (left zeroed)
+    int2* g_cnt;                           // [B*KH][parts] {older than tau, of age tau} in each part's slot range
+    int* g_pm;                             // [B*KH][parts] misses in each part's slice of the list
+    int* g_vict;                           // [B*KH][cap] slot taken by the r-th miss
+    unsigned* g_bar;                       // [B*KH][8] barrier counters of the pair
     int deferred;                          // the rows of the misses are not copied here: their slots go out as -(slot + 1)
     // 0: the whole update in one launch. The decode step splits it so that the attention need not wait for the evictions:
     // 1: the probe only (hits stamped and their slots written, misses marked -1 and recorded in the bitmap, hits counted);
@@ -361,6 +367,252 @@ __global__ void __launch_bounds__(LT) lru_update_kernel(const LruArgs a) {
     if (tid == 0 && a.stats) { a.stats[bh * 2] = s_hits; a.stats[bh * 2 + 1] = m; }
 }
 
+// The same update with EVERY CTA of a (b, kv head) pair working all the way through: a CTA owns a slice of the index list
+// and a range of the slots; what one CTA needs from the others crosses global memory behind four barriers of the pair
+// (bounded spins; the launch is cooperative, so the CTAs of a pair are resident together):
+//   probe own slice | B0 | ages of own slots -> shared histogram | B1 | threshold age (every CTA for itself), victim bitmaps of own
+//   slots, their counts | B2 | victims of own slots at their global ranks | B3 | own slice's misses take their victims
+// Same policy, same tables and slots afterwards as lru_update_kernel.
+__global__ void __launch_bounds__(LT) lru_update_multi_kernel(const LruArgs a) {
+    extern __shared__ int smem_i[];
+    const int P = a.parts;
+    const int cw = (a.C + 31) >> 5, nw = (a.cap + 31) >> 5;
+    const int cwpp = (cw + P - 1) / P, wpp = (nw + P - 1) / P;
+    unsigned* m_gt = reinterpret_cast<unsigned*>(smem_i);            // [cwpp] own slots older than tau
+    unsigned* m_eq = m_gt + cwpp;                                    // [cwpp] own slots of age tau
+    int* p_gt = reinterpret_cast<int*>(m_eq + cwpp);                 // [cwpp] prefixes inside the own range
+    int* p_eq = p_gt + cwpp;
+    unsigned* m_miss = reinterpret_cast<unsigned*>(p_eq + cwpp);     // [wpp] own list entries that missed
+    int* p_miss = reinterpret_cast<int*>(m_miss + wpp);              // [wpp]
+    unsigned short* age16 = reinterpret_cast<unsigned short*>(p_miss + wpp);   // [cwpp * 32]
+    __shared__ unsigned hist[NBIN];
+    __shared__ int wsum[LW];
+    __shared__ int s_hits, s_tau, s_r, s_gb, s_eb, s_mb;
+
+    const int h = blockIdx.x, b = blockIdx.y, part = blockIdx.z, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const long long bh = (long long)b * a.KH + h;
+    sl::pdl_trigger();
+    sl::pdl_wait();
+    const int n = min(a.cnt[bh], a.cap);
+    const int* list = a.idx + bh * a.cap;
+    int* out = a.slots_out + bh * a.cap;
+    int* t2s = a.tok2slot + bh * a.n_max;
+    int* s2t = a.slot2tok + bh * a.C;
+    int* lu = a.last_used + bh * a.C;
+    const int t = a.d_step ? (int)__ldg(a.d_step) : a.step;
+    const unsigned lt = (1u << lane) - 1u;
+    unsigned* bar = a.g_bar + bh * 8;
+    unsigned* cnt2 = a.g_count + bh * 2;
+
+    if (tid == 0) s_hits = 0;
+    for (int i = tid; i < NBIN; i += LT) hist[i] = 0;
+    if (part == 0 && tid >= 1 && tid <= 3) bar[tid] = 0u;           // the counters of B1..B3: nobody is near them before B0
+    __syncthreads();
+    if (n > a.C) {                          // the table cannot hold this step's attended set (every CTA of the pair sees it)
+        if (tid == 0 && part == 0) {
+            if (a.status) atomicExch(a.status, 3);
+            if (a.g_m) a.g_m[bh] = 0;
+        }
+        return;
+    }
+
+    // ---- probe of the own slice of the list: whole bitmap words [w0, w1)
+    const int w0 = min(nw, part * wpp), w1 = min(nw, w0 + wpp);
+    int myhits = 0;
+    for (int j0 = w0 * 32 + warp * 32; j0 < w1 * 32; j0 += LT * 8) {
+        int tok[8], sl_[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            const int j = j0 + u * LT + lane;
+            tok[u] = (j < n && j < w1 * 32) ? __ldg(list + j) : -1;
+        }
+#pragma unroll
+        for (int u = 0; u < 8; ++u) sl_[u] = tok[u] >= 0 ? t2s[tok[u]] : -1;
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            const int j = j0 + u * LT + lane;
+            if (tok[u] >= 0) {
+                if (sl_[u] >= 0) { lu[sl_[u]] = t; ++myhits; }
+                out[j] = sl_[u];
+            }
+            const unsigned mb = __ballot_sync(0xffffffffu, tok[u] >= 0 && sl_[u] < 0);
+            if (lane == 0 && (j0 + u * LT) < w1 * 32) m_miss[((j0 + u * LT) >> 5) - w0] = mb;
+        }
+    }
+    myhits = __reduce_add_sync(0xffffffffu, myhits);
+    if (lane == 0 && myhits) atomicAdd(&s_hits, myhits);
+    __syncthreads();
+    // ranks of the own misses inside the slice, and their number
+    int my_misses;
+    {
+        const int WPT = (wpp + LT - 1) / LT;
+        int cm = 0;
+        for (int k = 0; k < WPT; ++k) {
+            const int w = tid * WPT + k;
+            if (w < w1 - w0) cm += __popc(m_miss[w]);
+        }
+        int pm = block_exclusive_scan(cm, wsum, my_misses);
+        for (int k = 0; k < WPT; ++k) {
+            const int w = tid * WPT + k;
+            if (w < w1 - w0) { p_miss[w] = pm; pm += __popc(m_miss[w]); }
+        }
+    }
+    if (tid == 0) {
+        if (s_hits) atomicAdd(cnt2, (unsigned)s_hits);
+        a.g_pm[bh * P + part] = my_misses;
+    }
+    sl::grid_barrier(bar + 0, (unsigned)P, a.status);               // B0: every slice is probed, every hit stamped
+    const int total_hits = (int)__ldcg(cnt2);
+    const int m = n - total_hits;              // misses = victims needed
+    if (m == 0) {                               // everything was resident: nothing to evict
+        sl::grid_barrier(bar + 1, (unsigned)P, a.status);           // everybody has read the count
+        if (part == 0 && tid == 0) {
+            *cnt2 = 0u; bar[0] = 0u;
+            if (a.stats) { a.stats[bh * 2] = total_hits; a.stats[bh * 2 + 1] = 0; }
+            if (a.g_m) a.g_m[bh] = 0;
+        }
+        return;
+    }
+
+    // ---- ages of the own slots [32 cw0, 32 cw1) not used in this step, into the pair's histogram
+    const int cw0 = min(cw, part * cwpp), cw1 = min(cw, cw0 + cwpp);
+    const int s_lo = cw0 * 32, s_hi = min(a.C, cw1 * 32);
+    for (int s0 = s_lo + tid; s0 < s_hi; s0 += LT * 8) {
+        int l[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) l[u] = s0 + u * LT < s_hi ? __ldcg(lu + s0 + u * LT) : t;
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            if (s0 + u * LT < s_hi) {
+                const int age = l[u] < 0 ? AGE_MAX + 1 : min(t - l[u], AGE_MAX);
+                age16[s0 + u * LT - s_lo] = (unsigned short)age;
+                if (age > 0) atomicAdd(&hist[age], 1u);
+            }
+        }
+    }
+    __syncthreads();
+    unsigned* gh = a.g_hist + bh * NBIN;
+    for (int i = tid; i < NBIN; i += LT)
+        if (hist[i]) atomicAdd(gh + i, hist[i]);
+    sl::grid_barrier(bar + 1, (unsigned)P, a.status);               // B1: the histogram is complete
+    for (int i = tid; i < NBIN; i += LT) hist[i] = __ldcg(gh + i);
+    __syncthreads();
+    if (tid < 32) {                         // oldest first: largest age with a cumulative count >= m
+        const int BW = (NBIN + 31) >> 5;
+        const int blo = lane * BW, bhi = min(NBIN, blo + BW);
+        unsigned bs = 0;
+        for (int i = blo; i < bhi; ++i) bs += hist[i];
+        unsigned suf = bs;
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1) {
+            const unsigned v = __shfl_down_sync(0xffffffffu, suf, d);
+            if (lane + d < 32) suf += v;
+        }
+        const unsigned ball = __ballot_sync(0xffffffffu, suf >= (unsigned)m);
+        if (ball == 0u && lane == 0 && a.status) atomicExch(a.status, 4);   // table state is inconsistent
+        const int L = ball ? 31 - __clz(ball) : 0;
+        int tau_l = 0, gt_l = 0;
+        if (lane == L) {
+            unsigned cum = suf - bs;
+            for (int i = bhi - 1; i >= blo; --i) {
+                const unsigned v = hist[i];
+                if (cum + v >= (unsigned)m) { tau_l = i; gt_l = (int)cum; break; }
+                cum += v;
+            }
+        }
+        const int tau = __shfl_sync(0xffffffffu, tau_l, L);
+        const int r = m - __shfl_sync(0xffffffffu, gt_l, L);
+        if (lane == 0) { s_tau = tau; s_r = r; }
+    }
+    __syncthreads();
+    const int tau = s_tau, r = s_r;
+    // ---- victim bitmaps of the own slots and their counts
+#pragma unroll 4
+    for (int w = cw0 + warp; w < cw1; w += LW) {
+        const int s = w * 32 + lane;
+        const int age = s < a.C ? (int)age16[s - s_lo] : 0;
+        const unsigned g = __ballot_sync(0xffffffffu, age > tau);
+        const unsigned e = __ballot_sync(0xffffffffu, age == tau && age > 0);
+        if (lane == 0) { m_gt[w - cw0] = g; m_eq[w - cw0] = e; }
+    }
+    __syncthreads();
+    {
+        const int WPT = (cwpp + LT - 1) / LT;
+        int cg = 0, ce = 0;
+        for (int k = 0; k < WPT; ++k) {
+            const int w = tid * WPT + k;
+            if (w < cw1 - cw0) { cg += __popc(m_gt[w]); ce += __popc(m_eq[w]); }
+        }
+        int tg, te;
+        int pg = block_exclusive_scan(cg, wsum, tg);
+        int pe = block_exclusive_scan(ce, wsum, te);
+        for (int k = 0; k < WPT; ++k) {
+            const int w = tid * WPT + k;
+            if (w < cw1 - cw0) {
+                p_gt[w] = pg; p_eq[w] = pe;
+                pg += __popc(m_gt[w]); pe += __popc(m_eq[w]);
+            }
+        }
+        if (tid == 0) a.g_cnt[bh * P + part] = make_int2(tg, te);
+    }
+    sl::grid_barrier(bar + 2, (unsigned)P, a.status);               // B2: every range's counts are there
+    if (tid == 0) {                          // the ranges before this one, the slices before this one
+        int gb = 0, eb = 0, mb = 0;
+        for (int q = 0; q < part; ++q) {
+            const int2 c = __ldcg(a.g_cnt + bh * P + q);
+            gb += c.x; eb += c.y;
+            mb += __ldcg(a.g_pm + bh * P + q);
+        }
+        s_gb = gb; s_eb = eb; s_mb = mb;
+    }
+    // the pair's histogram is read by everybody by now: this CTA's share of it goes back to zero for the next call
+    for (int i = part * LT + tid; i < NBIN; i += P * LT) gh[i] = 0u;
+    __syncthreads();
+    int* vict = a.g_vict + bh * a.cap;
+#pragma unroll 4
+    for (int w = warp; w < cw1 - cw0; w += LW) {
+        const unsigned g = m_gt[w], e = m_eq[w];
+        const int gb = s_gb + p_gt[w] + __popc(g & lt), eb = s_eb + p_eq[w] + __popc(e & lt);
+        const bool isg = (g >> lane) & 1u, ise = (e >> lane) & 1u;
+        if (isg || (ise && eb < r)) vict[gb + min(eb, r)] = (cw0 + w) * 32 + lane;
+    }
+    sl::grid_barrier(bar + 3, (unsigned)P, a.status);               // B3: the victims stand at their ranks
+    // ---- the own slice's misses, in list order, take the victims in that order
+    int2* pairs = (a.g_pairs && !a.deferred) ? a.g_pairs + bh * a.cap : nullptr;
+    for (int wq = warp; wq < w1 - w0; wq += 4 * LW) {
+        int jv[4], vv[4], tokv[4], oldv[4], rankv[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const int w = wq + u * LW;
+            const unsigned mm = w < w1 - w0 ? m_miss[w] : 0u;
+            jv[u] = -1;
+            if ((mm >> lane) & 1u) {
+                jv[u] = (w0 + w) * 32 + lane;
+                rankv[u] = s_mb + p_miss[w] + __popc(mm & lt);
+                vv[u] = __ldcg(vict + rankv[u]);
+                tokv[u] = __ldg(list + jv[u]);
+                oldv[u] = s2t[vv[u]];
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            if (jv[u] >= 0) {
+                if (oldv[u] >= 0) t2s[oldv[u]] = -1;
+                t2s[tokv[u]] = vv[u];
+                s2t[vv[u]] = tokv[u];
+                lu[vv[u]] = t;
+                out[jv[u]] = a.deferred ? -(vv[u] + 1) : vv[u];
+                if (pairs) pairs[rankv[u]] = make_int2(tokv[u], vv[u]);
+            }
+        }
+    }
+    if (part == 0 && tid == 0) {
+        *cnt2 = 0u; bar[0] = 0u;              // everybody is past B1 (and so past reading the count and leaving B0)
+        if (a.g_m) a.g_m[bh] = m;
+        if (a.stats) { a.stats[bh * 2] = total_hits; a.stats[bh * 2 + 1] = m; }
+    }
+}
+
 // The rows of the step's misses, copied from the backing store into their slots by CP CTAs per (b, kv head):
 // the {key, slot} pairs and their number come from lru_update_kernel; 16-byte lanes, four rows in flight per group.
 constexpr int CT = 256;
@@ -408,6 +660,8 @@ __global__ void __launch_bounds__(CT) lru_copy_kernel(const LruArgs a) {
 }  // namespace
 
 namespace {
+
+int g_lru_multi = 1;       // 1: every CTA of a (b, kv head) pair works through the whole update; 0: the last one alone handles the misses
 
 int lru_parts(int B, int KH, int idx_capacity) {
     // enough CTAs to put every SM to work on the probe, at least 1024 list entries (one round of a CTA) each
@@ -461,6 +715,26 @@ int lru_launch(const int32_t* d_idx, int idx_capacity, const int32_t* d_cnt, int
         a.g_m = reinterpret_cast<int*>(a.g_count + (((size_t)B * KH * 2 + 63) / 64) * 64);
         a.g_miss = reinterpret_cast<unsigned*>(a.g_m + (((size_t)B * KH + 63) / 64) * 64);
         a.g_pairs = reinterpret_cast<int2*>(a.g_miss + (((size_t)B * KH * nw + 3) / 4) * 4);
+        // behind the pairs: what the CTAs of a pair exchange when all of them work through the update
+        const size_t bh = (size_t)B * KH;
+        a.g_hist = reinterpret_cast<unsigned*>(a.g_pairs + bh * idx_capacity);
+        a.g_bar = a.g_hist + ((bh * NBIN + 3) / 4) * 4;
+        a.g_cnt = reinterpret_cast<int2*>(a.g_bar + bh * 8);
+        a.g_pm = reinterpret_cast<int*>(a.g_cnt + bh * 64);
+        a.g_vict = a.g_pm + bh * 64;
+    }
+    if (g_lru_multi && phase == 0 && d_workspace && a.parts > 1 && B * KH * a.parts <= sl::sm_count()) {
+        const size_t cwpp = (cw + a.parts - 1) / a.parts, wpp = (nw + a.parts - 1) / a.parts;
+        const size_t smem_m = cwpp * 16 + wpp * 8 + cwpp * 64 + 16;
+        SL_CUDA_OK(sl::ensure_dyn_smem(reinterpret_cast<const void*>(lru_update_multi_kernel), smem_m));
+        SL_CUDA_OK(sl::launch_kernel(lru_update_multi_kernel, dim3((unsigned)KH, (unsigned)B, (unsigned)a.parts), dim3(LT), smem_m,
+                                     static_cast<cudaStream_t>(stream), true, a));
+        if (!deferred) {
+            const int cp = std::max(1, std::min(32, sl::sm_count() / std::max(1, B * KH)));
+            SL_CUDA_OK(sl::launch_kernel(lru_copy_kernel, dim3((unsigned)cp, (unsigned)KH, (unsigned)B), dim3(CT), 0,
+                                         static_cast<cudaStream_t>(stream), false, a));
+        }
+        return SL_OK;
     }
     SL_CUDA_OK(sl::ensure_dyn_smem(reinterpret_cast<const void*>(lru_update_kernel), smem));
     if (phase == 2) a.parts = 1;
@@ -480,8 +754,11 @@ extern "C" size_t sl_lru_workspace_bytes(int B, int KH, int idx_capacity) {
     if (B <= 0 || KH <= 0 || idx_capacity <= 0) return 0;
     const size_t nw = ((size_t)idx_capacity + 31) / 32;
     // counters, misses per pair, miss bitmaps, {key, slot} pairs of the misses
+    const size_t bh = (size_t)B * KH;
     return ((((size_t)B * KH * 2 + 63) / 64) * 64 + (((size_t)B * KH + 63) / 64) * 64 + (((size_t)B * KH * nw + 3) / 4) * 4) * 4 +
-           (size_t)B * KH * idx_capacity * 8;
+           (size_t)B * KH * idx_capacity * 8 +
+           // histogram of ages, barrier counters, per-part counts ({older, ties}, misses; at most 64 parts), victims
+           (((bh * NBIN + 3) / 4) * 4 + bh * 8) * 4 + bh * 64 * 8 + bh * 64 * 4 + bh * (size_t)idx_capacity * 4;
 }
 
 extern "C" int sl_lru_update(const int32_t* d_idx, int idx_capacity, const int32_t* d_cnt, int B, int KH,
@@ -539,3 +816,5 @@ extern "C" int sl_lru_evict(const int32_t* d_idx, int idx_capacity, const int32_
                       *resident, C, d_tok2slot, n_max, d_slot2tok, d_last_used, step, d_step, d_slots_scratch, d_stats, d_status,
                       d_workspace, workspace_bytes, stream, false, 2);
 }
+
+namespace sl { void set_lru_multi(int v) { g_lru_multi = v ? 1 : 0; } }

@@ -549,12 +549,22 @@ def test_errors_are_exceptions_not_crashes(ops):
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
 @pytest.mark.parametrize("B,KH,N,C,keep", [(2, 4, 3000, 400, 300), (1, 8, 5000, 1500, 1400), (3, 2, 200, 64, 64),
                                            (1, 4, 60000, 9000, 4200), (2, 2, 40000, 14000, 6500)])
-def test_lru_resident_buffer_is_results_invisible(ops, dtype, B, KH, N, C, keep):
+@pytest.mark.parametrize("multi", [1, 0])
+def test_lru_resident_buffer_is_results_invisible(ops, dtype, B, KH, N, C, keep, multi):
     """A dozen decode steps with drifting attended sets: slot tables bit-exact against the CPU
     model of the policy, resident rows equal to the backing rows, and attention over the resident
     buffer bit-identical to attention over the full cache. The long lists are probed by several CTAs
-    per (row, kv head); the last of them handles the misses. Fused K|V buffers on both sides in the
-    bf16 runs of the long lists."""
+    per (row, kv head): all of them work through the whole update (multi = 1, four barriers of the pair), or the
+    last of them handles the misses alone (multi = 0). Fused K|V buffers on both sides in the bf16 runs of the long lists."""
+    from spotlight_b200 import _lib
+    ops.configure(_lib.SL_OPT_LRU_MULTI_CTA, multi)
+    try:
+        _lru_steps(ops, dtype, B, KH, N, C, keep)
+    finally:
+        ops.configure(_lib.SL_OPT_LRU_MULTI_CTA, 1)
+
+
+def _lru_steps(ops, dtype, B, KH, N, C, keep):
     QH = KH * 2
     g = torch.Generator().manual_seed(B * 100 + C)
     k = torch.randn((B, N, KH, 128), generator=g).to(dtype)
