@@ -465,9 +465,9 @@ __global__ void __launch_bounds__(LT) lru_update_multi_kernel(const LruArgs a) {
     const int total_hits = (int)__ldcg(cnt2);
     const int m = n - total_hits;              // misses = victims needed
     if (m == 0) {                               // everything was resident: nothing to evict
-        sl::grid_barrier(bar + 1, (unsigned)P, a.status);           // everybody has read the count
-        if (part == 0 && tid == 0) {
-            *cnt2 = 0u; bar[0] = 0u;
+        // the last CTA of the pair to get here (a ticket, nobody waits) knows that everybody has read the count
+        if (tid == 0 && atomicAdd(bar + 4, 1u) == (unsigned)P - 1u) {
+            *cnt2 = 0u; bar[0] = 0u; bar[4] = 0u;
             if (a.stats) { a.stats[bh * 2] = total_hits; a.stats[bh * 2 + 1] = 0; }
             if (a.g_m) a.g_m[bh] = 0;
         }
