@@ -314,9 +314,10 @@ int sl_lru_update(const int32_t* d_idx, int idx_capacity, const int32_t* d_cnt, 
  * K|V caches or host memory with any strides), an optional step in DEVICE memory (*d_step, e.g. the decode
  * position, so that a replayed CUDA graph advances the table's clock) and an optional workspace of
  * sl_lru_workspace_bytes(B, KH, idx_capacity) bytes, zero-filled once and left zeroed by every call: with it
- * the probe of the index list is spread over several CTAs per (b, kv head) -- the step in which (nearly)
- * every attended key is already resident then costs a few microseconds instead of one CTA's walk over the
- * whole list -- and only the last of them to finish handles the misses. Results are those of sl_lru_update. */
+ * the update is spread over several CTAs per (b, kv head), each owning a slice of the index list and a range of the
+ * slots (a cooperative launch; what the CTAs of a pair need from one another crosses the workspace behind four bounded
+ * barriers of the pair; SL_OPT_LRU_MULTI_CTA = 0: only the probe is spread and the last CTA to finish handles the
+ * misses alone). Results are those of sl_lru_update. */
 size_t sl_lru_workspace_bytes(int B, int KH, int idx_capacity);
 int sl_lru_update_ex(const int32_t* d_idx, int idx_capacity, const int32_t* d_cnt, int B, int KH,
                      const void* k_backing, const void* v_backing, const sl_kv_layout* backing, int elem_bytes,

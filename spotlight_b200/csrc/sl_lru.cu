@@ -11,11 +11,12 @@
 //   output  the slot of every attended key, in the order of the index list, so attention over
 //           the resident buffer performs the same arithmetic as attention over the full cache.
 // The reference has no such stage; the policy is specified here and restated in the CPU checker.
-// The common step -- (nearly) every attended key is already resident -- is spread over several CTAs per
-// (b, kv head): each probes a slice of the index list (list -> token-to-slot map, two dependent loads per
-// entry, many in flight), stamps the hits, writes their slots and records the misses in a bitmap; the
-// last CTA of the pair to finish (a ticket, nobody waits) handles the misses alone: victim selection is a
-// histogram select over ages (no sort), the ordered assignments use bitmaps and block scans.
+// With a workspace the update is spread over several CTAs per (b, kv head). Each probes a slice of the index list
+// (list -> token-to-slot map, two dependent loads per entry, many in flight), stamps the hits, writes their slots and
+// records the misses in a bitmap. Then either all of them work through the evictions, each on its range of the slots
+// (lru_update_multi_kernel), or the last CTA of the pair to finish (a ticket, nobody waits) handles the misses alone
+// (lru_update_kernel). Victim selection is a histogram select over ages (no sort), the ordered assignments use bitmaps
+// and block scans.
 #include "sl_common.cuh"
 
 namespace {
