@@ -419,24 +419,7 @@ def run_ours(args, cfg):
         t = torch.tensor([ms_step, ms_e2e, wall_e2e], device=device, dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms_step, ms_e2e, wall_e2e = t.tolist()
-    extras = {}
-    if dist is not None and cfg.name == "headline" and not args.no_extras:
-        checksum = float(out_host.float().abs().sum())
-        g_all = g = None
-        del s
-        torch.cuda.empty_cache()
-        try:
-            extras = multi_rank_extras(args, device, dist, world, rank)
-        except Exception as e:
-            extras = {"multi_rank_extras_error": str(e)[:300]}
-        s = None
-    if rank != 0:
-        if dist is not None:
-            torch.cuda.synchronize(device)
-            dist.barrier()
-            os._exit(0)
-        return
-
+    checksum = float(out_host.float().abs().sum())
     us_layer = ms_step * 1e3 / L
     peak, peak_kind = peaks()
     by_scan = cfg.batch * n * cfg.kv_heads * 16 + cfg.batch * cfg.q_heads * 16
@@ -477,11 +460,42 @@ def run_ours(args, cfg):
         "code_build_ms_per_layer": code_build_ms,
         "prefill_code_build": PREFILL_CODE_BUILD,
         "clocks": clk,
-        "checksum": checksum if extras else float(out_host.float().abs().sum()),
+        "checksum": checksum,
     }
     if lru_info is not None:
         line["four_stage"] = lru_info
-    line.update(extras)
+    # With several ranks the measurements that exchange data between them come last, under a watchdog: if they stall
+    # (a rank that fell out, an exchange that waits), every rank gives up on them and rank 0 still prints the line.
+    if dist is not None and cfg.name == "headline" and not args.no_extras:
+        import threading
+        done = threading.Event()
+        limit = float(os.environ.get("SL_BENCH_EXTRAS_TIMEOUT_S", "360"))
+
+        def watchdog():
+            if done.wait(limit):
+                return
+            if rank == 0:
+                line["multi_rank_extras_error"] = f"gave up after {limit:.0f} s"
+                print(json.dumps(line), flush=True)
+            os._exit(0)
+
+        threading.Thread(target=watchdog, daemon=True).start()
+        g_all = g = None
+        del s
+        torch.cuda.empty_cache()
+        try:
+            extras = multi_rank_extras(args, device, dist, world, rank)
+        except Exception as e:
+            extras = {"multi_rank_extras_error": str(e)[:300]}
+        done.set()
+        s = None
+        line.update(extras)
+    if rank != 0:
+        if dist is not None:
+            torch.cuda.synchronize(device)
+            dist.barrier()
+            os._exit(0)
+        return
     if world == 1 and not args.no_reference_kernels and cfg.name == "headline":
         try:
             line["row_gather"] = row_gather(cfg, s, device)
