@@ -309,6 +309,19 @@ def time_four_stage(args, cfg, s, device, dist, tokens, drift=0.25, with_lru=Tru
             "note": "one CUDA graph for every token (device-side position and LRU clock); the query drifts, so the tables see hits and misses"}
 
 
+def _leave_together(device, dist):
+    """Meet the other ranks once more and exit without the group's teardown; a rank that cannot be met (it fell out
+    of an exchange measurement) is not waited for longer than a few seconds: the numbers are out by now."""
+    import threading
+    threading.Timer(20.0, lambda: os._exit(0)).start()
+    try:
+        torch.cuda.synchronize(device)
+        dist.barrier()
+    except Exception:
+        pass
+    os._exit(0)
+
+
 def time_graph(g, steps, warmup, device, dist=None):
     for _ in range(warmup):
         g.replay()
@@ -492,9 +505,7 @@ def run_ours(args, cfg):
         line.update(extras)
     if rank != 0:
         if dist is not None:
-            torch.cuda.synchronize(device)
-            dist.barrier()
-            os._exit(0)
+            _leave_together(device, dist)
         return
     if world == 1 and not args.no_reference_kernels and cfg.name == "headline":
         try:
@@ -518,9 +529,7 @@ def run_ours(args, cfg):
     print(json.dumps(line), flush=True)
     if dist is not None:      # captured graphs may hold communicator work: leave without the group's teardown
         sys.stdout.flush()
-        torch.cuda.synchronize(device)
-        dist.barrier()
-        os._exit(0)
+        _leave_together(device, dist)
 
 
 def run_decode_loop(args, cfg):
