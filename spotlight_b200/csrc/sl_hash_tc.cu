@@ -8,22 +8,26 @@
 // accumulators live in tensor memory (TMEM); input tiles arrive by TMA (cp.async.bulk.tensor, one CTA per copy,
 // this GPU's own memory) straight into the same swizzled layout.
 //
-// TMEM columns: D1 [0,256) fp32, H [256,384) packed bf16 pairs, D2 [384,512) fp32. Sixteen epilogue warps (a thread
-// owns one row = one TMEM lane and a quarter of the columns) and one issuing thread:
+// The MLP kernel (written for a hidden width D1 of 256; 128 halves the pieces). TMEM columns: D1 [0,D1) fp32, H [256,256+D1/2)
+// packed bf16 pairs, D2 [384,512) fp32. Sixteen epilogue warps (a thread owns one row = one TMEM lane and a quarter
+// of the columns) and one issuing thread:
 //   TMA   X tile [128 x 128] into one of two stages            -> x_full[stage]
-//   MMA1  D1[128 x 256] = X W1            (8 x  M128 N256 K16)  -> d1_full   (the input stage is free again)
-//   EPI1  D1 -> registers, torch's rounding points (matmul -> bf16, + bias -> bf16, SiLU -> bf16), packed
-//         pairs of bf16 written to H: the A operand of layer 2  -> h_full, h_full2 (a warp's columns in two halves:
-//         MMA2 starts on the first; after the second D1 is free, and MMA1 of the next tile, issued behind MMA2 of
-//         this one, runs under EPI2)
-//   MMA2  D2[128 x 128] = H W2            (16 x M128 N128 K16, A from TMEM) -> d2_full
+//   MMA1  D1[128 x D1] = X W1             (8 x  M128 N=D1 K16)  -> d1_full
+//   EPI1  D1 -> registers, torch's rounding points (matmul -> bf16, + bias -> bf16, SiLU -> bf16, + input -> bf16 in the
+//         residual form), packed pairs of bf16 written to H: the A operand of layer 2
+//                                                               -> h_full, h_full2 (a warp's columns in two halves:
+//         MMA2 starts on the first; after the second D1 is free and the input stage takes the next rows; MMA1 of the
+//         next tile, issued behind MMA2 of this one, runs under EPI2)
+//   MMA2  D2[128 x 128] = H W2            (D1/16 x M128 N128 K16, A from TMEM) -> d2_full
 //   EPI2  D2 -> registers, rounding points, sign bit of every value: a thread holds one 32-bit word of its
 //         row's code and stores it                              -> d2_free
-// The epilogue (one exp and one division per hidden value, at full fp32 accuracy so that the codes equal the
-// other kernels' bit for bit) takes several times longer than the contraction, so the kernel is bound by
-// instruction issue of the epilogue warps, not by the tensor core. Every wait on an mbarrier is bounded; a
-// wait that runs out raises the library's hash status word, the CTA lets its copies in flight land, frees its
-// TMEM and returns.
+// SiLU of a bf16 is a function of 16 bits: a table in shared memory, filled by the formula (accurate exp, IEEE division)
+// at the start of the kernel, serves all but exact zeros and outliers, which call the formula; so the codes equal the
+// other kernels' up to the order of the fp32 additions. Still the epilogue takes longer than the contraction: the
+// kernel is bound by instruction issue of the epilogue warps, not by the tensor core. The linear hash has a kernel of
+// its own further down (one contraction per tile, bound by the stream of its input rows). Every wait on an mbarrier is
+// bounded; a wait that runs out raises the library's hash status word, the CTA lets its copies in flight land, frees
+// its TMEM and returns.
 // Same arithmetic as the warp-level kernel in sl_hash_mma.cu up to the order of the fp32 additions.
 #include <cuda.h>
 
